@@ -1,0 +1,244 @@
+"""Storage format of one compressed K or V cache.
+
+``CompressedTensor`` / ``CompressedKV`` keep the field names, shapes, dtypes and
+error behaviour of the reference containers (reskv/tensors.py:11-162) so that
+code written against them keeps working:
+
+=================  ===========================================================
+field              contents, for ``B`` sequences, ``H`` KV heads, ``T`` tokens
+=================  ===========================================================
+``centroids``      FP16 ``[B,H,C,128]``, ``1 <= C <= 64``
+``cluster_ids``    integer ``[B,H,T]`` on entry, held as int8
+``payload``        FP16 ``[B,H,T,nnz]`` (bits 16), or int32 words: 4 (structured
+                   INT4) / ``4*bits`` (unstructured INT4/INT2, all 128 coords)
+``metadata``       int64 ``[B,H,T,2]`` bitmap, MSB first (unstructured FP16);
+                   int32 ``[B,H,T,4]`` (tiled / structured FP16);
+                   int32 ``[B,H,T,2]`` (structured INT4); ``None`` otherwise
+``scale``          FP16 ``[B,H,T]`` for quantised residuals, else ``None``
+=================  ===========================================================
+
+What differs from the reference is how the token axis is stored.  The reference
+re-concatenates every tensor whenever a decode group is appended
+(tensors.py:105-119).  Here the per-token tensors may be *windows* of larger
+buffers whose token axis has spare capacity: ``append`` writes the new group
+behind the live tokens and returns a longer window over the same memory,
+doubling the buffers only when they are full.  The kernels therefore take a
+token stride (tokens of capacity per ``(b, h)`` unit) next to the token count,
+and ``_native`` holds ``[B*H, T, w]`` views that need not be contiguous across
+units.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from .config import KernelPlan
+
+_INT_DTYPES = (torch.int8, torch.int16, torch.int32, torch.int64)
+
+
+def payload_width(plan: KernelPlan) -> int:
+    """Last-axis length of ``payload`` for ``plan`` (reference tensors.py:58-64)."""
+    if plan.bits == 16:
+        return plan.nnz
+    return 4 if plan.layout == "structured" else 4 * plan.bits
+
+
+def metadata_spec(plan: KernelPlan):
+    """``(words, dtype)`` of ``metadata`` for ``plan``, or ``None`` when unused."""
+    if plan.bits != 16 and plan.layout != "structured":
+        return None
+    if plan.layout == "unstructured":
+        return 2, torch.int64
+    return (2 if plan.bits == 4 else 4), torch.int32
+
+
+@dataclass
+class CompressedTensor:
+    """Compressed K or V cache of one layer; see the module docstring."""
+
+    centroids: torch.Tensor
+    cluster_ids: torch.Tensor
+    payload: torch.Tensor
+    metadata: torch.Tensor | None
+    scale: torch.Tensor | None
+    plan: KernelPlan
+    _native: tuple = field(default=(), init=False, repr=False)
+    # Backing buffers [B,H,capacity,...] of (ids, payload, metadata, scale); the
+    # public fields are their leading ``T`` tokens.
+    _buffers: tuple = field(default=(), init=False, repr=False)
+
+    def __post_init__(self):
+        c, ids, p = self.centroids, self.cluster_ids, self.payload
+        if c.ndim != 4 or c.shape[-1] != 128:
+            raise ValueError("centroids must have shape [B,H,C,128]")
+        if ids.ndim != 3 or ids.shape[:2] != c.shape[:2]:
+            raise ValueError("cluster IDs must have shape [B,H,T]")
+        if not 1 <= c.shape[2] <= 64:
+            raise ValueError("centroid count must be between 1 and 64")
+        if p.ndim != 4 or p.shape[:3] != ids.shape:
+            raise ValueError("payload must have shape [B,H,T,words_or_values]")
+        for t in (ids, p, self.metadata, self.scale):
+            if t is not None and t.device != c.device:
+                raise ValueError("all cache tensors must share a device")
+        if c.dtype != torch.float16:
+            raise ValueError("centroids must be FP16")
+        plan = self.plan
+        if p.dtype != (torch.float16 if plan.bits == 16 else torch.int32):
+            raise ValueError("payload dtype does not match the compression plan")
+        b, h, n = ids.shape
+        if min(b, h, n) < 1:
+            raise ValueError("cache dimensions must be nonempty")
+        if ids.dtype not in _INT_DTYPES:
+            raise ValueError("cluster IDs must be integer tensors")
+        if p.shape[-1] != payload_width(plan):
+            raise ValueError("payload width does not match the compression plan")
+        spec = metadata_spec(plan)
+        if spec is not None:
+            words, dtype = spec
+            m = self.metadata
+            if m is None or m.shape != (b, h, n, words) or m.dtype != dtype:
+                raise ValueError("sparse metadata shape/dtype does not match the compression plan")
+        elif self.metadata is not None:
+            raise ValueError("quantized unstructured payloads do not use sparse metadata")
+        if plan.bits != 16:
+            s = self.scale
+            if s is None or s.shape != (b, h, n) or s.dtype != torch.float16:
+                raise ValueError("quantized scales must be FP16 [B,H,T]")
+        elif self.scale is not None:
+            raise ValueError("FP16 sparse-only caches do not use quantization scales")
+        if not self._buffers:
+            # Plain tensors: they are their own buffers, capacity == T.
+            self.cluster_ids = ids.to(torch.int8).contiguous()
+            self.payload = p.contiguous()
+            self.metadata = self.metadata.contiguous() if self.metadata is not None else None
+            self.scale = self.scale.contiguous() if self.scale is not None else None
+            self._buffers = (self.cluster_ids, self.payload, self.metadata, self.scale)
+        cap = self._buffers[0].shape[2]
+
+        def rows(buf):
+            if buf is None:
+                return None
+            flat = buf.reshape(b * h, cap, -1)[:, :n]
+            return flat.squeeze(-1) if buf.ndim == 3 else flat
+
+        self._native = (
+            c.reshape(b * h, -1, 128).contiguous(),
+            *(rows(buf) for buf in self._buffers),
+        )
+
+    @classmethod
+    def _window(cls, centroids, buffers, length, plan) -> "CompressedTensor":
+        """Tensor over the first ``length`` tokens of capacity ``buffers``."""
+        self = cls.__new__(cls)
+        self.centroids = centroids
+        self.plan = plan
+        self._buffers = tuple(buffers)
+        views = [buf[:, :, :length] if buf is not None else None for buf in buffers]
+        self.cluster_ids, self.payload, self.metadata, self.scale = views
+        self._native = ()
+        self.__post_init__()
+        return self
+
+    # -- queries ----------------------------------------------------------
+    @property
+    def seq_len(self) -> int:
+        return self.cluster_ids.shape[-1]
+
+    @property
+    def token_stride(self) -> int:
+        """Tokens between consecutive ``(b, h)`` units in the backing buffers."""
+        return self._buffers[0].shape[2]
+
+    @property
+    def tensors(self) -> tuple:
+        """All stored tensors, including the flattened views passed to the kernels."""
+        return (self.centroids, self.cluster_ids, self.payload, self.metadata, self.scale, *self._native)
+
+    @property
+    def nbytes(self) -> int:
+        return _storage_bytes(self.tensors)
+
+    # -- updates ----------------------------------------------------------
+    def reserve(self, capacity: int) -> "CompressedTensor":
+        """Same tokens over buffers that hold at least ``capacity`` tokens."""
+        n = self.seq_len
+        if self.token_stride >= capacity:
+            return self
+        b, h = self.cluster_ids.shape[:2]
+        grown = []
+        for view in (self.cluster_ids, self.payload, self.metadata, self.scale):
+            if view is None:
+                grown.append(None)
+                continue
+            buf = view.new_empty((b, h, capacity) + tuple(view.shape[3:]))
+            buf[:, :, :n].copy_(view)
+            grown.append(buf)
+        return CompressedTensor._window(self.centroids, grown, n, self.plan)
+
+    def append(self, other: "CompressedTensor") -> "CompressedTensor":
+        """Tokens of ``self`` followed by those of ``other``.
+
+        The newer centroid table replaces the older one (reference
+        tensors.py:105-119).  Where the reference concatenates, this writes
+        ``other`` behind the live tokens of ``self``'s buffers and returns a
+        longer window over the same memory; only a full buffer is reallocated
+        (to twice the needed length).  ``self`` stays valid: its tokens are not
+        touched.
+        """
+        if self.plan != other.plan:
+            raise ValueError("cannot concatenate different cache plans")
+        n, total = self.seq_len, self.seq_len + other.seq_len
+        base = self if self.token_stride >= total else self.reserve(max(2 * total, 256))
+        news = (other.cluster_ids, other.payload, other.metadata, other.scale)
+        for buf, new in zip(base._buffers, news):
+            if buf is not None:
+                buf[:, :, n:total].copy_(new)
+        return CompressedTensor._window(other.centroids, base._buffers, total, self.plan)
+
+    def index_select(self, index: torch.Tensor) -> "CompressedTensor":
+        def take(t):
+            return t.index_select(0, index.to(t.device)) if t is not None else None
+
+        return CompressedTensor(
+            take(self.centroids),
+            take(self.cluster_ids),
+            take(self.payload),
+            take(self.metadata),
+            take(self.scale),
+            self.plan,
+        )
+
+
+@dataclass
+class CompressedKV:
+    """The compressed keys and values of one layer (reference tensors.py:135-152)."""
+
+    key: CompressedTensor
+    value: CompressedTensor
+
+    def __post_init__(self):
+        if self.key.plan != self.value.plan or self.key.cluster_ids.shape != self.value.cluster_ids.shape:
+            raise ValueError("K/V compression plans and token dimensions must agree")
+        if self.key.centroids.device != self.value.centroids.device:
+            raise ValueError("K/V caches must share a device")
+
+    @property
+    def seq_len(self) -> int:
+        return self.key.seq_len
+
+    @property
+    def nbytes(self) -> int:
+        return _storage_bytes((*self.key.tensors, *self.value.tensors))
+
+
+def _storage_bytes(tensors) -> int:
+    """Bytes in distinct backing storages; views of one storage count once."""
+    seen = {}
+    for t in tensors:
+        if isinstance(t, torch.Tensor):
+            s = t.untyped_storage()
+            seen[(t.device, s.data_ptr())] = s.nbytes()
+    return sum(seen.values())
