@@ -1,0 +1,368 @@
+"""Benchmark of the compressed-KV decode hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (the configuration the headline metric is quoted on): one decoder
+attention layer of Llama-3.1-8B shape -- 32 query heads, 8 KV heads, head_dim
+128, RoPE theta 500000 -- FP16, 8192-token context, sparsity 0.75, FP16
+residuals (unstructured bitmap layout), 32 clusters, 10 K-means iterations,
+recent window 32, group 64, batch 32.  K/V are the seeded cluster-mixture
+stand-in for model activations, queries and appended tokens ~ N(0,1).
+
+One *step* is one decode step of that layer for the whole batch: append the new
+token's K/V to the dense window (every 64th step the oldest 64 tokens are
+clustered incrementally and compressed) and run the fused split-K attention
+over compressed segment + window.  ``value`` counts tokens (= sequences x steps)
+per second with all inputs resident in HBM; ``e2e`` is the same loop driven
+from pinned host buffers (query / key / value of the step copied to the device,
+the attention output copied back, every step, inside the timed region).
+
+With ``torchrun`` (N > 1) every rank runs its own batch of 32 sequences -- the
+(sequence, KV head) units are independent, so there is no collective on the
+data path -- and the job value is N x 32 x K / max-over-ranks time.
+
+``--impl reference`` times the CPU restatement of the reference's own Python
+path (oracle/: reconstruct + RoPE + FP32 attention, reference.py:12-91) on the
+host cores, on a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+H_Q, H_KV, DIM, THETA = 32, 8, 128, 500000.0
+CLUSTERS, MAX_CLUSTERS, ITERS, RECENT, GROUP = 32, 64, 10, 32, 64
+METRIC = "Llama-3.1-8B decode tok/s @8K ctx b1-32; fused attn HBM GB/s vs peak"
+UNIT = "tok/s (one decoder attention layer: cache update + fused compressed attention)"
+
+# DRAM bytes per launch of the dominant kernel from the committed ncu capture
+# (profiles/), keyed by workload name; None until a capture exists.
+NCU_TRAFFIC_BYTES = {}
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--sparsity", type=float, default=0.75)
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def workload_name(a):
+    return f"llama31-8b-layer attn decode ctx{a.context} b{a.batch} s{a.sparsity} fp16 unstructured"
+
+
+def algorithmic_bytes(batch, t_comp, t_dense, nnz, ck, cv):
+    """Bytes one attention call has to read/write at minimum: per KV head the
+    compressed tokens (payload + 16-byte bitmap + 1-byte id, K and V), both
+    centroid tables and the dense window (K and V); plus query and output."""
+    per_token = 2 * (nnz * 2 + 16 + 1)
+    return batch * H_KV * (t_comp * per_token + (ck + cv) * 256 + t_dense * 512) + batch * H_Q * DIM * 2 * 2
+
+
+# ---- CPU arm (oracle) ----------------------------------------------------------------
+def cpu_attention_sample(a, budget_s):
+    """Oracle attention (+ amortised group compression) for ONE sequence of the
+    workload on the host cores; returns (tokens per second, description)."""
+    import numpy as np
+
+    from oracle import attention as oatt
+    from oracle import encode as oenc
+    from oracle import kmeans as okm
+
+    rng = np.random.default_rng(0)
+    t_c = (a.context - RECENT) // GROUP * GROUP
+    nnz = int(128 * (1 - a.sparsity))
+
+    def mix(t):
+        cen = rng.standard_normal((1, H_KV, 32, 128), dtype=np.float32)
+        which = rng.integers(0, 32, (1, H_KV, t))
+        x = np.take_along_axis(cen, np.broadcast_to(which[..., None], (1, H_KV, t, 128)), axis=2)
+        x = (x + 0.3 * rng.standard_normal((1, H_KV, t, 128), dtype=np.float32))
+        return (x * np.exp(rng.standard_normal((1, H_KV, 1, 128), dtype=np.float32))).astype(np.float16)
+
+    k, v = mix(t_c), mix(t_c)
+    cen = (rng.standard_normal((1, H_KV, 32, 128)) * 0.5).astype(np.float16)
+    ids = rng.integers(0, 32, (1, H_KV, t_c)).astype(np.int32)
+    caches = []
+    for x in (k, v):
+        p, m = oenc.encode_unstructured_fp16(x, cen, ids, nnz)
+        caches.append(dict(layout="unstructured", bits=16, centroids=cen, ids=ids, payload=p, metadata=m, scale=None))
+    q = rng.standard_normal((1, H_Q, 1, 128)).astype(np.float16)
+    freq = oatt.theta_frequencies(THETA)
+    qr = oatt.rotate(q, np.array([a.context]), freq).astype(np.float16)
+    kr, vr = mix(RECENT + GROUP // 2), mix(RECENT + GROUP // 2)
+    # one decode-time group compression, amortised over GROUP steps
+    t0 = time.perf_counter()
+    grp = mix(GROUP)
+    c2, i2, _ = okm.incremental(grp, cen, MAX_CLUSTERS)
+    oenc.encode_unstructured_fp16(grp, c2, i2, nnz)
+    oenc.encode_unstructured_fp16(grp, c2, i2, nnz)
+    compress_s = (time.perf_counter() - t0) / GROUP
+    steps, elapsed = 0, 0.0
+    while elapsed < budget_s and steps < 64:
+        t0 = time.perf_counter()
+        oatt.attention_compressed(q, caches[0], caches[1], position=a.context, inv_freq=freq, recent=(qr, kr, vr))
+        elapsed += time.perf_counter() - t0
+        steps += 1
+    per_step = elapsed / steps + compress_s
+    sample = (f"1 of {a.batch} sequences, {steps} decode steps of the workload (numpy oracle: decode bitmap, "
+              f"RoPE, FP32 attention) + 1/{GROUP} of one group compression")
+    return 1.0 / per_step, sample
+
+
+def cpu_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def run_reference(a):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps_budget = max(4.0, min(60.0, 0.2 * a.steps))
+    value, sample = cpu_attention_sample(a, steps_budget)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps,
+        "warmup": a.warmup, "ms_per_step": 1000.0 / value, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(a), "note": "CPU restatement of the reference path (oracle/), not the GPU"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cpu_cores(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ---- GPU arm -------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.path = index, None, f"/tmp/reskv_clocks_{os.getpid()}.csv"
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            self.proc.wait()
+
+    def summary(self):
+        sm, smax, reasons = [], [], set()
+        try:
+            for row in open(self.path):
+                f = [x.strip() for x in row.split(",")]
+                if len(f) < 9:
+                    continue
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                     f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        except (OSError, ValueError):
+            pass
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def rope(x, pos, inv_freq):
+    """Half-split RoPE of ``x [..., 128]`` at integer position ``pos`` (torch ops)."""
+    import torch
+
+    ang = float(pos) * inv_freq
+    cos, sin = torch.cos(ang), torch.sin(ang)
+    a, b = x.float()[..., :64], x.float()[..., 64:]
+    return torch.cat((a * cos - b * sin, b * cos + a * sin), dim=-1).to(x.dtype)
+
+
+def run_gpu(a):
+    import torch
+    import torch.distributed as dist
+
+    import reskv_b200._extension as ext
+    from reskv_b200 import ResKVKernelConfig, attention
+    from reskv_b200.cache import ResKVLayerCache
+    from reskv_b200.synthetic import gaussian, mixture
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ext.library()  # fail loudly if the native library is missing
+
+    B, K, W = a.batch, a.steps, a.warmup
+    nnz = int(128 * (1 - a.sparsity))
+    cfg = ResKVKernelConfig(sparsity=a.sparsity, bits=16, layout="unstructured", num_clusters=CLUSTERS,
+                            max_clusters=MAX_CLUSTERS, group_size=GROUP, recent_size=RECENT, kmeans_iterations=ITERS)
+    inv_freq = (THETA ** (-torch.arange(64, device=dev).float() / 64)).contiguous()
+
+    # ---- prefill: synthetic K/V of the prompt, compressed once (untimed) -------------
+    seed = 1000 * (rank + 1)
+    k_raw = mixture(B, H_KV, a.context, seed=seed, device=dev)
+    v_all = mixture(B, H_KV, a.context, seed=seed + 1, device=dev)
+    layer = ResKVLayerCache(cfg)
+    n_dense = a.context - (a.context - RECENT) // GROUP * GROUP
+    k_rot = k_raw.clone()
+    pos = torch.arange(a.context - n_dense, a.context, device=dev).float()[:, None] * inv_freq[None, :]
+    tail = k_raw[:, :, -n_dense:].float()
+    k_rot[:, :, -n_dense:] = torch.cat((tail[..., :64] * pos.cos() - tail[..., 64:] * pos.sin(),
+                                        tail[..., 64:] * pos.cos() + tail[..., :64] * pos.sin()), -1).half()
+    t0 = time.perf_counter()
+    layer.update(k_rot, v_all, {"raw_keys": k_raw})
+    torch.cuda.synchronize()
+    prefill_compress_ms = (time.perf_counter() - t0) * 1e3
+    del k_raw, v_all, k_rot, tail
+
+    total = W + 2 * K
+    q_all = gaussian(total, B, H_Q, 1, DIM, seed=seed + 2, device=dev)
+    k_new = gaussian(total, B, H_KV, 1, DIM, seed=seed + 3, device=dev)
+    v_new = gaussian(total, B, H_KV, 1, DIM, seed=seed + 4, device=dev)
+    host_q, host_k, host_v = (x[W + K:].cpu().pin_memory() for x in (q_all, k_new, v_new))
+    host_out = torch.empty((B, H_Q, 1, DIM), dtype=torch.float16).pin_memory()
+
+    state = {"pos": a.context, "bytes": 0.0, "calls": 0}
+    att_events, upd_events = [], []
+
+    def step(q, k, v, timed):
+        p = state["pos"]
+        k_r, q_r = rope(k, p, inv_freq), rope(q, p, inv_freq)
+        if timed:
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            e[0].record()
+        keys, values = layer.update(k_r, v, {"raw_keys": k})
+        if timed:
+            e[1].record()
+        out = attention(q, layer.compressed, position=p, inv_freq=inv_freq, recent=(q_r, keys, values))
+        if timed:
+            e[2].record()
+            upd_events.append((e[0], e[1]))
+            att_events.append((e[1], e[2]))
+            ck, cv = layer.compressed.key.centroids.shape[2], layer.compressed.value.centroids.shape[2]
+            state["bytes"] += algorithmic_bytes(B, layer.compressed.seq_len, keys.shape[2], nnz, ck, cv)
+            state["calls"] += 1
+        state["pos"] = p + 1
+        return out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(W):
+        step(q_all[i], k_new[i], v_new[i], False)
+
+    # ---- timed region 1: inputs resident in HBM ---------------------------------------
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = ext.launch_count
+    barrier()
+    with ClockSampler(local) as clocks:
+        start.record()
+        for i in range(W, W + K):
+            step(q_all[i], k_new[i], v_new[i], True)
+        stop.record()
+        barrier()
+    launches = ext.launch_count - launches0
+    ms_total = start.elapsed_time(stop)
+    att_ms = sum(s.elapsed_time(e) for s, e in att_events)
+    upd_ms = sum(s.elapsed_time(e) for s, e in upd_events)
+
+    # ---- timed region 2: host buffers in, host result out, every step -------------------
+    barrier()
+    start.record()
+    for i in range(K):
+        q = host_q[i].to(dev, non_blocking=True)
+        k = host_k[i].to(dev, non_blocking=True)
+        v = host_v[i].to(dev, non_blocking=True)
+        out = step(q, k, v, False)
+        host_out.copy_(out, non_blocking=True)
+    stop.record()
+    barrier()
+    ms_e2e = start.elapsed_time(stop)
+
+    times = torch.tensor([ms_total, ms_e2e, att_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, ms_e2e, att_ms_max = times.tolist()
+
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+        except (OSError, ValueError):
+            pass
+        peak, peak_kind = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
+        achieved = state["bytes"] / (att_ms * 1e-3) / 1e9
+        name = workload_name(a)
+        line = {
+            "metric": METRIC, "value": world * B * K / (ms_total * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K,
+            "warmup": W, "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": name, "batch_per_gpu": B, "context": a.context, "sparsity": a.sparsity,
+                       "q_heads": H_Q, "kv_heads": H_KV, "head_dim": DIM, "clusters": CLUSTERS,
+                       "kmeans_iterations": ITERS, "recent": RECENT, "group": GROUP,
+                       "l2": "inputs larger than L2 (compressed cache %.0f MB per step)" % (
+                           state["bytes"] / state["calls"] / 1e6),
+                       "sharding": "independent (sequence x KV-head) units per GPU, no collective"},
+            "clocks": clocks.summary(),
+            "e2e": {"value": world * B * K / (ms_e2e * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": int(host_q[0].nbytes + host_k[0].nbytes + host_v[0].nbytes),
+                    "d2h_bytes_per_step": int(host_out.nbytes)},
+            "gpu_launches": launches,
+            "roofline": {"bound": "hbm", "kernel": "decode_bitmap_partial_kernel + decode_merge_kernel (one attention call)",
+                         "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                         "frac": achieved / peak, "frac_of_8000": achieved / 8000.0,
+                         "algorithmic_bytes_per_call": state["bytes"] / state["calls"],
+                         "ms_per_call": att_ms / state["calls"], "traffic": NCU_TRAFFIC_BYTES.get(name)},
+            "phases_ms_per_step": {"attention": att_ms / K, "cache_update_incl_group_compression": upd_ms / K,
+                                   "prefill_cluster_and_compress_ms": prefill_compress_ms},
+        }
+        if world == 1 and not a.no_cpu_baseline:
+            value, sample = cpu_attention_sample(a, a.cpu_seconds)
+            line["cpu_baseline"] = {"value": value, "unit": UNIT, "cores": cpu_cores(), "kind": "port",
+                                    "sample": sample}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)

@@ -1,0 +1,161 @@
+/* C ABI of libreskv_b200.so: sm_100a kernels for the compressed-KV hot path.
+ *
+ * Every function takes plain device pointers, sizes and the CUDA stream to
+ * launch on (a cudaStream_t passed as void*), never allocates device memory
+ * unless it says so, never synchronises, and returns 0 on success or a
+ * negative RESKV_ERR_* code; reskv_last_error() then describes the failure
+ * (thread local).  Scratch memory is supplied by the caller: ask the matching
+ * *_workspace_bytes() function for the size.
+ *
+ * Conventions shared by all entry points
+ *   - head dimension is 128; B sequences, KH key/value heads, NH query heads;
+ *     a "unit" is one (sequence, KV head) pair, unit = b * KH + h.
+ *   - per-token tensors are addressed as base + (unit * tok_stride + t) * row,
+ *     where tok_stride >= tokens is the capacity of the backing buffer in
+ *     tokens (== tokens for plain contiguous tensors).
+ *   - pointers to rows that are staged with bulk copies (bitmaps, payloads)
+ *     must be 16-byte aligned.
+ *
+ * Each declaration cites the reference interface it replaces
+ * (file:line within the coralabo/ResKV checkout).
+ */
+#ifndef RESKV_B200_H
+#define RESKV_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RESKV_OK 0
+#define RESKV_ERR_INVALID (-1)   /* bad argument (shape, range, alignment, null pointer) */
+#define RESKV_ERR_WORKSPACE (-2) /* workspace missing or too small */
+#define RESKV_ERR_CUDA (-3)      /* a CUDA runtime call failed */
+#define RESKV_ERR_LIMIT (-4)     /* size beyond a documented fixed maximum */
+
+/* Bits of the 32-bit status word a kernel ORs into workspace[0] when something
+ * went wrong on the device (read it after synchronising the stream). */
+#define RESKV_STATUS_WAIT_TIMEOUT 1u /* a bounded wait on an async copy ran out */
+
+/* Message of the last failure on the calling thread ("" if none). */
+const char* reskv_last_error(void);
+
+/* Library version, major * 10000 + minor * 100 + patch. */
+int reskv_version(void);
+
+/* ---- fused decode attention: unstructured FP16 bitmap layout ---------------
+ *
+ * Replaces cluster_mass.decode_fp16 (reskv/csrc/cluster_mass.cu:1177-1296, the
+ * partial kernel :185-565 plus the split merge :1016-1104) and, when the
+ * recent_* pointers are given, the recent-window merge that follows it
+ * (reskv/_attention.py:117-143, cluster_mass.cu:1106-1169) in the same call.
+ *
+ *   q            f16 [B*NH,128]            query before RoPE
+ *   k_centroids  f16 [B*KH,CK,128]         v_centroids f16 [B*KH,CV,128]
+ *   k_ids/v_ids  i8  [B*KH,tok_stride]
+ *   k_payload    f16 [B*KH,tok_stride,nnz] retained residuals, ascending coordinate
+ *   k_bitmap     i64 [B*KH,tok_stride,2]   bit 63-d%64 of word d/64 marks coordinate d
+ *   start_pos    position of compressed token 0;  pos_q  position of the query
+ *   inv_freq     f32 [64] RoPE frequencies, or NULL for theta^(-i/64)
+ *   splits       partitions of the token axis, 0 = choose from the SM count
+ *   recent_q     f16 [B*NH,128] query after RoPE, recent_k (after RoPE) /
+ *                recent_v f16 [B*KH,recent_tokens,128]; all NULL / 0 for none
+ *   out          f16 [B*NH,128]
+ *   out_m,out_l  f32 [B*NH] running maximum and un-normalised sum of the
+ *                softmax over the compressed tokens only, or NULL
+ */
+size_t reskv_decode_bitmap_fp16_workspace_bytes(int batch, int kv_heads, int q_heads, int tokens, int splits);
+
+int reskv_decode_bitmap_fp16(const void* q, const void* k_centroids, const void* k_ids, const void* k_payload,
+                             const void* k_bitmap, const void* v_centroids, const void* v_ids,
+                             const void* v_payload, const void* v_bitmap, int batch, int kv_heads, int q_heads,
+                             int tokens, int64_t tok_stride, int k_clusters, int v_clusters, int nnz, int start_pos,
+                             int pos_q, float rope_theta, const float* inv_freq, float scaling, int splits,
+                             const void* recent_q, const void* recent_k, const void* recent_v, int recent_tokens,
+                             void* workspace, size_t workspace_bytes, void* out, float* out_m, float* out_l,
+                             void* stream);
+
+/* The split count reskv_decode_bitmap_fp16 uses for splits == 0. */
+int reskv_decode_auto_splits(int batch, int kv_heads, int tokens);
+
+/* ---- recent-window merge ------------------------------------------------------
+ * Replaces cluster_mass.merge_recent (cluster_mass.cu:1461-1508): joint softmax
+ * of a finished compressed-attention result (out, m, l) with dense recent
+ * tokens whose scaled scores [B*NH,recent_tokens] f32 the caller computed.
+ * Writes merged f16 [B*NH,128]; may alias comp_out. */
+int reskv_merge_recent_scores(const void* comp_out, const float* comp_m, const float* comp_l, const float* scores,
+                              const void* recent_v, int batch, int kv_heads, int q_heads, int recent_tokens,
+                              void* merged, void* stream);
+
+/* Replaces attention.merge_recent (reskv/csrc/attention.cu:598-663,839-906):
+ * same merge, scores computed here from the rotated query and rotated keys. */
+int reskv_merge_recent_qk(const void* comp_out, const float* comp_m, const float* comp_l, const void* recent_q,
+                          const void* recent_k, const void* recent_v, int batch, int kv_heads, int q_heads,
+                          int recent_tokens, float scaling, void* merged, void* stream);
+
+/* ---- residual packers ------------------------------------------------------------
+ * Common arguments: x f16 [B*KH,x_tok_stride,128] (pre-RoPE K or V), centroids
+ * f16 [B*KH,clusters,128], ids i32 [B*KH,tokens] (out-of-range ids are clamped,
+ * like the reference kernels do; the Python layer validates them first).  Outputs
+ * are addressed with out_tok_stride, so a group can be written straight behind
+ * the live tokens of a capacity buffer.  r = fp32(x) - fp32(c); the selection key
+ * is |fp16(r)|, larger first, lower coordinate on ties. */
+
+/* Unstructured FP16: payload f16 [.., nnz] in ascending coordinate order, bitmap
+ * i64 [.., 2] MSB first.  Replaces the torch path of _encode
+ * (reskv/compression.py:75-89), which the reference runs as ~10 library kernels. */
+int reskv_encode_bitmap_fp16(const void* x, const void* centroids, const int32_t* ids, int batch, int kv_heads,
+                             int tokens, int64_t x_tok_stride, int clusters, int nnz, void* payload, void* bitmap,
+                             int64_t out_tok_stride, void* stream);
+
+/* Unstructured INT4 / INT2: words i32 [.., 4*bits] holding all 128 coordinates
+ * (discarded ones 0), scale f16 [..].  Replaces compression.compress_quantized
+ * (reskv/csrc/compression.cu:244-383,392-421). */
+int reskv_encode_quantized(const void* x, const void* centroids, const int32_t* ids, int batch, int kv_heads,
+                           int tokens, int64_t x_tok_stride, int clusters, int nnz, int bits, void* words,
+                           void* scale, int64_t out_tok_stride, void* stream);
+
+/* Tiled (structured == 0, 16-bit masks) or 4:16 structured (4-bit indices) FP16:
+ * values f16 [.., nnz] in (tile, rank) order, meta i32 [.., 4].  Replaces
+ * compression.compress_fp16 (reskv/csrc/compression.cu:57-147,423-473). */
+int reskv_encode_tiled_fp16(const void* x, const void* centroids, const int32_t* ids, int batch, int kv_heads,
+                            int tokens, int64_t x_tok_stride, int clusters, int nnz, int structured, void* values,
+                            void* meta, int64_t out_tok_stride, void* stream);
+
+/* 1-of-4 structured INT4: packed i32 [.., 4], meta i32 [.., 2], scale f16 [..].
+ * Replaces compression.compress_structured_int4
+ * (reskv/csrc/compression.cu:153-239,475-504). */
+int reskv_encode_structured_int4(const void* x, const void* centroids, const int32_t* ids, int batch, int kv_heads,
+                                 int tokens, int64_t x_tok_stride, int clusters, void* packed, void* meta,
+                                 void* scale, int64_t out_tok_stride, void* stream);
+
+/* ---- clustering ------------------------------------------------------------------
+ * Lloyd iterations per (sequence, KV head); replaces the torch loop of cluster()
+ * (reskv/compression.py:19-53: cdist + argmin + one_hot + bmm per iteration).
+ * value == 0: FP32 centres, empty clusters keep their centre (K); value != 0:
+ * centres rounded to FP16 each iteration, empty clusters become 0 (V).
+ * Initial centres are the tokens at linspace(0, tokens-1, clusters).  Writes
+ * centroids f16 [B*KH,clusters,128] (after the last update) and ids i32
+ * [B*KH,tokens] (from the last assignment, i.e. relative to the centres before
+ * that update -- the reference's loop order). */
+size_t reskv_kmeans_workspace_bytes(int batch, int kv_heads, int clusters);
+
+int reskv_kmeans(const void* x, int batch, int kv_heads, int tokens, int64_t x_tok_stride, int clusters,
+                 int iterations, int value, void* workspace, size_t workspace_bytes, void* centroids, int32_t* ids,
+                 void* stream);
+
+/* Decode-time step; replaces _incremental_cluster (reskv/compression.py:56-69).
+ * Copies old_centroids f16 [B*KH,old_clusters,128] into new_centroids
+ * [B*KH,new_clusters,128]; when new_clusters == old_clusters + 1 the mean of the
+ * group's tokens becomes the extra centre; then assigns the tokens to the
+ * nearest centre. */
+int reskv_kmeans_incremental(const void* x, int batch, int kv_heads, int tokens, int64_t x_tok_stride,
+                             const void* old_centroids, int old_clusters, void* new_centroids, int new_clusters,
+                             int32_t* ids, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RESKV_B200_H */

@@ -52,26 +52,27 @@ def attention_dense(
     nh = query.shape[1]
     g = nh // kh
     freq = theta_frequencies(rope_theta) if inv_freq is None else inv_freq.astype(np.float32)
-    q = rotate(query, np.array([position]), freq)
+    # query heads of one KV head are batched as rows [B,kh,g,128] instead of
+    # repeating K and V g times (reference.py:80); the arithmetic is the same
+    q = rotate(query, np.array([position]), freq).reshape(b, kh, g, 128)
     k = rotate(keys, np.arange(start_position, start_position + t), freq)
-    k = np.repeat(k, g, axis=1)
-    v = np.repeat(values.astype(np.float32), g, axis=1)
+    v = values.astype(np.float32)
     scale = np.float32(128**-0.5 if scaling is None else scaling)
-    scores = np.matmul(q, k.transpose(0, 1, 3, 2)) * scale
+    scores = np.matmul(q, k.transpose(0, 1, 3, 2)) * scale  # [B,kh,g,T]
     stats = None
     if return_stats:
         m = scores.max(-1)
-        stats = (m[..., 0], np.exp(scores - m[..., None]).sum(-1)[..., 0])
+        stats = (m.reshape(b, nh), np.exp(scores - m[..., None]).sum(-1).reshape(b, nh))
     if recent is not None and recent[1].shape[2] > 0:
         qr, kr, vr = recent
-        kr = np.repeat(kr.astype(np.float32), g, axis=1)
-        rs = np.matmul(qr.astype(np.float32), kr.transpose(0, 1, 3, 2)) * scale
+        qr = qr.astype(np.float32).reshape(b, kh, g, 128)
+        rs = np.matmul(qr, kr.astype(np.float32).transpose(0, 1, 3, 2)) * scale
         scores = np.concatenate((scores, rs), axis=-1)
-        v = np.concatenate((v, np.repeat(vr.astype(np.float32), g, axis=1)), axis=2)
+        v = np.concatenate((v, vr.astype(np.float32)), axis=2)
     scores = scores - scores.max(-1, keepdims=True)
     p = np.exp(scores)
     p = p / p.sum(-1, keepdims=True)
-    out = np.matmul(p, v).astype(np.float32)
+    out = np.matmul(p, v).astype(np.float32).reshape(b, nh, 1, 128)
     return (out, *stats) if return_stats else out
 
 

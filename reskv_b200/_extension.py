@@ -1,0 +1,293 @@
+"""Loader and operator tables of the native library.
+
+The reference JIT-builds one pybind11 module per kernel family and plan
+(reskv/_extension.py:14-61) and calls its functions positionally
+(reskv/compression.py:90-99, reskv/_attention.py:59-143).  Here one
+ahead-of-time ``libreskv_b200.so`` (sm_100a, C ABI, see
+``include/reskv_b200.h``) is opened with ``ctypes``; ``load_extension`` keeps the
+reference's signature and returns an object that exposes the same operator
+names with the same positional arguments and return values.  Tensors stay
+torch-owned: outputs and scratch memory are allocated here with ``torch.empty``
+and the kernels run on the current CUDA stream.
+
+There is no CPU or eager fallback: a missing library, a device that is not
+compute capability 10.x, or a failing kernel call raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
+from functools import lru_cache
+from pathlib import Path
+
+import torch
+
+from .config import KernelPlan
+
+_LIB_PATH = Path(__file__).resolve().parent / "csrc" / "libreskv_b200.so"
+_FAMILIES = ("compression", "attention", "cluster_mass")
+
+ERR_INVALID, ERR_WORKSPACE, ERR_CUDA, ERR_LIMIT = -1, -2, -3, -4
+
+# name -> (restype, argtypes): exactly the declarations of include/reskv_b200.h
+_P, _I, _L, _F, _Z = c_void_p, c_int, c_int64, c_float, c_size_t
+SIGNATURES = {
+    "reskv_last_error": (c_char_p, []),
+    "reskv_version": (_I, []),
+    "reskv_decode_bitmap_fp16_workspace_bytes": (_Z, [_I, _I, _I, _I, _I]),
+    "reskv_decode_bitmap_fp16": (
+        _I,
+        [_P] * 9 + [_I, _I, _I, _I, _L, _I, _I, _I, _I, _I, _F, _P, _F, _I, _P, _P, _P, _I, _P, _Z, _P, _P, _P, _P],
+    ),
+    "reskv_decode_auto_splits": (_I, [_I, _I, _I]),
+    "reskv_merge_recent_scores": (_I, [_P] * 5 + [_I, _I, _I, _I, _P, _P]),
+    "reskv_merge_recent_qk": (_I, [_P] * 6 + [_I, _I, _I, _I, _F, _P, _P]),
+    "reskv_encode_bitmap_fp16": (_I, [_P, _P, _P, _I, _I, _I, _L, _I, _I, _P, _P, _L, _P]),
+    "reskv_encode_quantized": (_I, [_P, _P, _P, _I, _I, _I, _L, _I, _I, _I, _P, _P, _L, _P]),
+    "reskv_encode_tiled_fp16": (_I, [_P, _P, _P, _I, _I, _I, _L, _I, _I, _I, _P, _P, _L, _P]),
+    "reskv_encode_structured_int4": (_I, [_P, _P, _P, _I, _I, _I, _L, _I, _P, _P, _P, _L, _P]),
+    "reskv_kmeans_workspace_bytes": (_Z, [_I, _I, _I]),
+    "reskv_kmeans": (_I, [_P, _I, _I, _I, _L, _I, _I, _I, _P, _Z, _P, _P, _P]),
+    "reskv_kmeans_incremental": (_I, [_P, _I, _I, _I, _L, _P, _I, _P, _I, _P, _P]),
+}
+
+
+@lru_cache(maxsize=1)
+def library() -> ctypes.CDLL:
+    """The native library, with argument types set.  Raises if it was not built."""
+    if not _LIB_PATH.exists():
+        raise RuntimeError(
+            f"{_LIB_PATH} is missing: build it with `python -m reskv_b200.csrc.build` "
+            "(needs nvcc; there is no fallback path)"
+        )
+    lib = ctypes.CDLL(str(_LIB_PATH))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = restype, argtypes
+    return lib
+
+
+# Kernels launched through this module since import (bench.py reports it).
+launch_count = 0
+
+
+def check(rc: int, launches: int = 1) -> None:
+    """Count the launches of a successful call; turn a negative return code into the exception the reference would raise:
+    argument problems are ``ValueError`` (the reference's TORCH_CHECKs surface as
+    RuntimeError subclasses, its Python checks as ValueError; callers match on
+    the message), everything else ``RuntimeError``."""
+    if rc >= 0:
+        global launch_count
+        launch_count += launches
+        return
+    msg = library().reskv_last_error().decode()
+    if rc in (ERR_INVALID, ERR_LIMIT):
+        raise ValueError(msg)
+    raise RuntimeError(msg)
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None or t.numel() == 0 else t.data_ptr()
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+_CHECK_STATUS = os.environ.get("RESKV_CHECK_STATUS") == "1"
+
+
+class _Ops:
+    """Base of the operator tables: remembers the plan and device of the load."""
+
+    def __init__(self, plan: KernelPlan | None, device_index: int):
+        self.plan = plan
+        self.device = torch.device("cuda", device_index)
+        self.lib = library()
+
+
+class CompressionOps(_Ops):
+    """``compression`` family (reference pybind module compression.cu:508-512)."""
+
+    @staticmethod
+    def _dims(x, centroids, ids):
+        if x.dtype != torch.float16 or centroids.dtype != torch.float16 or ids.dtype != torch.int32:
+            raise ValueError("compression ops expect FP16 x/centroids and int32 ids")
+        if x.ndim != 4 or centroids.ndim != 4 or ids.ndim != 3 or x.shape[3] != 128 or centroids.shape[3] != 128:
+            raise ValueError("compression ops expect x[B,H,T,128], centroids[B,H,C,128], ids[B,H,T]")
+        if not (x.is_contiguous() and centroids.is_contiguous() and ids.is_contiguous()):
+            raise ValueError("compression ops expect contiguous tensors")
+        b, h, t, _ = x.shape
+        return b, h, t, centroids.shape[2]
+
+    def compress_bitmap_fp16(self, x, centroids, ids, nnz):
+        """Unstructured FP16 -> (payload f16 [B,H,T,nnz], bitmap i64 [B,H,T,2]).
+        The reference has no native op for this layout (torch ops,
+        compression.py:75-89); it is one kernel here."""
+        b, h, t, c = self._dims(x, centroids, ids)
+        payload = torch.empty((b, h, t, nnz), dtype=torch.float16, device=x.device)
+        bitmap = torch.empty((b, h, t, 2), dtype=torch.int64, device=x.device)
+        check(self.lib.reskv_encode_bitmap_fp16(x.data_ptr(), centroids.data_ptr(), ids.data_ptr(), b, h, t, t, c,
+                                                nnz, payload.data_ptr(), bitmap.data_ptr(), t, _stream(x.device)))
+        return payload, bitmap
+
+    def compress_fp16(self, x, centroids, ids, nnz, structured):
+        b, h, t, c = self._dims(x, centroids, ids)
+        values = torch.empty((b, h, t, nnz), dtype=torch.float16, device=x.device)
+        meta = torch.empty((b, h, t, 4), dtype=torch.int32, device=x.device)
+        check(self.lib.reskv_encode_tiled_fp16(x.data_ptr(), centroids.data_ptr(), ids.data_ptr(), b, h, t, t, c, nnz,
+                                               int(bool(structured)), values.data_ptr(), meta.data_ptr(), t,
+                                               _stream(x.device)))
+        return values, meta
+
+    def compress_quantized(self, x, centroids, ids, nnz, bits):
+        b, h, t, c = self._dims(x, centroids, ids)
+        words = torch.empty((b, h, t, 4 * bits), dtype=torch.int32, device=x.device)
+        scale = torch.empty((b, h, t), dtype=torch.float16, device=x.device)
+        check(self.lib.reskv_encode_quantized(x.data_ptr(), centroids.data_ptr(), ids.data_ptr(), b, h, t, t, c, nnz,
+                                              bits, words.data_ptr(), scale.data_ptr(), t, _stream(x.device)))
+        return words, scale
+
+    def compress_structured_int4(self, x, centroids, ids):
+        b, h, t, c = self._dims(x, centroids, ids)
+        packed = torch.empty((b, h, t, 4), dtype=torch.int32, device=x.device)
+        meta = torch.empty((b, h, t, 2), dtype=torch.int32, device=x.device)
+        scale = torch.empty((b, h, t), dtype=torch.float16, device=x.device)
+        check(self.lib.reskv_encode_structured_int4(x.data_ptr(), centroids.data_ptr(), ids.data_ptr(), b, h, t, t, c,
+                                                    packed.data_ptr(), meta.data_ptr(), scale.data_ptr(), t,
+                                                    _stream(x.device)))
+        return packed, meta, scale
+
+    def kmeans(self, x, count, iterations, value):
+        """Lloyd clustering -> (centroids f16 [B,H,C,128], ids i32 [B,H,T])."""
+        if x.dtype != torch.float16 or x.ndim != 4 or x.shape[3] != 128 or not x.is_contiguous():
+            raise ValueError("kmeans expects contiguous FP16 x[B,H,T,128]")
+        b, h, t, _ = x.shape
+        need = self.lib.reskv_kmeans_workspace_bytes(b, h, count)
+        if need == 0:
+            raise ValueError("kmeans: cluster count must be in [1,64]")
+        ws = torch.empty(need, dtype=torch.uint8, device=x.device)
+        centroids = torch.empty((b, h, count, 128), dtype=torch.float16, device=x.device)
+        ids = torch.empty((b, h, t), dtype=torch.int32, device=x.device)
+        check(self.lib.reskv_kmeans(x.data_ptr(), b, h, t, t, count, iterations, int(bool(value)), ws.data_ptr(), need,
+                                    centroids.data_ptr(), ids.data_ptr(), _stream(x.device)), launches=1 + 2 * iterations)
+        return centroids, ids
+
+    def kmeans_incremental(self, x, centroids, append):
+        """Decode-time step -> (centroids f16 [B,H,C or C+1,128], ids i32 [B,H,T])."""
+        b, h, t, _ = x.shape
+        old = centroids.shape[2]
+        new = old + int(bool(append))
+        centroids = centroids.contiguous()
+        out = torch.empty((b, h, new, 128), dtype=torch.float16, device=x.device)
+        ids = torch.empty((b, h, t), dtype=torch.int32, device=x.device)
+        check(self.lib.reskv_kmeans_incremental(x.data_ptr(), b, h, t, t, centroids.data_ptr(), old, out.data_ptr(),
+                                                new, ids.data_ptr(), _stream(x.device)))
+        return out, ids
+
+
+def _token_stride(rows: torch.Tensor, width: int) -> int:
+    """Tokens between units of a ``[units, T, width]`` (or ``[units, T]``) view."""
+    if rows.shape[0] == 1:
+        return rows.shape[1]
+    return rows.stride(0) // width
+
+
+class ClusterMassOps(_Ops):
+    """``cluster_mass`` family (reference pybind module cluster_mass.cu:1511-1516)."""
+
+    def decode_fp16(self, q, kc, ki, kp, km, vc, vi, vp, vm, kh, nh, start_pos, pos_q, rope_theta, scale,
+                    return_stats=True, splits=0, inv_freq=None, recent=None):
+        """Unstructured FP16 bitmap decode -> ``(out, m, l)`` (``(out,)`` without
+        stats), as cluster_mass.cu:1177-1296.  ``recent=(q_rot [B*nh,128], k_rot,
+        v [B,kh,Tr,128])`` additionally folds a dense window into the same launch
+        pair (not part of the reference signature)."""
+        bnh = q.shape[0]
+        b = bnh // nh
+        t, nnz = kp.shape[1], kp.shape[2]
+        stride = _token_stride(kp, nnz)
+        for rows, width in ((ki, 1), (km, 2), (vi, 1), (vp, nnz), (vm, 2)):
+            if _token_stride(rows, width) != stride:
+                raise ValueError("K and V cache tensors must share one token stride")
+        dev = q.device
+        need = self.lib.reskv_decode_bitmap_fp16_workspace_bytes(b, kh, nh, t, int(splits))
+        ws = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+        if _CHECK_STATUS:
+            ws[:256].zero_()
+        out = torch.empty((bnh, 128), dtype=torch.float16, device=dev)
+        m = torch.empty(bnh, dtype=torch.float32, device=dev) if return_stats else None
+        l = torch.empty(bnh, dtype=torch.float32, device=dev) if return_stats else None
+        rq = rk = rv = None
+        tr = 0
+        if recent is not None and recent[1].shape[2] > 0:
+            rq, rk, rv = (x.contiguous() for x in recent)
+            tr = rk.shape[2]
+        check(self.lib.reskv_decode_bitmap_fp16(
+            q.data_ptr(), kc.data_ptr(), ki.data_ptr(), kp.data_ptr(), km.data_ptr(), vc.data_ptr(), vi.data_ptr(),
+            vp.data_ptr(), vm.data_ptr(), b, kh, nh, t, stride, kc.shape[1], vc.shape[1], nnz, int(start_pos),
+            int(pos_q), float(rope_theta), _ptr(inv_freq), float(scale), int(splits), _ptr(rq), _ptr(rk), _ptr(rv), tr,
+            ws.data_ptr(), ws.numel(), out.data_ptr(), _ptr(m), _ptr(l), _stream(dev)), launches=2)
+        if _CHECK_STATUS:
+            status = int(ws[:4].view(torch.int32).item())
+            if status:
+                raise RuntimeError(f"decode_fp16: device status {status:#x} (bounded wait ran out)")
+        return (out, m, l) if return_stats else (out,)
+
+    def merge_recent(self, out, m, l, scores, v_recent, kh, nh):
+        b = out.shape[0] // nh
+        merged = torch.empty_like(out)
+        check(self.lib.reskv_merge_recent_scores(out.data_ptr(), m.data_ptr(), l.data_ptr(), scores.data_ptr(),
+                                                 v_recent.data_ptr(), b, kh, nh, v_recent.shape[2], merged.data_ptr(),
+                                                 _stream(out.device)))
+        return merged
+
+    def decode_structured_fp16(self, *args):
+        raise NotImplementedError("structured FP16 deferred decode is not built yet")
+
+    def decode_structured_int4(self, *args):
+        raise NotImplementedError("structured INT4 deferred decode is not built yet")
+
+
+class AttentionOps(_Ops):
+    """``attention`` family (reference pybind module attention.cu:1350-1355)."""
+
+    def merge_recent(self, out, m, l, q_rope, k_recent, v_recent, kh, nh, scale):
+        b = out.shape[0] // nh
+        merged = torch.empty_like(out)
+        check(self.lib.reskv_merge_recent_qk(out.data_ptr(), m.data_ptr(), l.data_ptr(), q_rope.data_ptr(),
+                                             k_recent.data_ptr(), v_recent.data_ptr(), b, kh, nh, k_recent.shape[2],
+                                             float(scale), merged.data_ptr(), _stream(out.device)))
+        return merged
+
+    def decode_fp16(self, *args):
+        raise NotImplementedError("tiled / structured FP16 per-token decode is not built yet")
+
+    def decode_int4(self, *args):
+        raise NotImplementedError("structured INT4 per-token decode is not built yet")
+
+    def decode_quantized(self, *args):
+        raise NotImplementedError("unstructured INT4/INT2 decode is not built yet")
+
+
+_TABLES = {"compression": CompressionOps, "attention": AttentionOps, "cluster_mass": ClusterMassOps}
+
+
+@lru_cache(maxsize=32)
+def load_extension(family: str, plan: KernelPlan | None = None, device_index: int = 0):
+    """Operator table of one kernel family (reference _extension.py:14-61).
+
+    Unlike the reference nothing is compiled here: the plan only selects
+    template instances inside the prebuilt library at call time."""
+    if family not in _FAMILIES:
+        raise ValueError(f"unknown native family: {family}")
+    if not torch.cuda.is_available():
+        raise RuntimeError("ResKV B200 kernels need a CUDA device (there is no CPU path)")
+    capability = torch.cuda.get_device_capability(device_index)
+    if capability[0] != 10:
+        raise RuntimeError(
+            f"libreskv_b200 is built for sm_100a only; device {device_index} has compute capability "
+            f"{capability[0]}.{capability[1]}"
+        )
+    return _TABLES[family](plan, device_index or 0)

@@ -1,0 +1,346 @@
+// Residual packers: x - centroid[id] -> top-magnitude selection -> compact layout.
+//
+// One warp encodes one token; lane l owns coordinates {l, l+32, l+64, l+96}.
+// With that ownership a warp vote of "lane keeps coordinate l+32i" *is* the
+// keep-mask of coordinates 32i..32i+31 (LSB = lowest coordinate), which makes
+// every metadata word of every layout one or two instructions, and ranks are
+// popcounts of votes.  Rounding points (they decide bit-exactness against the
+// reference): r = fp32(x) - fp32(c); the selection key is |fp16(r)|; FP16
+// layouts store fp16(r); quantisers divide the FP32 r with IEEE division.
+// Ties keep the lower coordinate.
+//
+// The global top-k of the unstructured layouts is a bisection on the 15-bit key
+// pattern: a vote per owned coordinate counts the keys >= candidate, so no data
+// moves between lanes.
+#include "common.cuh"
+
+namespace reskv {
+namespace {
+
+constexpr int kWarpsPerCta = 8;
+constexpr uint32_t kFull = 0xffffffffu;
+
+struct EncodeParams {
+    const __half* x;        // [units, x_stride, 128]
+    const __half* cen;      // [units, clusters, 128]
+    const int32_t* ids;     // [units, tokens]
+    void* payload;          // layout dependent
+    void* meta;             // layout dependent or null
+    __half* scale;          // [units, out_stride] or null
+    int64_t x_stride, out_stride;
+    int units, tokens, clusters, nnz;
+};
+
+struct Residual {
+    float r[4];       // fp32 residual of coordinates lane + 32 i
+    uint32_t key[4];  // bit pattern of |fp16(r)|, monotone in magnitude
+    __half h[4];      // fp16(r)
+};
+
+__device__ __forceinline__ Residual load_residual(const EncodeParams& p, int unit, int t, int lane) {
+    const __half* xr = p.x + (static_cast<size_t>(unit) * p.x_stride + t) * kHeadDim;
+    int id = p.ids[static_cast<size_t>(unit) * p.tokens + t];
+    id = min(max(id, 0), p.clusters - 1);
+    const __half* cr = p.cen + (static_cast<size_t>(unit) * p.clusters + id) * kHeadDim;
+    Residual out;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float r = __half2float(xr[lane + 32 * i]) - __half2float(__ldg(cr + lane + 32 * i));
+        out.r[i] = r;
+        out.h[i] = __float2half_rn(r);
+        out.key[i] = __half_as_ushort(out.h[i]) & 0x7fffu;
+    }
+    return out;
+}
+
+// keep[i] = coordinate lane+32i is among the `k` largest keys of the token,
+// lower coordinate first among equal keys.  vote[i] = warp mask of keep[i].
+__device__ __forceinline__ void select_topk(const uint32_t (&key)[4], int k, int lane, bool (&keep)[4],
+                                            uint32_t (&vote)[4]) {
+    // largest v with count(key >= v) >= k
+    uint32_t v = 0;
+#pragma unroll
+    for (int bit = 14; bit >= 0; --bit) {
+        const uint32_t cand = v | (1u << bit);
+        int cnt = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) cnt += __popc(__ballot_sync(kFull, key[i] >= cand));
+        if (cnt >= k) v = cand;
+    }
+    int above = 0;
+    uint32_t eq[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        above += __popc(__ballot_sync(kFull, key[i] > v));
+        eq[i] = __ballot_sync(kFull, key[i] == v);
+    }
+    const int need = k - above;  // how many of the keys equal to v are kept
+    const uint32_t below = (1u << lane) - 1u;
+    int before = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        keep[i] = key[i] > v || (key[i] == v && before + __popc(eq[i] & below) < need);
+        before += __popc(eq[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) vote[i] = __ballot_sync(kFull, keep[i]);
+}
+
+// ---- unstructured FP16: bitmap (MSB first) + packed values ----------------------
+__global__ void __launch_bounds__(kWarpsPerCta * 32) encode_bitmap_fp16_kernel(const EncodeParams p) {
+    const int lane = threadIdx.x & 31;
+    const long long rows = static_cast<long long>(p.units) * p.tokens;
+    for (long long row = static_cast<long long>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5); row < rows;
+         row += static_cast<long long>(gridDim.x) * kWarpsPerCta) {
+        const int unit = static_cast<int>(row / p.tokens), t = static_cast<int>(row % p.tokens);
+        const Residual res = load_residual(p, unit, t, lane);
+        bool keep[4];
+        uint32_t vote[4];
+        select_topk(res.key, p.nnz, lane, keep, vote);
+        const size_t orow = static_cast<size_t>(unit) * p.out_stride + t;
+        __half* pay = static_cast<__half*>(p.payload) + orow * p.nnz;
+        const uint32_t below = (1u << lane) - 1u;
+        int base = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (keep[i]) pay[base + __popc(vote[i] & below)] = res.h[i];
+            base += __popc(vote[i]);
+        }
+        if (lane == 0) {
+            // word w of the bitmap: coordinate d at bit 63 - d % 64
+            uint4 bm;
+            bm.y = __brev(vote[0]);
+            bm.x = __brev(vote[1]);
+            bm.w = __brev(vote[2]);
+            bm.z = __brev(vote[3]);
+            static_cast<uint4*>(p.meta)[orow] = bm;
+        }
+    }
+}
+
+// ---- unstructured INT4 / INT2: every coordinate stored, discarded ones as 0 ----------
+template <int BITS>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) encode_quantized_kernel(const EncodeParams p) {
+    constexpr int kQmax = (1 << (BITS - 1)) - 1;
+    constexpr int kPer = 32 / BITS;   // values per word, a power of two <= 16
+    const int lane = threadIdx.x & 31;
+    const long long rows = static_cast<long long>(p.units) * p.tokens;
+    for (long long row = static_cast<long long>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5); row < rows;
+         row += static_cast<long long>(gridDim.x) * kWarpsPerCta) {
+        const int unit = static_cast<int>(row / p.tokens), t = static_cast<int>(row % p.tokens);
+        const Residual res = load_residual(p, unit, t, lane);
+        bool keep[4];
+        uint32_t vote[4];
+        select_topk(res.key, p.nnz, lane, keep, vote);
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) amax = fmaxf(amax, keep[i] ? fabsf(res.r[i]) : 0.f);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, off));
+        const __half hs = amax > 0.f ? __float2half_rn(__fdiv_rn(amax, static_cast<float>(kQmax))) : __float2half_rn(1.f);
+        const float s = __half2float(hs);
+        const size_t orow = static_cast<size_t>(unit) * p.out_stride + t;
+        int32_t* words = static_cast<int32_t*>(p.payload) + orow * (4 * BITS);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            int q = 0;
+            if (keep[i]) {
+                const float f = rintf(__fdiv_rn(res.r[i], s));
+                q = static_cast<int>(fminf(fmaxf(f, -static_cast<float>(kQmax)), static_cast<float>(kQmax)));
+            }
+            // coordinate d = lane + 32 i sits at bit (d % kPer) * BITS of word d / kPer
+            uint32_t w = (static_cast<uint32_t>(q) & ((1u << BITS) - 1u)) << ((lane % kPer) * BITS);
+#pragma unroll
+            for (int off = 1; off < kPer; off <<= 1) w |= __shfl_xor_sync(kFull, w, off);
+            if (lane % kPer == 0) words[(lane + 32 * i) / kPer] = static_cast<int32_t>(w);
+        }
+        if (lane == 0) p.scale[orow] = hs;
+    }
+}
+
+// ---- tiled (mask) / structured 4:16 (indices) FP16 -----------------------------------
+// Tile j = coordinates 16j..16j+15 = half-warp (j % 2) of owned coordinate i = j / 2.
+template <bool STRUCT>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) encode_tiled_fp16_kernel(const EncodeParams p) {
+    const int lane = threadIdx.x & 31, sub = lane & 15;
+    const int per_tile = p.nnz / 8;
+    const long long rows = static_cast<long long>(p.units) * p.tokens;
+    for (long long row = static_cast<long long>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5); row < rows;
+         row += static_cast<long long>(gridDim.x) * kWarpsPerCta) {
+        const int unit = static_cast<int>(row / p.tokens), t = static_cast<int>(row % p.tokens);
+        const Residual res = load_residual(p, unit, t, lane);
+        const size_t orow = static_cast<size_t>(unit) * p.out_stride + t;
+        __half* val = static_cast<__half*>(p.payload) + orow * p.nnz;
+        int32_t* meta = static_cast<int32_t*>(p.meta) + orow * 4;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            // position of this coordinate in its tile's (key desc, index asc) order
+            int beat = 0;
+#pragma unroll
+            for (int off = 1; off < 16; ++off) {
+                const int src = (lane & 16) | ((sub + off) & 15);
+                const uint32_t other = __shfl_sync(kFull, res.key[i], src);
+                const int osub = (sub + off) & 15;
+                beat += (other > res.key[i]) || (other == res.key[i] && osub < sub);
+            }
+            const bool keep = beat < per_tile;
+            const uint32_t vote = __ballot_sync(kFull, keep);
+            const uint32_t tile_mask = (vote >> (lane & 16)) & 0xffffu;
+            const int rank = __popc(tile_mask & ((1u << sub) - 1u));
+            const int tile = 2 * i + (lane >> 4);
+            if (keep) val[tile * per_tile + rank] = res.h[i];
+            if constexpr (STRUCT) {
+                // four 4-bit in-tile indices, rank r at bit 4r; tile 2i low half, 2i+1 high half
+                uint32_t code = keep ? (static_cast<uint32_t>(sub) << (4 * rank + (lane & 16))) : 0u;
+                code = __reduce_or_sync(kFull, code);
+                if (lane == 0) meta[i] = static_cast<int32_t>(code);
+            } else {
+                if (lane == 0) meta[i] = static_cast<int32_t>(vote);
+            }
+        }
+    }
+}
+
+// ---- structured INT4: one coordinate of every four ------------------------------------
+__global__ void __launch_bounds__(kWarpsPerCta * 32) encode_structured_int4_kernel(const EncodeParams p) {
+    const int lane = threadIdx.x & 31, in_group = lane & 3;
+    const long long rows = static_cast<long long>(p.units) * p.tokens;
+    for (long long row = static_cast<long long>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5); row < rows;
+         row += static_cast<long long>(gridDim.x) * kWarpsPerCta) {
+        const int unit = static_cast<int>(row / p.tokens), t = static_cast<int>(row % p.tokens);
+        const Residual res = load_residual(p, unit, t, lane);
+        float comp[4];   // the group's chosen residual (valid in every lane of the group)
+        int which[4];
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t bk = res.key[i];
+            int bi = in_group;
+            float br = res.r[i];
+#pragma unroll
+            for (int off = 1; off < 4; off <<= 1) {
+                const uint32_t ok = __shfl_xor_sync(kFull, bk, off);
+                const int oi = __shfl_xor_sync(kFull, bi, off);
+                const float orr = __shfl_xor_sync(kFull, br, off);
+                if (ok > bk || (ok == bk && oi < bi)) bk = ok, bi = oi, br = orr;
+            }
+            comp[i] = br, which[i] = bi;
+            amax = fmaxf(amax, fabsf(br));
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, off));
+        const float s = amax > 0.f ? amax * (1.0f / 7.0f) : 1.0f;
+        const size_t orow = static_cast<size_t>(unit) * p.out_stride + t;
+        int32_t* packed = static_cast<int32_t*>(p.payload) + orow * 4;
+        int32_t* meta = static_cast<int32_t*>(p.meta) + orow * 2;
+        uint32_t mword[2] = {0u, 0u};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            // group g = 8 i + lane / 4; nibble g % 8 of word g / 8 = i; index bits 2 (g % 16) of meta word g / 16
+            const float f = rintf(__fdiv_rn(comp[i], s));
+            const int q = static_cast<int>(fminf(fmaxf(f, -7.f), 7.f));
+            const bool leader = in_group == 0;
+            uint32_t w = leader ? ((static_cast<uint32_t>(q) & 15u) << (4 * (lane >> 2))) : 0u;
+            w = __reduce_or_sync(kFull, w);
+            if (lane == 0) packed[i] = static_cast<int32_t>(w);
+            const int g = 8 * i + (lane >> 2);
+            if (leader) mword[i >> 1] |= static_cast<uint32_t>(which[i]) << (2 * (g & 15));
+        }
+        mword[0] = __reduce_or_sync(kFull, mword[0]);
+        mword[1] = __reduce_or_sync(kFull, mword[1]);
+        if (lane == 0) {
+            meta[0] = static_cast<int32_t>(mword[0]);
+            meta[1] = static_cast<int32_t>(mword[1]);
+            p.scale[orow] = __float2half_rn(s);
+        }
+    }
+}
+
+int check_common(const char* who, const void* x, const void* cen, const void* ids, const void* payload, int batch,
+                 int kv_heads, int tokens, int64_t x_stride, int clusters, int64_t out_stride) {
+    if (!x || !cen || !ids || !payload) return fail(RESKV_ERR_INVALID, "%s: null tensor pointer", who);
+    if (batch < 1 || kv_heads < 1 || tokens < 1) return fail(RESKV_ERR_INVALID, "%s: batch, heads and tokens must be positive", who);
+    if (clusters < 1 || clusters > kMaxClusters) return fail(RESKV_ERR_INVALID, "%s: centroid count must be in [1,64]", who);
+    if (x_stride < tokens || out_stride < tokens) return fail(RESKV_ERR_INVALID, "%s: token stride smaller than token count", who);
+    return RESKV_OK;
+}
+
+int grid_for(long long rows) {
+    const long long want = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
+    const long long cap = static_cast<long long>(sm_count()) * 16;
+    return static_cast<int>(want < cap ? want : cap);
+}
+
+}  // namespace
+}  // namespace reskv
+
+using namespace reskv;
+
+extern "C" int reskv_encode_bitmap_fp16(const void* x, const void* centroids, const int32_t* ids, int batch,
+                                        int kv_heads, int tokens, int64_t x_tok_stride, int clusters, int nnz,
+                                        void* payload, void* bitmap, int64_t out_tok_stride, void* stream) {
+    if (int rc = check_common("encode_bitmap_fp16", x, centroids, ids, payload, batch, kv_heads, tokens, x_tok_stride,
+                              clusters, out_tok_stride))
+        return rc;
+    if (!bitmap || !aligned16(bitmap)) return fail(RESKV_ERR_INVALID, "encode_bitmap_fp16: bitmap must be a 16-byte aligned pointer");
+    if (nnz < 1 || nnz > 127) return fail(RESKV_ERR_INVALID, "encode_bitmap_fp16: nnz must be in [1,127], got %d", nnz);
+    EncodeParams p{static_cast<const __half*>(x), static_cast<const __half*>(centroids), ids, payload, bitmap, nullptr,
+                   x_tok_stride, out_tok_stride, batch * kv_heads, tokens, clusters, nnz};
+    const long long rows = static_cast<long long>(p.units) * tokens;
+    encode_bitmap_fp16_kernel<<<grid_for(rows), kWarpsPerCta * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    return check_cuda(cudaGetLastError(), "encode_bitmap_fp16 launch");
+}
+
+extern "C" int reskv_encode_quantized(const void* x, const void* centroids, const int32_t* ids, int batch, int kv_heads,
+                                      int tokens, int64_t x_tok_stride, int clusters, int nnz, int bits, void* words,
+                                      void* scale, int64_t out_tok_stride, void* stream) {
+    if (int rc = check_common("encode_quantized", x, centroids, ids, words, batch, kv_heads, tokens, x_tok_stride,
+                              clusters, out_tok_stride))
+        return rc;
+    if (!scale) return fail(RESKV_ERR_INVALID, "encode_quantized: null scale pointer");
+    if (nnz != 32 && nnz != 64) return fail(RESKV_ERR_INVALID, "encode_quantized: nnz must be 32 or 64, got %d", nnz);
+    if (bits != 2 && bits != 4) return fail(RESKV_ERR_INVALID, "encode_quantized: bits must be 2 or 4, got %d", bits);
+    EncodeParams p{static_cast<const __half*>(x), static_cast<const __half*>(centroids), ids, words, nullptr,
+                   static_cast<__half*>(scale), x_tok_stride, out_tok_stride, batch * kv_heads, tokens, clusters, nnz};
+    const long long rows = static_cast<long long>(p.units) * tokens;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (bits == 4)
+        encode_quantized_kernel<4><<<grid_for(rows), kWarpsPerCta * 32, 0, s>>>(p);
+    else
+        encode_quantized_kernel<2><<<grid_for(rows), kWarpsPerCta * 32, 0, s>>>(p);
+    return check_cuda(cudaGetLastError(), "encode_quantized launch");
+}
+
+extern "C" int reskv_encode_tiled_fp16(const void* x, const void* centroids, const int32_t* ids, int batch,
+                                       int kv_heads, int tokens, int64_t x_tok_stride, int clusters, int nnz,
+                                       int structured, void* values, void* meta, int64_t out_tok_stride, void* stream) {
+    if (int rc = check_common("encode_tiled_fp16", x, centroids, ids, values, batch, kv_heads, tokens, x_tok_stride,
+                              clusters, out_tok_stride))
+        return rc;
+    if (!meta) return fail(RESKV_ERR_INVALID, "encode_tiled_fp16: null metadata pointer");
+    if (nnz <= 0 || nnz >= 128 || nnz % 8) return fail(RESKV_ERR_INVALID, "encode_tiled_fp16: nnz must be a multiple of 8 below 128, got %d", nnz);
+    if (structured && nnz != 32) return fail(RESKV_ERR_INVALID, "encode_tiled_fp16: the 4:16 index form needs nnz == 32");
+    EncodeParams p{static_cast<const __half*>(x), static_cast<const __half*>(centroids), ids, values, meta, nullptr,
+                   x_tok_stride, out_tok_stride, batch * kv_heads, tokens, clusters, nnz};
+    const long long rows = static_cast<long long>(p.units) * tokens;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (structured)
+        encode_tiled_fp16_kernel<true><<<grid_for(rows), kWarpsPerCta * 32, 0, s>>>(p);
+    else
+        encode_tiled_fp16_kernel<false><<<grid_for(rows), kWarpsPerCta * 32, 0, s>>>(p);
+    return check_cuda(cudaGetLastError(), "encode_tiled_fp16 launch");
+}
+
+extern "C" int reskv_encode_structured_int4(const void* x, const void* centroids, const int32_t* ids, int batch,
+                                            int kv_heads, int tokens, int64_t x_tok_stride, int clusters, void* packed,
+                                            void* meta, void* scale, int64_t out_tok_stride, void* stream) {
+    if (int rc = check_common("encode_structured_int4", x, centroids, ids, packed, batch, kv_heads, tokens,
+                              x_tok_stride, clusters, out_tok_stride))
+        return rc;
+    if (!meta || !scale) return fail(RESKV_ERR_INVALID, "encode_structured_int4: null metadata or scale pointer");
+    EncodeParams p{static_cast<const __half*>(x), static_cast<const __half*>(centroids), ids, packed, meta,
+                   static_cast<__half*>(scale), x_tok_stride, out_tok_stride, batch * kv_heads, tokens, clusters, 32};
+    const long long rows = static_cast<long long>(p.units) * tokens;
+    encode_structured_int4_kernel<<<grid_for(rows), kWarpsPerCta * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    return check_cuda(cudaGetLastError(), "encode_structured_int4 launch");
+}

@@ -1,0 +1,635 @@
+// Fused split-K decode attention over the unstructured FP16 bitmap layout, with
+// deferred value-centroid fusion.
+//
+// For a query q, compressed keys k_t = ck[idk_t] + rk_t and values
+// v_t = cv[idv_t] + rv_t (rk, rv sparse, stored as bitmap + packed FP16):
+//
+//   s_t  = scaling * < R(pos_q) q , R(start + t) k_t >          (half-split RoPE)
+//   out  = sum_t p_t v_t / sum_t p_t
+//        = ( sum_t p_t rv_t  +  sum_c beta_c cv[c] ) / l ,  beta_c = sum_{idv_t = c} p_t
+//
+// so the token loop only touches residuals and accumulates the per-cluster mass
+// beta; the value centroids are applied once, after the split-K reduction
+// (same decomposition as the reference, cluster_mass.cu:3-11).
+//
+// Kernel 1 (partial): grid (splits, units).  A CTA streams its token range in
+// tiles of 64 tokens.  Bitmaps and payloads of a tile are contiguous in global
+// memory, so each tile is four 1-D bulk copies (TMA) into a shared-memory ring,
+// completion tracked by one mbarrier per stage.  Each warp owns every eighth
+// token of a tile; a lane owns coordinates {l, l+32, l+64, l+96}, which keeps
+// both RoPE partners (d, d+64) in one lane.  A kept coordinate's payload index
+// is the popcount of the bitmap bits above it.  The key is rotated once and
+// shared by all query heads of the KV head (GQA); RoPE sin/cos advance by a
+// fixed rotation per token and are re-seeded every 16 tiles.
+//
+// Kernel 2 (merge): one CTA per query head reduces the split partials, applies
+// the value centroids, and -- when a dense recent window is given -- folds its
+// tokens into the same softmax.
+#include "common.cuh"
+
+namespace reskv {
+namespace {
+
+constexpr int kTile = 64;    // tokens per pipeline stage
+constexpr int kWarps = 8;    // warps per CTA
+constexpr int kThreads = kWarps * 32;
+constexpr int kTokPerWarp = kTile / kWarps;
+constexpr int kReseedTiles = 16;
+constexpr int kWsHeader = 256;  // bytes reserved at the start of the workspace (status word)
+
+struct DecodeParams {
+    const __half* q;
+    const __half* kc;
+    const int8_t* kid;
+    const __half* kp;
+    const uint4* kb;
+    const int8_t* vid;
+    const __half* vp;
+    const uint4* vb;
+    float* ws_m;
+    float* ws_l;
+    float* ws_delta;
+    float* ws_beta;
+    uint32_t* status;
+    const float* inv_freq;
+    int64_t tok_stride;
+    int kh, nh, tokens, ck, cv;
+    int start_pos, pos_q, splits, tiles_per_split;
+    float theta, scaling;
+};
+
+template <int NNZ>
+struct Stage {
+    uint4 kb[kTile];
+    uint4 vb[kTile];
+    __half kp[kTile * NNZ];
+    __half vp[kTile * NNZ];
+};
+
+__device__ __forceinline__ float rope_freq(const float* inv_freq, float theta, int i) {
+    return inv_freq ? inv_freq[i] : powf(theta, -static_cast<float>(i) / 64.0f);
+}
+
+// Sum GQA per-lane partials over the warp; every lane ends with all totals.
+template <int GQA>
+__device__ __forceinline__ void warp_sum_heads(float (&v)[GQA], int lane) {
+    if constexpr (GQA == 4) {
+        const bool up = lane & 16;
+        float send0 = up ? v[0] : v[2], send1 = up ? v[1] : v[3];
+        float keep0 = up ? v[2] : v[0], keep1 = up ? v[3] : v[1];
+        keep0 += __shfl_xor_sync(0xffffffffu, send0, 16);
+        keep1 += __shfl_xor_sync(0xffffffffu, send1, 16);
+        const bool up2 = lane & 8;
+        float send = up2 ? keep0 : keep1;
+        float y = (up2 ? keep1 : keep0) + __shfl_xor_sync(0xffffffffu, send, 8);
+        y += __shfl_xor_sync(0xffffffffu, y, 4);
+        y += __shfl_xor_sync(0xffffffffu, y, 2);
+        y += __shfl_xor_sync(0xffffffffu, y, 1);
+        // lanes [0,8) hold head 0, [8,16) head 1, [16,24) head 2, [24,32) head 3
+#pragma unroll
+        for (int h = 0; h < 4; ++h) v[h] = __shfl_sync(0xffffffffu, y, h * 8);
+    } else {
+#pragma unroll
+        for (int h = 0; h < GQA; ++h) {
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) v[h] += __shfl_xor_sync(0xffffffffu, v[h], off);
+        }
+    }
+}
+
+// Residual value of the lane's four coordinates of one token.
+// Bitmap words in memory order: x = word0 low half (coords 32..63), y = word0
+// high half (0..31), z = word1 low (96..127), w = word1 high (64..95); inside a
+// 32-bit half coordinate c sits at bit 31 - c % 32.
+template <int NNZ>
+__device__ __forceinline__ void decode4(const uint4 bm, const __half* row, int lane, float (&r)[4]) {
+    const uint32_t word[4] = {bm.y, bm.x, bm.w, bm.z};
+    int base = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t w = word[i];
+        const int rank = base + __popc(__funnelshift_rc(w, 0u, 32 - lane));
+        const bool kept = (w >> (31 - lane)) & 1u;
+        r[i] = kept ? __half2float(row[min(rank, NNZ - 1)]) : 0.0f;
+        base += __popc(w);
+    }
+}
+
+template <int GQA, int NNZ, int CVS>
+__global__ void __launch_bounds__(kThreads, 2) decode_bitmap_partial_kernel(const DecodeParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    constexpr int kStages = (NNZ <= 32) ? 4 : 3;
+    using StageT = Stage<NNZ>;
+    StageT* stages = reinterpret_cast<StageT*>(smem_raw);
+    __half* kc_s = reinterpret_cast<__half*>(smem_raw + sizeof(StageT) * kStages);
+    __shared__ uint64_t full_bar[kStages];
+    __shared__ float red_m[GQA][kWarps];
+    __shared__ float red_l[GQA][kWarps];
+    __shared__ uint32_t timed_out;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int split = blockIdx.x, unit = blockIdx.y;
+    const int b = unit / p.kh, hkv = unit % p.kh;
+
+    const int total_tiles = (p.tokens + kTile - 1) / kTile;
+    const int tile_begin = split * p.tiles_per_split;
+    const int tile_end = min(total_tiles, tile_begin + p.tiles_per_split);
+    const int ntiles = max(0, tile_end - tile_begin);
+
+    const size_t unit_tok = static_cast<size_t>(unit) * p.tok_stride;
+    const uint4* kb_g = p.kb + unit_tok;
+    const uint4* vb_g = p.vb + unit_tok;
+    const __half* kp_g = p.kp + unit_tok * NNZ;
+    const __half* vp_g = p.vp + unit_tok * NNZ;
+    const int8_t* kid_g = p.kid + unit_tok;
+    const int8_t* vid_g = p.vid + unit_tok;
+
+    if (tid == 0) {
+        timed_out = 0;
+        for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    auto issue = [&](int tile_rel) {
+        // one thread: four bulk copies of tile `tile_rel` into its ring slot
+        const int t0 = (tile_begin + tile_rel) * kTile;
+        const int n = min(kTile, p.tokens - t0);
+        StageT& st = stages[tile_rel % kStages];
+        uint64_t* bar = &full_bar[tile_rel % kStages];
+        const uint32_t bm_bytes = n * 16u, pl_bytes = n * NNZ * 2u;
+        mbar_arrive_expect_tx(bar, 2 * bm_bytes + 2 * pl_bytes);
+        bulk_g2s(st.kb, kb_g + t0, bm_bytes, bar);
+        bulk_g2s(st.vb, vb_g + t0, bm_bytes, bar);
+        bulk_g2s(st.kp, kp_g + static_cast<size_t>(t0) * NNZ, pl_bytes, bar);
+        bulk_g2s(st.vp, vp_g + static_cast<size_t>(t0) * NNZ, pl_bytes, bar);
+    };
+    if (tid == 0) {
+        for (int s = 0; s < kStages && s < ntiles; ++s) issue(s);
+    }
+
+    // key centroid table -> shared memory (FP16, as stored)
+    {
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(p.kc + static_cast<size_t>(unit) * p.ck * kHeadDim);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(kc_s);
+        for (int i = tid; i < p.ck * kHeadDim / 2; i += kThreads) dst[i] = __ldg(src + i);
+    }
+
+    // query, rotated at pos_q, pre-multiplied by scaling * log2(e)
+    const float f0 = rope_freq(p.inv_freq, p.theta, lane);
+    const float f1 = rope_freq(p.inv_freq, p.theta, lane + 32);
+    float qr[GQA][4];
+    {
+        float s0, c0, s1, c1;
+        sincosf(static_cast<float>(p.pos_q) * f0, &s0, &c0);
+        sincosf(static_cast<float>(p.pos_q) * f1, &s1, &c1);
+        const float mul = p.scaling * kLog2e;
+#pragma unroll
+        for (int h = 0; h < GQA; ++h) {
+            const __half* qh = p.q + (static_cast<size_t>(b) * p.nh + hkv * GQA + h) * kHeadDim;
+            const float a0 = __half2float(qh[lane]), a1 = __half2float(qh[lane + 32]);
+            const float a2 = __half2float(qh[lane + 64]), a3 = __half2float(qh[lane + 96]);
+            qr[h][0] = (a0 * c0 - a2 * s0) * mul;
+            qr[h][2] = (a2 * c0 + a0 * s0) * mul;
+            qr[h][1] = (a1 * c1 - a3 * s1) * mul;
+            qr[h][3] = (a3 * c1 + a1 * s1) * mul;
+        }
+    }
+    // fixed rotation between consecutive tokens of this warp (kWarps positions)
+    float ds0, dc0, ds1, dc1;
+    sincosf(static_cast<float>(kWarps) * f0, &ds0, &dc0);
+    sincosf(static_cast<float>(kWarps) * f1, &ds1, &dc1);
+
+    float m_run[GQA], l_run[GQA], acc[GQA][4], bet[GQA][CVS];
+#pragma unroll
+    for (int h = 0; h < GQA; ++h) {
+        m_run[h] = -INFINITY;
+        l_run[h] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[h][i] = 0.f;
+#pragma unroll
+        for (int i = 0; i < CVS; ++i) bet[h][i] = 0.f;
+    }
+
+    // cluster ids of this warp's tokens in the next tile, one token per lane < kTokPerWarp
+    auto load_ids = [&](int tile_rel, int& kid, int& vid) {
+        kid = vid = 0;
+        const int t = (tile_begin + tile_rel) * kTile + warp + kWarps * lane;
+        if (tile_rel < ntiles && lane < kTokPerWarp && t < p.tokens) {
+            kid = kid_g[t];
+            vid = vid_g[t];
+        }
+    };
+    int kid_next, vid_next;
+    load_ids(0, kid_next, vid_next);
+    __syncthreads();  // centroid table ready
+
+    float rs0 = 0.f, rc0 = 1.f, rs1 = 0.f, rc1 = 1.f;
+    bool lost = false;
+    for (int it = 0; it < ntiles; ++it) {
+        const int t0 = (tile_begin + it) * kTile;
+        const int kid_cur = kid_next, vid_cur = vid_next;
+        load_ids(it + 1, kid_next, vid_next);
+        if (it % kReseedTiles == 0) {
+            const float pos = static_cast<float>(p.start_pos + t0 + warp);
+            sincosf(pos * f0, &rs0, &rc0);
+            sincosf(pos * f1, &rs1, &rc1);
+        }
+        if (!mbar_wait(&full_bar[it % kStages], (it / kStages) & 1)) lost = true;
+        const StageT& st = stages[it % kStages];
+#pragma unroll 2
+        for (int j = 0; j < kTokPerWarp; ++j) {
+            const int tl = warp + kWarps * j;  // token within the tile
+            if (t0 + tl < p.tokens) {
+                const int kid = __shfl_sync(0xffffffffu, kid_cur, j);
+                const int vid = __shfl_sync(0xffffffffu, vid_cur, j);
+                float kv[4], vr[4];
+                decode4<NNZ>(st.kb[tl], st.kp + tl * NNZ, lane, kv);
+                decode4<NNZ>(st.vb[tl], st.vp + tl * NNZ, lane, vr);
+                const __half* crow = kc_s + min(max(kid, 0), p.ck - 1) * kHeadDim;
+                kv[0] += __half2float(crow[lane]);
+                kv[1] += __half2float(crow[lane + 32]);
+                kv[2] += __half2float(crow[lane + 64]);
+                kv[3] += __half2float(crow[lane + 96]);
+                const float k0 = kv[0] * rc0 - kv[2] * rs0, k2 = kv[2] * rc0 + kv[0] * rs0;
+                const float k1 = kv[1] * rc1 - kv[3] * rs1, k3 = kv[3] * rc1 + kv[1] * rs1;
+                float s[GQA];
+#pragma unroll
+                for (int h = 0; h < GQA; ++h)
+                    s[h] = qr[h][0] * k0 + qr[h][1] * k1 + qr[h][2] * k2 + qr[h][3] * k3;
+                warp_sum_heads<GQA>(s, lane);
+#pragma unroll
+                for (int h = 0; h < GQA; ++h) {
+                    const float m_new = fmaxf(m_run[h], s[h]);
+                    const float corr = fast_exp2(m_run[h] - m_new);
+                    const float pr = fast_exp2(s[h] - m_new);
+                    m_run[h] = m_new;
+                    l_run[h] = l_run[h] * corr + pr;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[h][i] = acc[h][i] * corr + pr * vr[i];
+#pragma unroll
+                    for (int i = 0; i < CVS; ++i)
+                        bet[h][i] = bet[h][i] * corr + ((lane + 32 * i == vid) ? pr : 0.f);
+                }
+            }
+            // advance this warp's RoPE state by kWarps positions
+            const float ns0 = rs0 * dc0 + rc0 * ds0, nc0 = rc0 * dc0 - rs0 * ds0;
+            const float ns1 = rs1 * dc1 + rc1 * ds1, nc1 = rc1 * dc1 - rs1 * ds1;
+            rs0 = ns0, rc0 = nc0, rs1 = ns1, rc1 = nc1;
+        }
+        __syncthreads();  // every warp is done with this ring slot
+        if (tid == 0 && it + kStages < ntiles) issue(it + kStages);
+    }
+    if (lost && lane == 0) atomicOr(&timed_out, 1u);
+
+    // ---- combine the warps of the CTA ------------------------------------------
+    if (lane == 0) {
+#pragma unroll
+        for (int h = 0; h < GQA; ++h) red_m[h][warp] = m_run[h], red_l[h][warp] = l_run[h];
+    }
+    __syncthreads();
+    // stage buffers are free now: reuse them for the cross-warp sums
+    float* red_acc = reinterpret_cast<float*>(smem_raw);               // [kWarps][GQA][128]
+    float* red_bet = red_acc + kWarps * GQA * kHeadDim;                // [kWarps][GQA][32*CVS]
+#pragma unroll
+    for (int h = 0; h < GQA; ++h) {
+        float fm = red_m[h][0];
+#pragma unroll
+        for (int w = 1; w < kWarps; ++w) fm = fmaxf(fm, red_m[h][w]);
+        const float sc = (m_run[h] == -INFINITY) ? 0.f : fast_exp2(m_run[h] - fm);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) red_acc[(warp * GQA + h) * kHeadDim + lane + 32 * i] = acc[h][i] * sc;
+#pragma unroll
+        for (int i = 0; i < CVS; ++i) red_bet[(warp * GQA + h) * (32 * CVS) + lane + 32 * i] = bet[h][i] * sc;
+    }
+    __syncthreads();
+    const size_t part = static_cast<size_t>(b) * p.nh + hkv * GQA;  // first query head of this unit
+    for (int idx = tid; idx < GQA * kHeadDim; idx += kThreads) {
+        const int h = idx / kHeadDim, d = idx % kHeadDim;
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) sum += red_acc[(w * GQA + h) * kHeadDim + d];
+        p.ws_delta[((part + h) * p.splits + split) * kHeadDim + d] = sum;
+    }
+    for (int idx = tid; idx < GQA * 32 * CVS; idx += kThreads) {
+        const int h = idx / (32 * CVS), c = idx % (32 * CVS);
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) sum += red_bet[(w * GQA + h) * (32 * CVS) + c];
+        p.ws_beta[((part + h) * p.splits + split) * kMaxClusters + c] = sum;
+    }
+    if (tid < GQA) {
+        const int h = tid;
+        float fm = red_m[h][0];
+        for (int w = 1; w < kWarps; ++w) fm = fmaxf(fm, red_m[h][w]);
+        float fl = 0.f;
+        for (int w = 0; w < kWarps; ++w)
+            fl += (red_m[h][w] == -INFINITY) ? 0.f : red_l[h][w] * fast_exp2(red_m[h][w] - fm);
+        p.ws_m[(part + h) * p.splits + split] = fm;  // log2 domain
+        p.ws_l[(part + h) * p.splits + split] = fl;
+    }
+    if (tid == 0 && timed_out) atomicOr(p.status, RESKV_STATUS_WAIT_TIMEOUT);
+}
+
+// ---- merge -----------------------------------------------------------------------
+struct MergeParams {
+    const float* ws_m;      // log2-domain maxima [BNH][splits], or natural-log m [BNH] when splits == 0
+    const float* ws_l;
+    const float* ws_delta;
+    const float* ws_beta;
+    const __half* vc;       // [B*KH,CV,128]
+    const __half* comp_out; // splits == 0: finished compressed result to merge with
+    const __half* rq;       // rotated query [BNH,128] or null
+    const __half* rk;       // rotated recent keys [B*KH,Tr,128] or null
+    const __half* rv;       // recent values
+    const float* rscores;   // precomputed scaled scores [BNH,Tr] (natural units) or null
+    __half* out;
+    float* out_m;
+    float* out_l;
+    int kh, nh, splits, cv, tr;
+    float scaling;
+};
+
+constexpr int kMergeThreads = 128;
+constexpr int kMaxRecent = 1024;  // recent tokens whose scores fit the shared buffer
+
+// One CTA per query head; thread d owns output coordinate d.
+__global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const MergeParams p) {
+    __shared__ float beta_s[kMaxClusters];
+    __shared__ float sc_s[kMaxRecent];
+    __shared__ float red[kMergeThreads / 32];
+    const int fq = blockIdx.x, d = threadIdx.x, lane = d & 31, warp = d >> 5;
+    const int b = fq / p.nh, head = fq % p.nh;
+    const int unit = b * p.kh + head / (p.nh / p.kh);
+
+    // compressed part: numerator `num`, max `m2` (log2 domain), sum `l`
+    float m2, l, num;
+    if (p.splits > 0) {
+        const float* pm = p.ws_m + static_cast<size_t>(fq) * p.splits;
+        const float* pl = p.ws_l + static_cast<size_t>(fq) * p.splits;
+        m2 = pm[0];
+        for (int s = 1; s < p.splits; ++s) m2 = fmaxf(m2, pm[s]);
+        l = 0.f, num = 0.f;
+        float bsum = 0.f;
+        for (int s = 0; s < p.splits; ++s) {
+            const float w = (pm[s] == -INFINITY) ? 0.f : fast_exp2(pm[s] - m2);
+            l += pl[s] * w;
+            const size_t row = static_cast<size_t>(fq) * p.splits + s;
+            num += p.ws_delta[row * kHeadDim + d] * w;
+            if (d < p.cv) bsum += p.ws_beta[row * kMaxClusters + d] * w;
+        }
+        if (d < kMaxClusters) beta_s[d] = (d < p.cv) ? bsum : 0.f;
+        __syncthreads();
+        const __half* vc = p.vc + static_cast<size_t>(unit) * p.cv * kHeadDim + d;
+        for (int c = 0; c < p.cv; ++c) num = fmaf(beta_s[c], __half2float(vc[c * kHeadDim]), num);
+        if (d == 0) {
+            if (p.out_m) p.out_m[fq] = m2 * kLn2;
+            if (p.out_l) p.out_l[fq] = l;
+        }
+    } else {
+        m2 = p.ws_m[fq] * kLog2e;
+        l = p.ws_l[fq];
+        num = __half2float(p.comp_out[static_cast<size_t>(fq) * kHeadDim + d]) * l;
+    }
+
+    if (p.tr > 0) {
+        // scores of the recent tokens (log2 domain) into shared memory
+        if (p.rscores) {
+            for (int t = d; t < p.tr; t += kMergeThreads)
+                sc_s[t] = p.rscores[static_cast<size_t>(fq) * p.tr + t] * kLog2e;
+        } else {
+            const __half* qrow = p.rq + static_cast<size_t>(fq) * kHeadDim;
+            float qv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) qv[i] = __half2float(qrow[lane + 32 * i]);
+            const float mul = p.scaling * kLog2e;
+            for (int t = warp; t < p.tr; t += kMergeThreads / 32) {
+                const __half* krow = p.rk + (static_cast<size_t>(unit) * p.tr + t) * kHeadDim;
+                float dot = 0.f;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) dot = fmaf(qv[i], __half2float(krow[lane + 32 * i]), dot);
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+                if (lane == 0) sc_s[t] = dot * mul;
+            }
+        }
+        __syncthreads();
+        float rm = -INFINITY;
+        for (int t = d; t < p.tr; t += kMergeThreads) rm = fmaxf(rm, sc_s[t]);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) rm = fmaxf(rm, __shfl_xor_sync(0xffffffffu, rm, off));
+        if (lane == 0) red[warp] = rm;
+        __syncthreads();
+        rm = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+        const float jm = fmaxf(rm, m2);
+        const float cw = (m2 == -INFINITY) ? 0.f : fast_exp2(m2 - jm);
+        float rnum = 0.f, rl = 0.f;
+        const __half* vrow = p.rv + static_cast<size_t>(unit) * p.tr * kHeadDim + d;
+        for (int t = 0; t < p.tr; ++t) {
+            const float w = fast_exp2(sc_s[t] - jm);
+            rl += w;
+            rnum = fmaf(w, __half2float(vrow[static_cast<size_t>(t) * kHeadDim]), rnum);
+        }
+        num = num * cw + rnum;
+        l = l * cw + rl;
+    }
+    p.out[static_cast<size_t>(fq) * kHeadDim + d] = __float2half_rn(num / fmaxf(l, 1e-20f));
+}
+
+template <int GQA, int NNZ, int CVS>
+int launch_partial(const DecodeParams& p, int units, cudaStream_t stream) {
+    constexpr int kStages = (NNZ <= 32) ? 4 : 3;
+    size_t smem = sizeof(Stage<NNZ>) * kStages + static_cast<size_t>(p.ck) * kHeadDim * sizeof(__half);
+    const size_t red_bytes = static_cast<size_t>(kWarps) * GQA * (kHeadDim + 32 * CVS) * sizeof(float);
+    if (smem < red_bytes) smem = red_bytes;
+    auto kern = decode_bitmap_partial_kernel<GQA, NNZ, CVS>;
+    static thread_local size_t configured = 0;
+    if (smem > configured) {
+        if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     static_cast<int>(smem)),
+                                "cudaFuncSetAttribute(decode_bitmap_partial)"))
+            return rc;
+        configured = smem;
+    }
+    kern<<<dim3(p.splits, units), kThreads, smem, stream>>>(p);
+    return check_cuda(cudaGetLastError(), "decode_bitmap_partial launch");
+}
+
+template <int GQA, int NNZ>
+int dispatch_cvs(const DecodeParams& p, int units, cudaStream_t s) {
+    return p.cv <= 32 ? launch_partial<GQA, NNZ, 1>(p, units, s) : launch_partial<GQA, NNZ, 2>(p, units, s);
+}
+
+template <int GQA>
+int dispatch_nnz(const DecodeParams& p, int nnz, int units, cudaStream_t s) {
+    return nnz == 32 ? dispatch_cvs<GQA, 32>(p, units, s) : dispatch_cvs<GQA, 64>(p, units, s);
+}
+
+int pick_splits(int units, int tokens) {
+    const int tiles = (tokens + kTile - 1) / kTile;
+    const int slots = sm_count() * 2;  // two CTAs per SM
+    int best = 1;
+    double best_cost = 1e30;
+    const int max_splits = tiles < 64 ? tiles : 64;
+    for (int s = 1; s <= max_splits; ++s) {
+        const int per = (tiles + s - 1) / s;
+        const int used = (tiles + per - 1) / per;  // splits that actually get tiles
+        if (used != s) continue;
+        const long ctas = static_cast<long>(units) * s;
+        const long waves = (ctas + slots - 1) / slots;
+        // time ~ waves * tiles per CTA, plus a per-split cost for the merge and CTA prologue
+        const double cost = static_cast<double>(waves) * (per + 1.5) + 0.02 * s;
+        if (cost < best_cost - 1e-9) best_cost = cost, best = s;
+    }
+    return best;
+}
+
+size_t workspace_bytes(int bnh, int splits) {
+    const size_t rows = static_cast<size_t>(bnh) * splits;
+    return kWsHeader + rows * (2 + kHeadDim + kMaxClusters) * sizeof(float);
+}
+
+}  // namespace
+}  // namespace reskv
+
+using namespace reskv;
+
+extern "C" int reskv_decode_auto_splits(int batch, int kv_heads, int tokens) {
+    if (batch < 1 || kv_heads < 1 || tokens < 1) return fail(RESKV_ERR_INVALID, "auto_splits: sizes must be positive");
+    return pick_splits(batch * kv_heads, tokens);
+}
+
+extern "C" size_t reskv_decode_bitmap_fp16_workspace_bytes(int batch, int kv_heads, int q_heads, int tokens,
+                                                           int splits) {
+    if (batch < 1 || kv_heads < 1 || q_heads < 1 || tokens < 1) return 0;
+    if (splits <= 0) splits = pick_splits(batch * kv_heads, tokens);
+    const int tiles = (tokens + kTile - 1) / kTile;
+    if (splits > tiles) splits = tiles;
+    return workspace_bytes(batch * q_heads, splits);
+}
+
+extern "C" int reskv_decode_bitmap_fp16(const void* q, const void* k_centroids, const void* k_ids,
+                                        const void* k_payload, const void* k_bitmap, const void* v_centroids,
+                                        const void* v_ids, const void* v_payload, const void* v_bitmap, int batch,
+                                        int kv_heads, int q_heads, int tokens, int64_t tok_stride, int k_clusters,
+                                        int v_clusters, int nnz, int start_pos, int pos_q, float rope_theta,
+                                        const float* inv_freq, float scaling, int splits, const void* recent_q,
+                                        const void* recent_k, const void* recent_v, int recent_tokens,
+                                        void* workspace, size_t workspace_bytes_given, void* out, float* out_m,
+                                        float* out_l, void* stream) {
+    if (!q || !k_centroids || !k_ids || !k_payload || !k_bitmap || !v_centroids || !v_ids || !v_payload ||
+        !v_bitmap || !out)
+        return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: null tensor pointer");
+    if (batch < 1 || kv_heads < 1 || q_heads < 1 || tokens < 1)
+        return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: batch, heads and tokens must be positive");
+    if (q_heads % kv_heads) return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: q_heads must be a multiple of kv_heads");
+    const int gqa = q_heads / kv_heads;
+    if (gqa != 1 && gqa != 4 && gqa != 8)
+        return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: supported query/kv head ratios are 1, 4 and 8, got %d", gqa);
+    if (nnz != 32 && nnz != 64) return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: nnz must be 32 or 64, got %d", nnz);
+    if (k_clusters < 1 || k_clusters > kMaxClusters || v_clusters < 1 || v_clusters > kMaxClusters)
+        return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: centroid counts must be in [1,64]");
+    if (tok_stride < tokens) return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: tok_stride < tokens");
+    if (pos_q < start_pos + tokens - 1)
+        return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: query position precedes compressed tokens");
+    if (!aligned16(k_payload) || !aligned16(v_payload) || !aligned16(k_bitmap) || !aligned16(v_bitmap))
+        return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: payload and bitmap pointers must be 16-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(k_centroids) & 3u) || (reinterpret_cast<uintptr_t>(q) & 1u))
+        return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: misaligned centroid or query pointer");
+    const bool has_recent = recent_tokens > 0;
+    if (recent_tokens < 0 || (has_recent && (!recent_q || !recent_k || !recent_v)))
+        return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: recent window needs rotated q, rotated k and v");
+    if (recent_tokens > kMaxRecent)
+        return fail(RESKV_ERR_LIMIT, "decode_bitmap_fp16: at most %d recent tokens, got %d", kMaxRecent, recent_tokens);
+
+    const int units = batch * kv_heads;
+    const int tiles = (tokens + kTile - 1) / kTile;
+    if (splits <= 0) splits = pick_splits(units, tokens);
+    if (splits > tiles) splits = tiles;
+    int per = (tiles + splits - 1) / splits;
+    splits = (tiles + per - 1) / per;  // drop splits that would get no tile
+    const size_t need = workspace_bytes(batch * q_heads, splits);
+    if (!workspace || workspace_bytes_given < need)
+        return fail(RESKV_ERR_WORKSPACE, "decode_bitmap_fp16: workspace of %zu bytes needed, %zu given", need,
+                    workspace_bytes_given);
+
+    const size_t rows = static_cast<size_t>(batch) * q_heads * splits;
+    float* wsf = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + kWsHeader);
+    DecodeParams p{};
+    p.q = static_cast<const __half*>(q);
+    p.kc = static_cast<const __half*>(k_centroids);
+    p.kid = static_cast<const int8_t*>(k_ids);
+    p.kp = static_cast<const __half*>(k_payload);
+    p.kb = static_cast<const uint4*>(k_bitmap);
+    p.vid = static_cast<const int8_t*>(v_ids);
+    p.vp = static_cast<const __half*>(v_payload);
+    p.vb = static_cast<const uint4*>(v_bitmap);
+    p.ws_m = wsf;
+    p.ws_l = wsf + rows;
+    p.ws_delta = wsf + 2 * rows;
+    p.ws_beta = wsf + 2 * rows + rows * kHeadDim;
+    p.status = static_cast<uint32_t*>(workspace);
+    p.inv_freq = inv_freq;
+    p.tok_stride = tok_stride;
+    p.kh = kv_heads, p.nh = q_heads, p.tokens = tokens, p.ck = k_clusters, p.cv = v_clusters;
+    p.start_pos = start_pos, p.pos_q = pos_q, p.splits = splits, p.tiles_per_split = per;
+    p.theta = rope_theta, p.scaling = scaling;
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int rc = gqa == 1 ? dispatch_nnz<1>(p, nnz, units, s)
+             : gqa == 4 ? dispatch_nnz<4>(p, nnz, units, s)
+                        : dispatch_nnz<8>(p, nnz, units, s);
+    if (rc) return rc;
+
+    MergeParams mp{};
+    mp.ws_m = p.ws_m, mp.ws_l = p.ws_l, mp.ws_delta = p.ws_delta, mp.ws_beta = p.ws_beta;
+    mp.vc = static_cast<const __half*>(v_centroids);
+    mp.rq = static_cast<const __half*>(recent_q);
+    mp.rk = static_cast<const __half*>(recent_k);
+    mp.rv = static_cast<const __half*>(recent_v);
+    mp.out = static_cast<__half*>(out);
+    mp.out_m = out_m, mp.out_l = out_l;
+    mp.kh = kv_heads, mp.nh = q_heads, mp.splits = splits, mp.cv = v_clusters, mp.tr = recent_tokens;
+    mp.scaling = scaling;
+    decode_merge_kernel<<<batch * q_heads, kMergeThreads, 0, s>>>(mp);
+    return check_cuda(cudaGetLastError(), "decode_merge launch");
+}
+
+static int merge_recent_common(const void* comp_out, const float* comp_m, const float* comp_l, const float* scores,
+                               const void* rq, const void* rk, const void* rv, int batch, int kv_heads, int q_heads,
+                               int recent_tokens, float scaling, void* merged, void* stream, const char* who) {
+    if (!comp_out || !comp_m || !comp_l || !rv || !merged) return fail(RESKV_ERR_INVALID, "%s: null tensor pointer", who);
+    if (batch < 1 || kv_heads < 1 || q_heads < 1 || q_heads % kv_heads)
+        return fail(RESKV_ERR_INVALID, "%s: bad batch or head counts", who);
+    if (recent_tokens < 1) return fail(RESKV_ERR_INVALID, "%s: recent_tokens must be positive", who);
+    if (recent_tokens > kMaxRecent)
+        return fail(RESKV_ERR_LIMIT, "%s: at most %d recent tokens, got %d", who, kMaxRecent, recent_tokens);
+    MergeParams mp{};
+    mp.ws_m = comp_m, mp.ws_l = comp_l;
+    mp.comp_out = static_cast<const __half*>(comp_out);
+    mp.rscores = scores;
+    mp.rq = static_cast<const __half*>(rq);
+    mp.rk = static_cast<const __half*>(rk);
+    mp.rv = static_cast<const __half*>(rv);
+    mp.out = static_cast<__half*>(merged);
+    mp.kh = kv_heads, mp.nh = q_heads, mp.splits = 0, mp.tr = recent_tokens, mp.scaling = scaling;
+    decode_merge_kernel<<<batch * q_heads, kMergeThreads, 0, static_cast<cudaStream_t>(stream)>>>(mp);
+    return check_cuda(cudaGetLastError(), "merge_recent launch");
+}
+
+extern "C" int reskv_merge_recent_scores(const void* comp_out, const float* comp_m, const float* comp_l,
+                                         const float* scores, const void* recent_v, int batch, int kv_heads,
+                                         int q_heads, int recent_tokens, void* merged, void* stream) {
+    if (!scores) return fail(RESKV_ERR_INVALID, "merge_recent_scores: null scores");
+    return merge_recent_common(comp_out, comp_m, comp_l, scores, nullptr, nullptr, recent_v, batch, kv_heads, q_heads,
+                               recent_tokens, 1.f, merged, stream, "merge_recent_scores");
+}
+
+extern "C" int reskv_merge_recent_qk(const void* comp_out, const float* comp_m, const float* comp_l,
+                                     const void* recent_q, const void* recent_k, const void* recent_v, int batch,
+                                     int kv_heads, int q_heads, int recent_tokens, float scaling, void* merged,
+                                     void* stream) {
+    if (!recent_q || !recent_k) return fail(RESKV_ERR_INVALID, "merge_recent_qk: null rotated q or k");
+    return merge_recent_common(comp_out, comp_m, comp_l, nullptr, recent_q, recent_k, recent_v, batch, kv_heads,
+                               q_heads, recent_tokens, scaling, merged, stream, "merge_recent_qk");
+}

@@ -1,0 +1,291 @@
+// Lloyd clustering of pre-RoPE K or V per (sequence, KV head): fused assignment +
+// centroid accumulation, centroid update, and the decode-time incremental step.
+//
+// Assignment is the exact nearest centre in FP32 (squared differences summed in
+// a fixed order), lowest index on ties.  Cluster sums are accumulated *exactly*:
+// an FP16 value is an integer multiple of 2^-24, so tokens are added as 2^24-
+// scaled integers (split into two 32-bit shared-memory counters per CTA, flushed
+// with 64-bit integer atomics).  Integer addition is associative, which makes
+// the new centres independent of scheduling and equal to the correctly rounded
+// mean -- results are reproducible run to run.
+//
+// K flavour: FP32 centres, an empty cluster keeps its centre.
+// V flavour: centres rounded to FP16 after every update, an empty cluster becomes 0.
+#include "common.cuh"
+
+namespace reskv {
+namespace {
+
+constexpr uint32_t kFull = 0xffffffffu;
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kChunk = 512;  // tokens per CTA: keeps the split 32-bit counters from overflowing
+constexpr float kFix = 16777216.0f;  // 2^24
+
+struct KmeansParams {
+    const __half* x;       // [units, x_stride, 128]
+    float* centres;        // [units, C, 128] working centres (FP32 values)
+    long long* sums;       // [units, C, 128] 2^24-scaled integer sums, zero on entry
+    int* counts;           // [units, C], zero on entry
+    int32_t* ids;          // [units, tokens]
+    int64_t x_stride;
+    int units, tokens, clusters;
+};
+
+struct InitIndex {
+    int idx[kMaxClusters];
+};
+
+__global__ void kmeans_init_kernel(KmeansParams p, InitIndex init, int value) {
+    const int unit = blockIdx.x;
+    for (int i = threadIdx.x; i < p.clusters * kHeadDim; i += blockDim.x) {
+        const int c = i / kHeadDim, d = i % kHeadDim;
+        const float v = __half2float(p.x[(static_cast<size_t>(unit) * p.x_stride + init.idx[c]) * kHeadDim + d]);
+        p.centres[(static_cast<size_t>(unit) * p.clusters + c) * kHeadDim + d] = v;
+        p.sums[(static_cast<size_t>(unit) * p.clusters + c) * kHeadDim + d] = 0;
+    }
+    for (int c = threadIdx.x; c < p.clusters; c += blockDim.x) p.counts[unit * p.clusters + c] = 0;
+    (void)value;
+}
+
+// Squared distance of the warp's token to each centre, reduced so that lane c
+// holds the total for centre cbase + c; returns (best distance, best index) in
+// every lane.  `xv` are the lane's coordinates {lane + 32 i}.
+__device__ __forceinline__ void nearest(const float* cen_s, int clusters, const float (&xv)[4], int lane, float& best,
+                                        int& best_c) {
+    best = INFINITY, best_c = 0;
+    for (int cbase = 0; cbase < clusters; cbase += 32) {
+        float part[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+            float acc = 0.f;
+            if (cbase + c < clusters) {
+                const float* row = cen_s + (cbase + c) * kHeadDim;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float df = xv[i] - row[lane + 32 * i];
+                    acc = fmaf(df, df, acc);
+                }
+            }
+            part[c] = acc;
+        }
+        // transposing butterfly: after the step with offset `off`, a lane keeps the
+        // half of its values whose centre index has the same `off` bit as the lane
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const bool up = lane & off;
+#pragma unroll
+            for (int c = 0; c < off; ++c) {
+                const float send = up ? part[c] : part[c + off];
+                const float keep = up ? part[c + off] : part[c];
+                part[c] = keep + __shfl_xor_sync(kFull, send, off);
+            }
+        }
+        float dist = (cbase + lane < clusters) ? part[0] : INFINITY;
+        int idx = cbase + lane;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float od = __shfl_xor_sync(kFull, dist, off);
+            const int oi = __shfl_xor_sync(kFull, idx, off);
+            if (od < dist || (od == dist && oi < idx)) dist = od, idx = oi;
+        }
+        if (dist < best) best = dist, best_c = idx;  // earlier block wins ties
+    }
+}
+
+// grid (chunks, units).  Assign the chunk's tokens; accumulate sums and counts.
+__global__ void __launch_bounds__(kThreads) kmeans_assign_kernel(const KmeansParams p, int accumulate) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    float* cen_s = reinterpret_cast<float*>(smem);                             // [C][128]
+    int* lo_s = reinterpret_cast<int*>(cen_s + p.clusters * kHeadDim);         // [C][128] low 20 bits
+    int* hi_s = lo_s + p.clusters * kHeadDim;                                  // [C][128] the rest
+    int* cnt_s = hi_s + p.clusters * kHeadDim;                                 // [C]
+    const int unit = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t_begin = blockIdx.x * kChunk, t_end = min(p.tokens, t_begin + kChunk);
+    const float* cen_g = p.centres + static_cast<size_t>(unit) * p.clusters * kHeadDim;
+    for (int i = tid; i < p.clusters * kHeadDim; i += kThreads) {
+        cen_s[i] = cen_g[i];
+        lo_s[i] = 0;
+        hi_s[i] = 0;
+    }
+    for (int c = tid; c < p.clusters; c += kThreads) cnt_s[c] = 0;
+    __syncthreads();
+    for (int t = t_begin + warp; t < t_end; t += kWarps) {
+        const __half* xr = p.x + (static_cast<size_t>(unit) * p.x_stride + t) * kHeadDim;
+        float xv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) xv[i] = __half2float(xr[lane + 32 * i]);
+        float best;
+        int c;
+        nearest(cen_s, p.clusters, xv, lane, best, c);
+        if (lane == 0) p.ids[static_cast<size_t>(unit) * p.tokens + t] = c;
+        if (accumulate) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const long long fx = static_cast<long long>(xv[i] * kFix);  // exact
+                atomicAdd(&lo_s[c * kHeadDim + lane + 32 * i], static_cast<int>(fx & 0xfffff));
+                atomicAdd(&hi_s[c * kHeadDim + lane + 32 * i], static_cast<int>(fx >> 20));
+            }
+            if (lane == 0) atomicAdd(&cnt_s[c], 1);
+        }
+    }
+    if (!accumulate) return;
+    __syncthreads();
+    long long* sums_g = p.sums + static_cast<size_t>(unit) * p.clusters * kHeadDim;
+    for (int i = tid; i < p.clusters * kHeadDim; i += kThreads) {
+        if (cnt_s[i / kHeadDim] > 0) {
+            const long long v = (static_cast<long long>(hi_s[i]) << 20) + lo_s[i];
+            atomicAdd(reinterpret_cast<unsigned long long*>(sums_g + i), static_cast<unsigned long long>(v));
+        }
+    }
+    for (int c = tid; c < p.clusters; c += kThreads)
+        if (cnt_s[c] > 0) atomicAdd(&p.counts[unit * p.clusters + c], cnt_s[c]);
+}
+
+// New centres from the exact sums; clears sums and counts for the next round.
+// `final_out` (FP16 [units, C, 128]) is written when non-null.
+__global__ void kmeans_update_kernel(KmeansParams p, int value, __half* final_out) {
+    const int unit = blockIdx.x;
+    for (int i = threadIdx.x; i < p.clusters * kHeadDim; i += blockDim.x) {
+        const size_t g = static_cast<size_t>(unit) * p.clusters * kHeadDim + i;
+        const int n = p.counts[unit * p.clusters + i / kHeadDim];
+        float c = p.centres[g];
+        if (n > 0) {
+            // exact integer sum / count, one rounding to FP32
+            c = static_cast<float>(static_cast<double>(p.sums[g]) * (1.0 / 16777216.0) / static_cast<double>(n));
+        } else if (value) {
+            c = 0.f;
+        }
+        if (value) c = __half2float(__float2half_rn(c));
+        p.centres[g] = c;
+        p.sums[g] = 0;
+        if (final_out) final_out[g] = __float2half_rn(c);
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < p.clusters; c += blockDim.x) p.counts[unit * p.clusters + c] = 0;
+}
+
+// Decode-time step: one CTA per unit.  Optionally appends the mean of the
+// group's tokens as centre `old_clusters`, then assigns the tokens.
+__global__ void __launch_bounds__(kThreads) kmeans_incremental_kernel(const __half* x, int64_t x_stride,
+                                                                      const __half* old_cen, int old_clusters,
+                                                                      __half* new_cen, int new_clusters, int tokens,
+                                                                      int32_t* ids) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    float* cen_s = reinterpret_cast<float*>(smem);  // [new_clusters][128]
+    const int unit = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const __half* xg = x + static_cast<size_t>(unit) * x_stride * kHeadDim;
+    for (int i = tid; i < old_clusters * kHeadDim; i += kThreads) {
+        const __half v = old_cen[static_cast<size_t>(unit) * old_clusters * kHeadDim + i];
+        cen_s[i] = __half2float(v);
+        new_cen[static_cast<size_t>(unit) * new_clusters * kHeadDim + i] = v;
+    }
+    if (new_clusters > old_clusters && tid < kHeadDim) {
+        // mean of the group, FP32 accumulation in token order, rounded to FP16
+        float s = 0.f;
+        for (int t = 0; t < tokens; ++t) s += __half2float(xg[static_cast<size_t>(t) * kHeadDim + tid]);
+        const __half m = __float2half_rn(s / static_cast<float>(tokens));
+        cen_s[old_clusters * kHeadDim + tid] = __half2float(m);
+        new_cen[(static_cast<size_t>(unit) * new_clusters + old_clusters) * kHeadDim + tid] = m;
+    }
+    __syncthreads();
+    for (int t = warp; t < tokens; t += kWarps) {
+        float xv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) xv[i] = __half2float(xg[static_cast<size_t>(t) * kHeadDim + lane + 32 * i]);
+        float best;
+        int c;
+        nearest(cen_s, new_clusters, xv, lane, best, c);
+        if (lane == 0) ids[static_cast<size_t>(unit) * tokens + t] = c;
+    }
+}
+
+// torch.linspace(0, t-1, count).long(): float32 steps formed with a fused
+// multiply-add, symmetric about the midpoint, truncated.
+void linspace_indices(int t, int count, int* out) {
+    if (count == 1) {
+        out[0] = 0;
+        return;
+    }
+    const float step = static_cast<float>(t - 1) / static_cast<float>(count - 1);
+    for (int i = 0; i < count; ++i) {
+        const double v = i < count / 2 ? static_cast<double>(step) * i
+                                       : static_cast<double>(t - 1) - static_cast<double>(step) * (count - 1 - i);
+        out[i] = static_cast<int>(static_cast<float>(v));
+    }
+}
+
+size_t kmeans_ws_bytes(int units, int clusters) {
+    const size_t per = static_cast<size_t>(units) * clusters;
+    return per * kHeadDim * (sizeof(float) + sizeof(long long)) + per * sizeof(int) + 256;
+}
+
+}  // namespace
+}  // namespace reskv
+
+using namespace reskv;
+
+extern "C" size_t reskv_kmeans_workspace_bytes(int batch, int kv_heads, int clusters) {
+    if (batch < 1 || kv_heads < 1 || clusters < 1 || clusters > kMaxClusters) return 0;
+    return kmeans_ws_bytes(batch * kv_heads, clusters);
+}
+
+extern "C" int reskv_kmeans(const void* x, int batch, int kv_heads, int tokens, int64_t x_tok_stride, int clusters,
+                            int iterations, int value, void* workspace, size_t workspace_bytes, void* centroids,
+                            int32_t* ids, void* stream) {
+    if (!x || !centroids || !ids) return fail(RESKV_ERR_INVALID, "kmeans: null tensor pointer");
+    if (batch < 1 || kv_heads < 1 || tokens < 1) return fail(RESKV_ERR_INVALID, "kmeans: batch, heads and tokens must be positive");
+    if (clusters < 1 || clusters > kMaxClusters) return fail(RESKV_ERR_INVALID, "kmeans: cluster count must be in [1,64], got %d", clusters);
+    if (iterations < 1) return fail(RESKV_ERR_INVALID, "kmeans: iterations must be positive");
+    if (x_tok_stride < tokens) return fail(RESKV_ERR_INVALID, "kmeans: token stride smaller than token count");
+    const int units = batch * kv_heads;
+    const size_t need = kmeans_ws_bytes(units, clusters);
+    if (!workspace || workspace_bytes < need)
+        return fail(RESKV_ERR_WORKSPACE, "kmeans: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    const size_t per = static_cast<size_t>(units) * clusters * kHeadDim;
+    KmeansParams p{};
+    p.x = static_cast<const __half*>(x);
+    p.sums = static_cast<long long*>(workspace);  // 8-byte aligned first
+    p.centres = reinterpret_cast<float*>(p.sums + per);
+    p.counts = reinterpret_cast<int*>(p.centres + per);
+    p.ids = ids;
+    p.x_stride = x_tok_stride;
+    p.units = units, p.tokens = tokens, p.clusters = clusters;
+    InitIndex init{};
+    if (tokens >= clusters) {
+        linspace_indices(tokens, clusters, init.idx);
+    } else {
+        // fewer tokens than centres: every token once, then tokens repeated in order
+        for (int c = 0; c < clusters; ++c) init.idx[c] = c % tokens;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    kmeans_init_kernel<<<units, 256, 0, s>>>(p, init, value);
+    const size_t smem = static_cast<size_t>(clusters) * kHeadDim * (sizeof(float) + 2 * sizeof(int)) + clusters * sizeof(int);
+    if (smem > 48 * 1024) {
+        if (int rc = check_cuda(cudaFuncSetAttribute(kmeans_assign_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     static_cast<int>(smem)),
+                                "cudaFuncSetAttribute(kmeans_assign)"))
+            return rc;
+    }
+    const dim3 grid((tokens + kChunk - 1) / kChunk, units);
+    for (int it = 0; it < iterations; ++it) {
+        kmeans_assign_kernel<<<grid, kThreads, smem, s>>>(p, 1);
+        kmeans_update_kernel<<<units, 256, 0, s>>>(p, value, it + 1 == iterations ? static_cast<__half*>(centroids) : nullptr);
+    }
+    return check_cuda(cudaGetLastError(), "kmeans launch");
+}
+
+extern "C" int reskv_kmeans_incremental(const void* x, int batch, int kv_heads, int tokens, int64_t x_tok_stride,
+                                        const void* old_centroids, int old_clusters, void* new_centroids,
+                                        int new_clusters, int32_t* ids, void* stream) {
+    if (!x || !old_centroids || !new_centroids || !ids) return fail(RESKV_ERR_INVALID, "kmeans_incremental: null tensor pointer");
+    if (batch < 1 || kv_heads < 1 || tokens < 1) return fail(RESKV_ERR_INVALID, "kmeans_incremental: batch, heads and tokens must be positive");
+    if (old_clusters < 1 || new_clusters > kMaxClusters || (new_clusters != old_clusters && new_clusters != old_clusters + 1))
+        return fail(RESKV_ERR_INVALID, "kmeans_incremental: centre counts must satisfy 1 <= old <= new <= old + 1 <= 64");
+    if (x_tok_stride < tokens) return fail(RESKV_ERR_INVALID, "kmeans_incremental: token stride smaller than token count");
+    const size_t smem = static_cast<size_t>(new_clusters) * kHeadDim * sizeof(float);
+    kmeans_incremental_kernel<<<batch * kv_heads, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x), x_tok_stride, static_cast<const __half*>(old_centroids), old_clusters,
+        static_cast<__half*>(new_centroids), new_clusters, tokens, ids);
+    return check_cuda(cudaGetLastError(), "kmeans_incremental launch");
+}

@@ -1,6 +1,7 @@
 """Shared fixtures.  ``gpu`` marks tests that need a CUDA device and the built
 sm_100a library; everything else must pass on a GPU-less machine."""
 
+import os
 import sys
 from pathlib import Path
 
@@ -8,8 +9,11 @@ import numpy as np
 import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
-if str(ROOT) not in sys.path:
-    sys.path.insert(0, str(ROOT))
+# have the decode wrappers read the device status word after every call
+os.environ.setdefault("RESKV_CHECK_STATUS", "1")
+for path in (str(ROOT), str(ROOT / "tests")):
+    if path not in sys.path:
+        sys.path.insert(0, path)
 
 
 def pytest_configure(config):

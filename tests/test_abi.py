@@ -1,0 +1,80 @@
+"""The C-ABI library: it loads, exports every declared symbol, and the Python
+binding table matches the header (no compute calls: this runs without a GPU)."""
+
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = ROOT / "include" / "reskv_b200.h"
+
+
+def declared_functions():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    text = re.sub(r"^\s*#.*$", "", text, flags=re.M)
+    out = {}
+    for m in re.finditer(r"([\w\s\*]+?)\b(reskv_\w+)\s*\(([^)]*)\)\s*;", text):
+        args = [a.strip() for a in m.group(3).split(",") if a.strip() and a.strip() != "void"]
+        out[m.group(2)] = (m.group(1).strip(), args)
+    return out
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from reskv_b200.csrc.build import build
+
+    return ctypes.CDLL(str(build()))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    decl = declared_functions()
+    assert len(decl) >= 14
+    for name in decl:
+        assert hasattr(lib, name), f"{name} declared in the header but not exported"
+
+
+def _ctype_of(c_arg: str):
+    c_arg = c_arg.strip()
+    if "*" in c_arg:
+        return ctypes.c_char_p if c_arg.startswith("const char") else ctypes.c_void_p
+    base = c_arg.split()[0] if " " in c_arg else c_arg
+    return {"int": ctypes.c_int, "int64_t": ctypes.c_int64, "float": ctypes.c_float, "size_t": ctypes.c_size_t}[base]
+
+
+def test_binding_table_matches_header():
+    from reskv_b200._extension import SIGNATURES
+
+    decl = declared_functions()
+    assert set(SIGNATURES) == set(decl)
+    for name, (ret, args) in decl.items():
+        restype, argtypes = SIGNATURES[name]
+        assert restype is _ctype_of(ret + (" x" if "*" not in ret else "")), name
+        assert [_ctype_of(a) for a in args] == list(argtypes), name
+
+
+def test_errors_are_reported_without_a_device(lib):
+    lib.reskv_last_error.restype = ctypes.c_char_p
+    lib.reskv_decode_auto_splits.argtypes = [ctypes.c_int] * 3
+    assert lib.reskv_decode_auto_splits(0, 8, 100) == -1
+    assert b"positive" in lib.reskv_last_error()
+    lib.reskv_decode_bitmap_fp16_workspace_bytes.restype = ctypes.c_size_t
+    lib.reskv_decode_bitmap_fp16_workspace_bytes.argtypes = [ctypes.c_int] * 5
+    assert lib.reskv_decode_bitmap_fp16_workspace_bytes(1, 8, 32, 8128, 4) == 256 + 32 * 4 * (2 + 128 + 64) * 4
+    lib.reskv_kmeans_workspace_bytes.restype = ctypes.c_size_t
+    lib.reskv_kmeans_workspace_bytes.argtypes = [ctypes.c_int] * 3
+    assert lib.reskv_kmeans_workspace_bytes(1, 8, 65) == 0
+    assert lib.reskv_version() >= 100
+
+
+def test_package_import_is_light():
+    import subprocess
+    import sys
+
+    subprocess.run(
+        [sys.executable, "-c",
+         "import sys; import reskv_b200; assert 'torch' not in sys.modules; "
+         "assert reskv_b200.ResKVKernelConfig().bits == 16; assert reskv_b200.ResKVConfig().bits == 16; "
+         "assert 'torch' not in sys.modules"],
+        check=True, cwd=ROOT)
