@@ -77,6 +77,17 @@ int reskv_decode_bitmap_fp16(const void* q, const void* k_centroids, const void*
                              void* workspace, size_t workspace_bytes, void* out, float* out_m, float* out_l,
                              void* stream);
 
+/* Selects the partial kernel reskv_decode_bitmap_fp16 launches: 0 = tensor-core
+ * tiles of 16 tokens (default), 1 = the simpler warp-per-token kernel (kept for
+ * cross-checking).  Process-wide; no counterpart in the reference. */
+int reskv_decode_set_variant(int variant);
+
+/* Profiling aid: cudaEvent_t handles that every following reskv_decode_bitmap_fp16
+ * call records on its stream immediately before and after the partial kernel, so
+ * that the kernel's own duration can be read without launch gaps.  NULL, NULL
+ * switches it off.  Process-wide; no counterpart in the reference. */
+int reskv_decode_set_timing_events(void* start, void* stop);
+
 /* The split count reskv_decode_bitmap_fp16 uses for splits == 0. */
 int reskv_decode_auto_splits(int batch, int kv_heads, int tokens);
 

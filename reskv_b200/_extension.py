@@ -42,6 +42,8 @@ SIGNATURES = {
         [_P] * 9 + [_I, _I, _I, _I, _L, _I, _I, _I, _I, _I, _F, _P, _F, _I, _P, _P, _P, _I, _P, _Z, _P, _P, _P, _P],
     ),
     "reskv_decode_auto_splits": (_I, [_I, _I, _I]),
+    "reskv_decode_set_variant": (_I, [_I]),
+    "reskv_decode_set_timing_events": (_I, [_P, _P]),
     "reskv_merge_recent_scores": (_I, [_P] * 5 + [_I, _I, _I, _I, _P, _P]),
     "reskv_merge_recent_qk": (_I, [_P] * 6 + [_I, _I, _I, _I, _F, _P, _P]),
     "reskv_encode_bitmap_fp16": (_I, [_P, _P, _P, _I, _I, _I, _L, _I, _I, _P, _P, _L, _P]),
@@ -74,8 +76,8 @@ launch_count = 0
 
 
 def check(rc: int, launches: int = 1) -> None:
-    """Count the launches of a successful call; turn a negative return code into the exception the reference would raise:
-    argument problems are ``ValueError`` (the reference's TORCH_CHECKs surface as
+    """Count the launches of a successful call; turn a negative return code into
+    the exception the reference would raise: argument problems are ``ValueError`` (the reference's TORCH_CHECKs surface as
     RuntimeError subclasses, its Python checks as ValueError; callers match on
     the message), everything else ``RuntimeError``."""
     if rc >= 0:

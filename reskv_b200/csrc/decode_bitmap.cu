@@ -331,6 +331,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_bitmap_partial_kernel(cons
     if (tid == 0 && timed_out) atomicOr(p.status, RESKV_STATUS_WAIT_TIMEOUT);
 }
 
+#include "decode_bitmap_mma.cuh"
+
 // ---- merge -----------------------------------------------------------------------
 struct MergeParams {
     const float* ws_m;      // log2-domain maxima [BNH][splits], or natural-log m [BNH] when splits == 0
@@ -443,20 +445,34 @@ int launch_partial(const DecodeParams& p, int units, cudaStream_t stream) {
     const size_t red_bytes = static_cast<size_t>(kWarps) * GQA * (kHeadDim + 32 * CVS) * sizeof(float);
     if (smem < red_bytes) smem = red_bytes;
     auto kern = decode_bitmap_partial_kernel<GQA, NNZ, CVS>;
-    static thread_local size_t configured = 0;
-    if (smem > configured) {
-        if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                     static_cast<int>(smem)),
-                                "cudaFuncSetAttribute(decode_bitmap_partial)"))
-            return rc;
-        configured = smem;
-    }
+    if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 static_cast<int>(smem)),
+                            "cudaFuncSetAttribute(decode_bitmap_partial)"))
+        return rc;
     kern<<<dim3(p.splits, units), kThreads, smem, stream>>>(p);
     return check_cuda(cudaGetLastError(), "decode_bitmap_partial launch");
 }
 
 template <int GQA, int NNZ>
+int launch_partial_mma(const DecodeParams& p, int units, cudaStream_t stream) {
+    const size_t smem = mma::smem_bytes<GQA, NNZ>(p.ck);
+    auto kern = mma::decode_bitmap_mma_kernel<GQA, NNZ>;
+    if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 static_cast<int>(smem)),
+                            "cudaFuncSetAttribute(decode_bitmap_mma)"))
+        return rc;
+    kern<<<dim3(p.splits, units), mma::kThreadsM, smem, stream>>>(p);
+    return check_cuda(cudaGetLastError(), "decode_bitmap_mma launch");
+}
+
+// 0 = tensor-core kernel (default), 1 = warp-per-token SIMT kernel
+int g_variant = 0;
+// optional events recorded right before / after the partial kernel (profiling aid)
+cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;
+
+template <int GQA, int NNZ>
 int dispatch_cvs(const DecodeParams& p, int units, cudaStream_t s) {
+    if (g_variant == 0) return launch_partial_mma<GQA, NNZ>(p, units, s);
     return p.cv <= 32 ? launch_partial<GQA, NNZ, 1>(p, units, s) : launch_partial<GQA, NNZ, 2>(p, units, s);
 }
 
@@ -493,6 +509,18 @@ size_t workspace_bytes(int bnh, int splits) {
 }  // namespace reskv
 
 using namespace reskv;
+
+extern "C" int reskv_decode_set_variant(int variant) {
+    if (variant != 0 && variant != 1) return fail(RESKV_ERR_INVALID, "decode_set_variant: 0 (tensor-core) or 1 (SIMT), got %d", variant);
+    g_variant = variant;
+    return RESKV_OK;
+}
+
+extern "C" int reskv_decode_set_timing_events(void* start, void* stop) {
+    g_ev_start = static_cast<cudaEvent_t>(start);
+    g_ev_stop = static_cast<cudaEvent_t>(stop);
+    return RESKV_OK;
+}
 
 extern "C" int reskv_decode_auto_splits(int batch, int kv_heads, int tokens) {
     if (batch < 1 || kv_heads < 1 || tokens < 1) return fail(RESKV_ERR_INVALID, "auto_splits: sizes must be positive");
@@ -576,10 +604,12 @@ extern "C" int reskv_decode_bitmap_fp16(const void* q, const void* k_centroids, 
     p.theta = rope_theta, p.scaling = scaling;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (g_ev_start) cudaEventRecord(g_ev_start, s);
     int rc = gqa == 1 ? dispatch_nnz<1>(p, nnz, units, s)
              : gqa == 4 ? dispatch_nnz<4>(p, nnz, units, s)
                         : dispatch_nnz<8>(p, nnz, units, s);
     if (rc) return rc;
+    if (g_ev_stop) cudaEventRecord(g_ev_stop, s);
 
     MergeParams mp{};
     mp.ws_m = p.ws_m, mp.ws_l = p.ws_l, mp.ws_delta = p.ws_delta, mp.ws_beta = p.ws_beta;

@@ -1,0 +1,580 @@
+// Tensor-core version of the partial decode kernel for the unstructured FP16 bitmap
+// layout.  Included by decode_bitmap.cu (needs DecodeParams and the helpers there).
+//
+// Why: the warp-per-token kernel spends ~250 warp instructions per (token, KV head)
+// and is issue bound at 8 % of HBM bandwidth.  Here a warp handles blocks of 16
+// tokens and both contractions run on mma.sync.m16n8k16 tiles:
+//
+//   S[16 tok x 8 heads]   = K'[16 tok x 128] . Qt^T          (8 k-steps, Qt split hi+lo FP16)
+//   O^T[128 x 8 heads]   += Vres^T[128 x 16 tok] . P[16 tok x 8 heads]   (8 m-blocks)
+//
+// The contraction order of an MMA is free, so coordinates are assigned to
+// fragment slots such that every lane owns *contiguous* 16-coordinate fields of
+// a token: lane (g = lane / 4, q = lane % 4) builds, for K, tokens g and g + 8,
+// coordinates [16q, 16q+16) and their RoPE partners [64+16q, 64+16q+16); for V,
+// tokens {2q, 2q+1, 2q+8, 2q+9}, coordinates [16g, 16g+16).  A field is one
+// 16-bit slice of the token's bitmap; its retained values are consecutive in the
+// payload, so decoding is a walk "bit set ? *ptr++ : 0" with no popcount per
+// coordinate (one table of 8 rank bases per token is built per block).
+//
+// RoPE: a token at tile offset j of a tile starting at position P0 scores
+//   < R(pos_q) q, R(P0 + j) k >  =  < R(pos_q - P0) q, R(j) k > ,
+// so keys are rotated by the in-tile offset only -- sin/cos of j * f_i come from a
+// 64 x 64 shared-memory table built once per CTA -- and the query is re-rotated
+// once per 64-token tile (by all threads, incrementally) into MMA B-fragment
+// order.  Softmax keeps a lazily updated running maximum per head (rescale only
+// when it grows by more than 2^8), P is rounded to FP16 once and that rounded
+// value is used for the sum, the cluster masses and the PV product alike.
+//
+// Precision: a single FP16 rounding of the rotated key is not enough (outlier
+// channels put the score error at ~1e-3, ten times the output tolerance on short
+// contexts), so K' enters the MMA as hi + lo FP16 halves: S = K'hi.Qhi + K'hi.Qlo
+// + K'lo.Qhi.  The sm_100 mixed-precision instructions keep that cheap:
+// add.f32.f16 adds the FP16 residual to the FP32 centroid in one instruction and
+// fma.f32.f16 forms lo = k' - hi without unpacking.
+#pragma once
+
+namespace mma {
+
+constexpr int kTileM = 64;        // tokens per pipeline stage
+constexpr int kWarpsM = 4;        // one 16-token block per warp and tile
+constexpr int kThreadsM = kWarpsM * 32;
+constexpr int kCenStride = 132;   // floats per centroid row in shared memory (row r starts 4r banks on)
+constexpr int kTrigStride = 64;   // float2 per row of the sin/cos table (swizzled, see trig_index)
+constexpr int kQStride = 132;     // halfs per query row
+constexpr int kQSets = 2;         // query stored as FP16 hi and lo
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+template <int NNZ>
+struct StageM {
+    uint4 kb[kTileM];
+    uint4 vb[kTileM];
+    __half kp[kTileM * NNZ];
+    __half vp[kTileM * NNZ];
+};
+
+template <int NNZ>
+constexpr int stages_for() {
+    return NNZ <= 32 ? 3 : 2;
+}
+
+// Shared-memory layouts chosen so that the 16-byte loads of a quarter warp
+// (lanes g = 2k, 2k+1; q = 0..3) fall into distinct banks.
+//
+// sin/cos table: row j (tile offset), frequency i = 16q + 4ks + 2e + u.  The four
+// lanes q of one (ks, e) read neighbouring 16-byte units; odd rows swap the two
+// 64-byte halves of every 128-byte line.
+__device__ __forceinline__ int trig_index(int j, int i) {
+    const int q = i >> 4, ks = (i >> 2) & 3, e = (i >> 1) & 1, u = i & 1;
+    const int unit = (((ks * 2 + e) * 4 + q) ^ ((j & 1) << 2));
+    return j * kTrigStride + unit * 2 + u;
+}
+// centroid row (FP32): coordinate d -> field f = d / 16, 16-byte unit (d / 4) % 4,
+// units of fields 2, 3, 6, 7 are swapped pairwise so lanes q and q + 2 differ.
+__device__ __forceinline__ int cen_index(int d) {
+    const int f = d >> 4, unit = ((d >> 2) & 3) ^ ((f >> 1) & 1);
+    return f * 16 + unit * 4 + (d & 3);
+}
+
+// d = fp16(bits) + c, one instruction (sm_100 mixed-precision add)
+__device__ __forceinline__ float add_f16_f32(unsigned short bits, float c) {
+    float d;
+    asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(d) : "h"(bits), "f"(c));
+    return d;
+}
+// d = fp16(a) * fp16(b) + c
+__device__ __forceinline__ float fma_f16_f16_f32(unsigned short a, unsigned short b, float c) {
+    float d;
+    asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(d) : "h"(a), "h"(b), "f"(c));
+    return d;
+}
+// (hi, lo) FP16 pairs of two FP32 values: hi = fp16(x), lo = fp16(x - hi)
+__device__ __forceinline__ void split_h2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+    const __half2 h = __floats2half2_rn(x0, x1);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    const unsigned short minus_one = 0xbc00;
+    const float l0 = fma_f16_f16_f32(__half_as_ushort(__low2half(h)), minus_one, x0);
+    const float l1 = fma_f16_f16_f32(__half_as_ushort(__high2half(h)), minus_one, x1);
+    const __half2 l = __floats2half2_rn(l0, l1);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+
+template <int GQA, int NNZ>
+constexpr size_t smem_bytes(int ck) {
+    return sizeof(StageM<NNZ>) * stages_for<NNZ>() + kTileM * kTrigStride * sizeof(float2) +
+           static_cast<size_t>(ck) * kCenStride * sizeof(float) + 2 * kQSets * GQA * kQStride * sizeof(__half) +
+           kWarpsM * 2 * 16 * sizeof(uint2) + kWarpsM * GQA * kMaxClusters * sizeof(float);
+}
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Byte offset, inside a token's 16-byte bitmap, of the 16-bit field that covers
+// coordinates [16f, 16f+16) (bit 15 = first coordinate).
+__device__ __forceinline__ int field_offset(int f) { return ((f & 4) ? 8 : 0) + 6 - 2 * (f & 3); }
+
+// Number of retained coordinates before each of the eight fields, one byte each.
+__device__ __forceinline__ uint2 rank_bases(const uint4 bm) {
+    const uint32_t w0 = bm.y, w1 = bm.x, w2 = bm.w, w3 = bm.z;
+    const uint32_t r1 = __popc(w0 >> 16), r2 = __popc(w0);
+    const uint32_t r3 = r2 + __popc(w1 >> 16), r4 = r2 + __popc(w1);
+    const uint32_t r5 = r4 + __popc(w2 >> 16), r6 = r4 + __popc(w2);
+    const uint32_t r7 = r6 + __popc(w3 >> 16);
+    return make_uint2((r1 << 8) | (r2 << 16) | (r3 << 24), r4 | (r5 << 8) | (r6 << 16) | (r7 << 24));
+}
+
+// One step of a field walk: the next coordinate's raw FP16 bits, or 0.
+__device__ __forceinline__ uint32_t walk16(uint32_t field, int e, const __half*& ptr) {
+    uint32_t v = 0;
+    if (field & (0x8000u >> e)) {
+        v = *reinterpret_cast<const unsigned short*>(ptr);
+        ++ptr;
+    }
+    return v;
+}
+
+__device__ __forceinline__ float h2f_bits(uint32_t bits) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(bits)));
+}
+
+template <int GQA, int NNZ>
+__global__ void __launch_bounds__(kThreadsM, 2) decode_bitmap_mma_kernel(const DecodeParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    constexpr int kStages = stages_for<NNZ>();
+    constexpr int kItems = (GQA * 32 + kThreadsM - 1) / kThreadsM;  // query items per thread
+    using StageT = StageM<NNZ>;
+    StageT* stages = reinterpret_cast<StageT*>(smem_raw);
+    float2* trig = reinterpret_cast<float2*>(smem_raw + sizeof(StageT) * kStages);
+    float* kc_s = reinterpret_cast<float*>(trig + kTileM * kTrigStride);
+    __half* qf = reinterpret_cast<__half*>(kc_s + static_cast<size_t>(p.ck) * kCenStride);  // [2 bufs][hi, lo][GQA][kQStride]
+    uint2* pre = reinterpret_cast<uint2*>(qf + 2 * kQSets * GQA * kQStride);  // [warps][K, V][16]
+    float* beta_s = reinterpret_cast<float*>(pre + kWarpsM * 2 * 16);  // [warps][GQA][64]
+    __shared__ uint64_t full_bar[kStages];
+    __shared__ float red_m[GQA][kWarpsM];
+    __shared__ float red_l[GQA][kWarpsM];
+    __shared__ uint32_t timed_out;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, qd = lane & 3;
+    const int split = blockIdx.x, unit = blockIdx.y;
+    const int b = unit / p.kh, hkv = unit % p.kh;
+    const int total_tiles = (p.tokens + kTileM - 1) / kTileM;
+    const int tile_begin = split * p.tiles_per_split;
+    const int ntiles = max(0, min(total_tiles, tile_begin + p.tiles_per_split) - tile_begin);
+
+    const size_t unit_tok = static_cast<size_t>(unit) * p.tok_stride;
+    const uint4* kb_g = p.kb + unit_tok;
+    const uint4* vb_g = p.vb + unit_tok;
+    const __half* kp_g = p.kp + unit_tok * NNZ;
+    const __half* vp_g = p.vp + unit_tok * NNZ;
+    const int8_t* kid_g = p.kid + unit_tok;
+    const int8_t* vid_g = p.vid + unit_tok;
+
+    if (tid == 0) {
+        timed_out = 0;
+        for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    auto issue = [&](int tile_rel) {
+        const int t0 = (tile_begin + tile_rel) * kTileM;
+        const int n = min(kTileM, p.tokens - t0);
+        StageT& st = stages[tile_rel % kStages];
+        uint64_t* bar = &full_bar[tile_rel % kStages];
+        const uint32_t bm_bytes = n * 16u, pl_bytes = n * NNZ * 2u;
+        mbar_arrive_expect_tx(bar, 2 * bm_bytes + 2 * pl_bytes);
+        bulk_g2s(st.kb, kb_g + t0, bm_bytes, bar);
+        bulk_g2s(st.vb, vb_g + t0, bm_bytes, bar);
+        bulk_g2s(st.kp, kp_g + static_cast<size_t>(t0) * NNZ, pl_bytes, bar);
+        bulk_g2s(st.vp, vp_g + static_cast<size_t>(t0) * NNZ, pl_bytes, bar);
+    };
+    if (tid == 0) {
+        for (int s = 0; s < kStages && s < ntiles; ++s) issue(s);
+    }
+
+    // ---- tables: sin/cos of (tile offset j) x (frequency i); key centroids; zeroed query rows ----
+    {
+        const int i = tid & 63, j0 = (tid >> 6) * 32;
+        const float f = rope_freq(p.inv_freq, p.theta, i);
+        float s, c, s1, c1;
+        sincosf(static_cast<float>(j0) * f, &s, &c);
+        sincosf(f, &s1, &c1);
+        for (int j = j0; j < j0 + 32; ++j) {
+            trig[trig_index(j, i)] = make_float2(c, s);
+            const float ns = s * c1 + c * s1, nc = c * c1 - s * s1;
+            s = ns, c = nc;
+        }
+        const __half* src = p.kc + static_cast<size_t>(unit) * p.ck * kHeadDim;
+        for (int idx = tid; idx < p.ck * (kHeadDim / 2); idx += kThreadsM) {
+            const int row = idx / (kHeadDim / 2), d = (idx % (kHeadDim / 2)) * 2;
+            const float2 v = __half22float2(*reinterpret_cast<const __half2*>(src + row * kHeadDim + d));
+            *reinterpret_cast<float2*>(kc_s + row * kCenStride + cen_index(d)) = v;
+        }
+        for (int idx = tid; idx < kWarpsM * GQA * kMaxClusters; idx += kThreadsM) beta_s[idx] = 0.f;
+    }
+
+    // ---- query state: item = (head, two adjacent frequencies i2, i2 + 1) ----------------------
+    // angle (pos_q - P0) * f goes down by 64 f per tile; seeded exactly every kReseedTiles tiles
+    float q_lo[kItems][2], q_hi[kItems][2], q_f[kItems][2];
+    float st_c[kItems][2], st_s[kItems][2], dn_c[kItems][2], dn_s[kItems][2];
+    const float q_mul = p.scaling * kLog2e;
+#pragma unroll
+    for (int it = 0; it < kItems; ++it) {
+        const int item = tid + it * kThreadsM;
+        const int h = item >> 5, i2 = (item & 31) * 2;
+        const bool on = item < GQA * 32;
+        const __half* qrow = p.q + (static_cast<size_t>(b) * p.nh + hkv * GQA + (on ? h : 0)) * kHeadDim;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            q_lo[it][u] = on ? __half2float(qrow[i2 + u]) * q_mul : 0.f;
+            q_hi[it][u] = on ? __half2float(qrow[i2 + u + 64]) * q_mul : 0.f;
+            q_f[it][u] = rope_freq(p.inv_freq, p.theta, i2 + u);
+            sincosf(static_cast<float>(kTileM) * q_f[it][u], &dn_s[it][u], &dn_c[it][u]);
+            st_c[it][u] = 1.f, st_s[it][u] = 0.f;
+        }
+    }
+
+    auto write_query = [&](int tile_rel) {
+        // Qt = R(pos_q - P0) q  for the tile that starts at token t0, as FP16 hi + lo
+        const int t0 = (tile_begin + tile_rel) * kTileM;
+        __half* base = qf + (tile_rel & 1) * (kQSets * GQA * kQStride);
+#pragma unroll
+        for (int it = 0; it < kItems; ++it) {
+            const int item = tid + it * kThreadsM;
+            if (item >= GQA * 32) continue;
+            const int h = item >> 5, i2 = (item & 31) * 2;
+            float lo[2], hi[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                if (tile_rel % kReseedTiles == 0) {
+                    const float delta = static_cast<float>(p.pos_q - (p.start_pos + t0));
+                    sincosf(delta * q_f[it][u], &st_s[it][u], &st_c[it][u]);
+                }
+                const float c = st_c[it][u], s = st_s[it][u];
+                lo[u] = q_lo[it][u] * c - q_hi[it][u] * s;
+                hi[u] = q_hi[it][u] * c + q_lo[it][u] * s;
+                // next tile: angle - 64 f
+                st_c[it][u] = c * dn_c[it][u] + s * dn_s[it][u];
+                st_s[it][u] = s * dn_c[it][u] - c * dn_s[it][u];
+            }
+            const __half2 lo_h = __floats2half2_rn(lo[0], lo[1]), hi_h = __floats2half2_rn(hi[0], hi[1]);
+            const float2 lo_f = __half22float2(lo_h), hi_f = __half22float2(hi_h);
+            __half* row_hi = base + h * kQStride;
+            __half* row_lo = base + (GQA + h) * kQStride;
+            *reinterpret_cast<__half2*>(row_hi + i2) = lo_h;
+            *reinterpret_cast<__half2*>(row_hi + i2 + 64) = hi_h;
+            *reinterpret_cast<__half2*>(row_lo + i2) = __floats2half2_rn(lo[0] - lo_f.x, lo[1] - lo_f.y);
+            *reinterpret_cast<__half2*>(row_lo + i2 + 64) = __floats2half2_rn(hi[0] - hi_f.x, hi[1] - hi_f.y);
+        }
+    };
+    if (ntiles > 0) write_query(0);
+
+    // ---- per-warp running state ---------------------------------------------------------------
+    float acc[8][4];          // O^T: m-block i -> coordinates 16g+i (c0,c1) and 16g+8+i (c2,c3); heads 2q, 2q+1
+    float m_used[2], l_part[2];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    m_used[0] = m_used[1] = -INFINITY;
+    l_part[0] = l_part[1] = 0.f;
+    float* beta_w = beta_s + warp * GQA * kMaxClusters;
+    uint2* pre_k = pre + warp * 32;
+    uint2* pre_v = pre_k + 16;
+
+    // cluster ids of this warp's 16 tokens of the next tile: lanes 0..15 key ids, 16..31 value ids
+    auto load_ids = [&](int tile_rel) -> int {
+        const int t = (tile_begin + tile_rel) * kTileM + warp * 16 + (lane & 15);
+        if (tile_rel < ntiles && t < p.tokens) return (lane < 16) ? kid_g[t] : vid_g[t];
+        return 0;
+    };
+    int ids_next = load_ids(0);
+    __syncthreads();  // tables and first query tile ready
+
+    // sin/cos of this lane's two rows (tile offsets 16 warp + g and + 8) and 16 frequencies: the
+    // same in every tile, so they live in registers for the whole kernel
+    float4 trA_r[8], trB_r[8];
+    {
+        const int tokA = warp * 16 + g, tokB = tokA + 8;
+        const float4* trA = reinterpret_cast<const float4*>(trig + tokA * kTrigStride);
+        const float4* trB = reinterpret_cast<const float4*>(trig + tokB * kTrigStride);
+        const int tr_swz = (tokA & 1) << 2;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            trA_r[u] = trA[(u * 4 + qd) ^ tr_swz];
+            trB_r[u] = trB[(u * 4 + qd) ^ tr_swz];
+        }
+    }
+
+    bool lost = false;
+    for (int it = 0; it < ntiles; ++it) {
+        const int t0 = (tile_begin + it) * kTileM;
+        const int ids_cur = ids_next;
+        ids_next = load_ids(it + 1);
+        if (!mbar_wait(&full_bar[it % kStages], (it / kStages) & 1)) lost = true;
+        const StageT& st = stages[it % kStages];
+        const int nvalid = min(16, p.tokens - (t0 + warp * 16));  // valid tokens of this warp's block
+        if (nvalid > 0) {
+            // rank bases of the block's 16 key bitmaps (lanes 0..15) and value bitmaps (16..31)
+            {
+                const int tok = warp * 16 + (lane & 15);
+                const uint4 bm = (lane < 16) ? st.kb[tok] : st.vb[tok];
+                pre_k[lane] = rank_bases(bm);  // pre_v == pre_k + 16
+            }
+            __syncwarp();
+
+            // ================= keys: rows g and g + 8 of the block =================
+            const int tokA = warp * 16 + g, tokB = tokA + 8;
+            const bool okA = g < nvalid, okB = g + 8 < nvalid;
+            const int kidA = min(max(__shfl_sync(0xffffffffu, ids_cur, g), 0), p.ck - 1);
+            const int kidB = min(max(__shfl_sync(0xffffffffu, ids_cur, g + 8), 0), p.ck - 1);
+            const unsigned char* kb_bytes = reinterpret_cast<const unsigned char*>(st.kb);
+            const unsigned char* pk_bytes = reinterpret_cast<const unsigned char*>(pre_k);
+            const int off_lo = field_offset(qd), off_hi = field_offset(4 + qd);
+            const uint32_t fAl = okA ? *reinterpret_cast<const unsigned short*>(kb_bytes + tokA * 16 + off_lo) : 0u;
+            const uint32_t fAh = okA ? *reinterpret_cast<const unsigned short*>(kb_bytes + tokA * 16 + off_hi) : 0u;
+            const uint32_t fBl = okB ? *reinterpret_cast<const unsigned short*>(kb_bytes + tokB * 16 + off_lo) : 0u;
+            const uint32_t fBh = okB ? *reinterpret_cast<const unsigned short*>(kb_bytes + tokB * 16 + off_hi) : 0u;
+            const __half* pAl = st.kp + tokA * NNZ + pk_bytes[g * 8 + qd];
+            const __half* pAh = st.kp + tokA * NNZ + pk_bytes[g * 8 + 4 + qd];
+            const __half* pBl = st.kp + tokB * NNZ + pk_bytes[(g + 8) * 8 + qd];
+            const __half* pBh = st.kp + tokB * NNZ + pk_bytes[(g + 8) * 8 + 4 + qd];
+            // FP32 centroid rows; the lane's low field starts at 16q, its partner field at 64 + 16q
+            const float* cA = kc_s + kidA * kCenStride + 16 * qd;
+            const float* cB = kc_s + kidB * kCenStride + 16 * qd;
+            const int cen_swz = (qd >> 1) & 1;  // 16-byte unit swap of this lane's fields
+            const __half* qbuf = qf + (it & 1) * (kQSets * GQA * kQStride) + g * kQStride + 16 * qd;
+            const bool q_on = g < GQA;  // rows of the B operand beyond the real heads are zero
+
+            // three independent accumulators (hi.hi, hi.lo, lo.hi) keep the MMA dependency chains short
+            float sc[4] = {0.f, 0.f, 0.f, 0.f}, sc2[4] = {0.f, 0.f, 0.f, 0.f}, sc3[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                // four coordinates 16q + 4ks .. +3 and their partners + 64, both tokens:
+                // k = centroid (+ residual where the bitmap bit is set)
+                const int cu = (ks ^ cen_swz) * 4;
+                float4 al = *reinterpret_cast<const float4*>(cA + cu), ah = *reinterpret_cast<const float4*>(cA + 64 + cu);
+                float4 bl = *reinterpret_cast<const float4*>(cB + cu), bh = *reinterpret_cast<const float4*>(cB + 64 + cu);
+                float* kAl = &al.x; float* kAh = &ah.x; float* kBl = &bl.x; float* kBh = &bh.x;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const uint32_t bit = 0x8000u >> (4 * ks + e);
+                    if (fAl & bit) { kAl[e] = add_f16_f32(*reinterpret_cast<const unsigned short*>(pAl), kAl[e]); ++pAl; }
+                    if (fAh & bit) { kAh[e] = add_f16_f32(*reinterpret_cast<const unsigned short*>(pAh), kAh[e]); ++pAh; }
+                    if (fBl & bit) { kBl[e] = add_f16_f32(*reinterpret_cast<const unsigned short*>(pBl), kBl[e]); ++pBl; }
+                    if (fBh & bit) { kBh[e] = add_f16_f32(*reinterpret_cast<const unsigned short*>(pBh), kBh[e]); ++pBh; }
+                }
+                float rAl[4], rAh[4], rBl[4], rBh[4];
+#pragma unroll
+                for (int e2 = 0; e2 < 2; ++e2) {
+                    const float4 ta = trA_r[ks * 2 + e2];  // (cos, sin) of two neighbouring frequencies
+                    const float4 tb = trB_r[ks * 2 + e2];
+                    const int e = 2 * e2;
+                    rAl[e] = kAl[e] * ta.x - kAh[e] * ta.y;
+                    rAh[e] = kAh[e] * ta.x + kAl[e] * ta.y;
+                    rAl[e + 1] = kAl[e + 1] * ta.z - kAh[e + 1] * ta.w;
+                    rAh[e + 1] = kAh[e + 1] * ta.z + kAl[e + 1] * ta.w;
+                    rBl[e] = kBl[e] * tb.x - kBh[e] * tb.y;
+                    rBh[e] = kBh[e] * tb.x + kBl[e] * tb.y;
+                    rBl[e + 1] = kBl[e + 1] * tb.z - kBh[e + 1] * tb.w;
+                    rBh[e + 1] = kBh[e + 1] * tb.z + kBl[e + 1] * tb.w;
+                }
+                // k-step ks (low half of the head) and ks + 4 (high half)
+                uint2 qh_l = make_uint2(0u, 0u), qh_h = qh_l, ql_l = qh_l, ql_h = qh_l;
+                if (q_on) {
+                    qh_l = *reinterpret_cast<const uint2*>(qbuf + 4 * ks);
+                    qh_h = *reinterpret_cast<const uint2*>(qbuf + 64 + 4 * ks);
+                    ql_l = *reinterpret_cast<const uint2*>(qbuf + GQA * kQStride + 4 * ks);
+                    ql_h = *reinterpret_cast<const uint2*>(qbuf + GQA * kQStride + 64 + 4 * ks);
+                }
+                uint32_t a0, a1, a2, a3, l0, l1, l2, l3;
+                split_h2(rAl[0], rAl[1], a0, l0);
+                split_h2(rBl[0], rBl[1], a1, l1);
+                split_h2(rAl[2], rAl[3], a2, l2);
+                split_h2(rBl[2], rBl[3], a3, l3);
+                mma_16816(sc, a0, a1, a2, a3, qh_l.x, qh_l.y);
+                mma_16816(sc2, a0, a1, a2, a3, ql_l.x, ql_l.y);
+                mma_16816(sc3, l0, l1, l2, l3, qh_l.x, qh_l.y);
+                split_h2(rAh[0], rAh[1], a0, l0);
+                split_h2(rBh[0], rBh[1], a1, l1);
+                split_h2(rAh[2], rAh[3], a2, l2);
+                split_h2(rBh[2], rBh[3], a3, l3);
+                mma_16816(sc, a0, a1, a2, a3, qh_h.x, qh_h.y);
+                mma_16816(sc2, a0, a1, a2, a3, ql_h.x, ql_h.y);
+                mma_16816(sc3, l0, l1, l2, l3, qh_h.x, qh_h.y);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sc[i] += sc2[i] + sc3[i];
+            // sc: c0,c1 = (token g, heads 2q, 2q+1), c2,c3 = (token g+8, ...), log2 domain
+            if (!okA) sc[0] = sc[1] = -INFINITY;
+            if (!okB) sc[2] = sc[3] = -INFINITY;
+
+            // ================= softmax (lazy running maximum) =================
+            float mt[2] = {fmaxf(sc[0], sc[2]), fmaxf(sc[1], sc[3])};
+#pragma unroll
+            for (int off = 4; off < 32; off <<= 1) {
+                mt[0] = fmaxf(mt[0], __shfl_xor_sync(0xffffffffu, mt[0], off));
+                mt[1] = fmaxf(mt[1], __shfl_xor_sync(0xffffffffu, mt[1], off));
+            }
+            const bool grow = mt[0] > m_used[0] + kRescaleThreshold || mt[1] > m_used[1] + kRescaleThreshold;
+            if (__any_sync(0xffffffffu, grow)) {
+                float alpha[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const float m_new = fmaxf(m_used[u], mt[u]);
+                    alpha[u] = (m_used[u] == -INFINITY) ? 0.f : fast_exp2(m_used[u] - m_new);
+                    m_used[u] = m_new;
+                    l_part[u] *= alpha[u];
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    acc[i][0] *= alpha[0], acc[i][2] *= alpha[0];
+                    acc[i][1] *= alpha[1], acc[i][3] *= alpha[1];
+                }
+                __syncwarp();
+#pragma unroll
+                for (int h = 0; h < GQA; ++h) {
+                    const float a = __shfl_sync(0xffffffffu, alpha[h & 1], h >> 1);
+                    for (int c = lane; c < kMaxClusters; c += 32) beta_w[h * kMaxClusters + c] *= a;
+                }
+                __syncwarp();
+            }
+            float pr[4];
+            pr[0] = fast_exp2(sc[0] - m_used[0]), pr[1] = fast_exp2(sc[1] - m_used[1]);
+            pr[2] = fast_exp2(sc[2] - m_used[0]), pr[3] = fast_exp2(sc[3] - m_used[1]);
+            const __half2 p01 = __floats2half2_rn(pr[0], pr[1]), p23 = __floats2half2_rn(pr[2], pr[3]);
+            const float2 p01f = __half22float2(p01), p23f = __half22float2(p23);
+            l_part[0] += p01f.x + p23f.x;
+            l_part[1] += p01f.y + p23f.y;
+            {
+                // cluster mass: beta[head][value id of the token] += p
+                const int vidA = min(max(__shfl_sync(0xffffffffu, ids_cur, 16 + g), 0), kMaxClusters - 1);
+                const int vidB = min(max(__shfl_sync(0xffffffffu, ids_cur, 24 + g), 0), kMaxClusters - 1);
+                const int h0 = 2 * qd, h1 = 2 * qd + 1;
+                if (h0 < GQA) {
+                    if (okA) atomicAdd(&beta_w[h0 * kMaxClusters + vidA], p01f.x);
+                    if (okB) atomicAdd(&beta_w[h0 * kMaxClusters + vidB], p23f.x);
+                }
+                if (h1 < GQA) {
+                    if (okA) atomicAdd(&beta_w[h1 * kMaxClusters + vidA], p01f.y);
+                    if (okB) atomicAdd(&beta_w[h1 * kMaxClusters + vidB], p23f.y);
+                }
+            }
+            // P as B operand (tokens x heads): transpose the two 8x8 halves
+            const uint32_t pb0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p01));
+            const uint32_t pb1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p23));
+
+            // ================= values: tokens 2q, 2q+1, 2q+8, 2q+9; coordinates [16g, 16g+16) =================
+            {
+                const unsigned char* vb_bytes = reinterpret_cast<const unsigned char*>(st.vb);
+                const unsigned char* pv_bytes = reinterpret_cast<const unsigned char*>(pre_v);
+                const int off = field_offset(g);
+                const int r0 = 2 * qd, r1 = 2 * qd + 1, r2 = 2 * qd + 8, r3 = 2 * qd + 9;
+                const int tk0 = warp * 16 + r0, tk1 = warp * 16 + r1, tk2 = warp * 16 + r2, tk3 = warp * 16 + r3;
+                const uint32_t f0 = r0 < nvalid ? *reinterpret_cast<const unsigned short*>(vb_bytes + tk0 * 16 + off) : 0u;
+                const uint32_t f1 = r1 < nvalid ? *reinterpret_cast<const unsigned short*>(vb_bytes + tk1 * 16 + off) : 0u;
+                const uint32_t f2 = r2 < nvalid ? *reinterpret_cast<const unsigned short*>(vb_bytes + tk2 * 16 + off) : 0u;
+                const uint32_t f3 = r3 < nvalid ? *reinterpret_cast<const unsigned short*>(vb_bytes + tk3 * 16 + off) : 0u;
+                const __half* p0 = st.vp + tk0 * NNZ + pv_bytes[r0 * 8 + g];
+                const __half* p1 = st.vp + tk1 * NNZ + pv_bytes[r1 * 8 + g];
+                const __half* p2 = st.vp + tk2 * NNZ + pv_bytes[r2 * 8 + g];
+                const __half* p3 = st.vp + tk3 * NNZ + pv_bytes[r3 * 8 + g];
+                uint32_t v01[16], v23[16];  // (token 2q | token 2q+1 << 16), (2q+8 | 2q+9 << 16) per coordinate
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    v01[e] = walk16(f0, e, p0) | (walk16(f1, e, p1) << 16);
+                    v23[e] = walk16(f2, e, p2) | (walk16(f3, e, p3) << 16);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) mma_16816(acc[i], v01[i], v01[8 + i], v23[i], v23[8 + i], pb0, pb1);
+            }
+            __syncwarp();  // rank-base table is rewritten next tile
+        }
+        if (it + 1 < ntiles) write_query(it + 1);
+        __syncthreads();  // ring slot free, next query tile visible
+        if (tid == 0 && it + kStages < ntiles) issue(it + kStages);
+    }
+    if (lost && lane == 0) atomicOr(&timed_out, 1u);
+
+    // ---- combine warps, write the split partial ----------------------------------------------
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+        l_part[0] += __shfl_xor_sync(0xffffffffu, l_part[0], off);
+        l_part[1] += __shfl_xor_sync(0xffffffffu, l_part[1], off);
+    }
+    if (g == 0) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int h = 2 * qd + u;
+            if (h < GQA) red_m[h][warp] = m_used[u], red_l[h][warp] = l_part[u];
+        }
+    }
+    __syncthreads();
+    float* red_acc = reinterpret_cast<float*>(smem_raw);  // [warps][GQA][128], stage memory is free now
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int h = 2 * qd + u;
+        if (h < GQA) {
+            float fm = red_m[h][0];
+#pragma unroll
+            for (int w = 1; w < kWarpsM; ++w) fm = fmaxf(fm, red_m[h][w]);
+            const float scale = (m_used[u] == -INFINITY) ? 0.f : fast_exp2(m_used[u] - fm);
+            float* dst = red_acc + (warp * GQA + h) * kHeadDim + 16 * g;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                dst[i] = acc[i][u] * scale;
+                dst[8 + i] = acc[i][2 + u] * scale;
+            }
+        }
+    }
+    __syncthreads();
+    const size_t part = static_cast<size_t>(b) * p.nh + hkv * GQA;
+    for (int idx = tid; idx < GQA * kHeadDim; idx += kThreadsM) {
+        const int h = idx / kHeadDim, d = idx % kHeadDim;
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarpsM; ++w) sum += red_acc[(w * GQA + h) * kHeadDim + d];
+        p.ws_delta[((part + h) * p.splits + split) * kHeadDim + d] = sum;
+    }
+    for (int idx = tid; idx < GQA * kMaxClusters; idx += kThreadsM) {
+        const int h = idx / kMaxClusters, c = idx % kMaxClusters;
+        float fm = red_m[h][0];
+#pragma unroll
+        for (int w = 1; w < kWarpsM; ++w) fm = fmaxf(fm, red_m[h][w]);
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarpsM; ++w) {
+            const float scale = (red_m[h][w] == -INFINITY) ? 0.f : fast_exp2(red_m[h][w] - fm);
+            sum += beta_s[(w * GQA + h) * kMaxClusters + c] * scale;
+        }
+        p.ws_beta[((part + h) * p.splits + split) * kMaxClusters + c] = sum;
+    }
+    if (tid < GQA) {
+        const int h = tid;
+        float fm = red_m[h][0];
+        for (int w = 1; w < kWarpsM; ++w) fm = fmaxf(fm, red_m[h][w]);
+        float fl = 0.f;
+        for (int w = 0; w < kWarpsM; ++w)
+            fl += (red_m[h][w] == -INFINITY) ? 0.f : red_l[h][w] * fast_exp2(red_m[h][w] - fm);
+        p.ws_m[(part + h) * p.splits + split] = fm;
+        p.ws_l[(part + h) * p.splits + split] = fl;
+    }
+    if (tid == 0 && timed_out) atomicOr(p.status, RESKV_STATUS_WAIT_TIMEOUT);
+}
+
+}  // namespace mma

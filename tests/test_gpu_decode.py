@@ -12,6 +12,17 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
+@pytest.fixture(autouse=True, params=["tensor-core", "simt"])
+def kernel_variant(request):
+    """Every test runs against both partial kernels."""
+    from reskv_b200._extension import library
+
+    lib = library()
+    assert lib.reskv_decode_set_variant(0 if request.param == "tensor-core" else 1) == 0
+    yield request.param
+    lib.reskv_decode_set_variant(0)
+
+
 def _plan(nnz):
     from reskv_b200.config import KernelPlan
 
@@ -135,7 +146,7 @@ def test_large_finite_recent_scores(nnz):
     cen = data[:, :, :1].contiguous()
     ids = torch.zeros(1, 1, 128, dtype=torch.int32)
     kc = oracle_cache(data, cen, ids, "unstructured", 16, nnz)
-    plan = ResKVKernelConfig(sparsity=1 - nnz / 128, centroid_fusion="deferred").resolve(1)
+    plan = ResKVKernelConfig(sparsity=1 - nnz / 128, layout="unstructured").resolve(1)
     cache = CompressedKV(to_compressed(kc, plan, DEV), to_compressed(kc, plan, DEV))
     query = torch.full((1, 4, 1, 128), 100.0, dtype=torch.float16)
     recent = (query, torch.full((1, 1, 32, 128), 100.0, dtype=torch.float16),
