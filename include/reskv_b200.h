@@ -77,6 +77,34 @@ int reskv_decode_bitmap_fp16(const void* q, const void* k_centroids, const void*
                              void* workspace, size_t workspace_bytes, void* out, float* out_m, float* out_l,
                              void* stream);
 
+/* ---- fused decode attention: the other residual layouts -----------------------------
+ * Same contract as reskv_decode_bitmap_fp16 for
+ *   RESKV_LAYOUT_UNSTRUCTURED, bits 4 / 2: payload i32 [.., 4*bits] (all 128 coords),
+ *       no metadata, scale f16 [..] -- replaces attention.decode_quantized
+ *       (reskv/csrc/attention.cu:967-1348);
+ *   RESKV_LAYOUT_TILED, bits 16: payload f16 [.., 64], metadata i32 [.., 4] (16-bit
+ *       tile masks) -- replaces attention.decode_fp16 (attention.cu:196-596,665-835);
+ *   RESKV_LAYOUT_STRUCTURED, bits 16: payload f16 [.., 32], metadata i32 [.., 4]
+ *       (4-bit in-tile indices) -- replaces attention.decode_fp16 and
+ *       cluster_mass.decode_structured_fp16 (cluster_mass.cu:567-997,1298-1459);
+ *   RESKV_LAYOUT_STRUCTURED, bits 4: payload i32 [.., 4], metadata i32 [.., 2], scale
+ *       f16 [..] -- replaces attention.decode_int4 and
+ *       cluster_mass.decode_structured_int4.
+ * Per-token and deferred centroid fusion of the reference are the same sum; one
+ * kernel serves both op families (value centroids are applied after the split
+ * merge).  Workspace size as reskv_decode_bitmap_fp16_workspace_bytes. */
+#define RESKV_LAYOUT_UNSTRUCTURED 0
+#define RESKV_LAYOUT_TILED 1
+#define RESKV_LAYOUT_STRUCTURED 2
+
+int reskv_decode_packed(int layout, int bits, const void* q, const void* k_centroids, const void* k_ids,
+                        const void* k_payload, const void* k_meta, const void* k_scale, const void* v_centroids,
+                        const void* v_ids, const void* v_payload, const void* v_meta, const void* v_scale, int batch,
+                        int kv_heads, int q_heads, int tokens, int64_t tok_stride, int k_clusters, int v_clusters,
+                        int start_pos, int pos_q, float rope_theta, const float* inv_freq, float scaling, int splits,
+                        const void* recent_q, const void* recent_k, const void* recent_v, int recent_tokens,
+                        void* workspace, size_t workspace_bytes, void* out, float* out_m, float* out_l, void* stream);
+
 /* Selects the partial kernel reskv_decode_bitmap_fp16 launches: 0 = tensor-core
  * tiles of 16 tokens (default), 1 = the simpler warp-per-token kernel (kept for
  * cross-checking).  Process-wide; no counterpart in the reference. */

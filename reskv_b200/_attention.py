@@ -68,25 +68,19 @@ def attention(
         if any(x.device != query.device or x.dtype != torch.float16 for x in recent):
             raise ValueError("recent tensors must be FP16 on the query device")
     suffix = (kh, nh, int(start_position), int(position), float(rope_theta), scale)
-    if plan.centroid_fusion == "deferred" and plan.layout == "unstructured":
-        fused = (qr.reshape(b * nh, 128), kr, vr) if has_recent else None
-        (out,) = ext.decode_fp16(q, kc, ki, kp, km, vc, vi, vp, vm, *suffix, False, plan.splits, freq, fused)
-        return out.reshape(b, nh, 1, 128)
-    empty = query.new_empty(0)
-    freq = freq if freq is not None else torch.empty(0, dtype=torch.float32, device=query.device)
+    fused = (qr.reshape(b * nh, 128), kr, vr) if has_recent else None
+    # every decode op takes the dense window as an extra argument and folds it into its
+    # merge kernel, so no separate merge_recent launch (or bmm) is needed here
     if plan.centroid_fusion == "deferred":
-        fn = ext.decode_structured_int4 if plan.bits == 4 else ext.decode_structured_fp16
-        out, m, norm = fn(q, kc, ki, kp, km, ks if ks is not None else empty, vc, vi, vp, vm,
-                          vs if vs is not None else empty, *suffix, True, plan.splits, freq)
+        if plan.layout == "unstructured":
+            result = ext.decode_fp16(q, kc, ki, kp, km, vc, vi, vp, vm, *suffix, False, plan.splits, freq, fused)
+        else:
+            fn = ext.decode_structured_int4 if plan.bits == 4 else ext.decode_structured_fp16
+            result = fn(q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, *suffix, False, plan.splits, freq, fused)
     elif plan.layout == "unstructured":
-        out, m, norm = ext.decode_quantized(q, kc, ki, kp, ks, vc, vi, vp, vs, *suffix, plan.bits, plan.bits,
-                                            plan.splits, freq)
+        result = ext.decode_quantized(q, kc, ki, kp, ks, vc, vi, vp, vs, *suffix, plan.bits, plan.bits, plan.splits,
+                                      freq, fused)
     else:
         fn = ext.decode_int4 if plan.bits == 4 else ext.decode_fp16
-        out, m, norm = fn(q, kc, ki, kp, km, ks if ks is not None else empty, vc, vi, vp, vm,
-                          vs if vs is not None else empty, *suffix, plan.splits, freq)
-    if has_recent:
-        merge = load_extension("attention", plan, query.device.index or 0)
-        out = merge.merge_recent(out, m, norm, qr.reshape(b * nh, 128).contiguous(), kr.contiguous(),
-                                 vr.contiguous(), kh, nh, scale)
-    return out.reshape(b, nh, 1, 128)
+        result = fn(q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, *suffix, plan.splits, freq, fused)
+    return result[0].reshape(b, nh, 1, 128)

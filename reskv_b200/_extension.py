@@ -41,6 +41,10 @@ SIGNATURES = {
         _I,
         [_P] * 9 + [_I, _I, _I, _I, _L, _I, _I, _I, _I, _I, _F, _P, _F, _I, _P, _P, _P, _I, _P, _Z, _P, _P, _P, _P],
     ),
+    "reskv_decode_packed": (
+        _I,
+        [_I, _I] + [_P] * 11 + [_I, _I, _I, _I, _L, _I, _I, _I, _I, _F, _P, _F, _I, _P, _P, _P, _I, _P, _Z, _P, _P, _P, _P],
+    ),
     "reskv_decode_auto_splits": (_I, [_I, _I, _I]),
     "reskv_decode_set_variant": (_I, [_I]),
     "reskv_decode_set_timing_events": (_I, [_P, _P]),
@@ -197,45 +201,76 @@ def _token_stride(rows: torch.Tensor, width: int) -> int:
     return rows.stride(0) // width
 
 
+LAYOUT_UNSTRUCTURED, LAYOUT_TILED, LAYOUT_STRUCTURED = 0, 1, 2
+
+
+def _decode(lib, layout, bits, q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, kh, nh, start_pos, pos_q, rope_theta, scale,
+            splits, inv_freq, return_stats=True, recent=None):
+    """Allocate outputs and scratch, call the decode entry point of a layout.
+
+    ``layout is None`` selects the unstructured FP16 bitmap kernel, otherwise
+    ``reskv_decode_packed``.  ``recent = (q_rot [B*nh,128], k_rot, v [B,kh,Tr,128])``
+    folds a dense window into the same launch pair.
+    """
+    bnh = q.shape[0]
+    b = bnh // nh
+    t, width = kp.shape[1], kp.shape[2]
+    stride = _token_stride(kp, width)
+    for rows in (ki, km, ks, vi, vp, vm, vs):
+        if rows is not None and rows.numel() and _token_stride(rows, rows.shape[2] if rows.ndim == 3 else 1) != stride:
+            raise ValueError("K and V cache tensors must share one token stride")
+    dev = q.device
+    need = lib.reskv_decode_bitmap_fp16_workspace_bytes(b, kh, nh, t, int(splits))
+    ws = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+    if _CHECK_STATUS:
+        ws[:256].zero_()
+    out = torch.empty((bnh, 128), dtype=torch.float16, device=dev)
+    m = torch.empty(bnh, dtype=torch.float32, device=dev) if return_stats else None
+    l = torch.empty(bnh, dtype=torch.float32, device=dev) if return_stats else None
+    rq = rk = rv = None
+    tr = 0
+    if recent is not None and recent[1].shape[2] > 0:
+        rq, rk, rv = (x.contiguous() for x in recent)
+        tr = rk.shape[2]
+    tail = (b, kh, nh, t, stride, kc.shape[1], vc.shape[1])
+    rest = (int(start_pos), int(pos_q), float(rope_theta), _ptr(inv_freq), float(scale), int(splits), _ptr(rq),
+            _ptr(rk), _ptr(rv), tr, ws.data_ptr(), ws.numel(), out.data_ptr(), _ptr(m), _ptr(l), _stream(dev))
+    if layout is None:
+        rc = lib.reskv_decode_bitmap_fp16(q.data_ptr(), kc.data_ptr(), ki.data_ptr(), kp.data_ptr(), km.data_ptr(),
+                                          vc.data_ptr(), vi.data_ptr(), vp.data_ptr(), vm.data_ptr(), *tail, width,
+                                          *rest)
+    else:
+        rc = lib.reskv_decode_packed(layout, bits, q.data_ptr(), kc.data_ptr(), ki.data_ptr(), kp.data_ptr(),
+                                     _ptr(km), _ptr(ks), vc.data_ptr(), vi.data_ptr(), vp.data_ptr(), _ptr(vm),
+                                     _ptr(vs), *tail, *rest)
+    check(rc, launches=2)
+    if _CHECK_STATUS:
+        status = int(ws[:4].view(torch.int32).item())
+        if status:
+            raise RuntimeError(f"decode: device status {status:#x} (bounded wait ran out)")
+    return (out, m, l) if return_stats else (out,)
+
+
 class ClusterMassOps(_Ops):
     """``cluster_mass`` family (reference pybind module cluster_mass.cu:1511-1516)."""
 
     def decode_fp16(self, q, kc, ki, kp, km, vc, vi, vp, vm, kh, nh, start_pos, pos_q, rope_theta, scale,
                     return_stats=True, splits=0, inv_freq=None, recent=None):
         """Unstructured FP16 bitmap decode -> ``(out, m, l)`` (``(out,)`` without
-        stats), as cluster_mass.cu:1177-1296.  ``recent=(q_rot [B*nh,128], k_rot,
-        v [B,kh,Tr,128])`` additionally folds a dense window into the same launch
-        pair (not part of the reference signature)."""
-        bnh = q.shape[0]
-        b = bnh // nh
-        t, nnz = kp.shape[1], kp.shape[2]
-        stride = _token_stride(kp, nnz)
-        for rows, width in ((ki, 1), (km, 2), (vi, 1), (vp, nnz), (vm, 2)):
-            if _token_stride(rows, width) != stride:
-                raise ValueError("K and V cache tensors must share one token stride")
-        dev = q.device
-        need = self.lib.reskv_decode_bitmap_fp16_workspace_bytes(b, kh, nh, t, int(splits))
-        ws = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
-        if _CHECK_STATUS:
-            ws[:256].zero_()
-        out = torch.empty((bnh, 128), dtype=torch.float16, device=dev)
-        m = torch.empty(bnh, dtype=torch.float32, device=dev) if return_stats else None
-        l = torch.empty(bnh, dtype=torch.float32, device=dev) if return_stats else None
-        rq = rk = rv = None
-        tr = 0
-        if recent is not None and recent[1].shape[2] > 0:
-            rq, rk, rv = (x.contiguous() for x in recent)
-            tr = rk.shape[2]
-        check(self.lib.reskv_decode_bitmap_fp16(
-            q.data_ptr(), kc.data_ptr(), ki.data_ptr(), kp.data_ptr(), km.data_ptr(), vc.data_ptr(), vi.data_ptr(),
-            vp.data_ptr(), vm.data_ptr(), b, kh, nh, t, stride, kc.shape[1], vc.shape[1], nnz, int(start_pos),
-            int(pos_q), float(rope_theta), _ptr(inv_freq), float(scale), int(splits), _ptr(rq), _ptr(rk), _ptr(rv), tr,
-            ws.data_ptr(), ws.numel(), out.data_ptr(), _ptr(m), _ptr(l), _stream(dev)), launches=2)
-        if _CHECK_STATUS:
-            status = int(ws[:4].view(torch.int32).item())
-            if status:
-                raise RuntimeError(f"decode_fp16: device status {status:#x} (bounded wait ran out)")
-        return (out, m, l) if return_stats else (out,)
+        stats), as cluster_mass.cu:1177-1296.  ``recent`` (not part of the
+        reference signature) fuses the dense window into the same call."""
+        return _decode(self.lib, None, 16, q, kc, ki, kp, km, None, vc, vi, vp, vm, None, kh, nh, start_pos, pos_q,
+                       rope_theta, scale, splits, inv_freq, return_stats, recent)
+
+    def decode_structured_fp16(self, q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, kh, nh, start_pos, pos_q, rope_theta,
+                               scale, return_stats=True, splits=0, inv_freq=None, recent=None):
+        return _decode(self.lib, LAYOUT_STRUCTURED, 16, q, kc, ki, kp, km, None, vc, vi, vp, vm, None, kh, nh,
+                       start_pos, pos_q, rope_theta, scale, splits, inv_freq, return_stats, recent)
+
+    def decode_structured_int4(self, q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, kh, nh, start_pos, pos_q, rope_theta,
+                               scale, return_stats=True, splits=0, inv_freq=None, recent=None):
+        return _decode(self.lib, LAYOUT_STRUCTURED, 4, q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, kh, nh, start_pos,
+                       pos_q, rope_theta, scale, splits, inv_freq, return_stats, recent)
 
     def merge_recent(self, out, m, l, scores, v_recent, kh, nh):
         b = out.shape[0] // nh
@@ -245,15 +280,28 @@ class ClusterMassOps(_Ops):
                                                  _stream(out.device)))
         return merged
 
-    def decode_structured_fp16(self, *args):
-        raise NotImplementedError("structured FP16 deferred decode is not built yet")
-
-    def decode_structured_int4(self, *args):
-        raise NotImplementedError("structured INT4 deferred decode is not built yet")
-
 
 class AttentionOps(_Ops):
     """``attention`` family (reference pybind module attention.cu:1350-1355)."""
+
+    def decode_fp16(self, q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, kh, nh, start_pos, pos_q, rope_theta, scale,
+                    splits=0, inv_freq=None, recent=None):
+        """Tiled (64 values per token) or 4:16 structured (32 values) FP16 decode."""
+        layout = LAYOUT_TILED if kp.shape[2] == 64 else LAYOUT_STRUCTURED
+        return _decode(self.lib, layout, 16, q, kc, ki, kp, km, None, vc, vi, vp, vm, None, kh, nh, start_pos, pos_q,
+                       rope_theta, scale, splits, inv_freq, True, recent)
+
+    def decode_int4(self, q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, kh, nh, start_pos, pos_q, rope_theta, scale,
+                    splits=0, inv_freq=None, recent=None):
+        return _decode(self.lib, LAYOUT_STRUCTURED, 4, q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, kh, nh, start_pos,
+                       pos_q, rope_theta, scale, splits, inv_freq, True, recent)
+
+    def decode_quantized(self, q, kc, ki, kp, ks, vc, vi, vp, vs, kh, nh, start_pos, pos_q, rope_theta, scale, k_bits,
+                         v_bits, splits=0, inv_freq=None, recent=None):
+        if k_bits != v_bits or k_bits not in (2, 4):
+            raise ValueError("decode_quantized expects equal key and value bit widths of 2 or 4")
+        return _decode(self.lib, LAYOUT_UNSTRUCTURED, k_bits, q, kc, ki, kp, None, ks, vc, vi, vp, None, vs, kh, nh,
+                       start_pos, pos_q, rope_theta, scale, splits, inv_freq, True, recent)
 
     def merge_recent(self, out, m, l, q_rope, k_recent, v_recent, kh, nh, scale):
         b = out.shape[0] // nh
@@ -262,15 +310,6 @@ class AttentionOps(_Ops):
                                              k_recent.data_ptr(), v_recent.data_ptr(), b, kh, nh, k_recent.shape[2],
                                              float(scale), merged.data_ptr(), _stream(out.device)))
         return merged
-
-    def decode_fp16(self, *args):
-        raise NotImplementedError("tiled / structured FP16 per-token decode is not built yet")
-
-    def decode_int4(self, *args):
-        raise NotImplementedError("structured INT4 per-token decode is not built yet")
-
-    def decode_quantized(self, *args):
-        raise NotImplementedError("unstructured INT4/INT2 decode is not built yet")
 
 
 _TABLES = {"compression": CompressionOps, "attention": AttentionOps, "cluster_mass": ClusterMassOps}

@@ -41,11 +41,13 @@ struct DecodeParams {
     const __half* q;
     const __half* kc;
     const int8_t* kid;
-    const __half* kp;
-    const uint4* kb;
+    const void* kp;   // payload rows
+    const void* kb;   // metadata rows (bitmaps, tile masks / indices) or null
     const int8_t* vid;
-    const __half* vp;
-    const uint4* vb;
+    const void* vp;
+    const void* vb;
+    const __half* ks;  // per-token scales of quantised layouts or null
+    const __half* vs;
     float* ws_m;
     float* ws_l;
     float* ws_delta;
@@ -56,14 +58,6 @@ struct DecodeParams {
     int kh, nh, tokens, ck, cv;
     int start_pos, pos_q, splits, tiles_per_split;
     float theta, scaling;
-};
-
-template <int NNZ>
-struct Stage {
-    uint4 kb[kTile];
-    uint4 vb[kTile];
-    __half kp[kTile * NNZ];
-    __half vp[kTile * NNZ];
 };
 
 __device__ __forceinline__ float rope_freq(const float* inv_freq, float theta, int i) {
@@ -97,29 +91,124 @@ __device__ __forceinline__ void warp_sum_heads(float (&v)[GQA], int lane) {
     }
 }
 
-// Residual value of the lane's four coordinates of one token.
-// Bitmap words in memory order: x = word0 low half (coords 32..63), y = word0
-// high half (0..31), z = word1 low (96..127), w = word1 high (64..95); inside a
-// 32-bit half coordinate c sits at bit 31 - c % 32.
-template <int NNZ>
-__device__ __forceinline__ void decode4(const uint4 bm, const __half* row, int lane, float (&r)[4]) {
-    const uint32_t word[4] = {bm.y, bm.x, bm.w, bm.z};
-    int base = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const uint32_t w = word[i];
-        const int rank = base + __popc(__funnelshift_rc(w, 0u, 32 - lane));
-        const bool kept = (w >> (31 - lane)) & 1u;
-        r[i] = kept ? __half2float(row[min(rank, NNZ - 1)]) : 0.0f;
-        base += __popc(w);
-    }
-}
+// ---- residual layouts --------------------------------------------------------------------
+// A layout says how many payload / metadata bytes a token has and how a lane
+// turns them into the residual of its four coordinates {lane + 32 i}.
 
-template <int GQA, int NNZ, int CVS>
-__global__ void __launch_bounds__(kThreads, 2) decode_bitmap_partial_kernel(const DecodeParams p) {
+// Unstructured FP16: 2 x u64 bitmap, MSB first (reference compression.py:84-88).
+// Words in memory order: x = word0 low half (coords 32..63), y = word0 high half
+// (0..31), z = word1 low (96..127), w = word1 high (64..95); inside a 32-bit half
+// coordinate c sits at bit 31 - c % 32; payload index = retained coordinates before it.
+template <int NNZ>
+struct LayoutBitmap {
+    static constexpr int kPayloadBytes = NNZ * 2, kMetaBytes = 16;
+    static constexpr bool kScale = false;
+    __device__ static void decode(const unsigned char* pay, const unsigned char* meta, float, int lane,
+                                  float (&r)[4]) {
+        const uint4 bm = *reinterpret_cast<const uint4*>(meta);
+        const __half* row = reinterpret_cast<const __half*>(pay);
+        const uint32_t word[4] = {bm.y, bm.x, bm.w, bm.z};
+        int base = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t w = word[i];
+            const int rank = base + __popc(__funnelshift_rc(w, 0u, 32 - lane));
+            const bool kept = (w >> (31 - lane)) & 1u;
+            r[i] = kept ? __half2float(row[min(rank, NNZ - 1)]) : 0.0f;
+            base += __popc(w);
+        }
+    }
+};
+
+// Unstructured INT4 / INT2: every coordinate stored, value i of a word at bit
+// i * BITS, two's complement, times the token's scale (reference.py:16-20).
+template <int BITS>
+struct LayoutQuant {
+    static constexpr int kPayloadBytes = 16 * BITS, kMetaBytes = 0;
+    static constexpr bool kScale = true;
+    __device__ static void decode(const unsigned char* pay, const unsigned char*, float scale, int lane,
+                                  float (&r)[4]) {
+        constexpr int kPer = 32 / BITS, kSign = 1 << (BITS - 1);
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(pay);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int d = lane + 32 * i;
+            const int c = (w[d / kPer] >> ((d % kPer) * BITS)) & ((1 << BITS) - 1);
+            r[i] = static_cast<float>((c ^ kSign) - kSign) * scale;
+        }
+    }
+};
+
+// Tiled FP16 (STRUCT = false): one 16-bit LSB-first mask per 16-wide tile, values
+// in (tile, ascending coordinate) order.  4:16 structured FP16 (STRUCT = true):
+// four 4-bit in-tile indices per tile (reference.py:37-48).  Metadata word i
+// carries tile 2i in its low and tile 2i+1 in its high half.
+template <int NNZ, bool STRUCT>
+struct LayoutTiled {
+    static constexpr int kPayloadBytes = NNZ * 2, kMetaBytes = 16;
+    static constexpr bool kScale = false;
+    __device__ static void decode(const unsigned char* pay, const unsigned char* meta, float, int lane,
+                                  float (&r)[4]) {
+        const uint4 mw = *reinterpret_cast<const uint4*>(meta);
+        const __half* row = reinterpret_cast<const __half*>(pay);
+        const uint32_t word[4] = {mw.x, mw.y, mw.z, mw.w};
+        const int local = lane & 15, shift = lane & 16;
+        constexpr int kPerTile = NNZ / 8;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t code = (word[i] >> shift) & 0xffffu;
+            const int tile = 2 * i + (lane >> 4);
+            float v = 0.f;
+            if constexpr (STRUCT) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (((code >> (4 * k)) & 15u) == static_cast<uint32_t>(local)) v = __half2float(row[tile * 4 + k]);
+            } else {
+                if ((code >> local) & 1u) v = __half2float(row[tile * kPerTile + __popc(code & ((1u << local) - 1u))]);
+            }
+            r[i] = v;
+        }
+    }
+};
+
+// 1-of-4 structured INT4: 32 signed nibbles + 32 two-bit in-group indices
+// (reference.py:27-36).
+struct LayoutStructInt4 {
+    static constexpr int kPayloadBytes = 16, kMetaBytes = 8;
+    static constexpr bool kScale = true;
+    __device__ static void decode(const unsigned char* pay, const unsigned char* meta, float scale, int lane,
+                                  float (&r)[4]) {
+        const uint4 pw = *reinterpret_cast<const uint4*>(pay);
+        const uint2 mw = *reinterpret_cast<const uint2*>(meta);
+        const uint32_t packed[4] = {pw.x, pw.y, pw.z, pw.w};
+        const uint32_t m[2] = {mw.x, mw.y};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int gi = 8 * i + (lane >> 2);
+            const uint32_t sel = (m[gi >> 4] >> (2 * (gi & 15))) & 3u;
+            const int nib = (packed[gi >> 3] >> (4 * (gi & 7))) & 15;
+            r[i] = (sel == static_cast<uint32_t>(lane & 3)) ? static_cast<float>((nib ^ 8) - 8) * scale : 0.f;
+        }
+    }
+};
+
+template <class L>
+struct Stage {
+    alignas(16) unsigned char kp[kTile * L::kPayloadBytes];
+    alignas(16) unsigned char vp[kTile * L::kPayloadBytes];
+    alignas(16) unsigned char km[kTile * (L::kMetaBytes ? L::kMetaBytes : 1)];
+    alignas(16) unsigned char vm[kTile * (L::kMetaBytes ? L::kMetaBytes : 1)];
+};
+
+// Warp-per-token partial kernel, generic over the residual layout.
+template <int GQA, class L, int CVS>
+__global__ void __launch_bounds__(kThreads, 2) decode_simt_partial_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    constexpr int kStages = (NNZ <= 32) ? 4 : 3;
-    using StageT = Stage<NNZ>;
+    constexpr int kStages = (sizeof(Stage<L>) <= 10240) ? 4 : 3;
+    // metadata rows that are not a multiple of 16 bytes cannot be bulk-copied at every
+    // token offset: such metadata is copied by the threads themselves
+    constexpr bool kMetaBulk = (L::kMetaBytes % 16) == 0;
+    using StageT = Stage<L>;
     StageT* stages = reinterpret_cast<StageT*>(smem_raw);
     __half* kc_s = reinterpret_cast<__half*>(smem_raw + sizeof(StageT) * kStages);
     __shared__ uint64_t full_bar[kStages];
@@ -137,12 +226,14 @@ __global__ void __launch_bounds__(kThreads, 2) decode_bitmap_partial_kernel(cons
     const int ntiles = max(0, tile_end - tile_begin);
 
     const size_t unit_tok = static_cast<size_t>(unit) * p.tok_stride;
-    const uint4* kb_g = p.kb + unit_tok;
-    const uint4* vb_g = p.vb + unit_tok;
-    const __half* kp_g = p.kp + unit_tok * NNZ;
-    const __half* vp_g = p.vp + unit_tok * NNZ;
+    const unsigned char* kp_g = static_cast<const unsigned char*>(p.kp) + unit_tok * L::kPayloadBytes;
+    const unsigned char* vp_g = static_cast<const unsigned char*>(p.vp) + unit_tok * L::kPayloadBytes;
+    const unsigned char* km_g = static_cast<const unsigned char*>(p.kb) + unit_tok * L::kMetaBytes;
+    const unsigned char* vm_g = static_cast<const unsigned char*>(p.vb) + unit_tok * L::kMetaBytes;
     const int8_t* kid_g = p.kid + unit_tok;
     const int8_t* vid_g = p.vid + unit_tok;
+    const __half* ks_g = L::kScale ? p.ks + unit_tok : nullptr;
+    const __half* vs_g = L::kScale ? p.vs + unit_tok : nullptr;
 
     if (tid == 0) {
         timed_out = 0;
@@ -152,21 +243,40 @@ __global__ void __launch_bounds__(kThreads, 2) decode_bitmap_partial_kernel(cons
     __syncthreads();
 
     auto issue = [&](int tile_rel) {
-        // one thread: four bulk copies of tile `tile_rel` into its ring slot
+        // one thread: bulk copies of tile `tile_rel` into its ring slot
         const int t0 = (tile_begin + tile_rel) * kTile;
         const int n = min(kTile, p.tokens - t0);
         StageT& st = stages[tile_rel % kStages];
         uint64_t* bar = &full_bar[tile_rel % kStages];
-        const uint32_t bm_bytes = n * 16u, pl_bytes = n * NNZ * 2u;
-        mbar_arrive_expect_tx(bar, 2 * bm_bytes + 2 * pl_bytes);
-        bulk_g2s(st.kb, kb_g + t0, bm_bytes, bar);
-        bulk_g2s(st.vb, vb_g + t0, bm_bytes, bar);
-        bulk_g2s(st.kp, kp_g + static_cast<size_t>(t0) * NNZ, pl_bytes, bar);
-        bulk_g2s(st.vp, vp_g + static_cast<size_t>(t0) * NNZ, pl_bytes, bar);
+        const uint32_t pl_bytes = n * L::kPayloadBytes;
+        const uint32_t md_bytes = (kMetaBulk && L::kMetaBytes) ? n * L::kMetaBytes : 0u;
+        mbar_arrive_expect_tx(bar, 2 * pl_bytes + 2 * md_bytes);
+        bulk_g2s(st.kp, kp_g + static_cast<size_t>(t0) * L::kPayloadBytes, pl_bytes, bar);
+        bulk_g2s(st.vp, vp_g + static_cast<size_t>(t0) * L::kPayloadBytes, pl_bytes, bar);
+        if (md_bytes) {
+            bulk_g2s(st.km, km_g + static_cast<size_t>(t0) * L::kMetaBytes, md_bytes, bar);
+            bulk_g2s(st.vm, vm_g + static_cast<size_t>(t0) * L::kMetaBytes, md_bytes, bar);
+        }
+    };
+    auto copy_meta = [&](int tile_rel) {
+        // all threads: metadata of tile `tile_rel` with plain 4-byte loads
+        if constexpr (!kMetaBulk && L::kMetaBytes > 0) {
+            if (tile_rel >= ntiles) return;
+            const int t0 = (tile_begin + tile_rel) * kTile;
+            const int words = min(kTile, p.tokens - t0) * (L::kMetaBytes / 4);
+            StageT& st = stages[tile_rel % kStages];
+            const uint32_t* ksrc = reinterpret_cast<const uint32_t*>(km_g + static_cast<size_t>(t0) * L::kMetaBytes);
+            const uint32_t* vsrc = reinterpret_cast<const uint32_t*>(vm_g + static_cast<size_t>(t0) * L::kMetaBytes);
+            for (int i = tid; i < words; i += kThreads) {
+                reinterpret_cast<uint32_t*>(st.km)[i] = __ldg(ksrc + i);
+                reinterpret_cast<uint32_t*>(st.vm)[i] = __ldg(vsrc + i);
+            }
+        }
     };
     if (tid == 0) {
         for (int s = 0; s < kStages && s < ntiles; ++s) issue(s);
     }
+    for (int s = 0; s < kStages; ++s) copy_meta(s);
 
     // key centroid table -> shared memory (FP16, as stored)
     {
@@ -211,25 +321,32 @@ __global__ void __launch_bounds__(kThreads, 2) decode_bitmap_partial_kernel(cons
         for (int i = 0; i < CVS; ++i) bet[h][i] = 0.f;
     }
 
-    // cluster ids of this warp's tokens in the next tile, one token per lane < kTokPerWarp
-    auto load_ids = [&](int tile_rel, int& kid, int& vid) {
+    // ids (and scales) of this warp's tokens in the next tile, one token per lane < kTokPerWarp
+    auto load_ids = [&](int tile_rel, int& kid, int& vid, float& ksc, float& vsc) {
         kid = vid = 0;
+        ksc = vsc = 0.f;
         const int t = (tile_begin + tile_rel) * kTile + warp + kWarps * lane;
         if (tile_rel < ntiles && lane < kTokPerWarp && t < p.tokens) {
             kid = kid_g[t];
             vid = vid_g[t];
+            if constexpr (L::kScale) {
+                ksc = __half2float(ks_g[t]);
+                vsc = __half2float(vs_g[t]);
+            }
         }
     };
     int kid_next, vid_next;
-    load_ids(0, kid_next, vid_next);
-    __syncthreads();  // centroid table ready
+    float ksc_next, vsc_next;
+    load_ids(0, kid_next, vid_next, ksc_next, vsc_next);
+    __syncthreads();  // centroid table (and hand-copied metadata) ready
 
     float rs0 = 0.f, rc0 = 1.f, rs1 = 0.f, rc1 = 1.f;
     bool lost = false;
     for (int it = 0; it < ntiles; ++it) {
         const int t0 = (tile_begin + it) * kTile;
         const int kid_cur = kid_next, vid_cur = vid_next;
-        load_ids(it + 1, kid_next, vid_next);
+        const float ksc_cur = ksc_next, vsc_cur = vsc_next;
+        load_ids(it + 1, kid_next, vid_next, ksc_next, vsc_next);
         if (it % kReseedTiles == 0) {
             const float pos = static_cast<float>(p.start_pos + t0 + warp);
             sincosf(pos * f0, &rs0, &rc0);
@@ -243,9 +360,14 @@ __global__ void __launch_bounds__(kThreads, 2) decode_bitmap_partial_kernel(cons
             if (t0 + tl < p.tokens) {
                 const int kid = __shfl_sync(0xffffffffu, kid_cur, j);
                 const int vid = __shfl_sync(0xffffffffu, vid_cur, j);
+                float ksc = 0.f, vsc = 0.f;
+                if constexpr (L::kScale) {
+                    ksc = __shfl_sync(0xffffffffu, ksc_cur, j);
+                    vsc = __shfl_sync(0xffffffffu, vsc_cur, j);
+                }
                 float kv[4], vr[4];
-                decode4<NNZ>(st.kb[tl], st.kp + tl * NNZ, lane, kv);
-                decode4<NNZ>(st.vb[tl], st.vp + tl * NNZ, lane, vr);
+                L::decode(st.kp + tl * L::kPayloadBytes, st.km + tl * L::kMetaBytes, ksc, lane, kv);
+                L::decode(st.vp + tl * L::kPayloadBytes, st.vm + tl * L::kMetaBytes, vsc, lane, vr);
                 const __half* crow = kc_s + min(max(kid, 0), p.ck - 1) * kHeadDim;
                 kv[0] += __half2float(crow[lane]);
                 kv[1] += __half2float(crow[lane + 32]);
@@ -279,6 +401,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_bitmap_partial_kernel(cons
         }
         __syncthreads();  // every warp is done with this ring slot
         if (tid == 0 && it + kStages < ntiles) issue(it + kStages);
+        copy_meta(it + kStages);
     }
     if (lost && lane == 0) atomicOr(&timed_out, 1u);
 
@@ -438,19 +561,24 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Merge
     p.out[static_cast<size_t>(fq) * kHeadDim + d] = __float2half_rn(num / fmaxf(l, 1e-20f));
 }
 
-template <int GQA, int NNZ, int CVS>
-int launch_partial(const DecodeParams& p, int units, cudaStream_t stream) {
-    constexpr int kStages = (NNZ <= 32) ? 4 : 3;
-    size_t smem = sizeof(Stage<NNZ>) * kStages + static_cast<size_t>(p.ck) * kHeadDim * sizeof(__half);
+template <int GQA, class L, int CVS>
+int launch_simt_cvs(const DecodeParams& p, int units, cudaStream_t stream) {
+    constexpr int kStages = (sizeof(Stage<L>) <= 10240) ? 4 : 3;
+    size_t smem = sizeof(Stage<L>) * kStages + static_cast<size_t>(p.ck) * kHeadDim * sizeof(__half);
     const size_t red_bytes = static_cast<size_t>(kWarps) * GQA * (kHeadDim + 32 * CVS) * sizeof(float);
     if (smem < red_bytes) smem = red_bytes;
-    auto kern = decode_bitmap_partial_kernel<GQA, NNZ, CVS>;
+    auto kern = decode_simt_partial_kernel<GQA, L, CVS>;
     if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  static_cast<int>(smem)),
-                            "cudaFuncSetAttribute(decode_bitmap_partial)"))
+                            "cudaFuncSetAttribute(decode_simt_partial)"))
         return rc;
     kern<<<dim3(p.splits, units), kThreads, smem, stream>>>(p);
-    return check_cuda(cudaGetLastError(), "decode_bitmap_partial launch");
+    return check_cuda(cudaGetLastError(), "decode_simt_partial launch");
+}
+
+template <int GQA, class L>
+int launch_simt(const DecodeParams& p, int units, cudaStream_t s) {
+    return p.cv <= 32 ? launch_simt_cvs<GQA, L, 1>(p, units, s) : launch_simt_cvs<GQA, L, 2>(p, units, s);
 }
 
 template <int GQA, int NNZ>
@@ -470,15 +598,21 @@ int g_variant = 0;
 // optional events recorded right before / after the partial kernel (profiling aid)
 cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;
 
-template <int GQA, int NNZ>
-int dispatch_cvs(const DecodeParams& p, int units, cudaStream_t s) {
-    if (g_variant == 0) return launch_partial_mma<GQA, NNZ>(p, units, s);
-    return p.cv <= 32 ? launch_partial<GQA, NNZ, 1>(p, units, s) : launch_partial<GQA, NNZ, 2>(p, units, s);
-}
+enum LayoutId { kBitmap32, kBitmap64, kQuant4, kQuant2, kTiled64, kStruct32, kStructInt4 };
 
 template <int GQA>
-int dispatch_nnz(const DecodeParams& p, int nnz, int units, cudaStream_t s) {
-    return nnz == 32 ? dispatch_cvs<GQA, 32>(p, units, s) : dispatch_cvs<GQA, 64>(p, units, s);
+int dispatch_layout(const DecodeParams& p, LayoutId layout, int units, cudaStream_t s) {
+    switch (layout) {
+        case kBitmap32:
+            return g_variant == 0 ? launch_partial_mma<GQA, 32>(p, units, s) : launch_simt<GQA, LayoutBitmap<32>>(p, units, s);
+        case kBitmap64:
+            return g_variant == 0 ? launch_partial_mma<GQA, 64>(p, units, s) : launch_simt<GQA, LayoutBitmap<64>>(p, units, s);
+        case kQuant4: return launch_simt<GQA, LayoutQuant<4>>(p, units, s);
+        case kQuant2: return launch_simt<GQA, LayoutQuant<2>>(p, units, s);
+        case kTiled64: return launch_simt<GQA, LayoutTiled<64, false>>(p, units, s);
+        case kStruct32: return launch_simt<GQA, LayoutTiled<32, true>>(p, units, s);
+        default: return launch_simt<GQA, LayoutStructInt4>(p, units, s);
+    }
 }
 
 int pick_splits(int units, int tokens) {
@@ -536,6 +670,106 @@ extern "C" size_t reskv_decode_bitmap_fp16_workspace_bytes(int batch, int kv_hea
     return workspace_bytes(batch * q_heads, splits);
 }
 
+namespace {
+struct DecodeArgs {
+    const void *q, *kc, *kid, *kp, *km, *ks, *vc, *vid, *vp, *vm, *vs;
+    int batch, kv_heads, q_heads, tokens;
+    int64_t tok_stride;
+    int ck, cv, start_pos, pos_q;
+    float theta;
+    const float* inv_freq;
+    float scaling;
+    int splits;
+    const void *rq, *rk, *rv;
+    int recent_tokens;
+    void* workspace;
+    size_t workspace_bytes;
+    void* out;
+    float *out_m, *out_l;
+    void* stream;
+};
+
+int decode_common(const DecodeArgs& a, LayoutId layout, bool has_meta, bool has_scale, const char* who) {
+    if (!a.q || !a.kc || !a.kid || !a.kp || !a.vc || !a.vid || !a.vp || !a.out)
+        return fail(RESKV_ERR_INVALID, "%s: null tensor pointer", who);
+    if (has_meta && (!a.km || !a.vm)) return fail(RESKV_ERR_INVALID, "%s: null metadata pointer", who);
+    if (has_scale && (!a.ks || !a.vs)) return fail(RESKV_ERR_INVALID, "%s: null scale pointer", who);
+    if (a.batch < 1 || a.kv_heads < 1 || a.q_heads < 1 || a.tokens < 1)
+        return fail(RESKV_ERR_INVALID, "%s: batch, heads and tokens must be positive", who);
+    if (a.q_heads % a.kv_heads) return fail(RESKV_ERR_INVALID, "%s: q_heads must be a multiple of kv_heads", who);
+    const int gqa = a.q_heads / a.kv_heads;
+    if (gqa != 1 && gqa != 4 && gqa != 8)
+        return fail(RESKV_ERR_INVALID, "%s: supported query/kv head ratios are 1, 4 and 8, got %d", who, gqa);
+    if (a.ck < 1 || a.ck > kMaxClusters || a.cv < 1 || a.cv > kMaxClusters)
+        return fail(RESKV_ERR_INVALID, "%s: centroid counts must be in [1,64]", who);
+    if (a.tok_stride < a.tokens) return fail(RESKV_ERR_INVALID, "%s: tok_stride < tokens", who);
+    if (a.pos_q < a.start_pos + a.tokens - 1)
+        return fail(RESKV_ERR_INVALID, "%s: query position precedes compressed tokens", who);
+    if (!aligned16(a.kp) || !aligned16(a.vp) || (has_meta && layout != kStructInt4 && (!aligned16(a.km) || !aligned16(a.vm))))
+        return fail(RESKV_ERR_INVALID, "%s: payload and metadata pointers must be 16-byte aligned", who);
+    if ((reinterpret_cast<uintptr_t>(a.kc) & 3u) || (reinterpret_cast<uintptr_t>(a.q) & 1u))
+        return fail(RESKV_ERR_INVALID, "%s: misaligned centroid or query pointer", who);
+    const bool has_recent = a.recent_tokens > 0;
+    if (a.recent_tokens < 0 || (has_recent && (!a.rq || !a.rk || !a.rv)))
+        return fail(RESKV_ERR_INVALID, "%s: recent window needs rotated q, rotated k and v", who);
+    if (a.recent_tokens > kMaxRecent)
+        return fail(RESKV_ERR_LIMIT, "%s: at most %d recent tokens, got %d", who, kMaxRecent, a.recent_tokens);
+
+    const int units = a.batch * a.kv_heads;
+    const int tiles = (a.tokens + kTile - 1) / kTile;
+    int splits = a.splits;
+    if (splits <= 0) splits = pick_splits(units, a.tokens);
+    if (splits > tiles) splits = tiles;
+    const int per = (tiles + splits - 1) / splits;
+    splits = (tiles + per - 1) / per;  // drop splits that would get no tile
+    const size_t need = workspace_bytes(a.batch * a.q_heads, splits);
+    if (!a.workspace || a.workspace_bytes < need)
+        return fail(RESKV_ERR_WORKSPACE, "%s: workspace of %zu bytes needed, %zu given", who, need, a.workspace_bytes);
+
+    const size_t rows = static_cast<size_t>(a.batch) * a.q_heads * splits;
+    float* wsf = reinterpret_cast<float*>(static_cast<unsigned char*>(a.workspace) + kWsHeader);
+    DecodeParams p{};
+    p.q = static_cast<const __half*>(a.q);
+    p.kc = static_cast<const __half*>(a.kc);
+    p.kid = static_cast<const int8_t*>(a.kid);
+    p.kp = a.kp, p.kb = a.km;
+    p.vid = static_cast<const int8_t*>(a.vid);
+    p.vp = a.vp, p.vb = a.vm;
+    p.ks = static_cast<const __half*>(a.ks), p.vs = static_cast<const __half*>(a.vs);
+    p.ws_m = wsf;
+    p.ws_l = wsf + rows;
+    p.ws_delta = wsf + 2 * rows;
+    p.ws_beta = wsf + 2 * rows + rows * kHeadDim;
+    p.status = static_cast<uint32_t*>(a.workspace);
+    p.inv_freq = a.inv_freq;
+    p.tok_stride = a.tok_stride;
+    p.kh = a.kv_heads, p.nh = a.q_heads, p.tokens = a.tokens, p.ck = a.ck, p.cv = a.cv;
+    p.start_pos = a.start_pos, p.pos_q = a.pos_q, p.splits = splits, p.tiles_per_split = per;
+    p.theta = a.theta, p.scaling = a.scaling;
+
+    cudaStream_t s = static_cast<cudaStream_t>(a.stream);
+    if (g_ev_start) cudaEventRecord(g_ev_start, s);
+    int rc = gqa == 1 ? dispatch_layout<1>(p, layout, units, s)
+             : gqa == 4 ? dispatch_layout<4>(p, layout, units, s)
+                        : dispatch_layout<8>(p, layout, units, s);
+    if (rc) return rc;
+    if (g_ev_stop) cudaEventRecord(g_ev_stop, s);
+
+    MergeParams mp{};
+    mp.ws_m = p.ws_m, mp.ws_l = p.ws_l, mp.ws_delta = p.ws_delta, mp.ws_beta = p.ws_beta;
+    mp.vc = static_cast<const __half*>(a.vc);
+    mp.rq = static_cast<const __half*>(a.rq);
+    mp.rk = static_cast<const __half*>(a.rk);
+    mp.rv = static_cast<const __half*>(a.rv);
+    mp.out = static_cast<__half*>(a.out);
+    mp.out_m = a.out_m, mp.out_l = a.out_l;
+    mp.kh = a.kv_heads, mp.nh = a.q_heads, mp.splits = splits, mp.cv = a.cv, mp.tr = a.recent_tokens;
+    mp.scaling = a.scaling;
+    decode_merge_kernel<<<a.batch * a.q_heads, kMergeThreads, 0, s>>>(mp);
+    return check_cuda(cudaGetLastError(), "decode_merge launch");
+}
+}  // namespace
+
 extern "C" int reskv_decode_bitmap_fp16(const void* q, const void* k_centroids, const void* k_ids,
                                         const void* k_payload, const void* k_bitmap, const void* v_centroids,
                                         const void* v_ids, const void* v_payload, const void* v_bitmap, int batch,
@@ -545,84 +779,41 @@ extern "C" int reskv_decode_bitmap_fp16(const void* q, const void* k_centroids, 
                                         const void* recent_k, const void* recent_v, int recent_tokens,
                                         void* workspace, size_t workspace_bytes_given, void* out, float* out_m,
                                         float* out_l, void* stream) {
-    if (!q || !k_centroids || !k_ids || !k_payload || !k_bitmap || !v_centroids || !v_ids || !v_payload ||
-        !v_bitmap || !out)
-        return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: null tensor pointer");
-    if (batch < 1 || kv_heads < 1 || q_heads < 1 || tokens < 1)
-        return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: batch, heads and tokens must be positive");
-    if (q_heads % kv_heads) return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: q_heads must be a multiple of kv_heads");
-    const int gqa = q_heads / kv_heads;
-    if (gqa != 1 && gqa != 4 && gqa != 8)
-        return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: supported query/kv head ratios are 1, 4 and 8, got %d", gqa);
     if (nnz != 32 && nnz != 64) return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: nnz must be 32 or 64, got %d", nnz);
-    if (k_clusters < 1 || k_clusters > kMaxClusters || v_clusters < 1 || v_clusters > kMaxClusters)
-        return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: centroid counts must be in [1,64]");
-    if (tok_stride < tokens) return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: tok_stride < tokens");
-    if (pos_q < start_pos + tokens - 1)
-        return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: query position precedes compressed tokens");
-    if (!aligned16(k_payload) || !aligned16(v_payload) || !aligned16(k_bitmap) || !aligned16(v_bitmap))
-        return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: payload and bitmap pointers must be 16-byte aligned");
-    if ((reinterpret_cast<uintptr_t>(k_centroids) & 3u) || (reinterpret_cast<uintptr_t>(q) & 1u))
-        return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: misaligned centroid or query pointer");
-    const bool has_recent = recent_tokens > 0;
-    if (recent_tokens < 0 || (has_recent && (!recent_q || !recent_k || !recent_v)))
-        return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16: recent window needs rotated q, rotated k and v");
-    if (recent_tokens > kMaxRecent)
-        return fail(RESKV_ERR_LIMIT, "decode_bitmap_fp16: at most %d recent tokens, got %d", kMaxRecent, recent_tokens);
+    const DecodeArgs a{q, k_centroids, k_ids, k_payload, k_bitmap, nullptr, v_centroids, v_ids, v_payload, v_bitmap,
+                       nullptr, batch, kv_heads, q_heads, tokens, tok_stride, k_clusters, v_clusters, start_pos, pos_q,
+                       rope_theta, inv_freq, scaling, splits, recent_q, recent_k, recent_v, recent_tokens, workspace,
+                       workspace_bytes_given, out, out_m, out_l, stream};
+    return decode_common(a, nnz == 32 ? kBitmap32 : kBitmap64, true, false, "decode_bitmap_fp16");
+}
 
-    const int units = batch * kv_heads;
-    const int tiles = (tokens + kTile - 1) / kTile;
-    if (splits <= 0) splits = pick_splits(units, tokens);
-    if (splits > tiles) splits = tiles;
-    int per = (tiles + splits - 1) / splits;
-    splits = (tiles + per - 1) / per;  // drop splits that would get no tile
-    const size_t need = workspace_bytes(batch * q_heads, splits);
-    if (!workspace || workspace_bytes_given < need)
-        return fail(RESKV_ERR_WORKSPACE, "decode_bitmap_fp16: workspace of %zu bytes needed, %zu given", need,
-                    workspace_bytes_given);
-
-    const size_t rows = static_cast<size_t>(batch) * q_heads * splits;
-    float* wsf = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + kWsHeader);
-    DecodeParams p{};
-    p.q = static_cast<const __half*>(q);
-    p.kc = static_cast<const __half*>(k_centroids);
-    p.kid = static_cast<const int8_t*>(k_ids);
-    p.kp = static_cast<const __half*>(k_payload);
-    p.kb = static_cast<const uint4*>(k_bitmap);
-    p.vid = static_cast<const int8_t*>(v_ids);
-    p.vp = static_cast<const __half*>(v_payload);
-    p.vb = static_cast<const uint4*>(v_bitmap);
-    p.ws_m = wsf;
-    p.ws_l = wsf + rows;
-    p.ws_delta = wsf + 2 * rows;
-    p.ws_beta = wsf + 2 * rows + rows * kHeadDim;
-    p.status = static_cast<uint32_t*>(workspace);
-    p.inv_freq = inv_freq;
-    p.tok_stride = tok_stride;
-    p.kh = kv_heads, p.nh = q_heads, p.tokens = tokens, p.ck = k_clusters, p.cv = v_clusters;
-    p.start_pos = start_pos, p.pos_q = pos_q, p.splits = splits, p.tiles_per_split = per;
-    p.theta = rope_theta, p.scaling = scaling;
-
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (g_ev_start) cudaEventRecord(g_ev_start, s);
-    int rc = gqa == 1 ? dispatch_nnz<1>(p, nnz, units, s)
-             : gqa == 4 ? dispatch_nnz<4>(p, nnz, units, s)
-                        : dispatch_nnz<8>(p, nnz, units, s);
-    if (rc) return rc;
-    if (g_ev_stop) cudaEventRecord(g_ev_stop, s);
-
-    MergeParams mp{};
-    mp.ws_m = p.ws_m, mp.ws_l = p.ws_l, mp.ws_delta = p.ws_delta, mp.ws_beta = p.ws_beta;
-    mp.vc = static_cast<const __half*>(v_centroids);
-    mp.rq = static_cast<const __half*>(recent_q);
-    mp.rk = static_cast<const __half*>(recent_k);
-    mp.rv = static_cast<const __half*>(recent_v);
-    mp.out = static_cast<__half*>(out);
-    mp.out_m = out_m, mp.out_l = out_l;
-    mp.kh = kv_heads, mp.nh = q_heads, mp.splits = splits, mp.cv = v_clusters, mp.tr = recent_tokens;
-    mp.scaling = scaling;
-    decode_merge_kernel<<<batch * q_heads, kMergeThreads, 0, s>>>(mp);
-    return check_cuda(cudaGetLastError(), "decode_merge launch");
+extern "C" int reskv_decode_packed(int layout, int bits, const void* q, const void* k_centroids, const void* k_ids,
+                                   const void* k_payload, const void* k_meta, const void* k_scale,
+                                   const void* v_centroids, const void* v_ids, const void* v_payload,
+                                   const void* v_meta, const void* v_scale, int batch, int kv_heads, int q_heads,
+                                   int tokens, int64_t tok_stride, int k_clusters, int v_clusters, int start_pos,
+                                   int pos_q, float rope_theta, const float* inv_freq, float scaling, int splits,
+                                   const void* recent_q, const void* recent_k, const void* recent_v, int recent_tokens,
+                                   void* workspace, size_t workspace_bytes_given, void* out, float* out_m,
+                                   float* out_l, void* stream) {
+    LayoutId id;
+    bool meta = true, scale = false;
+    if (layout == RESKV_LAYOUT_UNSTRUCTURED && (bits == 4 || bits == 2)) {
+        id = bits == 4 ? kQuant4 : kQuant2, meta = false, scale = true;
+    } else if (layout == RESKV_LAYOUT_TILED && bits == 16) {
+        id = kTiled64;
+    } else if (layout == RESKV_LAYOUT_STRUCTURED && bits == 16) {
+        id = kStruct32;
+    } else if (layout == RESKV_LAYOUT_STRUCTURED && bits == 4) {
+        id = kStructInt4, scale = true;
+    } else {
+        return fail(RESKV_ERR_INVALID, "decode_packed: no kernel for layout %d with %d-bit residuals", layout, bits);
+    }
+    const DecodeArgs a{q, k_centroids, k_ids, k_payload, k_meta, k_scale, v_centroids, v_ids, v_payload, v_meta,
+                       v_scale, batch, kv_heads, q_heads, tokens, tok_stride, k_clusters, v_clusters, start_pos, pos_q,
+                       rope_theta, inv_freq, scaling, splits, recent_q, recent_k, recent_v, recent_tokens, workspace,
+                       workspace_bytes_given, out, out_m, out_l, stream};
+    return decode_common(a, id, meta, scale, "decode_packed");
 }
 
 static int merge_recent_common(const void* comp_out, const float* comp_m, const float* comp_l, const float* scores,

@@ -178,10 +178,10 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_bitmap_mma_kernel(const D
     const int ntiles = max(0, min(total_tiles, tile_begin + p.tiles_per_split) - tile_begin);
 
     const size_t unit_tok = static_cast<size_t>(unit) * p.tok_stride;
-    const uint4* kb_g = p.kb + unit_tok;
-    const uint4* vb_g = p.vb + unit_tok;
-    const __half* kp_g = p.kp + unit_tok * NNZ;
-    const __half* vp_g = p.vp + unit_tok * NNZ;
+    const uint4* kb_g = static_cast<const uint4*>(p.kb) + unit_tok;
+    const uint4* vb_g = static_cast<const uint4*>(p.vb) + unit_tok;
+    const __half* kp_g = static_cast<const __half*>(p.kp) + unit_tok * NNZ;
+    const __half* vp_g = static_cast<const __half*>(p.vp) + unit_tok * NNZ;
     const int8_t* kid_g = p.kid + unit_tok;
     const int8_t* vid_g = p.vid + unit_tok;
 
