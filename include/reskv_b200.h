@@ -105,6 +105,42 @@ int reskv_decode_packed(int layout, int bits, const void* q, const void* k_centr
                         const void* recent_q, const void* recent_k, const void* recent_v, int recent_tokens,
                         void* workspace, size_t workspace_bytes, void* out, float* out_m, float* out_l, void* stream);
 
+/* ---- decode attention for callers that cannot provide scratch memory -------------------
+ * No counterpart in the reference (its ops allocate their partial buffers with
+ * torch::empty on every call, cluster_mass.cu:1222-1232).
+ *
+ * Same computation, arguments and results as reskv_decode_bitmap_fp16, minus the
+ * workspace: the split-K partials go to a fixed RESKV_NOALLOC_SCRATCH_BYTES array
+ * that is part of the library image, so neither the caller nor the library calls
+ * cudaMalloc / cudaFree (or any allocator) on this path.  It is meant for hosts
+ * that have no allocator to offer at the call site: an inference server that gave
+ * all device memory to its own pool at start-up, a plug-in invoked from a latency-
+ * critical loop where an allocation would serialise the device, or a C / C++ /
+ * cgo host that links the library without torch's caching allocator.
+ *
+ *   - Limit: batch * q_heads * splits * 776 + 256 bytes must fit the array
+ *     (8 MiB: e.g. 1024 query heads x 10 splits).  Larger problems are refused
+ *     with RESKV_ERR_LIMIT and a message; pass a smaller `splits` or use the
+ *     workspace variant.
+ *   - Every GPU on which the library is loaded holds the array until exit.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress) and keeps it; make that first call outside any
+ *     stream capture.
+ *   - All calls on a device share the array and it keeps the last call's contents;
+ *     the call clears the 256-byte status header itself.  Two calls whose kernels
+ *     can overlap on the GPU (different streams, or graphs replayed concurrently)
+ *     race on it: serialise them. */
+#define RESKV_NOALLOC_SCRATCH_BYTES (8 * 1024 * 1024)
+
+int reskv_decode_bitmap_fp16_noalloc(const void* q, const void* k_centroids, const void* k_ids,
+                                     const void* k_payload, const void* k_bitmap, const void* v_centroids,
+                                     const void* v_ids, const void* v_payload, const void* v_bitmap, int batch,
+                                     int kv_heads, int q_heads, int tokens, int64_t tok_stride, int k_clusters,
+                                     int v_clusters, int nnz, int start_pos, int pos_q, float rope_theta,
+                                     const float* inv_freq, float scaling, int splits, const void* recent_q,
+                                     const void* recent_k, const void* recent_v, int recent_tokens, void* out,
+                                     float* out_m, float* out_l, void* stream);
+
 /* Selects the partial kernel reskv_decode_bitmap_fp16 launches: 0 = tensor-core
  * tiles of 16 tokens (default), 1 = the simpler warp-per-token kernel (kept for
  * cross-checking).  Process-wide; no counterpart in the reference. */

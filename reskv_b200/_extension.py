@@ -45,6 +45,10 @@ SIGNATURES = {
         _I,
         [_I, _I] + [_P] * 11 + [_I, _I, _I, _I, _L, _I, _I, _I, _I, _F, _P, _F, _I, _P, _P, _P, _I, _P, _Z, _P, _P, _P, _P],
     ),
+    "reskv_decode_bitmap_fp16_noalloc": (
+        _I,
+        [_P] * 9 + [_I, _I, _I, _I, _L, _I, _I, _I, _I, _I, _F, _P, _F, _I, _P, _P, _P, _I, _P, _P, _P, _P],
+    ),
     "reskv_decode_auto_splits": (_I, [_I, _I, _I]),
     "reskv_decode_set_variant": (_I, [_I]),
     "reskv_decode_set_timing_events": (_I, [_P, _P]),

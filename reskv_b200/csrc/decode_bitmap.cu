@@ -816,6 +816,73 @@ extern "C" int reskv_decode_packed(int layout, int bits, const void* q, const vo
     return decode_common(a, id, meta, scale, "decode_packed");
 }
 
+// ---- decode without any caller- or library-side allocation -----------------------------
+// Scratch for the split partials lives in this fixed array inside the library image.
+// Every GPU that loads the library carries it until the process exits.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[RESKV_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+// Device address of g_noalloc_scratch on the current device.  In host code the
+// array's name is only a handle for the runtime, not something a kernel can
+// dereference, so the address is looked up once per device (with that device
+// current) and remembered.
+int noalloc_scratch_address(void** out) {
+    static void* cached[64] = {nullptr};
+    int dev = 0;
+    if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+    if (dev < 0 || dev >= 64) return fail(RESKV_ERR_LIMIT, "decode_bitmap_fp16_noalloc: device index %d not supported", dev);
+    if (!cached[dev]) {
+        void* ptr = nullptr;
+        if (int rc = check_cuda(cudaGetSymbolAddress(&ptr, g_noalloc_scratch),
+                                "cudaGetSymbolAddress(built-in decode scratch)"))
+            return rc;
+        cached[dev] = ptr;
+    }
+    *out = cached[dev];
+    return RESKV_OK;
+}
+}  // namespace
+
+extern "C" int reskv_decode_bitmap_fp16_noalloc(const void* q, const void* k_centroids, const void* k_ids,
+                                                const void* k_payload, const void* k_bitmap,
+                                                const void* v_centroids, const void* v_ids, const void* v_payload,
+                                                const void* v_bitmap, int batch, int kv_heads, int q_heads,
+                                                int tokens, int64_t tok_stride, int k_clusters, int v_clusters,
+                                                int nnz, int start_pos, int pos_q, float rope_theta,
+                                                const float* inv_freq, float scaling, int splits,
+                                                const void* recent_q, const void* recent_k, const void* recent_v,
+                                                int recent_tokens, void* out, float* out_m, float* out_l,
+                                                void* stream) {
+    if (batch < 1 || kv_heads < 1 || q_heads < 1 || tokens < 1)
+        return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16_noalloc: batch, heads and tokens must be positive");
+    if (nnz != 32 && nnz != 64)
+        return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16_noalloc: nnz must be 32 or 64, got %d", nnz);
+    // the same split arithmetic as the allocating entry point, to size the scratch first
+    const int tiles = (tokens + kTile - 1) / kTile;
+    int eff = splits > 0 ? splits : pick_splits(batch * kv_heads, tokens);
+    if (eff > tiles) eff = tiles;
+    const int per = (tiles + eff - 1) / eff;
+    eff = (tiles + per - 1) / per;
+    const size_t need = workspace_bytes(batch * q_heads, eff);
+    if (need > static_cast<size_t>(RESKV_NOALLOC_SCRATCH_BYTES))
+        return fail(RESKV_ERR_LIMIT,
+                    "decode_bitmap_fp16_noalloc: %d query heads x %d splits need %zu bytes of scratch, the built-in "
+                    "array holds %d; pass fewer splits or call reskv_decode_bitmap_fp16 with your own workspace",
+                    batch * q_heads, eff, need, RESKV_NOALLOC_SCRATCH_BYTES);
+    void* scratch = nullptr;
+    if (int rc = noalloc_scratch_address(&scratch)) return rc;
+    // the array still holds the previous call's data; only the status header has to start at zero
+    // (every partial slot that the merge reads is written by this call's partial kernel first)
+    if (int rc = check_cuda(cudaMemsetAsync(scratch, 0, kWsHeader, static_cast<cudaStream_t>(stream)),
+                            "cudaMemsetAsync(built-in decode scratch header)"))
+        return rc;
+    const DecodeArgs a{q, k_centroids, k_ids, k_payload, k_bitmap, nullptr, v_centroids, v_ids, v_payload, v_bitmap,
+                       nullptr, batch, kv_heads, q_heads, tokens, tok_stride, k_clusters, v_clusters, start_pos, pos_q,
+                       rope_theta, inv_freq, scaling, splits, recent_q, recent_k, recent_v, recent_tokens, scratch,
+                       static_cast<size_t>(RESKV_NOALLOC_SCRATCH_BYTES), out, out_m, out_l, stream};
+    return decode_common(a, nnz == 32 ? kBitmap32 : kBitmap64, true, false, "decode_bitmap_fp16_noalloc");
+}
+
 static int merge_recent_common(const void* comp_out, const float* comp_m, const float* comp_l, const float* scores,
                                const void* rq, const void* rk, const void* rv, int batch, int kv_heads, int q_heads,
                                int recent_tokens, float scaling, void* merged, void* stream, const char* who) {
