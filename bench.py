@@ -54,7 +54,7 @@ NCU_TRAFFIC_BYTES = {}
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--steps", type=int, default=512)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=32)
@@ -62,6 +62,8 @@ def parse():
     ap.add_argument("--sparsity", type=float, default=0.75)
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep", action="store_true",
+                    help="also time attention and a prefill compression at batch 1/4/8/16/32 (extra key 'sweep')")
     return ap.parse_args()
 
 
@@ -155,33 +157,59 @@ def run_reference(a):
 
 # ---- GPU arm -------------------------------------------------------------------------
 class ClockSampler:
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """Samples SM clocks and throttle reasons with nvidia-smi in the background.
+
+    Started early (nvidia-smi takes a moment to come up); ``mark()`` brackets the
+    timed region and ``summary()`` only uses samples whose timestamp lies inside."""
+
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
         self.index, self.proc, self.path = index, None, f"/tmp/reskv_clocks_{os.getpid()}.csv"
+        self.t0 = self.t1 = None
 
-    def __enter__(self):
+    def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
         return self
 
-    def __exit__(self, *exc):
+    def mark(self):
+        import datetime
+
+        now = datetime.datetime.now()
+        if self.t0 is None:
+            self.t0 = now
+        else:
+            self.t1 = now
+
+    def stop(self):
         if self.proc:
             self.proc.terminate()
             self.proc.wait()
+            self.proc = None
 
     def summary(self):
-        sm, smax, reasons = [], [], set()
+        import datetime
+
+        self.stop()
+        sm, smax, reasons, total = [], [], set(), 0
         try:
             for row in open(self.path):
                 f = [x.strip() for x in row.split(",")]
                 if len(f) < 9:
+                    continue
+                total += 1
+                try:
+                    ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f")
+                except ValueError:
+                    continue
+                if self.t0 and self.t1 and not (self.t0 <= ts <= self.t1):
                     continue
                 sm.append(float(f[1]))
                 smax.append(float(f[2]))
@@ -192,9 +220,9 @@ class ClockSampler:
         except (OSError, ValueError):
             pass
         if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "samples_total": total}
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "samples_total": total}
 
 
 def rope(x, pos, inv_freq):
@@ -205,6 +233,49 @@ def rope(x, pos, inv_freq):
     cos, sin = torch.cos(ang), torch.sin(ang)
     a, b = x.float()[..., :64], x.float()[..., 64:]
     return torch.cat((a * cos - b * sin, b * cos + a * sin), dim=-1).to(x.dtype)
+
+
+def run_sweep(a, dev, cfg, inv_freq, nnz):
+    """Attention kernel time and prefill compression time per batch size (CUDA events, 20 calls each)."""
+    import torch
+
+    import reskv_b200._extension as ext
+    from reskv_b200 import attention, compress
+    from reskv_b200.synthetic import gaussian, mixture
+
+    lib = ext.library()
+    out = []
+    for batch in (1, 4, 8, 16, 32):
+        k = mixture(batch, H_KV, a.context, seed=7, device=dev)
+        v = mixture(batch, H_KV, a.context, seed=8, device=dev)
+        n = (a.context - RECENT) // GROUP * GROUP
+        kc, vc = k[:, :, :n].contiguous(), v[:, :, :n].contiguous()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        compress(kc, vc, cfg)  # warm-up
+        ev[0].record()
+        cache = compress(kc, vc, cfg)
+        ev[1].record()
+        q = gaussian(batch, H_Q, 1, DIM, seed=9, device=dev)
+        qr = rope(q, a.context, inv_freq)
+        kr, vr = k[:, :, n:].contiguous(), v[:, :, n:].contiguous()
+        for e in ev[2:]:
+            e.record()
+        times = []
+        for i in range(24):
+            lib.reskv_decode_set_timing_events(ev[2].cuda_event, ev[3].cuda_event)
+            attention(q, cache, position=a.context, inv_freq=inv_freq, recent=(qr, kr, vr))
+            lib.reskv_decode_set_timing_events(None, None)
+            torch.cuda.synchronize()
+            if i >= 4:
+                times.append(ev[2].elapsed_time(ev[3]))
+        torch.cuda.synchronize()
+        ms = statistics.median(times)
+        nbytes = algorithmic_bytes(batch, n, a.context - n, nnz, CLUSTERS, CLUSTERS)
+        out.append({"batch": batch, "attention_partial_kernel_ms": ms, "GBps": nbytes / ms / 1e6,
+                    "splits": lib.reskv_decode_auto_splits(batch, H_KV, n),
+                    "prefill_cluster_and_compress_ms": ev[0].elapsed_time(ev[1])})
+        del k, v, kc, vc, cache
+    return out
 
 
 def run_gpu(a):
@@ -224,6 +295,7 @@ def run_gpu(a):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     ext.library()  # fail loudly if the native library is missing
+    clocks = ClockSampler(local).start()
 
     B, K, W = a.batch, a.steps, a.warmup
     nnz = int(128 * (1 - a.sparsity))
@@ -301,12 +373,13 @@ def run_gpu(a):
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = ext.launch_count
     barrier()
-    with ClockSampler(local) as clocks:
-        start.record()
-        for i in range(W, W + K):
-            step(q_all[i], k_new[i], v_new[i], True, q_rot[i], k_rot[i])
-        stop.record()
-        barrier()
+    clocks.mark()
+    start.record()
+    for i in range(W, W + K):
+        step(q_all[i], k_new[i], v_new[i], True, q_rot[i], k_rot[i])
+    stop.record()
+    barrier()
+    clocks.mark()
     launches = ext.launch_count - launches0
     ms_total = start.elapsed_time(stop)
     att_ms = sum(s.elapsed_time(e) for s, e in att_events)
@@ -331,6 +404,10 @@ def run_gpu(a):
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms_total, ms_e2e, att_ms_max = times.tolist()
 
+    sweep = None
+    if a.sweep and world == 1:
+        sweep = run_sweep(a, dev, cfg, inv_freq, nnz)
+    clock_summary = clocks.summary()
     if rank == 0:
         peaks = {}
         try:
@@ -350,7 +427,7 @@ def run_gpu(a):
                        "l2": "inputs larger than L2 (compressed cache %.0f MB per step)" % (
                            state["bytes"] / state["calls"] / 1e6),
                        "sharding": "independent (sequence x KV-head) units per GPU, no collective"},
-            "clocks": clocks.summary(),
+            "clocks": clock_summary,
             "e2e": {"value": world * B * K / (ms_e2e * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": int(host_q[0].nbytes + host_k[0].nbytes + host_v[0].nbytes),
                     "d2h_bytes_per_step": int(host_out.nbytes)},
@@ -366,6 +443,8 @@ def run_gpu(a):
             "phases_ms_per_step": {"attention": att_ms / K, "cache_update_incl_group_compression": upd_ms / K,
                                    "prefill_cluster_and_compress_ms": prefill_compress_ms},
         }
+        if sweep is not None:
+            line["sweep"] = sweep
         if world == 1 and not a.no_cpu_baseline:
             value, sample = cpu_attention_sample(a, a.cpu_seconds)
             line["cpu_baseline"] = {"value": value, "unit": UNIT, "cores": cpu_cores(), "kind": "port",

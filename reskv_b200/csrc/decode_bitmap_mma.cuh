@@ -300,8 +300,14 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_bitmap_mma_kernel(const D
     // cluster ids of this warp's 16 tokens of the next tile: lanes 0..15 key ids, 16..31 value ids
     auto load_ids = [&](int tile_rel) -> int {
         const int t = (tile_begin + tile_rel) * kTileM + warp * 16 + (lane & 15);
-        if (tile_rel < ntiles && t < p.tokens) return (lane < 16) ? kid_g[t] : vid_g[t];
-        return 0;
+        int id = 0;
+        if (tile_rel < ntiles && t < p.tokens) {
+            // volatile: issue the load here, a whole tile ahead of its use, instead of letting the
+            // compiler sink it next to the consumer
+            const int8_t* src = ((lane < 16) ? kid_g : vid_g) + t;
+            asm volatile("ld.global.nc.s8 %0, [%1];" : "=r"(id) : "l"(src));
+        }
+        return id;
     };
     int ids_next = load_ids(0);
     __syncthreads();  // tables and first query tile ready
@@ -420,6 +426,29 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_bitmap_mma_kernel(const D
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i) sc[i] += sc2[i] + sc3[i];
+            // ================= values: tokens 2q, 2q+1, 2q+8, 2q+9; coordinates [16g, 16g+16) =================
+            uint32_t v01[16], v23[16];  // (token 2q | token 2q+1 << 16), (2q+8 | 2q+9 << 16) per coordinate
+            {
+                const unsigned char* vb_bytes = reinterpret_cast<const unsigned char*>(st.vb);
+                const unsigned char* pv_bytes = reinterpret_cast<const unsigned char*>(pre_v);
+                const int off = field_offset(g);
+                const int r0 = 2 * qd, r1 = 2 * qd + 1, r2 = 2 * qd + 8, r3 = 2 * qd + 9;
+                const int tk0 = warp * 16 + r0, tk1 = warp * 16 + r1, tk2 = warp * 16 + r2, tk3 = warp * 16 + r3;
+                const uint32_t f0 = r0 < nvalid ? *reinterpret_cast<const unsigned short*>(vb_bytes + tk0 * 16 + off) : 0u;
+                const uint32_t f1 = r1 < nvalid ? *reinterpret_cast<const unsigned short*>(vb_bytes + tk1 * 16 + off) : 0u;
+                const uint32_t f2 = r2 < nvalid ? *reinterpret_cast<const unsigned short*>(vb_bytes + tk2 * 16 + off) : 0u;
+                const uint32_t f3 = r3 < nvalid ? *reinterpret_cast<const unsigned short*>(vb_bytes + tk3 * 16 + off) : 0u;
+                const __half* p0 = st.vp + tk0 * NNZ + pv_bytes[r0 * 8 + g];
+                const __half* p1 = st.vp + tk1 * NNZ + pv_bytes[r1 * 8 + g];
+                const __half* p2 = st.vp + tk2 * NNZ + pv_bytes[r2 * 8 + g];
+                const __half* p3 = st.vp + tk3 * NNZ + pv_bytes[r3 * 8 + g];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    v01[e] = walk16(f0, e, p0) | (walk16(f1, e, p1) << 16);
+                    v23[e] = walk16(f2, e, p2) | (walk16(f3, e, p3) << 16);
+                }
+            }
+
             // sc: c0,c1 = (token g, heads 2q, 2q+1), c2,c3 = (token g+8, ...), log2 domain
             if (!okA) sc[0] = sc[1] = -INFINITY;
             if (!okB) sc[2] = sc[3] = -INFINITY;
@@ -479,30 +508,9 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_bitmap_mma_kernel(const D
             const uint32_t pb0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p01));
             const uint32_t pb1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p23));
 
-            // ================= values: tokens 2q, 2q+1, 2q+8, 2q+9; coordinates [16g, 16g+16) =================
-            {
-                const unsigned char* vb_bytes = reinterpret_cast<const unsigned char*>(st.vb);
-                const unsigned char* pv_bytes = reinterpret_cast<const unsigned char*>(pre_v);
-                const int off = field_offset(g);
-                const int r0 = 2 * qd, r1 = 2 * qd + 1, r2 = 2 * qd + 8, r3 = 2 * qd + 9;
-                const int tk0 = warp * 16 + r0, tk1 = warp * 16 + r1, tk2 = warp * 16 + r2, tk3 = warp * 16 + r3;
-                const uint32_t f0 = r0 < nvalid ? *reinterpret_cast<const unsigned short*>(vb_bytes + tk0 * 16 + off) : 0u;
-                const uint32_t f1 = r1 < nvalid ? *reinterpret_cast<const unsigned short*>(vb_bytes + tk1 * 16 + off) : 0u;
-                const uint32_t f2 = r2 < nvalid ? *reinterpret_cast<const unsigned short*>(vb_bytes + tk2 * 16 + off) : 0u;
-                const uint32_t f3 = r3 < nvalid ? *reinterpret_cast<const unsigned short*>(vb_bytes + tk3 * 16 + off) : 0u;
-                const __half* p0 = st.vp + tk0 * NNZ + pv_bytes[r0 * 8 + g];
-                const __half* p1 = st.vp + tk1 * NNZ + pv_bytes[r1 * 8 + g];
-                const __half* p2 = st.vp + tk2 * NNZ + pv_bytes[r2 * 8 + g];
-                const __half* p3 = st.vp + tk3 * NNZ + pv_bytes[r3 * 8 + g];
-                uint32_t v01[16], v23[16];  // (token 2q | token 2q+1 << 16), (2q+8 | 2q+9 << 16) per coordinate
+            // O^T += Vres^T . P
 #pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    v01[e] = walk16(f0, e, p0) | (walk16(f1, e, p1) << 16);
-                    v23[e] = walk16(f2, e, p2) | (walk16(f3, e, p3) << 16);
-                }
-#pragma unroll
-                for (int i = 0; i < 8; ++i) mma_16816(acc[i], v01[i], v01[8 + i], v23[i], v23[8 + i], pb0, pb1);
-            }
+            for (int i = 0; i < 8; ++i) mma_16816(acc[i], v01[i], v01[8 + i], v23[i], v23[8 + i], pb0, pb1);
             __syncwarp();  // rank-base table is rewritten next tile
         }
         if (it + 1 < ntiles) write_query(it + 1);
