@@ -48,7 +48,10 @@ UNIT = "tok/s (one decoder attention layer: cache update + fused compressed atte
 
 # DRAM bytes per launch of the dominant kernel from the committed ncu capture
 # (profiles/), keyed by workload name; None until a capture exists.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    # profiles/decode_bitmap_mma_b32_ctx8192_s075.md: dram__bytes_read.sum + dram__bytes_write.sum of one launch
+    "llama31-8b-layer attn decode ctx8192 b32 s0.75 fp16 unstructured": 339.5e6 + 8.4e6,
+}
 
 
 def parse():
