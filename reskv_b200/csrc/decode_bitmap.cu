@@ -25,44 +25,10 @@
 // Kernel 2 (merge): one CTA per query head reduces the split partials, applies
 // the value centroids, and -- when a dense recent window is given -- folds its
 // tokens into the same softmax.
-#include "common.cuh"
+#include "decode_common.cuh"
 
 namespace reskv {
 namespace {
-
-constexpr int kTile = 64;    // tokens per pipeline stage
-constexpr int kWarps = 8;    // warps per CTA
-constexpr int kThreads = kWarps * 32;
-constexpr int kTokPerWarp = kTile / kWarps;
-constexpr int kReseedTiles = 16;
-constexpr int kWsHeader = 256;  // bytes reserved at the start of the workspace (status word)
-
-struct DecodeParams {
-    const __half* q;
-    const __half* kc;
-    const int8_t* kid;
-    const void* kp;   // payload rows
-    const void* kb;   // metadata rows (bitmaps, tile masks / indices) or null
-    const int8_t* vid;
-    const void* vp;
-    const void* vb;
-    const __half* ks;  // per-token scales of quantised layouts or null
-    const __half* vs;
-    float* ws_m;
-    float* ws_l;
-    float* ws_delta;
-    float* ws_beta;
-    uint32_t* status;
-    const float* inv_freq;
-    int64_t tok_stride;
-    int kh, nh, tokens, ck, cv;
-    int start_pos, pos_q, splits, tiles_per_split;
-    float theta, scaling;
-};
-
-__device__ __forceinline__ float rope_freq(const float* inv_freq, float theta, int i) {
-    return inv_freq ? inv_freq[i] : powf(theta, -static_cast<float>(i) / 64.0f);
-}
 
 // Sum GQA per-lane partials over the warp; every lane ends with all totals.
 template <int GQA>
@@ -454,7 +420,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_simt_partial_kernel(const 
     if (tid == 0 && timed_out) atomicOr(p.status, RESKV_STATUS_WAIT_TIMEOUT);
 }
 
-#include "decode_bitmap_mma.cuh"
+#include "decode_mma.cuh"
 
 // ---- merge -----------------------------------------------------------------------
 struct MergeParams {
@@ -583,8 +549,9 @@ int launch_simt(const DecodeParams& p, int units, cudaStream_t s) {
 
 template <int GQA, int NNZ>
 int launch_partial_mma(const DecodeParams& p, int units, cudaStream_t stream) {
-    const size_t smem = mma::smem_bytes<GQA, NNZ>(p.ck);
-    auto kern = mma::decode_bitmap_mma_kernel<GQA, NNZ>;
+    using ML = mma::LayoutMmaBitmap<NNZ>;
+    const size_t smem = mma::smem_bytes<GQA, ML>(p.ck);
+    auto kern = mma::decode_mma_kernel<GQA, ML>;
     if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  static_cast<int>(smem)),
                             "cudaFuncSetAttribute(decode_bitmap_mma)"))
@@ -607,11 +574,22 @@ int dispatch_layout(const DecodeParams& p, LayoutId layout, int units, cudaStrea
             return g_variant == 0 ? launch_partial_mma<GQA, 32>(p, units, s) : launch_simt<GQA, LayoutBitmap<32>>(p, units, s);
         case kBitmap64:
             return g_variant == 0 ? launch_partial_mma<GQA, 64>(p, units, s) : launch_simt<GQA, LayoutBitmap<64>>(p, units, s);
-        case kQuant4: return launch_simt<GQA, LayoutQuant<4>>(p, units, s);
-        case kQuant2: return launch_simt<GQA, LayoutQuant<2>>(p, units, s);
-        case kTiled64: return launch_simt<GQA, LayoutTiled<64, false>>(p, units, s);
-        case kStruct32: return launch_simt<GQA, LayoutTiled<32, true>>(p, units, s);
-        default: return launch_simt<GQA, LayoutStructInt4>(p, units, s);
+        case kQuant4:
+            return g_variant == 0 ? launch_packed_mma(p, 0, GQA, units, s) : launch_simt<GQA, LayoutQuant<4>>(p, units, s);
+        case kQuant2:
+            return g_variant == 0 ? launch_packed_mma(p, 1, GQA, units, s) : launch_simt<GQA, LayoutQuant<2>>(p, units, s);
+        case kTiled64:
+            return g_variant == 0 ? launch_packed_mma(p, 2, GQA, units, s)
+                                  : launch_simt<GQA, LayoutTiled<64, false>>(p, units, s);
+        case kStruct32:
+            return g_variant == 0 ? launch_packed_mma(p, 3, GQA, units, s)
+                                  : launch_simt<GQA, LayoutTiled<32, true>>(p, units, s);
+        default: {
+            // 8-byte metadata rows can only be bulk-copied when every tile starts 16-byte aligned
+            const bool bulk_ok = p.tokens % 2 == 0 && p.tok_stride % 2 == 0 && aligned16(p.kb) && aligned16(p.vb);
+            return (g_variant == 0 && bulk_ok) ? launch_packed_mma(p, 4, GQA, units, s)
+                                               : launch_simt<GQA, LayoutStructInt4>(p, units, s);
+        }
     }
 }
 

@@ -1,0 +1,54 @@
+// Definitions shared by the decode translation units.
+#pragma once
+
+#include "common.cuh"
+
+namespace reskv {
+
+struct DecodeParams;
+// Launches the tensor-core partial kernel of a non-bitmap layout (decode_packed_mma.cu).
+// layout: 0 = INT4, 1 = INT2 (unstructured), 2 = tiled FP16, 3 = structured FP16, 4 = structured INT4.
+int launch_packed_mma(const DecodeParams& p, int layout, int gqa, int units, cudaStream_t stream);
+
+namespace {
+
+constexpr int kTile = 64;    // tokens per pipeline stage
+constexpr int kWarps = 8;    // warps per CTA
+constexpr int kThreads = kWarps * 32;
+constexpr int kTokPerWarp = kTile / kWarps;
+constexpr int kReseedTiles = 16;
+constexpr int kWsHeader = 256;  // bytes reserved at the start of the workspace (status word)
+
+}  // namespace
+
+struct DecodeParams {
+    const __half* q;
+    const __half* kc;
+    const int8_t* kid;
+    const void* kp;   // payload rows
+    const void* kb;   // metadata rows (bitmaps, tile masks / indices) or null
+    const int8_t* vid;
+    const void* vp;
+    const void* vb;
+    const __half* ks;  // per-token scales of quantised layouts or null
+    const __half* vs;
+    float* ws_m;
+    float* ws_l;
+    float* ws_delta;
+    float* ws_beta;
+    uint32_t* status;
+    const float* inv_freq;
+    int64_t tok_stride;
+    int kh, nh, tokens, ck, cv;
+    int start_pos, pos_q, splits, tiles_per_split;
+    float theta, scaling;
+};
+
+namespace {
+
+__device__ __forceinline__ float rope_freq(const float* inv_freq, float theta, int i) {
+    return inv_freq ? inv_freq[i] : powf(theta, -static_cast<float>(i) / 64.0f);
+}
+
+}  // namespace
+}  // namespace reskv

@@ -1,5 +1,8 @@
-// Tensor-core version of the partial decode kernel for the unstructured FP16 bitmap
-// layout.  Included by decode_bitmap.cu (needs DecodeParams and the helpers there).
+// Tensor-core version of the partial decode kernel, generic over the residual layout
+// (the description below is written for the unstructured FP16 bitmap layout; the
+// other layouts only differ in how a lane obtains the 16 coordinates of a field,
+// see the *Field structs).  Included by decode_bitmap.cu and decode_packed_mma.cu
+// (needs DecodeParams and rope_freq from decode_common.cuh).
 //
 // Why: the warp-per-token kernel spends ~250 warp instructions per (token, KV head)
 // and is issue bound at 8 % of HBM bandwidth.  Here a warp handles blocks of 16
@@ -45,17 +48,17 @@ constexpr int kQStride = 132;     // halfs per query row
 constexpr int kQSets = 2;         // query stored as FP16 hi and lo
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
-template <int NNZ>
+template <class ML>
 struct StageM {
-    uint4 kb[kTileM];
-    uint4 vb[kTileM];
-    __half kp[kTileM * NNZ];
-    __half vp[kTileM * NNZ];
+    alignas(16) unsigned char kp[kTileM * ML::kPayloadBytes];
+    alignas(16) unsigned char vp[kTileM * ML::kPayloadBytes];
+    alignas(16) unsigned char km[kTileM * (ML::kMetaBytes ? ML::kMetaBytes : 1)];
+    alignas(16) unsigned char vm[kTileM * (ML::kMetaBytes ? ML::kMetaBytes : 1)];
 };
 
-template <int NNZ>
+template <class ML>
 constexpr int stages_for() {
-    return NNZ <= 32 ? 3 : 2;
+    return sizeof(StageM<ML>) <= 10240 ? 3 : 2;
 }
 
 // Shared-memory layouts chosen so that the 16-byte loads of a quarter warp
@@ -99,9 +102,9 @@ __device__ __forceinline__ void split_h2(float x0, float x1, uint32_t& hi, uint3
     lo = *reinterpret_cast<const uint32_t*>(&l);
 }
 
-template <int GQA, int NNZ>
+template <int GQA, class ML>
 constexpr size_t smem_bytes(int ck) {
-    return sizeof(StageM<NNZ>) * stages_for<NNZ>() + kTileM * kTrigStride * sizeof(float2) +
+    return sizeof(StageM<ML>) * stages_for<ML>() + kTileM * kTrigStride * sizeof(float2) +
            static_cast<size_t>(ck) * kCenStride * sizeof(float) + 2 * kQSets * GQA * kQStride * sizeof(__half) +
            kWarpsM * 2 * 16 * sizeof(uint2) + kWarpsM * GQA * kMaxClusters * sizeof(float);
 }
@@ -153,12 +156,188 @@ __device__ __forceinline__ float h2f_bits(uint32_t bits) {
     return __half2float(__ushort_as_half(static_cast<unsigned short>(bits)));
 }
 
-template <int GQA, int NNZ>
-__global__ void __launch_bounds__(kThreadsM, 2) decode_bitmap_mma_kernel(const DecodeParams p) {
+// ---- fields: the 16 coordinates [16 f, 16 f + 16) of one token, as a lane consumes them --------
+// add4(ks, k, scale): k[e] += residual of coordinate 4 ks + e   (key side; k holds the FP32 centroid)
+// bits4(ks, h):       h[e]  = FP16 bit pattern of the coordinate's MMA operand value (value side)
+// Both must be called with ks = 0, 1, 2, 3 in order (the sparse layouts walk a pointer).
+
+// Sparse FP16 layouts: a 16-bit keep mask (bit 15 = first coordinate) and a pointer to the
+// field's first retained value; retained values are consecutive in the payload row.
+struct WalkField {
+    uint32_t mask;
+    const __half* ptr;
+    __device__ __forceinline__ void add4(int ks, float (&k)[4], unsigned short) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (mask & (0x8000u >> (4 * ks + e))) {
+                k[e] = add_f16_f32(*reinterpret_cast<const unsigned short*>(ptr), k[e]);
+                ++ptr;
+            }
+        }
+    }
+    __device__ __forceinline__ void bits4(int ks, uint32_t (&h)[4]) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h[e] = walk16(mask, 4 * ks + e, ptr);
+    }
+};
+
+// Unstructured FP16: MSB-first bitmap; rank bases from the per-block table `pre` (8 bytes per token).
+template <int NNZ>
+struct LayoutMmaBitmap {
+    static constexpr int kPayloadBytes = NNZ * 2, kMetaBytes = 16;
+    static constexpr bool kScale = false, kPrefix = true, kScaleP = false;
+    using Field = WalkField;
+    __device__ static __forceinline__ Field field(const unsigned char* pay, const unsigned char* meta,
+                                                  const unsigned char* pre, int tok, int f, bool ok) {
+        Field fd;
+        fd.mask = ok ? *reinterpret_cast<const unsigned short*>(meta + tok * 16 + field_offset(f)) : 0u;
+        fd.ptr = reinterpret_cast<const __half*>(pay) + tok * NNZ + pre[(tok & 15) * 8 + f];
+        return fd;
+    }
+};
+
+// Tiled FP16 (INDEXED = false): one LSB-first 16-bit mask per tile = field.  Structured 4:16
+// (INDEXED = true): four 4-bit in-tile indices.  Metadata word w carries tile 2w (low half) and
+// 2w + 1 (high half), i.e. tile f sits at byte 2 f; its values start at f * NNZ / 8.
+template <int NNZ, bool INDEXED>
+struct LayoutMmaTiled {
+    static constexpr int kPayloadBytes = NNZ * 2, kMetaBytes = 16;
+    static constexpr bool kScale = false, kPrefix = false, kScaleP = false;
+    using Field = WalkField;
+    __device__ static __forceinline__ Field field(const unsigned char* pay, const unsigned char* meta,
+                                                  const unsigned char*, int tok, int f, bool ok) {
+        uint32_t code = ok ? *reinterpret_cast<const unsigned short*>(meta + tok * 16 + 2 * f) : 0u;
+        if constexpr (INDEXED) {
+            const uint32_t c = code;
+            code = ok ? ((1u << (c & 15u)) | (1u << ((c >> 4) & 15u)) | (1u << ((c >> 8) & 15u)) | (1u << (c >> 12))) : 0u;
+        }
+        Field fd;
+        fd.mask = __brev(code) >> 16;  // LSB-first -> bit 15 = first coordinate
+        fd.ptr = reinterpret_cast<const __half*>(pay) + tok * NNZ + f * (NNZ / 8);
+        return fd;
+    }
+};
+
+// Pair of small integer codes -> two exact FP16 integers.  `x` holds code a in bits [0, BITS) and
+// code b in bits [16 + SHIFT, 16 + SHIFT + BITS) (both as stored, two's complement).  Setting the
+// FP16 exponent bits makes each half 1024 + (code ^ sign) * 2^shift; one HFMA2 rescales and removes
+// the offsets.
+template <int BITS, int SHIFT>
+__device__ __forceinline__ uint32_t codes_to_h2(uint32_t x) {
+    constexpr uint32_t kSign = 1u << (BITS - 1);
+    constexpr uint32_t kKeep = ((1u << BITS) - 1u) | (((1u << BITS) - 1u) << (16 + SHIFT));
+    const uint32_t y = ((x & kKeep) ^ (kSign | (kSign << (16 + SHIFT)))) | 0x64006400u;
+    const __half2 mul = __floats2half2_rn(1.0f, 1.0f / static_cast<float>(1 << SHIFT));
+    const __half2 sub = __floats2half2_rn(-1024.0f - static_cast<float>(kSign),
+                                          -(1024.0f / static_cast<float>(1 << SHIFT)) - static_cast<float>(kSign));
+    const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&y), mul, sub);
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+// Unstructured INT4 / INT2: all 16 coordinates of a field are stored (2 words / 1 word);
+// residual = code * scale (scale FP16 per token).
+template <int BITS>
+struct QuantField {
+    uint32_t w0, w1;
+    // codes of coordinates 4 ks + {0,1} and 4 ks + {2,3} as FP16 pairs
+    __device__ __forceinline__ void pairs(int ks, uint32_t& p01, uint32_t& p23) const {
+        if constexpr (BITS == 4) {
+            const uint32_t w = (ks < 2) ? w0 : w1;
+            const uint32_t two = (w >> (16 * (ks & 1))) & 0xffffu;      // coordinates 4ks..4ks+3, a nibble each
+            const uint32_t b0 = two & 0xffu, b1 = two >> 8;
+            p01 = codes_to_h2<4, 4>(b0 | (b0 << 16));                    // lo nibble -> low half, hi nibble (x16) -> high half
+            p23 = codes_to_h2<4, 4>(b1 | (b1 << 16));
+        } else {
+            const uint32_t byte = (w0 >> (8 * ks)) & 0xffu;              // four 2-bit codes
+            const uint32_t n0 = byte & 15u, n1 = byte >> 4;
+            p01 = codes_to_h2<2, 2>(n0 | (n0 << 16));
+            p23 = codes_to_h2<2, 2>(n1 | (n1 << 16));
+        }
+    }
+    __device__ __forceinline__ void add4(int ks, float (&k)[4], unsigned short scale) const {
+        uint32_t p01, p23;
+        pairs(ks, p01, p23);
+        k[0] = fma_f16_f16_f32(static_cast<unsigned short>(p01 & 0xffffu), scale, k[0]);
+        k[1] = fma_f16_f16_f32(static_cast<unsigned short>(p01 >> 16), scale, k[1]);
+        k[2] = fma_f16_f16_f32(static_cast<unsigned short>(p23 & 0xffffu), scale, k[2]);
+        k[3] = fma_f16_f16_f32(static_cast<unsigned short>(p23 >> 16), scale, k[3]);
+    }
+    __device__ __forceinline__ void bits4(int ks, uint32_t (&h)[4]) const {
+        uint32_t p01, p23;
+        pairs(ks, p01, p23);
+        h[0] = p01 & 0xffffu, h[1] = p01 >> 16, h[2] = p23 & 0xffffu, h[3] = p23 >> 16;
+    }
+};
+
+template <int BITS>
+struct LayoutMmaQuant {
+    static constexpr int kPayloadBytes = 16 * BITS, kMetaBytes = 0;
+    static constexpr bool kScale = true, kPrefix = false, kScaleP = true;
+    using Field = QuantField<BITS>;
+    __device__ static __forceinline__ Field field(const unsigned char* pay, const unsigned char*,
+                                                  const unsigned char*, int tok, int f, bool ok) {
+        Field fd{0u, 0u};
+        if (ok) {
+            if constexpr (BITS == 4) {
+                const uint2 w = *reinterpret_cast<const uint2*>(pay + tok * 64 + 8 * f);
+                fd.w0 = w.x, fd.w1 = w.y;
+            } else {
+                fd.w0 = *reinterpret_cast<const uint32_t*>(pay + tok * 32 + 4 * f);
+            }
+        }
+        return fd;
+    }
+};
+
+// 1-of-4 structured INT4: per 4-coordinate group one signed nibble and a 2-bit position.
+struct StructInt4Field {
+    uint32_t c01, c23;  // the field's four group codes as FP16 pairs
+    uint32_t sel;       // four 2-bit in-group positions
+    __device__ __forceinline__ unsigned short code(int ks) const {
+        const uint32_t p = (ks < 2) ? c01 : c23;
+        return static_cast<unsigned short>((ks & 1) ? (p >> 16) : (p & 0xffffu));
+    }
+    __device__ __forceinline__ void add4(int ks, float (&k)[4], unsigned short scale) const {
+        const uint32_t pos = (sel >> (2 * ks)) & 3u;
+        const unsigned short c = code(ks);
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (pos == static_cast<uint32_t>(e)) k[e] = fma_f16_f16_f32(c, scale, k[e]);
+    }
+    __device__ __forceinline__ void bits4(int ks, uint32_t (&h)[4]) const {
+        const uint32_t pos = (sel >> (2 * ks)) & 3u;
+        const uint32_t c = code(ks);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h[e] = (pos == static_cast<uint32_t>(e)) ? c : 0u;
+    }
+};
+
+struct LayoutMmaStructInt4 {
+    static constexpr int kPayloadBytes = 16, kMetaBytes = 8;
+    static constexpr bool kScale = true, kPrefix = false, kScaleP = true;
+    using Field = StructInt4Field;
+    __device__ static __forceinline__ Field field(const unsigned char* pay, const unsigned char* meta,
+                                                  const unsigned char*, int tok, int f, bool ok) {
+        Field fd{0u, 0u, 0u};
+        if (ok) {
+            // groups 4f..4f+3: nibbles = 16 bits at byte 2f of the packed row, positions = byte f of the metadata row
+            const uint32_t nib = *reinterpret_cast<const unsigned short*>(pay + tok * 16 + 2 * f);
+            const uint32_t b0 = nib & 0xffu, b1 = nib >> 8;
+            fd.c01 = codes_to_h2<4, 4>(b0 | (b0 << 16));
+            fd.c23 = codes_to_h2<4, 4>(b1 | (b1 << 16));
+            fd.sel = meta[tok * 8 + f];
+        }
+        return fd;
+    }
+};
+
+template <int GQA, class ML>
+__global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    constexpr int kStages = stages_for<NNZ>();
+    constexpr int kStages = stages_for<ML>();
     constexpr int kItems = (GQA * 32 + kThreadsM - 1) / kThreadsM;  // query items per thread
-    using StageT = StageM<NNZ>;
+    using StageT = StageM<ML>;
+    using Field = typename ML::Field;
     StageT* stages = reinterpret_cast<StageT*>(smem_raw);
     float2* trig = reinterpret_cast<float2*>(smem_raw + sizeof(StageT) * kStages);
     float* kc_s = reinterpret_cast<float*>(trig + kTileM * kTrigStride);
@@ -178,12 +357,14 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_bitmap_mma_kernel(const D
     const int ntiles = max(0, min(total_tiles, tile_begin + p.tiles_per_split) - tile_begin);
 
     const size_t unit_tok = static_cast<size_t>(unit) * p.tok_stride;
-    const uint4* kb_g = static_cast<const uint4*>(p.kb) + unit_tok;
-    const uint4* vb_g = static_cast<const uint4*>(p.vb) + unit_tok;
-    const __half* kp_g = static_cast<const __half*>(p.kp) + unit_tok * NNZ;
-    const __half* vp_g = static_cast<const __half*>(p.vp) + unit_tok * NNZ;
+    const unsigned char* km_g = static_cast<const unsigned char*>(p.kb) + unit_tok * ML::kMetaBytes;
+    const unsigned char* vm_g = static_cast<const unsigned char*>(p.vb) + unit_tok * ML::kMetaBytes;
+    const unsigned char* kp_g = static_cast<const unsigned char*>(p.kp) + unit_tok * ML::kPayloadBytes;
+    const unsigned char* vp_g = static_cast<const unsigned char*>(p.vp) + unit_tok * ML::kPayloadBytes;
     const int8_t* kid_g = p.kid + unit_tok;
     const int8_t* vid_g = p.vid + unit_tok;
+    const __half* ks_g = ML::kScale ? p.ks + unit_tok : nullptr;
+    const __half* vs_g = ML::kScale ? p.vs + unit_tok : nullptr;
 
     if (tid == 0) {
         timed_out = 0;
@@ -196,12 +377,16 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_bitmap_mma_kernel(const D
         const int n = min(kTileM, p.tokens - t0);
         StageT& st = stages[tile_rel % kStages];
         uint64_t* bar = &full_bar[tile_rel % kStages];
-        const uint32_t bm_bytes = n * 16u, pl_bytes = n * NNZ * 2u;
-        mbar_arrive_expect_tx(bar, 2 * bm_bytes + 2 * pl_bytes);
-        bulk_g2s(st.kb, kb_g + t0, bm_bytes, bar);
-        bulk_g2s(st.vb, vb_g + t0, bm_bytes, bar);
-        bulk_g2s(st.kp, kp_g + static_cast<size_t>(t0) * NNZ, pl_bytes, bar);
-        bulk_g2s(st.vp, vp_g + static_cast<size_t>(t0) * NNZ, pl_bytes, bar);
+        // 8-byte metadata rows stay bulk-copyable: tiles start at multiples of 64 tokens and the host
+        // selects this kernel for them only when token count and token stride are even
+        const uint32_t md_bytes = n * ML::kMetaBytes, pl_bytes = n * ML::kPayloadBytes;
+        mbar_arrive_expect_tx(bar, 2 * md_bytes + 2 * pl_bytes);
+        if (ML::kMetaBytes) {
+            bulk_g2s(st.km, km_g + static_cast<size_t>(t0) * ML::kMetaBytes, md_bytes, bar);
+            bulk_g2s(st.vm, vm_g + static_cast<size_t>(t0) * ML::kMetaBytes, md_bytes, bar);
+        }
+        bulk_g2s(st.kp, kp_g + static_cast<size_t>(t0) * ML::kPayloadBytes, pl_bytes, bar);
+        bulk_g2s(st.vp, vp_g + static_cast<size_t>(t0) * ML::kPayloadBytes, pl_bytes, bar);
     };
     if (tid == 0) {
         for (int s = 0; s < kStages && s < ntiles; ++s) issue(s);
@@ -297,19 +482,27 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_bitmap_mma_kernel(const D
     uint2* pre_k = pre + warp * 32;
     uint2* pre_v = pre_k + 16;
 
-    // cluster ids of this warp's 16 tokens of the next tile: lanes 0..15 key ids, 16..31 value ids
-    auto load_ids = [&](int tile_rel) -> int {
+    // cluster ids (and FP16 scales) of this warp's 16 tokens of the next tile: lanes 0..15 hold the
+    // key side of token `lane`, lanes 16..31 the value side of token `lane - 16`
+    auto load_ids = [&](int tile_rel, int& id, uint32_t& scale) {
         const int t = (tile_begin + tile_rel) * kTileM + warp * 16 + (lane & 15);
-        int id = 0;
+        id = 0, scale = 0u;
         if (tile_rel < ntiles && t < p.tokens) {
-            // volatile: issue the load here, a whole tile ahead of its use, instead of letting the
-            // compiler sink it next to the consumer
+            // volatile: issue the loads here, a whole tile ahead of their use, instead of letting the
+            // compiler sink them next to the consumer
             const int8_t* src = ((lane < 16) ? kid_g : vid_g) + t;
             asm volatile("ld.global.nc.s8 %0, [%1];" : "=r"(id) : "l"(src));
+            if constexpr (ML::kScale) {
+                const __half* ssrc = ((lane < 16) ? ks_g : vs_g) + t;
+                unsigned short h;
+                asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(h) : "l"(ssrc));
+                scale = h;
+            }
         }
-        return id;
     };
-    int ids_next = load_ids(0);
+    int ids_next;
+    uint32_t scl_next;
+    load_ids(0, ids_next, scl_next);
     __syncthreads();  // tables and first query tile ready
 
     // sin/cos of this lane's two rows (tile offsets 16 warp + g and + 8) and 16 frequencies: the
@@ -331,35 +524,30 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_bitmap_mma_kernel(const D
     for (int it = 0; it < ntiles; ++it) {
         const int t0 = (tile_begin + it) * kTileM;
         const int ids_cur = ids_next;
-        ids_next = load_ids(it + 1);
+        const uint32_t scl_cur = scl_next;
+        load_ids(it + 1, ids_next, scl_next);
         if (!mbar_wait(&full_bar[it % kStages], (it / kStages) & 1)) lost = true;
         const StageT& st = stages[it % kStages];
         const int nvalid = min(16, p.tokens - (t0 + warp * 16));  // valid tokens of this warp's block
         if (nvalid > 0) {
-            // rank bases of the block's 16 key bitmaps (lanes 0..15) and value bitmaps (16..31)
-            {
+            if constexpr (ML::kPrefix) {
+                // rank bases of the block's 16 key bitmaps (lanes 0..15) and value bitmaps (16..31)
                 const int tok = warp * 16 + (lane & 15);
-                const uint4 bm = (lane < 16) ? st.kb[tok] : st.vb[tok];
+                const uint4 bm = reinterpret_cast<const uint4*>((lane < 16) ? st.km : st.vm)[tok];
                 pre_k[lane] = rank_bases(bm);  // pre_v == pre_k + 16
+                __syncwarp();
             }
-            __syncwarp();
 
             // ================= keys: rows g and g + 8 of the block =================
             const int tokA = warp * 16 + g, tokB = tokA + 8;
             const bool okA = g < nvalid, okB = g + 8 < nvalid;
             const int kidA = min(max(__shfl_sync(0xffffffffu, ids_cur, g), 0), p.ck - 1);
             const int kidB = min(max(__shfl_sync(0xffffffffu, ids_cur, g + 8), 0), p.ck - 1);
-            const unsigned char* kb_bytes = reinterpret_cast<const unsigned char*>(st.kb);
             const unsigned char* pk_bytes = reinterpret_cast<const unsigned char*>(pre_k);
-            const int off_lo = field_offset(qd), off_hi = field_offset(4 + qd);
-            const uint32_t fAl = okA ? *reinterpret_cast<const unsigned short*>(kb_bytes + tokA * 16 + off_lo) : 0u;
-            const uint32_t fAh = okA ? *reinterpret_cast<const unsigned short*>(kb_bytes + tokA * 16 + off_hi) : 0u;
-            const uint32_t fBl = okB ? *reinterpret_cast<const unsigned short*>(kb_bytes + tokB * 16 + off_lo) : 0u;
-            const uint32_t fBh = okB ? *reinterpret_cast<const unsigned short*>(kb_bytes + tokB * 16 + off_hi) : 0u;
-            const __half* pAl = st.kp + tokA * NNZ + pk_bytes[g * 8 + qd];
-            const __half* pAh = st.kp + tokA * NNZ + pk_bytes[g * 8 + 4 + qd];
-            const __half* pBl = st.kp + tokB * NNZ + pk_bytes[(g + 8) * 8 + qd];
-            const __half* pBh = st.kp + tokB * NNZ + pk_bytes[(g + 8) * 8 + 4 + qd];
+            Field fAl = ML::field(st.kp, st.km, pk_bytes, tokA, qd, okA), fAh = ML::field(st.kp, st.km, pk_bytes, tokA, 4 + qd, okA);
+            Field fBl = ML::field(st.kp, st.km, pk_bytes, tokB, qd, okB), fBh = ML::field(st.kp, st.km, pk_bytes, tokB, 4 + qd, okB);
+            const unsigned short kscA = static_cast<unsigned short>(__shfl_sync(0xffffffffu, scl_cur, g));
+            const unsigned short kscB = static_cast<unsigned short>(__shfl_sync(0xffffffffu, scl_cur, g + 8));
             // FP32 centroid rows; the lane's low field starts at 16q, its partner field at 64 + 16q
             const float* cA = kc_s + kidA * kCenStride + 16 * qd;
             const float* cB = kc_s + kidB * kCenStride + 16 * qd;
@@ -374,17 +562,14 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_bitmap_mma_kernel(const D
                 // four coordinates 16q + 4ks .. +3 and their partners + 64, both tokens:
                 // k = centroid (+ residual where the bitmap bit is set)
                 const int cu = (ks ^ cen_swz) * 4;
-                float4 al = *reinterpret_cast<const float4*>(cA + cu), ah = *reinterpret_cast<const float4*>(cA + 64 + cu);
-                float4 bl = *reinterpret_cast<const float4*>(cB + cu), bh = *reinterpret_cast<const float4*>(cB + 64 + cu);
-                float* kAl = &al.x; float* kAh = &ah.x; float* kBl = &bl.x; float* kBh = &bh.x;
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const uint32_t bit = 0x8000u >> (4 * ks + e);
-                    if (fAl & bit) { kAl[e] = add_f16_f32(*reinterpret_cast<const unsigned short*>(pAl), kAl[e]); ++pAl; }
-                    if (fAh & bit) { kAh[e] = add_f16_f32(*reinterpret_cast<const unsigned short*>(pAh), kAh[e]); ++pAh; }
-                    if (fBl & bit) { kBl[e] = add_f16_f32(*reinterpret_cast<const unsigned short*>(pBl), kBl[e]); ++pBl; }
-                    if (fBh & bit) { kBh[e] = add_f16_f32(*reinterpret_cast<const unsigned short*>(pBh), kBh[e]); ++pBh; }
-                }
+                const float4 al = *reinterpret_cast<const float4*>(cA + cu), ah = *reinterpret_cast<const float4*>(cA + 64 + cu);
+                const float4 bl = *reinterpret_cast<const float4*>(cB + cu), bh = *reinterpret_cast<const float4*>(cB + 64 + cu);
+                float kAl[4] = {al.x, al.y, al.z, al.w}, kAh[4] = {ah.x, ah.y, ah.z, ah.w};
+                float kBl[4] = {bl.x, bl.y, bl.z, bl.w}, kBh[4] = {bh.x, bh.y, bh.z, bh.w};
+                fAl.add4(ks, kAl, kscA);
+                fAh.add4(ks, kAh, kscA);
+                fBl.add4(ks, kBl, kscB);
+                fBh.add4(ks, kBh, kscB);
                 float rAl[4], rAh[4], rBl[4], rBh[4];
 #pragma unroll
                 for (int e2 = 0; e2 < 2; ++e2) {
@@ -429,23 +614,24 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_bitmap_mma_kernel(const D
             // ================= values: tokens 2q, 2q+1, 2q+8, 2q+9; coordinates [16g, 16g+16) =================
             uint32_t v01[16], v23[16];  // (token 2q | token 2q+1 << 16), (2q+8 | 2q+9 << 16) per coordinate
             {
-                const unsigned char* vb_bytes = reinterpret_cast<const unsigned char*>(st.vb);
                 const unsigned char* pv_bytes = reinterpret_cast<const unsigned char*>(pre_v);
-                const int off = field_offset(g);
                 const int r0 = 2 * qd, r1 = 2 * qd + 1, r2 = 2 * qd + 8, r3 = 2 * qd + 9;
-                const int tk0 = warp * 16 + r0, tk1 = warp * 16 + r1, tk2 = warp * 16 + r2, tk3 = warp * 16 + r3;
-                const uint32_t f0 = r0 < nvalid ? *reinterpret_cast<const unsigned short*>(vb_bytes + tk0 * 16 + off) : 0u;
-                const uint32_t f1 = r1 < nvalid ? *reinterpret_cast<const unsigned short*>(vb_bytes + tk1 * 16 + off) : 0u;
-                const uint32_t f2 = r2 < nvalid ? *reinterpret_cast<const unsigned short*>(vb_bytes + tk2 * 16 + off) : 0u;
-                const uint32_t f3 = r3 < nvalid ? *reinterpret_cast<const unsigned short*>(vb_bytes + tk3 * 16 + off) : 0u;
-                const __half* p0 = st.vp + tk0 * NNZ + pv_bytes[r0 * 8 + g];
-                const __half* p1 = st.vp + tk1 * NNZ + pv_bytes[r1 * 8 + g];
-                const __half* p2 = st.vp + tk2 * NNZ + pv_bytes[r2 * 8 + g];
-                const __half* p3 = st.vp + tk3 * NNZ + pv_bytes[r3 * 8 + g];
+                Field f0 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r0, g, r0 < nvalid);
+                Field f1 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r1, g, r1 < nvalid);
+                Field f2 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r2, g, r2 < nvalid);
+                Field f3 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r3, g, r3 < nvalid);
 #pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    v01[e] = walk16(f0, e, p0) | (walk16(f1, e, p1) << 16);
-                    v23[e] = walk16(f2, e, p2) | (walk16(f3, e, p3) << 16);
+                for (int ks = 0; ks < 4; ++ks) {
+                    uint32_t h0[4], h1[4], h2[4], h3[4];
+                    f0.bits4(ks, h0);
+                    f1.bits4(ks, h1);
+                    f2.bits4(ks, h2);
+                    f3.bits4(ks, h3);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        v01[4 * ks + e] = h0[e] | (h1[e] << 16);
+                        v23[4 * ks + e] = h2[e] | (h3[e] << 16);
+                    }
                 }
             }
 
@@ -486,7 +672,7 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_bitmap_mma_kernel(const D
             float pr[4];
             pr[0] = fast_exp2(sc[0] - m_used[0]), pr[1] = fast_exp2(sc[1] - m_used[1]);
             pr[2] = fast_exp2(sc[2] - m_used[0]), pr[3] = fast_exp2(sc[3] - m_used[1]);
-            const __half2 p01 = __floats2half2_rn(pr[0], pr[1]), p23 = __floats2half2_rn(pr[2], pr[3]);
+            __half2 p01 = __floats2half2_rn(pr[0], pr[1]), p23 = __floats2half2_rn(pr[2], pr[3]);
             const float2 p01f = __half22float2(p01), p23f = __half22float2(p23);
             l_part[0] += p01f.x + p23f.x;
             l_part[1] += p01f.y + p23f.y;
@@ -503,6 +689,13 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_bitmap_mma_kernel(const D
                     if (okA) atomicAdd(&beta_w[h1 * kMaxClusters + vidA], p01f.y);
                     if (okB) atomicAdd(&beta_w[h1 * kMaxClusters + vidB], p23f.y);
                 }
+            }
+            if constexpr (ML::kScaleP) {
+                // quantised values enter the MMA as integer codes: their per-token scale rides on P
+                const float vsA = h2f_bits(__shfl_sync(0xffffffffu, scl_cur, 16 + g));
+                const float vsB = h2f_bits(__shfl_sync(0xffffffffu, scl_cur, 24 + g));
+                p01 = __floats2half2_rn(p01f.x * vsA, p01f.y * vsA);
+                p23 = __floats2half2_rn(p23f.x * vsB, p23f.y * vsB);
             }
             // P as B operand (tokens x heads): transpose the two 8x8 halves
             const uint32_t pb0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p01));

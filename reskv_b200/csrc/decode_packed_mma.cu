@@ -1,0 +1,39 @@
+// Tensor-core partial decode kernels for the layouts other than the unstructured FP16 bitmap:
+// unstructured INT4 / INT2, tiled FP16, 4:16 structured FP16, 1-of-4 structured INT4.
+// Same kernel template as the bitmap layout (decode_mma.cuh); only the field policy differs.
+#include "decode_common.cuh"
+
+namespace reskv {
+namespace {
+#include "decode_mma.cuh"
+
+template <int GQA, class ML>
+int launch(const DecodeParams& p, int units, cudaStream_t stream) {
+    const size_t smem = mma::smem_bytes<GQA, ML>(p.ck);
+    auto kern = mma::decode_mma_kernel<GQA, ML>;
+    if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 static_cast<int>(smem)),
+                            "cudaFuncSetAttribute(decode_mma packed)"))
+        return rc;
+    kern<<<dim3(p.splits, units), mma::kThreadsM, smem, stream>>>(p);
+    return check_cuda(cudaGetLastError(), "decode_mma (packed layout) launch");
+}
+
+template <int GQA>
+int by_layout(const DecodeParams& p, int layout, int units, cudaStream_t s) {
+    switch (layout) {
+        case 0: return launch<GQA, mma::LayoutMmaQuant<4>>(p, units, s);
+        case 1: return launch<GQA, mma::LayoutMmaQuant<2>>(p, units, s);
+        case 2: return launch<GQA, mma::LayoutMmaTiled<64, false>>(p, units, s);
+        case 3: return launch<GQA, mma::LayoutMmaTiled<32, true>>(p, units, s);
+        default: return launch<GQA, mma::LayoutMmaStructInt4>(p, units, s);
+    }
+}
+}  // namespace
+
+int launch_packed_mma(const DecodeParams& p, int layout, int gqa, int units, cudaStream_t stream) {
+    return gqa == 1 ? by_layout<1>(p, layout, units, stream)
+           : gqa == 4 ? by_layout<4>(p, layout, units, stream)
+                      : by_layout<8>(p, layout, units, stream);
+}
+}  // namespace reskv

@@ -14,6 +14,17 @@ from oracle import layouts as olay
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
+
+@pytest.fixture(autouse=True, params=["tensor-core", "simt"])
+def kernel_variant(request):
+    """Every test runs with both families of partial kernels."""
+    from reskv_b200._extension import library
+
+    lib = library()
+    assert lib.reskv_decode_set_variant(0 if request.param == "tensor-core" else 1) == 0
+    yield request.param
+    lib.reskv_decode_set_variant(0)
+
 CASES = [
     (16, 0.5, "tiled", "per_token"),
     (16, 0.5, "unstructured", "deferred"),
