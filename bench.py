@@ -65,6 +65,11 @@ def parse():
     ap.add_argument("--sparsity", type=float, default=0.75)
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--model-batches", default="",
+                    help="comma list: also run the random-weight Llama-3.1-8B-shaped model end to end (prefill of "
+                         "--context tokens, greedy decode) with the compressed and with a dense FP16 cache "
+                         "(extra key 'model')")
+    ap.add_argument("--model-new-tokens", type=int, default=128)
     ap.add_argument("--sweep", action="store_true",
                     help="also time attention and a prefill compression at batch 1/4/8/16/32 (extra key 'sweep')")
     return ap.parse_args()
@@ -281,6 +286,56 @@ def run_sweep(a, dev, cfg, inv_freq, nnz):
     return out
 
 
+def run_model(a, dev):
+    """Prefill + greedy decode of the Llama-3.1-8B-shaped model (random FP16 weights, uniform random
+    prompt ids as in the reference's benchmarks/timing.py:60-66) with both cache kinds."""
+    import torch
+
+    from reskv_b200 import ResKVKernelConfig
+    from reskv_b200.models import LlamaShape, ResKVLlama
+
+    cfg = ResKVKernelConfig(sparsity=a.sparsity, bits=16, layout="unstructured", num_clusters=CLUSTERS,
+                            max_clusters=MAX_CLUSTERS, group_size=GROUP, recent_size=RECENT, kmeans_iterations=ITERS)
+    shape = LlamaShape()
+    model = ResKVLlama(shape, cfg, device=dev, seed=0)
+    out = []
+    n_new = a.model_new_tokens
+    for batch in [int(x) for x in a.model_batches.split(",")]:
+        ids = torch.randint(128, shape.vocab, (batch, a.context), generator=torch.Generator().manual_seed(42)).to(dev)
+        for kind in ("reskv", "dense"):
+            model.cache_kind = kind
+            model.caches = None
+            torch.cuda.empty_cache()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            logits = model.prefill(ids, reserve=n_new + 8)
+            torch.cuda.synchronize()
+            prefill_ms = (time.perf_counter() - t0) * 1e3
+            tok = logits.argmax(-1)
+            mode = "graph"
+            try:
+                model.begin_graph_decode(batch)
+                step = model.decode_graph
+                for _ in range(4):  # warm-up steps (first one captures)
+                    tok = step(tok).argmax(-1)
+            except RuntimeError:  # dense baseline without flash_attn: eager SDPA
+                mode, step = "eager", model.decode
+                for _ in range(4):
+                    tok = step(tok).argmax(-1)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(n_new):
+                tok = step(tok).argmax(-1)
+            torch.cuda.synchronize()
+            decode_ms = (time.perf_counter() - t0) * 1e3
+            out.append({"batch": batch, "cache": kind, "decode_loop": mode, "context": a.context, "new_tokens": n_new,
+                        "prefill_ms": prefill_ms, "tpot_ms": decode_ms / n_new,
+                        "decode_tok_per_s": batch * n_new / (decode_ms * 1e-3),
+                        "cache_bytes": model.cache_bytes()})
+        model.caches = None
+    return out
+
+
 def run_gpu(a):
     import torch
     import torch.distributed as dist
@@ -410,6 +465,11 @@ def run_gpu(a):
     sweep = None
     if a.sweep and world == 1:
         sweep = run_sweep(a, dev, cfg, inv_freq, nnz)
+    model_runs = None
+    if a.model_batches and world == 1:
+        del layer, q_all, k_new, v_new, q_rot, k_rot
+        torch.cuda.empty_cache()
+        model_runs = run_model(a, dev)
     clock_summary = clocks.summary()
     if rank == 0:
         peaks = {}
@@ -448,6 +508,8 @@ def run_gpu(a):
         }
         if sweep is not None:
             line["sweep"] = sweep
+        if model_runs is not None:
+            line["model"] = model_runs
         if world == 1 and not a.no_cpu_baseline:
             value, sample = cpu_attention_sample(a, a.cpu_seconds)
             line["cpu_baseline"] = {"value": value, "unit": UNIT, "cores": cpu_cores(), "kind": "port",

@@ -105,6 +105,34 @@ int reskv_decode_packed(int layout, int bits, const void* q, const void* k_centr
                         const void* recent_q, const void* recent_k, const void* recent_v, int recent_tokens,
                         void* workspace, size_t workspace_bytes, void* out, float* out_m, float* out_l, void* stream);
 
+/* ---- decode steps that can be captured in a CUDA graph --------------------------------
+ * No counterpart in the reference (its decode loop is eager Python,
+ * benchmarks/timing.py:105-145, and passes positions by value).
+ *
+ * step_state is two int32 in device memory: {query position, tokens in the dense
+ * window including the token of this step}.  reskv_window_append writes the new
+ * token's rotated key, raw key and value (f16 [B*KH,128] each) into slot
+ * step_state[1] - 1 of the window buffers (f16 [B*KH,window_capacity,128]);
+ * reskv_decode_step is reskv_decode_bitmap_fp16 /
+ * reskv_decode_packed with the query position and the window length read from
+ * step_state inside the kernels (layout UNSTRUCTURED with bits 16 selects the bitmap
+ * kernels, nnz = payload width); reskv_step_advance adds to both numbers.  A graph that
+ * holds "advance(0, 1), then per layer append + decode, advance(1, 0)" can be replayed for consecutive steps until the
+ * compressed segment changes (every group_size steps). */
+int reskv_window_append(void* window_k, void* window_raw, void* window_v, const void* k_rot, const void* k_raw,
+                        const void* v, int batch, int kv_heads, int window_capacity, const int32_t* step_state,
+                        void* stream);
+
+int reskv_decode_step(int layout, int bits, int nnz, const void* q, const void* k_centroids, const void* k_ids,
+                      const void* k_payload, const void* k_meta, const void* k_scale, const void* v_centroids,
+                      const void* v_ids, const void* v_payload, const void* v_meta, const void* v_scale, int batch,
+                      int kv_heads, int q_heads, int tokens, int64_t tok_stride, int k_clusters, int v_clusters,
+                      int start_pos, float rope_theta, const float* inv_freq, float scaling, int splits,
+                      const void* recent_q, const void* window_k, const void* window_v, int window_capacity,
+                      const int32_t* step_state, void* workspace, size_t workspace_bytes, void* out, void* stream);
+
+int reskv_step_advance(int32_t* step_state, int position_increment, int window_increment, void* stream);
+
 /* ---- decode attention for callers that cannot provide scratch memory -------------------
  * No counterpart in the reference (its ops allocate their partial buffers with
  * torch::empty on every call, cluster_mass.cu:1222-1232).

@@ -49,6 +49,12 @@ SIGNATURES = {
         _I,
         [_P] * 9 + [_I, _I, _I, _I, _L, _I, _I, _I, _I, _I, _F, _P, _F, _I, _P, _P, _P, _I, _P, _P, _P, _P],
     ),
+    "reskv_window_append": (_I, [_P] * 6 + [_I, _I, _I, _P, _P]),
+    "reskv_decode_step": (
+        _I,
+        [_I, _I, _I] + [_P] * 11 + [_I, _I, _I, _I, _L, _I, _I, _I, _F, _P, _F, _I, _P, _P, _P, _I, _P, _P, _Z, _P, _P],
+    ),
+    "reskv_step_advance": (_I, [_P, _I, _I, _P]),
     "reskv_decode_auto_splits": (_I, [_I, _I, _I]),
     "reskv_decode_set_variant": (_I, [_I]),
     "reskv_decode_set_timing_events": (_I, [_P, _P]),

@@ -257,8 +257,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_simt_partial_kernel(const 
     float qr[GQA][4];
     {
         float s0, c0, s1, c1;
-        sincosf(static_cast<float>(p.pos_q) * f0, &s0, &c0);
-        sincosf(static_cast<float>(p.pos_q) * f1, &s1, &c1);
+        const float pq = static_cast<float>(query_position(p));
+        sincosf(pq * f0, &s0, &c0);
+        sincosf(pq * f1, &s1, &c1);
         const float mul = p.scaling * kLog2e;
 #pragma unroll
         for (int h = 0; h < GQA; ++h) {
@@ -439,6 +440,8 @@ struct MergeParams {
     float* out_l;
     int kh, nh, splits, cv, tr;
     float scaling;
+    const int32_t* dyn;  // device step state: dyn[1] = recent tokens (overrides tr), or null
+    int recent_cap;      // tokens between units in rk / rv (== tr for contiguous windows)
 };
 
 constexpr int kMergeThreads = 128;
@@ -483,19 +486,20 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Merge
         num = __half2float(p.comp_out[static_cast<size_t>(fq) * kHeadDim + d]) * l;
     }
 
-    if (p.tr > 0) {
+    const int tr = p.dyn ? min(p.dyn[1], kMaxRecent) : p.tr;
+    if (tr > 0) {
         // scores of the recent tokens (log2 domain) into shared memory
         if (p.rscores) {
-            for (int t = d; t < p.tr; t += kMergeThreads)
-                sc_s[t] = p.rscores[static_cast<size_t>(fq) * p.tr + t] * kLog2e;
+            for (int t = d; t < tr; t += kMergeThreads)
+                sc_s[t] = p.rscores[static_cast<size_t>(fq) * tr + t] * kLog2e;
         } else {
             const __half* qrow = p.rq + static_cast<size_t>(fq) * kHeadDim;
             float qv[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) qv[i] = __half2float(qrow[lane + 32 * i]);
             const float mul = p.scaling * kLog2e;
-            for (int t = warp; t < p.tr; t += kMergeThreads / 32) {
-                const __half* krow = p.rk + (static_cast<size_t>(unit) * p.tr + t) * kHeadDim;
+            for (int t = warp; t < tr; t += kMergeThreads / 32) {
+                const __half* krow = p.rk + (static_cast<size_t>(unit) * p.recent_cap + t) * kHeadDim;
                 float dot = 0.f;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) dot = fmaf(qv[i], __half2float(krow[lane + 32 * i]), dot);
@@ -506,7 +510,7 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Merge
         }
         __syncthreads();
         float rm = -INFINITY;
-        for (int t = d; t < p.tr; t += kMergeThreads) rm = fmaxf(rm, sc_s[t]);
+        for (int t = d; t < tr; t += kMergeThreads) rm = fmaxf(rm, sc_s[t]);
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) rm = fmaxf(rm, __shfl_xor_sync(0xffffffffu, rm, off));
         if (lane == 0) red[warp] = rm;
@@ -515,8 +519,8 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Merge
         const float jm = fmaxf(rm, m2);
         const float cw = (m2 == -INFINITY) ? 0.f : fast_exp2(m2 - jm);
         float rnum = 0.f, rl = 0.f;
-        const __half* vrow = p.rv + static_cast<size_t>(unit) * p.tr * kHeadDim + d;
-        for (int t = 0; t < p.tr; ++t) {
+        const __half* vrow = p.rv + static_cast<size_t>(unit) * p.recent_cap * kHeadDim + d;
+        for (int t = 0; t < tr; ++t) {
             const float w = fast_exp2(sc_s[t] - jm);
             rl += w;
             rnum = fmaf(w, __half2float(vrow[static_cast<size_t>(t) * kHeadDim]), rnum);
@@ -665,6 +669,8 @@ struct DecodeArgs {
     void* out;
     float *out_m, *out_l;
     void* stream;
+    const int32_t* dyn = nullptr;  // device step state {pos_q, recent tokens}
+    int recent_cap = 0;            // window capacity in tokens when dyn is given
 };
 
 int decode_common(const DecodeArgs& a, LayoutId layout, bool has_meta, bool has_scale, const char* who) {
@@ -681,8 +687,10 @@ int decode_common(const DecodeArgs& a, LayoutId layout, bool has_meta, bool has_
     if (a.ck < 1 || a.ck > kMaxClusters || a.cv < 1 || a.cv > kMaxClusters)
         return fail(RESKV_ERR_INVALID, "%s: centroid counts must be in [1,64]", who);
     if (a.tok_stride < a.tokens) return fail(RESKV_ERR_INVALID, "%s: tok_stride < tokens", who);
-    if (a.pos_q < a.start_pos + a.tokens - 1)
+    if (!a.dyn && a.pos_q < a.start_pos + a.tokens - 1)
         return fail(RESKV_ERR_INVALID, "%s: query position precedes compressed tokens", who);
+    if (a.dyn && (a.recent_cap < 1 || a.recent_cap > kMaxRecent || !a.rq || !a.rk || !a.rv))
+        return fail(RESKV_ERR_INVALID, "%s: a step state needs the window buffers and a capacity in [1,%d]", who, kMaxRecent);
     if (!aligned16(a.kp) || !aligned16(a.vp) || (has_meta && layout != kStructInt4 && (!aligned16(a.km) || !aligned16(a.vm))))
         return fail(RESKV_ERR_INVALID, "%s: payload and metadata pointers must be 16-byte aligned", who);
     if ((reinterpret_cast<uintptr_t>(a.kc) & 3u) || (reinterpret_cast<uintptr_t>(a.q) & 1u))
@@ -724,6 +732,7 @@ int decode_common(const DecodeArgs& a, LayoutId layout, bool has_meta, bool has_
     p.kh = a.kv_heads, p.nh = a.q_heads, p.tokens = a.tokens, p.ck = a.ck, p.cv = a.cv;
     p.start_pos = a.start_pos, p.pos_q = a.pos_q, p.splits = splits, p.tiles_per_split = per;
     p.theta = a.theta, p.scaling = a.scaling;
+    p.dyn = a.dyn;
 
     cudaStream_t s = static_cast<cudaStream_t>(a.stream);
     if (g_ev_start) cudaEventRecord(g_ev_start, s);
@@ -743,6 +752,7 @@ int decode_common(const DecodeArgs& a, LayoutId layout, bool has_meta, bool has_
     mp.out_m = a.out_m, mp.out_l = a.out_l;
     mp.kh = a.kv_heads, mp.nh = a.q_heads, mp.splits = splits, mp.cv = a.cv, mp.tr = a.recent_tokens;
     mp.scaling = a.scaling;
+    mp.dyn = a.dyn, mp.recent_cap = a.dyn ? a.recent_cap : a.recent_tokens;
     decode_merge_kernel<<<a.batch * a.q_heads, kMergeThreads, 0, s>>>(mp);
     return check_cuda(cudaGetLastError(), "decode_merge launch");
 }
@@ -792,6 +802,40 @@ extern "C" int reskv_decode_packed(int layout, int bits, const void* q, const vo
                        rope_theta, inv_freq, scaling, splits, recent_q, recent_k, recent_v, recent_tokens, workspace,
                        workspace_bytes_given, out, out_m, out_l, stream};
     return decode_common(a, id, meta, scale, "decode_packed");
+}
+
+extern "C" int reskv_decode_step(int layout, int bits, int nnz, const void* q, const void* k_centroids,
+                                 const void* k_ids, const void* k_payload, const void* k_meta, const void* k_scale,
+                                 const void* v_centroids, const void* v_ids, const void* v_payload,
+                                 const void* v_meta, const void* v_scale, int batch, int kv_heads, int q_heads,
+                                 int tokens, int64_t tok_stride, int k_clusters, int v_clusters, int start_pos,
+                                 float rope_theta, const float* inv_freq, float scaling, int splits,
+                                 const void* recent_q, const void* window_k, const void* window_v,
+                                 int window_capacity, const int32_t* step_state, void* workspace,
+                                 size_t workspace_bytes_given, void* out, void* stream) {
+    if (!step_state) return fail(RESKV_ERR_INVALID, "decode_step: null step state");
+    LayoutId id;
+    bool meta = true, scale = false;
+    if (layout == RESKV_LAYOUT_UNSTRUCTURED && bits == 16 && (nnz == 32 || nnz == 64)) {
+        id = nnz == 32 ? kBitmap32 : kBitmap64;
+    } else if (layout == RESKV_LAYOUT_UNSTRUCTURED && (bits == 4 || bits == 2)) {
+        id = bits == 4 ? kQuant4 : kQuant2, meta = false, scale = true;
+    } else if (layout == RESKV_LAYOUT_TILED && bits == 16) {
+        id = kTiled64;
+    } else if (layout == RESKV_LAYOUT_STRUCTURED && bits == 16) {
+        id = kStruct32;
+    } else if (layout == RESKV_LAYOUT_STRUCTURED && bits == 4) {
+        id = kStructInt4, scale = true;
+    } else {
+        return fail(RESKV_ERR_INVALID, "decode_step: no kernel for layout %d with %d-bit residuals (nnz %d)", layout, bits, nnz);
+    }
+    DecodeArgs a{q, k_centroids, k_ids, k_payload, k_meta, k_scale, v_centroids, v_ids, v_payload, v_meta, v_scale,
+                 batch, kv_heads, q_heads, tokens, tok_stride, k_clusters, v_clusters, start_pos, 0, rope_theta,
+                 inv_freq, scaling, splits, recent_q, window_k, window_v, 0, workspace, workspace_bytes_given, out,
+                 nullptr, nullptr, stream};
+    a.dyn = step_state;
+    a.recent_cap = window_capacity;
+    return decode_common(a, id, meta, scale, "decode_step");
 }
 
 // ---- decode without any caller- or library-side allocation -----------------------------
@@ -879,6 +923,7 @@ static int merge_recent_common(const void* comp_out, const float* comp_m, const 
     mp.rv = static_cast<const __half*>(rv);
     mp.out = static_cast<__half*>(merged);
     mp.kh = kv_heads, mp.nh = q_heads, mp.splits = 0, mp.tr = recent_tokens, mp.scaling = scaling;
+    mp.recent_cap = recent_tokens;
     decode_merge_kernel<<<batch * q_heads, kMergeThreads, 0, static_cast<cudaStream_t>(stream)>>>(mp);
     return check_cuda(cudaGetLastError(), "merge_recent launch");
 }

@@ -42,7 +42,14 @@ struct DecodeParams {
     int kh, nh, tokens, ck, cv;
     int start_pos, pos_q, splits, tiles_per_split;
     float theta, scaling;
+    // optional device-resident step state {query position, dense-window tokens}: when set it
+    // overrides pos_q (and the merge kernel's recent-token count), so that a captured CUDA graph
+    // can be replayed for consecutive decode steps
+    const int32_t* dyn;
 };
+
+// query position of this launch: from the device step state when one is attached
+__device__ __forceinline__ int query_position(const DecodeParams& p) { return p.dyn ? p.dyn[0] : p.pos_q; }
 
 namespace {
 

@@ -447,7 +447,7 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
                 if (tile_rel % kReseedTiles == 0) {
-                    const float delta = static_cast<float>(p.pos_q - (p.start_pos + t0));
+                    const float delta = static_cast<float>(query_position(p) - (p.start_pos + t0));
                     sincosf(delta * q_f[it][u], &st_s[it][u], &st_c[it][u]);
                 }
                 const float c = st_c[it][u], s = st_s[it][u];
