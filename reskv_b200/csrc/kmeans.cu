@@ -2,7 +2,12 @@
 // centroid accumulation, centroid update, and the decode-time incremental step.
 //
 // Assignment is the exact nearest centre in FP32 (squared differences summed in
-// a fixed order), lowest index on ties.  Cluster sums are accumulated *exactly*:
+// a fixed order), lowest index on ties.  The bulk of it runs on the tensor cores:
+// |c|^2 - 2 x.c for 16 tokens x 8 centres per mma.sync (centres split into FP16
+// hi + lo so the products are exact), which ranks the centres up to an error far
+// below the FP32 sum's own; a token whose two best candidates are closer than a
+// conservative bound on that error is re-ranked by the exact FP32 sum, so the
+// ids are those of the exact computation.  Cluster sums are accumulated *exactly*:
 // an FP16 value is an integer multiple of 2^-24, so tokens are added as 2^24-
 // scaled integers (split into two 32-bit shared-memory counters per CTA, flushed
 // with 64-bit integer atomics).  Integer addition is associative, which makes
@@ -93,14 +98,34 @@ __device__ __forceinline__ void nearest(const float* cen_s, int clusters, const 
     }
 }
 
-// grid (chunks, units).  Assign the chunk's tokens; accumulate sums and counts.
-__global__ void __launch_bounds__(kThreads) kmeans_assign_kernel(const KmeansParams p, int accumulate) {
+constexpr int kCenHalfStride = 132;  // FP16 centre rows: stride = 2 banks mod 32, so B-fragment loads do not collide
+constexpr float kTieBound = 1.0f / 32768.0f;  // re-rank when (d2 - d1) <= kTieBound * (|x|^2 + max |c|^2)
+
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Offset (in coordinates) of MMA k-step `ks` for quad lane `q`: a lane owns coordinates
+// [16 q, 16 q + 16) and [64 + 16 q, 64 + 16 q + 16), four per k-step.
+__device__ __forceinline__ int kstep_offset(int ks, int q) { return (ks < 4 ? 0 : 48) + 16 * q + 4 * ks; }
+
+// grid (chunks, units).  Tensor-core assignment of the chunk's tokens (see the file header), then
+// exact accumulation of sums and counts.  HILO = centres are FP32 (key flavour): use hi + lo FP16.
+template <bool HILO>
+__global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const KmeansParams p, int padded) {
     extern __shared__ __align__(16) unsigned char smem[];
-    float* cen_s = reinterpret_cast<float*>(smem);                             // [C][128]
-    int* lo_s = reinterpret_cast<int*>(cen_s + p.clusters * kHeadDim);         // [C][128] low 20 bits
-    int* hi_s = lo_s + p.clusters * kHeadDim;                                  // [C][128] the rest
-    int* cnt_s = hi_s + p.clusters * kHeadDim;                                 // [C]
-    const int unit = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    float* cen_s = reinterpret_cast<float*>(smem);                              // [C][128] FP32 centres (exact path)
+    int* lo_s = reinterpret_cast<int*>(cen_s + p.clusters * kHeadDim);          // [C][128] low 20 bits
+    int* hi_s = lo_s + p.clusters * kHeadDim;                                   // [C][128] the rest
+    int* cnt_s = hi_s + p.clusters * kHeadDim;                                  // [C]
+    float* cn_s = reinterpret_cast<float*>(cnt_s + kMaxClusters);               // [padded] |c|^2, +inf for padding
+    __half* ch_s = reinterpret_cast<__half*>(cn_s + kMaxClusters);              // [padded][132] FP16 hi
+    __half* cl_s = ch_s + padded * kCenHalfStride;                              // [padded][132] FP16 lo (HILO)
+    __shared__ float cmax_s;
+    const int unit = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, q = lane & 3;
     const int t_begin = blockIdx.x * kChunk, t_end = min(p.tokens, t_begin + kChunk);
     const float* cen_g = p.centres + static_cast<size_t>(unit) * p.clusters * kHeadDim;
     for (int i = tid; i < p.clusters * kHeadDim; i += kThreads) {
@@ -108,28 +133,153 @@ __global__ void __launch_bounds__(kThreads) kmeans_assign_kernel(const KmeansPar
         lo_s[i] = 0;
         hi_s[i] = 0;
     }
-    for (int c = tid; c < p.clusters; c += kThreads) cnt_s[c] = 0;
+    for (int i = tid; i < padded * kHeadDim; i += kThreads) {
+        const int c = i / kHeadDim, d = i % kHeadDim;
+        const float v = c < p.clusters ? cen_g[i] : 0.f;
+        const __half h = __float2half_rn(v);
+        ch_s[c * kCenHalfStride + d] = h;
+        if (HILO) cl_s[c * kCenHalfStride + d] = __float2half_rn(v - __half2float(h));
+    }
+    for (int c = tid; c < kMaxClusters; c += kThreads) cnt_s[c] = 0;
     __syncthreads();
-    for (int t = t_begin + warp; t < t_end; t += kWarps) {
-        const __half* xr = p.x + (static_cast<size_t>(unit) * p.x_stride + t) * kHeadDim;
-        float xv[4];
+    // |c|^2 of the value the MMA actually sees (hi + lo), one warp per centre
+    for (int c = warp; c < padded; c += kWarps) {
+        float acc = 0.f;
+        if (c < p.clusters) {
+            for (int d = lane; d < kHeadDim; d += 32) {
+                float v = __half2float(ch_s[c * kCenHalfStride + d]);
+                if (HILO) v += __half2float(cl_s[c * kCenHalfStride + d]);
+                acc = fmaf(v, v, acc);
+            }
+            for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(kFull, acc, off);
+        } else {
+            acc = INFINITY;
+        }
+        if (lane == 0) cn_s[c] = acc;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float m = 0.f;
+        for (int c = 0; c < p.clusters; ++c) m = fmaxf(m, cn_s[c]);
+        cmax_s = m;
+    }
+    __syncthreads();
+    const float cmax = cmax_s;
+    const __half* xu = p.x + static_cast<size_t>(unit) * p.x_stride * kHeadDim;
+
+    for (int t0 = t_begin + warp * 16; t0 < t_end; t0 += kWarps * 16) {
+        // A fragments: rows t0 + g and t0 + g + 8, the lane's 32 coordinates of each
+        const int r0 = t0 + g, r1 = t0 + g + 8;
+        uint32_t a[8][4];
+        {
+            uint4 v[2][4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) xv[i] = __half2float(xr[lane + 32 * i]);
-        float best;
-        int c;
-        nearest(cen_s, p.clusters, xv, lane, best, c);
-        if (lane == 0) p.ids[static_cast<size_t>(unit) * p.tokens + t] = c;
-        if (accumulate) {
+            for (int r = 0; r < 2; ++r) {
+                const int row = r ? r1 : r0;
+                const uint4* src = reinterpret_cast<const uint4*>(xu + static_cast<size_t>(row) * kHeadDim);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    v[r][k] = row < t_end ? __ldg(src + (k < 2 ? 0 : 8) + 2 * q + (k & 1)) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                a[2 * k][0] = v[0][k].x, a[2 * k][1] = v[1][k].x, a[2 * k][2] = v[0][k].y, a[2 * k][3] = v[1][k].y;
+                a[2 * k + 1][0] = v[0][k].z, a[2 * k + 1][1] = v[1][k].z, a[2 * k + 1][2] = v[0][k].w, a[2 * k + 1][3] = v[1][k].w;
+            }
+        }
+        // |x|^2 of the 16 rows: diagonal of X X^T (B fragments are the A registers themselves)
+        float xn0, xn1;
+        {
+            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                mma_f16(s0, a[ks][0], a[ks][1], a[ks][2], a[ks][3], a[ks][0], a[ks][2]);
+                mma_f16(s1, a[ks][0], a[ks][1], a[ks][2], a[ks][3], a[ks][1], a[ks][3]);
+            }
+            // row g x token g sits in lane (g, g / 2), element g % 2; row g + 8 x token g + 8 likewise in s1[2..3]
+            const float mine0 = (g & 1) ? s0[1] : s0[0], mine1 = (g & 1) ? s1[3] : s1[2];
+            xn0 = __shfl_sync(kFull, mine0, 4 * g + (g >> 1));
+            xn1 = __shfl_sync(kFull, mine1, 4 * g + (g >> 1));
+        }
+        float d1[2] = {INFINITY, INFINITY}, d2[2] = {INFINITY, INFINITY};
+        int c1[2] = {0, 0};
+        for (int nb = 0; nb < padded / 8; ++nb) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            const __half* hrow = ch_s + (nb * 8 + g) * kCenHalfStride;
+            const __half* lrow = cl_s + (nb * 8 + g) * kCenHalfStride;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                const uint2 bh = *reinterpret_cast<const uint2*>(hrow + kstep_offset(ks, q));
+                mma_f16(acc, a[ks][0], a[ks][1], a[ks][2], a[ks][3], bh.x, bh.y);
+                if (HILO) {
+                    const uint2 bl = *reinterpret_cast<const uint2*>(lrow + kstep_offset(ks, q));
+                    mma_f16(acc, a[ks][0], a[ks][1], a[ks][2], a[ks][3], bl.x, bl.y);
+                }
+            }
+            const int col = nb * 8 + 2 * q;
+            const float n0 = cn_s[col], n1 = cn_s[col + 1];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = e >> 1, c = col + (e & 1);
+                const float d = fmaf(-2.f, acc[e], (e & 1) ? n1 : n0);
+                if (d < d1[r]) {
+                    d2[r] = d1[r], d1[r] = d, c1[r] = c;
+                } else if (d < d2[r]) {
+                    d2[r] = d;
+                }
+            }
+        }
+#pragma unroll
+        for (int off = 1; off <= 2; off <<= 1) {
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const float od1 = __shfl_xor_sync(kFull, d1[r], off), od2 = __shfl_xor_sync(kFull, d2[r], off);
+                const int oc1 = __shfl_xor_sync(kFull, c1[r], off);
+                if (od1 < d1[r] || (od1 == d1[r] && oc1 < c1[r])) {
+                    d2[r] = fminf(d1[r], od2), d1[r] = od1, c1[r] = oc1;
+                } else {
+                    d2[r] = fminf(d2[r], od1);
+                }
+            }
+        }
+        // near-ties: re-rank with the exact FP32 sum (all lanes of the warp take part)
+        const bool tie0 = r0 < t_end && (d2[0] - d1[0]) <= kTieBound * (xn0 + cmax);
+        const bool tie1 = r1 < t_end && (d2[1] - d1[1]) <= kTieBound * (xn1 + cmax);
+        uint32_t redo0 = __ballot_sync(kFull, tie0 && q == 0), redo1 = __ballot_sync(kFull, tie1 && q == 0);
+        for (int half = 0; half < 2; ++half) {
+            uint32_t redo = half ? redo1 : redo0;
+            while (redo) {
+                const int src = __ffs(redo) - 1;
+                redo &= redo - 1;
+                const int row = t0 + (src >> 2) + 8 * half;
+                const __half* xr = xu + static_cast<size_t>(row) * kHeadDim;
+                float xv[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) xv[i] = __half2float(xr[lane + 32 * i]);
+                float best;
+                int c;
+                nearest(cen_s, p.clusters, xv, lane, best, c);
+                if ((lane >> 2) == (src >> 2)) c1[half] = c;
+            }
+        }
+        if (q == 0) {
+            if (r0 < t_end) p.ids[static_cast<size_t>(unit) * p.tokens + r0] = c1[0];
+            if (r1 < t_end) p.ids[static_cast<size_t>(unit) * p.tokens + r1] = c1[1];
+        }
+        // exact accumulation, one token at a time with the warp across its coordinates
+        const int rows = min(16, t_end - t0);
+        for (int r = 0; r < rows; ++r) {
+            const int c = __shfl_sync(kFull, (r & 8) ? c1[1] : c1[0], 4 * (r & 7));
+            const __half* xr = xu + static_cast<size_t>(t0 + r) * kHeadDim;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const long long fx = static_cast<long long>(xv[i] * kFix);  // exact
+                const long long fx = static_cast<long long>(__half2float(xr[lane + 32 * i]) * kFix);  // exact
                 atomicAdd(&lo_s[c * kHeadDim + lane + 32 * i], static_cast<int>(fx & 0xfffff));
                 atomicAdd(&hi_s[c * kHeadDim + lane + 32 * i], static_cast<int>(fx >> 20));
             }
             if (lane == 0) atomicAdd(&cnt_s[c], 1);
         }
     }
-    if (!accumulate) return;
     __syncthreads();
     long long* sums_g = p.sums + static_cast<size_t>(unit) * p.clusters * kHeadDim;
     for (int i = tid; i < p.clusters * kHeadDim; i += kThreads) {
@@ -260,16 +410,19 @@ extern "C" int reskv_kmeans(const void* x, int batch, int kv_heads, int tokens, 
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     kmeans_init_kernel<<<units, 256, 0, s>>>(p, init, value);
-    const size_t smem = static_cast<size_t>(clusters) * kHeadDim * (sizeof(float) + 2 * sizeof(int)) + clusters * sizeof(int);
+    const int padded = (clusters + 7) / 8 * 8;
+    const size_t smem = static_cast<size_t>(clusters) * kHeadDim * (sizeof(float) + 2 * sizeof(int)) +
+                        kMaxClusters * (sizeof(int) + sizeof(float)) +
+                        static_cast<size_t>(padded) * kCenHalfStride * sizeof(__half) * (value ? 1 : 2);
+    auto kernel = value ? kmeans_assign_mma_kernel<false> : kmeans_assign_mma_kernel<true>;
     if (smem > 48 * 1024) {
-        if (int rc = check_cuda(cudaFuncSetAttribute(kmeans_assign_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                     static_cast<int>(smem)),
+        if (int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
                                 "cudaFuncSetAttribute(kmeans_assign)"))
             return rc;
     }
     const dim3 grid((tokens + kChunk - 1) / kChunk, units);
     for (int it = 0; it < iterations; ++it) {
-        kmeans_assign_kernel<<<grid, kThreads, smem, s>>>(p, 1);
+        kernel<<<grid, kThreads, smem, s>>>(p, padded);
         kmeans_update_kernel<<<units, 256, 0, s>>>(p, value, it + 1 == iterations ? static_cast<__half*>(centroids) : nullptr);
     }
     return check_cuda(cudaGetLastError(), "kmeans launch");
