@@ -70,6 +70,8 @@ def parse():
                          "--context tokens, greedy decode) with the compressed and with a dense FP16 cache "
                          "(extra key 'model')")
     ap.add_argument("--model-new-tokens", type=int, default=128)
+    ap.add_argument("--plans", action="store_true",
+                    help="also time the attention kernel of every residual layout at --batch / --context (extra key 'plans')")
     ap.add_argument("--sweep", action="store_true",
                     help="also time attention and a prefill compression at batch 1/4/8/16/32 (extra key 'sweep')")
     return ap.parse_args()
@@ -286,6 +288,62 @@ def run_sweep(a, dev, cfg, inv_freq, nnz):
     return out
 
 
+PLANS = (  # (name, sparsity, bits, layout, K+V bytes per compressed token and KV head)
+    ("fp16_unstructured_s075", 0.75, 16, "unstructured", 162),
+    ("fp16_unstructured_s050", 0.5, 16, "unstructured", 290),
+    ("fp16_tiled_s050", 0.5, 16, "tiled", 290),
+    ("fp16_structured_4of16", 0.75, 16, "structured", 162),
+    ("int4_unstructured_s050", 0.5, 4, "unstructured", 134),
+    ("int2_unstructured_s050", 0.5, 2, "unstructured", 70),
+    ("int4_structured_1of4", 0.75, 4, "structured", 54),
+)
+
+
+def run_plans(a, dev, inv_freq):
+    """Partial-kernel time of the decode attention for each residual layout (CUDA events around the
+    launch, 20 calls each) at the configured batch and context; K-means iterations as configured."""
+    import torch
+
+    import reskv_b200._extension as ext
+    from reskv_b200 import ResKVKernelConfig, attention, compress
+    from reskv_b200.synthetic import gaussian, mixture
+
+    lib = ext.library()
+    k = mixture(a.batch, H_KV, a.context, seed=7, device=dev)
+    v = mixture(a.batch, H_KV, a.context, seed=8, device=dev)
+    n = (a.context - RECENT) // GROUP * GROUP
+    kc, vc = k[:, :, :n].contiguous(), v[:, :, :n].contiguous()
+    q = gaussian(a.batch, H_Q, 1, DIM, seed=9, device=dev)
+    qr = rope(q, a.context, inv_freq)
+    kr, vr = k[:, :, n:].contiguous(), v[:, :, n:].contiguous()
+    out = []
+    for name, sparsity, bits, layout, per_token in PLANS:
+        cfg = ResKVKernelConfig(sparsity=sparsity, bits=bits, layout=layout, num_clusters=CLUSTERS,
+                                max_clusters=MAX_CLUSTERS, group_size=GROUP, recent_size=RECENT,
+                                kmeans_iterations=ITERS)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        compress(kc, vc, cfg)  # warm-up
+        ev[0].record()
+        cache = compress(kc, vc, cfg)
+        ev[1].record()
+        for e in ev[2:]:
+            e.record()
+        times = []
+        for i in range(24):
+            lib.reskv_decode_set_timing_events(ev[2].cuda_event, ev[3].cuda_event)
+            attention(q, cache, position=a.context, inv_freq=inv_freq, recent=(qr, kr, vr))
+            lib.reskv_decode_set_timing_events(None, None)
+            torch.cuda.synchronize()
+            if i >= 4:
+                times.append(ev[2].elapsed_time(ev[3]))
+        ms = statistics.median(times)
+        nbytes = a.batch * H_KV * (n * per_token + 2 * CLUSTERS * 256 + (a.context - n) * 512) + a.batch * H_Q * DIM * 4
+        out.append({"plan": name, "attention_partial_kernel_ms": ms, "GBps": nbytes / ms / 1e6,
+                    "cluster_and_compress_ms": ev[0].elapsed_time(ev[1])})
+        del cache
+    return out
+
+
 def run_model(a, dev):
     """Prefill + greedy decode of the Llama-3.1-8B-shaped model (random FP16 weights, uniform random
     prompt ids as in the reference's benchmarks/timing.py:60-66) with both cache kinds."""
@@ -465,6 +523,7 @@ def run_gpu(a):
     sweep = None
     if a.sweep and world == 1:
         sweep = run_sweep(a, dev, cfg, inv_freq, nnz)
+    plans = run_plans(a, dev, inv_freq) if a.plans and world == 1 else None
     model_runs = None
     if a.model_batches and world == 1:
         del layer, q_all, k_new, v_new, q_rot, k_rot
@@ -508,6 +567,8 @@ def run_gpu(a):
         }
         if sweep is not None:
             line["sweep"] = sweep
+        if plans is not None:
+            line["plans"] = plans
         if model_runs is not None:
             line["model"] = model_runs
         if world == 1 and not a.no_cpu_baseline:

@@ -62,10 +62,10 @@ __device__ __forceinline__ void select_topk(const uint32_t (&key)[4], int k, int
 #pragma unroll
     for (int bit = 14; bit >= 0; --bit) {
         const uint32_t cand = v | (1u << bit);
-        int cnt = 0;
+        int mine = 0;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) cnt += __popc(__ballot_sync(kFull, key[i] >= cand));
-        if (cnt >= k) v = cand;
+        for (int i = 0; i < 4; ++i) mine += key[i] >= cand;
+        if (__reduce_add_sync(kFull, mine) >= k) v = cand;
     }
     int above = 0;
     uint32_t eq[4];

@@ -299,6 +299,7 @@ class ResKVLlama:
 
         self._tok_in = torch.zeros(batch, dtype=torch.long, device=self.device)
         self._graph = None
+        self._warmed = False
         if self.cache_kind == "reskv":
             live = self.caches[0].live
             self._state = torch.tensor([self.length, live], dtype=torch.int32, device=self.device)
@@ -325,8 +326,9 @@ class ResKVLlama:
             self._graph = None
             return logits
         self._tok_in.copy_(tokens)
-        if self._graph is None:
-            # warm-up outside capture (library handles, lazy inits), on a state copy that is restored
+        if self._graph is None and not self._warmed:
+            # once: a warm-up outside capture (library handles, lazy inits), on a state copy that is restored
+            self._warmed = True
             saved = self._state.clone()
             saved_len = None if self.cache_kind == "reskv" else self._seqlens.clone()
             side = torch.cuda.Stream(device=self.device)
@@ -337,6 +339,7 @@ class ResKVLlama:
             self._state.copy_(saved)
             if saved_len is not None:
                 self._seqlens.copy_(saved_len)
+        if self._graph is None:
             self._graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self._graph):
                 self._logits_out = self._step_body(self._tok_in)
