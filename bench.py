@@ -70,6 +70,9 @@ def parse():
                          "--context tokens, greedy decode) with the compressed and with a dense FP16 cache "
                          "(extra key 'model')")
     ap.add_argument("--model-new-tokens", type=int, default=128)
+    ap.add_argument("--model-tp", action="store_true",
+                    help="under torchrun: run the --model-batches model tensor-parallel over all ranks (NCCL "
+                         "all-reduce after the output and down projections) instead of skipping it")
     ap.add_argument("--plans", action="store_true",
                     help="also time the attention kernel of every residual layout at --batch / --context (extra key 'plans')")
     ap.add_argument("--sweep", action="store_true",
@@ -344,10 +347,12 @@ def run_plans(a, dev, inv_freq):
     return out
 
 
-def run_model(a, dev):
+def run_model(a, dev, group=None):
     """Prefill + greedy decode of the Llama-3.1-8B-shaped model (random FP16 weights, uniform random
-    prompt ids as in the reference's benchmarks/timing.py:60-66) with both cache kinds."""
+    prompt ids as in the reference's benchmarks/timing.py:60-66) with both cache kinds.  With a process
+    group the model is tensor-parallel over it and times are the maximum over ranks."""
     import torch
+    import torch.distributed as dist
 
     from reskv_b200 import ResKVKernelConfig
     from reskv_b200.models import LlamaShape, ResKVLlama
@@ -355,8 +360,16 @@ def run_model(a, dev):
     cfg = ResKVKernelConfig(sparsity=a.sparsity, bits=16, layout="unstructured", num_clusters=CLUSTERS,
                             max_clusters=MAX_CLUSTERS, group_size=GROUP, recent_size=RECENT, kmeans_iterations=ITERS)
     shape = LlamaShape()
-    model = ResKVLlama(shape, cfg, device=dev, seed=0)
+    model = ResKVLlama(shape, cfg, device=dev, seed=0, group=group)
     out = []
+
+    def slowest(ms):
+        if group is None:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        return t.item()
+
     n_new = a.model_new_tokens
     for batch in [int(x) for x in a.model_batches.split(",")]:
         ids = torch.randint(128, shape.vocab, (batch, a.context), generator=torch.Generator().manual_seed(42)).to(dev)
@@ -368,7 +381,7 @@ def run_model(a, dev):
             t0 = time.perf_counter()
             logits = model.prefill(ids, reserve=n_new + 8)
             torch.cuda.synchronize()
-            prefill_ms = (time.perf_counter() - t0) * 1e3
+            prefill_ms = slowest((time.perf_counter() - t0) * 1e3)
             tok = logits.argmax(-1)
             mode = "graph"
             try:
@@ -385,8 +398,9 @@ def run_model(a, dev):
             for _ in range(n_new):
                 tok = step(tok).argmax(-1)
             torch.cuda.synchronize()
-            decode_ms = (time.perf_counter() - t0) * 1e3
+            decode_ms = slowest((time.perf_counter() - t0) * 1e3)
             out.append({"batch": batch, "cache": kind, "decode_loop": mode, "context": a.context, "new_tokens": n_new,
+                        "tensor_parallel": model.tp,
                         "prefill_ms": prefill_ms, "tpot_ms": decode_ms / n_new,
                         "decode_tok_per_s": batch * n_new / (decode_ms * 1e-3),
                         "cache_bytes": model.cache_bytes()})
@@ -525,10 +539,10 @@ def run_gpu(a):
         sweep = run_sweep(a, dev, cfg, inv_freq, nnz)
     plans = run_plans(a, dev, inv_freq) if a.plans and world == 1 else None
     model_runs = None
-    if a.model_batches and world == 1:
+    if a.model_batches and (world == 1 or a.model_tp):
         del layer, q_all, k_new, v_new, q_rot, k_rot
         torch.cuda.empty_cache()
-        model_runs = run_model(a, dev)
+        model_runs = run_model(a, dev, dist.group.WORLD if world > 1 else None)
     clock_summary = clocks.summary()
     if rank == 0:
         peaks = {}

@@ -109,16 +109,22 @@ int reskv_decode_packed(int layout, int bits, const void* q, const void* k_centr
  * No counterpart in the reference (its decode loop is eager Python,
  * benchmarks/timing.py:105-145, and passes positions by value).
  *
- * step_state is two int32 in device memory: {query position, tokens in the dense
- * window including the token of this step}.  reskv_window_append writes the new
- * token's rotated key, raw key and value (f16 [B*KH,128] each) into slot
- * step_state[1] - 1 of the window buffers (f16 [B*KH,window_capacity,128]);
- * reskv_decode_step is reskv_decode_bitmap_fp16 /
- * reskv_decode_packed with the query position and the window length read from
- * step_state inside the kernels (layout UNSTRUCTURED with bits 16 selects the bitmap
- * kernels, nnz = payload width); reskv_step_advance adds to both numbers.  A graph that
- * holds "advance(0, 1), then per layer append + decode, advance(1, 0)" can be replayed for consecutive steps until the
- * compressed segment changes (every group_size steps). */
+ * step_state is four int32 in device memory: {query position, tokens in the dense
+ * window including the token of this step, compressed tokens or -1, reserved}.
+ * reskv_window_append writes the new token's rotated key, raw key and value
+ * (f16 [B*KH,128] each) into slot step_state[1] - 1 of the window buffers
+ * (f16 [B*KH,window_capacity,128]); reskv_decode_step is reskv_decode_bitmap_fp16 /
+ * reskv_decode_packed with the query position, the window length and -- when
+ * step_state[2] >= 0 -- the compressed token count read from step_state inside the
+ * kernels (layout UNSTRUCTURED with bits 16 selects the bitmap kernels, nnz = payload
+ * width; `tokens` then only sizes the split count and is what the kernels use when
+ * step_state[2] < 0; a count above tok_stride is cut to tok_stride; with 8-byte
+ * metadata rows the count must keep the parity of `tokens`); reskv_step_advance adds
+ * to the first two numbers.  A graph that holds "advance(0, 1), then per layer append +
+ * decode, advance(1, 0)" can be replayed for consecutive steps.  It stays valid across
+ * group compressions if the compressed segment grows in place (same addresses, token
+ * stride and centroid-table shape: pass tables padded to a fixed number of rows, unused
+ * rows finite) and the host writes the new counts into step_state between replays. */
 int reskv_window_append(void* window_k, void* window_raw, void* window_v, const void* k_rot, const void* k_raw,
                         const void* v, int batch, int kv_heads, int window_capacity, const int32_t* step_state,
                         void* stream);

@@ -186,9 +186,11 @@ __global__ void __launch_bounds__(kThreads, 2) decode_simt_partial_kernel(const 
     const int split = blockIdx.x, unit = blockIdx.y;
     const int b = unit / p.kh, hkv = unit % p.kh;
 
-    const int total_tiles = (p.tokens + kTile - 1) / kTile;
-    const int tile_begin = split * p.tiles_per_split;
-    const int tile_end = min(total_tiles, tile_begin + p.tiles_per_split);
+    const int tokens = token_count(p);
+    const int total_tiles = (tokens + kTile - 1) / kTile;
+    const int per_split = split_tiles(p, total_tiles);
+    const int tile_begin = split * per_split;
+    const int tile_end = min(total_tiles, tile_begin + per_split);
     const int ntiles = max(0, tile_end - tile_begin);
 
     const size_t unit_tok = static_cast<size_t>(unit) * p.tok_stride;
@@ -211,7 +213,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_simt_partial_kernel(const 
     auto issue = [&](int tile_rel) {
         // one thread: bulk copies of tile `tile_rel` into its ring slot
         const int t0 = (tile_begin + tile_rel) * kTile;
-        const int n = min(kTile, p.tokens - t0);
+        const int n = min(kTile, tokens - t0);
         StageT& st = stages[tile_rel % kStages];
         uint64_t* bar = &full_bar[tile_rel % kStages];
         const uint32_t pl_bytes = n * L::kPayloadBytes;
@@ -229,7 +231,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_simt_partial_kernel(const 
         if constexpr (!kMetaBulk && L::kMetaBytes > 0) {
             if (tile_rel >= ntiles) return;
             const int t0 = (tile_begin + tile_rel) * kTile;
-            const int words = min(kTile, p.tokens - t0) * (L::kMetaBytes / 4);
+            const int words = min(kTile, tokens - t0) * (L::kMetaBytes / 4);
             StageT& st = stages[tile_rel % kStages];
             const uint32_t* ksrc = reinterpret_cast<const uint32_t*>(km_g + static_cast<size_t>(t0) * L::kMetaBytes);
             const uint32_t* vsrc = reinterpret_cast<const uint32_t*>(vm_g + static_cast<size_t>(t0) * L::kMetaBytes);
@@ -293,7 +295,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_simt_partial_kernel(const 
         kid = vid = 0;
         ksc = vsc = 0.f;
         const int t = (tile_begin + tile_rel) * kTile + warp + kWarps * lane;
-        if (tile_rel < ntiles && lane < kTokPerWarp && t < p.tokens) {
+        if (tile_rel < ntiles && lane < kTokPerWarp && t < tokens) {
             kid = kid_g[t];
             vid = vid_g[t];
             if constexpr (L::kScale) {
@@ -324,7 +326,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_simt_partial_kernel(const 
 #pragma unroll 2
         for (int j = 0; j < kTokPerWarp; ++j) {
             const int tl = warp + kWarps * j;  // token within the tile
-            if (t0 + tl < p.tokens) {
+            if (t0 + tl < tokens) {
                 const int kid = __shfl_sync(0xffffffffu, kid_cur, j);
                 const int vid = __shfl_sync(0xffffffffu, vid_cur, j);
                 float ksc = 0.f, vsc = 0.f;

@@ -42,11 +42,26 @@ struct DecodeParams {
     int kh, nh, tokens, ck, cv;
     int start_pos, pos_q, splits, tiles_per_split;
     float theta, scaling;
-    // optional device-resident step state {query position, dense-window tokens}: when set it
-    // overrides pos_q (and the merge kernel's recent-token count), so that a captured CUDA graph
-    // can be replayed for consecutive decode steps
+    // optional device-resident step state {query position, dense-window tokens, compressed tokens
+    // or -1, reserved}: when set it overrides pos_q, the merge kernel's recent-token count and
+    // (third word, if not negative) `tokens`, so that a captured CUDA graph can be replayed for
+    // consecutive decode steps and across group compressions
     const int32_t* dyn;
 };
+
+// compressed tokens of this launch: from the device step state when it carries a count
+__device__ __forceinline__ int token_count(const DecodeParams& p) {
+    if (p.dyn) {
+        const int t = p.dyn[2];
+        if (t >= 0) return static_cast<int>(min(static_cast<int64_t>(t), p.tok_stride));
+    }
+    return p.tokens;
+}
+
+// tiles per split: the host's figure, or the same formula on the device-side token count
+__device__ __forceinline__ int split_tiles(const DecodeParams& p, int total_tiles) {
+    return p.dyn ? (total_tiles + p.splits - 1) / p.splits : p.tiles_per_split;
+}
 
 // query position of this launch: from the device step state when one is attached
 __device__ __forceinline__ int query_position(const DecodeParams& p) { return p.dyn ? p.dyn[0] : p.pos_q; }

@@ -352,9 +352,11 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, qd = lane & 3;
     const int split = blockIdx.x, unit = blockIdx.y;
     const int b = unit / p.kh, hkv = unit % p.kh;
-    const int total_tiles = (p.tokens + kTileM - 1) / kTileM;
-    const int tile_begin = split * p.tiles_per_split;
-    const int ntiles = max(0, min(total_tiles, tile_begin + p.tiles_per_split) - tile_begin);
+    const int tokens = token_count(p);
+    const int total_tiles = (tokens + kTileM - 1) / kTileM;
+    const int per_split = split_tiles(p, total_tiles);
+    const int tile_begin = split * per_split;
+    const int ntiles = max(0, min(total_tiles, tile_begin + per_split) - tile_begin);
 
     const size_t unit_tok = static_cast<size_t>(unit) * p.tok_stride;
     const unsigned char* km_g = static_cast<const unsigned char*>(p.kb) + unit_tok * ML::kMetaBytes;
@@ -374,7 +376,7 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
     __syncthreads();
     auto issue = [&](int tile_rel) {
         const int t0 = (tile_begin + tile_rel) * kTileM;
-        const int n = min(kTileM, p.tokens - t0);
+        const int n = min(kTileM, tokens - t0);
         StageT& st = stages[tile_rel % kStages];
         uint64_t* bar = &full_bar[tile_rel % kStages];
         // 8-byte metadata rows stay bulk-copyable: tiles start at multiples of 64 tokens and the host
@@ -487,7 +489,7 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
     auto load_ids = [&](int tile_rel, int& id, uint32_t& scale) {
         const int t = (tile_begin + tile_rel) * kTileM + warp * 16 + (lane & 15);
         id = 0, scale = 0u;
-        if (tile_rel < ntiles && t < p.tokens) {
+        if (tile_rel < ntiles && t < tokens) {
             // volatile: issue the loads here, a whole tile ahead of their use, instead of letting the
             // compiler sink them next to the consumer
             const int8_t* src = ((lane < 16) ? kid_g : vid_g) + t;
@@ -528,7 +530,7 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
         load_ids(it + 1, ids_next, scl_next);
         if (!mbar_wait(&full_bar[it % kStages], (it / kStages) & 1)) lost = true;
         const StageT& st = stages[it % kStages];
-        const int nvalid = min(16, p.tokens - (t0 + warp * 16));  // valid tokens of this warp's block
+        const int nvalid = min(16, tokens - (t0 + warp * 16));  // valid tokens of this warp's block
         if (nvalid > 0) {
             if constexpr (ML::kPrefix) {
                 // rank bases of the block's 16 key bitmaps (lanes 0..15) and value bitmaps (16..31)

@@ -247,7 +247,7 @@ class ResKVLlama:
             # attention of this step already includes it
             check(lib.reskv_step_advance(self._state.data_ptr(), 0, 1, stream))
         x = self.embed[tok].unsqueeze(1)
-        for layer, cache in zip(self.layers, self.caches):
+        for index, (layer, cache) in enumerate(zip(self.layers, self.caches)):
             q, k, v = self._qkv(layer, x)
             qr, kr = _rope(q, cos, sin), _rope(k, cos, sin)
             if self.cache_kind == "reskv":
@@ -258,8 +258,9 @@ class ResKVLlama:
                                               cap, self._state.data_ptr(), stream))
                 key, val = cache.compressed.key, cache.compressed.value
                 plan = key.plan
-                kc, ki, kp, km, ks = key._native
-                vc, vi, vp, vm, vs = val._native
+                _, ki, kp, km, ks = key._native
+                _, vi, vp, vm, vs = val._native
+                kc, vc = self._centroids[index]
                 layout = {"unstructured": LAYOUT_UNSTRUCTURED, "tiled": LAYOUT_TILED, "structured": LAYOUT_STRUCTURED}[plan.layout]
                 qf = q.reshape(b * self.h_q, 128).contiguous()
                 qrf = qr.reshape(b * self.h_q, 128).contiguous()
@@ -268,6 +269,8 @@ class ResKVLlama:
                 def ptr(t):
                     return None if t is None else t.data_ptr()
 
+                # token count and centroid tables are read from the step state / fixed-shape tables,
+                # so the captured launch stays valid when a group is compressed between replays
                 check(lib.reskv_decode_step(layout, plan.bits, kp.shape[2], qf.data_ptr(), kc.data_ptr(), ki.data_ptr(),
                                             kp.data_ptr(), ptr(km), ptr(ks), vc.data_ptr(), vi.data_ptr(), vp.data_ptr(),
                                             ptr(vm), ptr(vs), b, self.h_kv, self.h_q, key.seq_len, key.token_stride,
@@ -301,8 +304,12 @@ class ResKVLlama:
         self._graph = None
         self._warmed = False
         if self.cache_kind == "reskv":
-            live = self.caches[0].live
-            self._state = torch.tensor([self.length, live], dtype=torch.int32, device=self.device)
+            self._state = torch.zeros(4, dtype=torch.int32, device=self.device)
+            # centroid tables at their final shape (zero rows beyond the live count), one pair per layer
+            rows = self.kernel_config.max_clusters
+            self._centroids = [tuple(torch.zeros((batch * self.h_kv, rows, 128), dtype=torch.float16, device=self.device)
+                                     for _ in range(2)) for _ in self.caches]
+            self._sync_graph_inputs()
             need = library().reskv_decode_bitmap_fp16_workspace_bytes(batch, self.h_kv, self.h_q, 1 << 20, 64)
             self._workspace = torch.zeros(need, dtype=torch.uint8, device=self.device)
         else:
@@ -314,17 +321,35 @@ class ResKVLlama:
                 c.k = c.k.transpose(1, 2).contiguous()
                 c.v = c.v.transpose(1, 2).contiguous()
 
+    def _sync_graph_inputs(self):
+        """Refresh what a captured step reads: counts in the step state, centroid tables, and the
+        addresses of the compressed buffers (a buffer that had to grow invalidates the graph)."""
+        comp = self.caches[0].compressed
+        self._state.copy_(torch.tensor([self.length, self.caches[0].live, comp.seq_len if comp is not None else -1, 0],
+                                       dtype=torch.int32))
+        addresses = []
+        for cache, (kc, vc) in zip(self.caches, self._centroids):
+            if cache.compressed is None:
+                raise RuntimeError("graph decode needs a compressed segment (prompt shorter than recent + group)")
+            for table, tensor in ((kc, cache.compressed.key), (vc, cache.compressed.value)):
+                native = tensor._native
+                table[:, :native[0].shape[1]].copy_(native[0])
+                addresses += [t.data_ptr() for t in native[1:] if t is not None] + [tensor.token_stride]
+        if addresses != getattr(self, "_graph_addresses", None):
+            self._graph_addresses = addresses
+            self._graph = None
+
     @torch.no_grad()
     def decode_graph(self, tokens: torch.Tensor) -> torch.Tensor:
         """Same result as ``decode`` but replaying a captured CUDA graph of the step."""
         if self.cache_kind == "reskv" and self.caches[0].live + 1 == self.caches[0].keys.shape[2]:
-            # this token fills the window: the eager step compresses the oldest group before it
-            # attends (as the reference does); afterwards the compressed segment is a different one,
-            # so the step state is re-seeded and the graph captured again
-            logits = self.decode(tokens)
-            self._state.copy_(torch.tensor([self.length, self.caches[0].live], dtype=torch.int32))
-            self._graph = None
-            return logits
+            # this token fills the window.  The eager step appends it and then compresses the oldest
+            # group before attending (as the reference does); the group does not contain the new
+            # token, so compressing it first and appending afterwards gives the same cache.  That is
+            # done here, outside the graph; the graph then only needs the new counts.
+            for cache in self.caches:
+                cache._compress_oldest_group()
+            self._sync_graph_inputs()
         self._tok_in.copy_(tokens)
         if self._graph is None and not self._warmed:
             # once: a warm-up outside capture (library handles, lazy inits), on a state copy that is restored

@@ -104,8 +104,8 @@ def test_generation_across_the_compression_boundary():
 
 @pytest.mark.gpu
 def test_graph_decode_matches_eager_decode():
-    """Replaying the captured step (device-side position / window length) gives the eager
-    step's logits, across a group compression (new capture)."""
+    """Replaying the captured step (device-side position, window length and compressed-token
+    count) gives the eager step's logits, across group compressions, with a single capture."""
     from reskv_b200 import ResKVKernelConfig
     from reskv_b200.models import LlamaShape, ResKVLlama
 
@@ -123,5 +123,8 @@ def test_graph_decode_matches_eager_decode():
         lg = graph.decode_graph(tok).clone()
         torch.testing.assert_close(lg, le, atol=2e-2, rtol=2e-2)
         tok = le.argmax(-1)
+        if step == 0:
+            captured = graph._graph
+    assert graph._graph is captured, "the step was captured again"
     assert graph.caches[0].compressed.seq_len == eager.caches[0].compressed.seq_len
     assert graph.caches[0].live == eager.caches[0].live and graph.length == eager.length
