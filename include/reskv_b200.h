@@ -139,6 +139,28 @@ int reskv_decode_step(int layout, int bits, int nnz, const void* q, const void* 
 
 int reskv_step_advance(int32_t* step_state, int position_increment, int window_increment, void* stream);
 
+/* ---- the rest of a decoder layer's decode step, fused -----------------------------------
+ * No counterpart in the reference (it runs Hugging Face modules, modeling.py); a decode
+ * step at small batch is bound by launch count, and these replace ~30 tensor-op launches
+ * per layer by three.  All tensors f16, row-major, on the device.
+ *
+ * reskv_rms_norm:   out[r] = x[r] * rsqrt(mean(x[r]^2) + eps) * weight, FP32 inside; dim % 8 == 0,
+ *                   pointers 16-byte aligned.
+ * reskv_rope_split: qkv [batch, (q_heads + 2 kv_heads) * 128] is the fused projection of one new
+ *                   token per sequence, heads ordered q | k | v.  Writes the raw query (optional)
+ *                   and the query rotated to position step_state[0] ([batch*q_heads,128] each);
+ *                   the key rotated, the raw key and the value go to slot step_state[1] - 1 of
+ *                   the window buffers ([batch*kv_heads,window_capacity,128]) when those are
+ *                   given, and / or to k_rot / v_out ([batch*kv_heads,128]).
+ * reskv_silu_mul:   out[r][j] = silu(gate_up[r][j]) * gate_up[r][ffn + j]; gate_up [rows, 2 ffn]. */
+int reskv_rms_norm(const void* x, const void* weight, void* out, int rows, int dim, float eps, void* stream);
+
+int reskv_rope_split(const void* qkv, int batch, int q_heads, int kv_heads, const float* inv_freq,
+                     const int32_t* step_state, void* q_raw, void* q_rot, void* k_rot, void* v_out, void* window_k,
+                     void* window_raw, void* window_v, int window_capacity, void* stream);
+
+int reskv_silu_mul(const void* gate_up, void* out, int rows, int ffn, void* stream);
+
 /* ---- decode attention for callers that cannot provide scratch memory -------------------
  * No counterpart in the reference (its ops allocate their partial buffers with
  * torch::empty on every call, cluster_mass.cu:1222-1232).

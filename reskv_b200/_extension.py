@@ -55,6 +55,9 @@ SIGNATURES = {
         [_I, _I, _I] + [_P] * 11 + [_I, _I, _I, _I, _L, _I, _I, _I, _F, _P, _F, _I, _P, _P, _P, _I, _P, _P, _Z, _P, _P],
     ),
     "reskv_step_advance": (_I, [_P, _I, _I, _P]),
+    "reskv_rms_norm": (_I, [_P, _P, _P, _I, _I, _F, _P]),
+    "reskv_rope_split": (_I, [_P, _I, _I, _I, _P, _P] + [_P] * 7 + [_I, _P]),
+    "reskv_silu_mul": (_I, [_P, _P, _I, _I, _P]),
     "reskv_decode_auto_splits": (_I, [_I, _I, _I]),
     "reskv_decode_set_variant": (_I, [_I]),
     "reskv_decode_set_timing_events": (_I, [_P, _P]),

@@ -239,61 +239,78 @@ class ResKVLlama:
 
         lib = library()
         b = tok.shape[0]
+        d = self.shape.hidden
         stream = _stream(self.device)
-        ang = self._state[0:1].float()[:, None] * self.inv_freq[None, :]
-        cos, sin = ang.cos(), ang.sin()
-        if self.cache_kind == "reskv":
-            # count the new token into the window first: append writes slot count - 1 and the
+        state = self._state.data_ptr()
+        reskv = self.cache_kind == "reskv"
+
+        def half(*shape):
+            return torch.empty(shape, dtype=torch.float16, device=self.device)
+
+        def norm(x, weight):
+            out = half(b, d)
+            check(lib.reskv_rms_norm(x.data_ptr(), weight.data_ptr(), out.data_ptr(), b, d, float(self.shape.rms_eps), stream))
+            return out
+
+        def ptr(t):
+            return None if t is None else t.data_ptr()
+
+        def project(x, inp, weight):
+            """x + inp @ weight^T, summed over the tensor-parallel group."""
+            if self.tp == 1:
+                return torch.addmm(x, inp, weight.t())
+            return x + self._all_reduce(F.linear(inp, weight))
+
+        if reskv:
+            # count the new token into the window first: it goes to slot count - 1 and the
             # attention of this step already includes it
-            check(lib.reskv_step_advance(self._state.data_ptr(), 0, 1, stream))
-        x = self.embed[tok].unsqueeze(1)
+            check(lib.reskv_step_advance(state, 0, 1, stream))
+        x = self.embed[tok]
         for index, (layer, cache) in enumerate(zip(self.layers, self.caches)):
-            q, k, v = self._qkv(layer, x)
-            qr, kr = _rope(q, cos, sin), _rope(k, cos, sin)
-            if self.cache_kind == "reskv":
+            qkv = F.linear(norm(x, layer["norm1"]), layer["wqkv"])
+            q_rot = half(b * self.h_q, 128)
+            if reskv:
                 cap = cache.keys.shape[2]
-                kraw = k.contiguous()
-                check(lib.reskv_window_append(cache.keys.data_ptr(), cache.raw_keys.data_ptr(), cache.values.data_ptr(),
-                                              kr.contiguous().data_ptr(), kraw.data_ptr(), v.data_ptr(), b, self.h_kv,
-                                              cap, self._state.data_ptr(), stream))
+                q_raw = half(b * self.h_q, 128)
+                check(lib.reskv_rope_split(qkv.data_ptr(), b, self.h_q, self.h_kv, self.inv_freq.data_ptr(), state,
+                                           q_raw.data_ptr(), q_rot.data_ptr(), None, None, cache.keys.data_ptr(),
+                                           cache.raw_keys.data_ptr(), cache.values.data_ptr(), cap, stream))
                 key, val = cache.compressed.key, cache.compressed.value
                 plan = key.plan
                 _, ki, kp, km, ks = key._native
                 _, vi, vp, vm, vs = val._native
                 kc, vc = self._centroids[index]
                 layout = {"unstructured": LAYOUT_UNSTRUCTURED, "tiled": LAYOUT_TILED, "structured": LAYOUT_STRUCTURED}[plan.layout]
-                qf = q.reshape(b * self.h_q, 128).contiguous()
-                qrf = qr.reshape(b * self.h_q, 128).contiguous()
-                out = torch.empty((b * self.h_q, 128), dtype=torch.float16, device=self.device)
-
-                def ptr(t):
-                    return None if t is None else t.data_ptr()
-
+                att = half(b, self.h_q * 128)
                 # token count and centroid tables are read from the step state / fixed-shape tables,
                 # so the captured launch stays valid when a group is compressed between replays
-                check(lib.reskv_decode_step(layout, plan.bits, kp.shape[2], qf.data_ptr(), kc.data_ptr(), ki.data_ptr(),
+                check(lib.reskv_decode_step(layout, plan.bits, kp.shape[2], q_raw.data_ptr(), kc.data_ptr(), ki.data_ptr(),
                                             kp.data_ptr(), ptr(km), ptr(ks), vc.data_ptr(), vi.data_ptr(), vp.data_ptr(),
                                             ptr(vm), ptr(vs), b, self.h_kv, self.h_q, key.seq_len, key.token_stride,
                                             kc.shape[1], vc.shape[1], 0, float(self.shape.rope_theta),
-                                            self.inv_freq.data_ptr(), float(self.scaling), plan.splits, qrf.data_ptr(),
-                                            cache.keys.data_ptr(), cache.values.data_ptr(), cap, self._state.data_ptr(),
-                                            self._workspace.data_ptr(), self._workspace.numel(), out.data_ptr(), stream),
+                                            self.inv_freq.data_ptr(), float(self.scaling), plan.splits, q_rot.data_ptr(),
+                                            cache.keys.data_ptr(), cache.values.data_ptr(), cap, state,
+                                            self._workspace.data_ptr(), self._workspace.numel(), att.data_ptr(), stream),
                       launches=2)
-                att = out.reshape(b, 1, self.h_q * 128)
             elif _flash_kvcache is not None:
-                att = _flash_kvcache(qr.transpose(1, 2), cache.k, cache.v, k=kr.transpose(1, 2), v=v.transpose(1, 2),
+                k_rot, v_new = half(b, 1, self.h_kv, 128), half(b, 1, self.h_kv, 128)
+                check(lib.reskv_rope_split(qkv.data_ptr(), b, self.h_q, self.h_kv, self.inv_freq.data_ptr(), state,
+                                           None, q_rot.data_ptr(), k_rot.data_ptr(), v_new.data_ptr(), None, None, None,
+                                           0, stream))
+                att = _flash_kvcache(q_rot.view(b, 1, self.h_q, 128), cache.k, cache.v, k=k_rot, v=v_new,
                                      cache_seqlens=self._seqlens, softmax_scale=self.scaling, causal=True)
-                att = att.reshape(b, 1, self.h_q * 128)
+                att = att.reshape(b, self.h_q * 128)
             else:
                 raise RuntimeError("graph decode of the dense baseline needs flash_attn")
-            x = x + self._all_reduce(F.linear(att, layer["wo"]))
-            x = x + self._mlp(layer, _rms_norm(x, layer["norm2"], self.shape.rms_eps))
-        if self.cache_kind == "reskv":
-            check(lib.reskv_step_advance(self._state.data_ptr(), 1, 0, stream))
-        else:
-            self._state[0:1] += 1
+            x = project(x, att, layer["wo"])
+            gate_up = F.linear(norm(x, layer["norm2"]), layer["w_gate_up"])
+            act = half(b, self.ffn)
+            check(lib.reskv_silu_mul(gate_up.data_ptr(), act.data_ptr(), b, self.ffn, stream))
+            x = project(x, act, layer["w_down"])
+        check(lib.reskv_step_advance(state, 1, 0, stream))
+        if not reskv:
             self._seqlens += 1
-        return self._logits(x)
+        return F.linear(norm(x, self.final_norm), self.lm_head).float()
 
     @torch.no_grad()
     def begin_graph_decode(self, batch: int):

@@ -131,3 +131,49 @@ def test_window_append_and_advance():
     for w, n in zip(win, new):
         assert torch.equal(w[:, 4], n)
         assert not w[:, :4].any() and not w[:, 5:].any()
+
+
+def test_layer_helpers_match_tensor_ops():
+    """RMS norm, QKV split + RoPE + window append, SiLU * up against plain tensor arithmetic."""
+    from reskv_b200 import _extension as ext
+    from reskv_b200.models.llama import _rms_norm, _rope
+
+    lib = ext.library()
+    stream = ext._stream(torch.device(DEV))
+    g = torch.Generator(device=DEV).manual_seed(5)
+    b, hq, hkv, d, ffn, cap, pos, live = 3, 8, 2, 512, 640, 12, 777, 5
+
+    x = (torch.randn(b, d, generator=g, device=DEV) * 3).half()
+    w = torch.randn(d, generator=g, device=DEV).half()
+    out = torch.empty_like(x)
+    ext.check(lib.reskv_rms_norm(x.data_ptr(), w.data_ptr(), out.data_ptr(), b, d, 1e-5, stream))
+    torch.testing.assert_close(out, _rms_norm(x, w, 1e-5), atol=2e-3, rtol=2e-3)
+
+    qkv = torch.randn(b, (hq + 2 * hkv) * 128, generator=g, device=DEV).half()
+    inv = (500000.0 ** (-torch.arange(64, device=DEV).float() / 64)).contiguous()
+    state = torch.tensor([pos, live, -1, 0], dtype=torch.int32, device=DEV)
+    q_raw, q_rot = (torch.empty(b * hq, 128, dtype=torch.float16, device=DEV) for _ in range(2))
+    k_rot, v_out = (torch.empty(b * hkv, 128, dtype=torch.float16, device=DEV) for _ in range(2))
+    win = [torch.zeros(b * hkv, cap, 128, dtype=torch.float16, device=DEV) for _ in range(3)]
+    ext.check(lib.reskv_rope_split(qkv.data_ptr(), b, hq, hkv, inv.data_ptr(), state.data_ptr(), q_raw.data_ptr(),
+                                   q_rot.data_ptr(), k_rot.data_ptr(), v_out.data_ptr(), *(t.data_ptr() for t in win),
+                                   cap, stream))
+    torch.cuda.synchronize()
+    q, k, v = qkv.split((hq * 128, hkv * 128, hkv * 128), dim=-1)
+    ang = float(pos) * inv
+    cos, sin = ang.cos()[None], ang.sin()[None]
+    want_q = _rope(q.reshape(b, hq, 1, 128), cos, sin).reshape(b * hq, 128)
+    want_k = _rope(k.reshape(b, hkv, 1, 128), cos, sin).reshape(b * hkv, 128)
+    assert torch.equal(q_raw, q.reshape(b * hq, 128)) and torch.equal(v_out, v.reshape(b * hkv, 128))
+    torch.testing.assert_close(q_rot, want_q, atol=2e-3, rtol=2e-3)
+    torch.testing.assert_close(k_rot, want_k, atol=2e-3, rtol=2e-3)
+    assert torch.equal(win[0][:, live - 1], k_rot) and torch.equal(win[1][:, live - 1], k.reshape(b * hkv, 128))
+    assert torch.equal(win[2][:, live - 1], v_out)
+    for t in win:
+        assert not t[:, :live - 1].any() and not t[:, live:].any()
+
+    gu = torch.randn(b, 2 * ffn, generator=g, device=DEV).half()
+    act = torch.empty(b, ffn, dtype=torch.float16, device=DEV)
+    ext.check(lib.reskv_silu_mul(gu.data_ptr(), act.data_ptr(), b, ffn, stream))
+    want = torch.nn.functional.silu(gu[:, :ffn]) * gu[:, ffn:]
+    torch.testing.assert_close(act, want, atol=1e-3, rtol=2e-3)
