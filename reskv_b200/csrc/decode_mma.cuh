@@ -44,21 +44,37 @@ constexpr int kWarpsM = 4;        // one 16-token block per warp and tile
 constexpr int kThreadsM = kWarpsM * 32;
 constexpr int kCenStride = 132;   // floats per centroid row in shared memory (row r starts 4r banks on)
 constexpr int kTrigStride = 64;   // float2 per row of the sin/cos table (swizzled, see trig_index)
+constexpr int kTrigRowsCompact = 16;  // compact table: angles 8 m f_i (rows m = 0..7) and g f_i (rows 8 + g)
 constexpr int kQStride = 132;     // halfs per query row
 constexpr int kQSets = 2;         // query stored as FP16 hi and lo
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
+// Payload rows are staged kPad bytes apart from dense when the layout asks for it: lanes that walk
+// the same field of different tokens then start in different banks.
 template <class ML>
 struct StageM {
-    alignas(16) unsigned char kp[kTileM * ML::kPayloadBytes];
-    alignas(16) unsigned char vp[kTileM * ML::kPayloadBytes];
+    alignas(16) unsigned char kp[kTileM * (ML::kPayloadBytes + ML::kPad)];
+    alignas(16) unsigned char vp[kTileM * (ML::kPayloadBytes + ML::kPad)];
     alignas(16) unsigned char km[kTileM * (ML::kMetaBytes ? ML::kMetaBytes : 1)];
     alignas(16) unsigned char vm[kTileM * (ML::kMetaBytes ? ML::kMetaBytes : 1)];
 };
 
 template <class ML>
 constexpr int stages_for() {
-    return sizeof(StageM<ML>) <= 10240 ? 3 : 2;
+    return sizeof(StageM<ML>) <= 12800 ? 3 : 2;
+}
+
+// The sin/cos values a lane keeps in registers are read once from a shared table.  The full table
+// (64 tile offsets x 64 frequencies, 32 KB) is the cheapest to read; layouts whose ring of stages
+// is large use a 16-row table instead (a tile offset j = 8 m + g is the sum of two table angles,
+// the lane combines its rows by angle addition), so that two CTAs still fit one SM.
+template <class ML>
+constexpr bool compact_trig() {
+    return sizeof(StageM<ML>) * stages_for<ML>() > 40000;
+}
+template <class ML>
+constexpr int trig_rows() {
+    return compact_trig<ML>() ? kTrigRowsCompact : kTileM;
 }
 
 // Shared-memory layouts chosen so that the 16-byte loads of a quarter warp
@@ -104,7 +120,7 @@ __device__ __forceinline__ void split_h2(float x0, float x1, uint32_t& hi, uint3
 
 template <int GQA, class ML>
 constexpr size_t smem_bytes(int ck) {
-    return sizeof(StageM<ML>) * stages_for<ML>() + kTileM * kTrigStride * sizeof(float2) +
+    return sizeof(StageM<ML>) * stages_for<ML>() + trig_rows<ML>() * kTrigStride * sizeof(float2) +
            static_cast<size_t>(ck) * kCenStride * sizeof(float) + 2 * kQSets * GQA * kQStride * sizeof(__half) +
            kWarpsM * 2 * 16 * sizeof(uint2) + kWarpsM * GQA * kMaxClusters * sizeof(float);
 }
@@ -184,14 +200,14 @@ struct WalkField {
 // Unstructured FP16: MSB-first bitmap; rank bases from the per-block table `pre` (8 bytes per token).
 template <int NNZ>
 struct LayoutMmaBitmap {
-    static constexpr int kPayloadBytes = NNZ * 2, kMetaBytes = 16;
+    static constexpr int kPayloadBytes = NNZ * 2, kMetaBytes = 16, kPad = 16;
     static constexpr bool kScale = false, kPrefix = true, kScaleP = false;
     using Field = WalkField;
     __device__ static __forceinline__ Field field(const unsigned char* pay, const unsigned char* meta,
                                                   const unsigned char* pre, int tok, int f, bool ok) {
         Field fd;
         fd.mask = ok ? *reinterpret_cast<const unsigned short*>(meta + tok * 16 + field_offset(f)) : 0u;
-        fd.ptr = reinterpret_cast<const __half*>(pay) + tok * NNZ + pre[(tok & 15) * 8 + f];
+        fd.ptr = reinterpret_cast<const __half*>(pay + tok * (kPayloadBytes + kPad)) + pre[(tok & 15) * 8 + f];
         return fd;
     }
 };
@@ -201,7 +217,7 @@ struct LayoutMmaBitmap {
 // 2w + 1 (high half), i.e. tile f sits at byte 2 f; its values start at f * NNZ / 8.
 template <int NNZ, bool INDEXED>
 struct LayoutMmaTiled {
-    static constexpr int kPayloadBytes = NNZ * 2, kMetaBytes = 16;
+    static constexpr int kPayloadBytes = NNZ * 2, kMetaBytes = 16, kPad = 16;
     static constexpr bool kScale = false, kPrefix = false, kScaleP = false;
     using Field = WalkField;
     __device__ static __forceinline__ Field field(const unsigned char* pay, const unsigned char* meta,
@@ -213,7 +229,7 @@ struct LayoutMmaTiled {
         }
         Field fd;
         fd.mask = __brev(code) >> 16;  // LSB-first -> bit 15 = first coordinate
-        fd.ptr = reinterpret_cast<const __half*>(pay) + tok * NNZ + f * (NNZ / 8);
+        fd.ptr = reinterpret_cast<const __half*>(pay + tok * (kPayloadBytes + kPad)) + f * (NNZ / 8);
         return fd;
     }
 };
@@ -271,7 +287,7 @@ struct QuantField {
 
 template <int BITS>
 struct LayoutMmaQuant {
-    static constexpr int kPayloadBytes = 16 * BITS, kMetaBytes = 0;
+    static constexpr int kPayloadBytes = 16 * BITS, kMetaBytes = 0, kPad = 0;
     static constexpr bool kScale = true, kPrefix = false, kScaleP = true;
     using Field = QuantField<BITS>;
     __device__ static __forceinline__ Field field(const unsigned char* pay, const unsigned char*,
@@ -313,7 +329,7 @@ struct StructInt4Field {
 };
 
 struct LayoutMmaStructInt4 {
-    static constexpr int kPayloadBytes = 16, kMetaBytes = 8;
+    static constexpr int kPayloadBytes = 16, kMetaBytes = 8, kPad = 0;
     static constexpr bool kScale = true, kPrefix = false, kScaleP = true;
     using Field = StructInt4Field;
     __device__ static __forceinline__ Field field(const unsigned char* pay, const unsigned char* meta,
@@ -340,7 +356,7 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
     using Field = typename ML::Field;
     StageT* stages = reinterpret_cast<StageT*>(smem_raw);
     float2* trig = reinterpret_cast<float2*>(smem_raw + sizeof(StageT) * kStages);
-    float* kc_s = reinterpret_cast<float*>(trig + kTileM * kTrigStride);
+    float* kc_s = reinterpret_cast<float*>(trig + trig_rows<ML>() * kTrigStride);
     __half* qf = reinterpret_cast<__half*>(kc_s + static_cast<size_t>(p.ck) * kCenStride);  // [2 bufs][hi, lo][GQA][kQStride]
     uint2* pre = reinterpret_cast<uint2*>(qf + 2 * kQSets * GQA * kQStride);  // [warps][K, V][16]
     float* beta_s = reinterpret_cast<float*>(pre + kWarpsM * 2 * 16);  // [warps][GQA][64]
@@ -370,7 +386,7 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
 
     if (tid == 0) {
         timed_out = 0;
-        for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], 1);
+        for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], ML::kPad ? 1 + kThreadsM : 1);
         mbar_fence_init();
     }
     __syncthreads();
@@ -382,29 +398,57 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
         // 8-byte metadata rows stay bulk-copyable: tiles start at multiples of 64 tokens and the host
         // selects this kernel for them only when token count and token stride are even
         const uint32_t md_bytes = n * ML::kMetaBytes, pl_bytes = n * ML::kPayloadBytes;
-        mbar_arrive_expect_tx(bar, 2 * md_bytes + 2 * pl_bytes);
-        if (ML::kMetaBytes) {
-            bulk_g2s(st.km, km_g + static_cast<size_t>(t0) * ML::kMetaBytes, md_bytes, bar);
-            bulk_g2s(st.vm, vm_g + static_cast<size_t>(t0) * ML::kMetaBytes, md_bytes, bar);
+        const unsigned char* kp_src = kp_g + static_cast<size_t>(t0) * ML::kPayloadBytes;
+        const unsigned char* vp_src = vp_g + static_cast<size_t>(t0) * ML::kPayloadBytes;
+        if constexpr (ML::kPad != 0) {
+            // metadata in bulk by one thread; payload rows in 16-byte pieces by everyone, into padded rows
+            if (tid == 0) {
+                mbar_arrive_expect_tx(bar, 2 * md_bytes);
+                bulk_g2s(st.km, km_g + static_cast<size_t>(t0) * ML::kMetaBytes, md_bytes, bar);
+                bulk_g2s(st.vm, vm_g + static_cast<size_t>(t0) * ML::kMetaBytes, md_bytes, bar);
+            }
+            constexpr int kPieces = ML::kPayloadBytes / 16, kRow = ML::kPayloadBytes + ML::kPad;
+            for (int c = tid; c < n * kPieces; c += kThreadsM) {
+                const int dst = (c / kPieces) * kRow + (c % kPieces) * 16;
+                cp_async16(st.kp + dst, kp_src + c * 16);
+                cp_async16(st.vp + dst, vp_src + c * 16);
+            }
+            cp_async_arrive(bar);
+        } else if (tid == 0) {
+            mbar_arrive_expect_tx(bar, 2 * md_bytes + 2 * pl_bytes);
+            if (ML::kMetaBytes) {
+                bulk_g2s(st.km, km_g + static_cast<size_t>(t0) * ML::kMetaBytes, md_bytes, bar);
+                bulk_g2s(st.vm, vm_g + static_cast<size_t>(t0) * ML::kMetaBytes, md_bytes, bar);
+            }
+            bulk_g2s(st.kp, kp_src, pl_bytes, bar);
+            bulk_g2s(st.vp, vp_src, pl_bytes, bar);
         }
-        bulk_g2s(st.kp, kp_g + static_cast<size_t>(t0) * ML::kPayloadBytes, pl_bytes, bar);
-        bulk_g2s(st.vp, vp_g + static_cast<size_t>(t0) * ML::kPayloadBytes, pl_bytes, bar);
     };
-    if (tid == 0) {
-        for (int s = 0; s < kStages && s < ntiles; ++s) issue(s);
-    }
+    for (int s = 0; s < kStages && s < ntiles; ++s) issue(s);
 
     // ---- tables: sin/cos of (tile offset j) x (frequency i); key centroids; zeroed query rows ----
     {
-        const int i = tid & 63, j0 = (tid >> 6) * 32;
+        const int i = tid & 63, half = tid >> 6;
         const float f = rope_freq(p.inv_freq, p.theta, i);
-        float s, c, s1, c1;
-        sincosf(static_cast<float>(j0) * f, &s, &c);
-        sincosf(f, &s1, &c1);
-        for (int j = j0; j < j0 + 32; ++j) {
-            trig[trig_index(j, i)] = make_float2(c, s);
-            const float ns = s * c1 + c * s1, nc = c * c1 - s * s1;
-            s = ns, c = nc;
+        if constexpr (compact_trig<ML>()) {
+            // half 0 fills rows 0..7 (angle step 8 f), half 1 rows 8..15 (step f)
+            float s1, c1, s = 0.f, c = 1.f;
+            sincosf((half ? 1.f : 8.f) * f, &s1, &c1);
+            for (int r = 0; r < 8; ++r) {
+                trig[(half * 8 + r) * kTrigStride + i] = make_float2(c, s);
+                const float ns = s * c1 + c * s1, nc = c * c1 - s * s1;
+                s = ns, c = nc;
+            }
+        } else {
+            const int j0 = half * 32;
+            float s, c, s1, c1;
+            sincosf(static_cast<float>(j0) * f, &s, &c);
+            sincosf(f, &s1, &c1);
+            for (int j = j0; j < j0 + 32; ++j) {
+                trig[trig_index(j, i)] = make_float2(c, s);
+                const float ns = s * c1 + c * s1, nc = c * c1 - s * s1;
+                s = ns, c = nc;
+            }
         }
         const __half* src = p.kc + static_cast<size_t>(unit) * p.ck * kHeadDim;
         for (int idx = tid; idx < p.ck * (kHeadDim / 2); idx += kThreadsM) {
@@ -510,7 +554,18 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
     // sin/cos of this lane's two rows (tile offsets 16 warp + g and + 8) and 16 frequencies: the
     // same in every tile, so they live in registers for the whole kernel
     float4 trA_r[8], trB_r[8];
-    {
+    if constexpr (compact_trig<ML>()) {
+        // row A = tile offset 16 warp + g = 8 (2 warp) + g, row B = 8 (2 warp + 1) + g
+        const float4* fine = reinterpret_cast<const float4*>(trig + (8 + g) * kTrigStride + 16 * qd);
+        const float4* baseA = reinterpret_cast<const float4*>(trig + (2 * warp) * kTrigStride + 16 * qd);
+        const float4* baseB = reinterpret_cast<const float4*>(trig + (2 * warp + 1) * kTrigStride + 16 * qd);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {  // frequencies 16 qd + 2u, + 1 as (cos, sin, cos, sin)
+            const float4 f = fine[u], a = baseA[u], b = baseB[u];
+            trA_r[u] = make_float4(a.x * f.x - a.y * f.y, a.y * f.x + a.x * f.y, a.z * f.z - a.w * f.w, a.w * f.z + a.z * f.w);
+            trB_r[u] = make_float4(b.x * f.x - b.y * f.y, b.y * f.x + b.x * f.y, b.z * f.z - b.w * f.w, b.w * f.z + b.z * f.w);
+        }
+    } else {
         const int tokA = warp * 16 + g, tokB = tokA + 8;
         const float4* trA = reinterpret_cast<const float4*>(trig + tokA * kTrigStride);
         const float4* trB = reinterpret_cast<const float4*>(trig + tokB * kTrigStride);
@@ -710,7 +765,7 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
         }
         if (it + 1 < ntiles) write_query(it + 1);
         __syncthreads();  // ring slot free, next query tile visible
-        if (tid == 0 && it + kStages < ntiles) issue(it + kStages);
+        if (it + kStages < ntiles) issue(it + kStages);
     }
     if (lost && lane == 0) atomicOr(&timed_out, 1u);
 
