@@ -456,7 +456,6 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
             const float2 v = __half22float2(*reinterpret_cast<const __half2*>(src + row * kHeadDim + d));
             *reinterpret_cast<float2*>(kc_s + row * kCenStride + cen_index(d)) = v;
         }
-        for (int idx = tid; idx < kWarpsM * GQA * kMaxClusters; idx += kThreadsM) beta_s[idx] = 0.f;
     }
 
     // ---- query state: item = (head, two adjacent frequencies i2, i2 + 1) ----------------------
@@ -524,7 +523,11 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
     m_used[0] = m_used[1] = -INFINITY;
     l_part[0] = l_part[1] = 0.f;
-    float* beta_w = beta_s + warp * GQA * kMaxClusters;
+    // cluster mass beta[value cluster][head] of this warp's tokens, accumulated by the tensor cores as
+    // onehot(value id)^T . P: rows = clusters 16 mb + g (+ 8), columns = heads 2q, 2q + 1
+    float bacc[4][4];
+#pragma unroll
+    for (int mb = 0; mb < 4; ++mb) bacc[mb][0] = bacc[mb][1] = bacc[mb][2] = bacc[mb][3] = 0.f;
     uint2* pre_k = pre + warp * 32;
     uint2* pre_v = pre_k + 16;
 
@@ -718,13 +721,11 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
                     acc[i][0] *= alpha[0], acc[i][2] *= alpha[0];
                     acc[i][1] *= alpha[1], acc[i][3] *= alpha[1];
                 }
-                __syncwarp();
 #pragma unroll
-                for (int h = 0; h < GQA; ++h) {
-                    const float a = __shfl_sync(0xffffffffu, alpha[h & 1], h >> 1);
-                    for (int c = lane; c < kMaxClusters; c += 32) beta_w[h * kMaxClusters + c] *= a;
+                for (int mb = 0; mb < 4; ++mb) {
+                    bacc[mb][0] *= alpha[0], bacc[mb][2] *= alpha[0];
+                    bacc[mb][1] *= alpha[1], bacc[mb][3] *= alpha[1];
                 }
-                __syncwarp();
             }
             float pr[4];
             pr[0] = fast_exp2(sc[0] - m_used[0]), pr[1] = fast_exp2(sc[1] - m_used[1]);
@@ -733,18 +734,25 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
             const float2 p01f = __half22float2(p01), p23f = __half22float2(p23);
             l_part[0] += p01f.x + p23f.x;
             l_part[1] += p01f.y + p23f.y;
+            // P as B operand (tokens x heads): transpose the two 8x8 halves
+            uint32_t pb0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p01));
+            uint32_t pb1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p23));
             {
-                // cluster mass: beta[head][value id of the token] += p
-                const int vidA = min(max(__shfl_sync(0xffffffffu, ids_cur, 16 + g), 0), kMaxClusters - 1);
-                const int vidB = min(max(__shfl_sync(0xffffffffu, ids_cur, 24 + g), 0), kMaxClusters - 1);
-                const int h0 = 2 * qd, h1 = 2 * qd + 1;
-                if (h0 < GQA) {
-                    if (okA) atomicAdd(&beta_w[h0 * kMaxClusters + vidA], p01f.x);
-                    if (okB) atomicAdd(&beta_w[h0 * kMaxClusters + vidB], p23f.x);
-                }
-                if (h1 < GQA) {
-                    if (okA) atomicAdd(&beta_w[h1 * kMaxClusters + vidA], p01f.y);
-                    if (okB) atomicAdd(&beta_w[h1 * kMaxClusters + vidB], p23f.y);
+                // cluster mass: one-hot rows A[c][t] = (value id of token t == c), built two tokens at a
+                // time by a packed FP16 compare; tokens beyond the end have p = 0
+                const int w0 = __shfl_sync(0xffffffffu, ids_cur, 16 + 2 * qd), w1 = __shfl_sync(0xffffffffu, ids_cur, 17 + 2 * qd);
+                const int w2 = __shfl_sync(0xffffffffu, ids_cur, 24 + 2 * qd), w3 = __shfl_sync(0xffffffffu, ids_cur, 25 + 2 * qd);
+                const __half2 gg = __half2half2(__int2half_rn(g));
+                const __half2 d01 = __hsub2(__halves2half2(__int2half_rn(w0), __int2half_rn(w1)), gg);
+                const __half2 d23 = __hsub2(__halves2half2(__int2half_rn(w2), __int2half_rn(w3)), gg);
+#pragma unroll
+                for (int mb = 0; mb < 4; ++mb) {
+                    if (16 * mb < p.cv) {
+                        const __half2 lo = __float2half2_rn(16.f * mb), hi = __float2half2_rn(16.f * mb + 8.f);
+                        const __half2 a0 = __heq2(d01, lo), a1 = __heq2(d01, hi), a2 = __heq2(d23, lo), a3 = __heq2(d23, hi);
+                        mma_16816(bacc[mb], *reinterpret_cast<const uint32_t*>(&a0), *reinterpret_cast<const uint32_t*>(&a1),
+                                  *reinterpret_cast<const uint32_t*>(&a2), *reinterpret_cast<const uint32_t*>(&a3), pb0, pb1);
+                    }
                 }
             }
             if constexpr (ML::kScaleP) {
@@ -753,10 +761,9 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
                 const float vsB = h2f_bits(__shfl_sync(0xffffffffu, scl_cur, 24 + g));
                 p01 = __floats2half2_rn(p01f.x * vsA, p01f.y * vsA);
                 p23 = __floats2half2_rn(p23f.x * vsB, p23f.y * vsB);
+                pb0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p01));
+                pb1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p23));
             }
-            // P as B operand (tokens x heads): transpose the two 8x8 halves
-            const uint32_t pb0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p01));
-            const uint32_t pb1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p23));
 
             // O^T += Vres^T . P
 #pragma unroll
@@ -797,6 +804,11 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
             for (int i = 0; i < 8; ++i) {
                 dst[i] = acc[i][u] * scale;
                 dst[8 + i] = acc[i][2 + u] * scale;
+            }
+            if (qd * 2 + u < GQA) {
+                float* bdst = beta_s + (warp * GQA + h) * kMaxClusters + g;
+#pragma unroll
+                for (int mb = 0; mb < 4; ++mb) bdst[16 * mb] = bacc[mb][u], bdst[16 * mb + 8] = bacc[mb][2 + u];
             }
         }
     }
