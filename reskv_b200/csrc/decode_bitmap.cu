@@ -695,8 +695,8 @@ int decode_common(const DecodeArgs& a, LayoutId layout, bool has_meta, bool has_
         return fail(RESKV_ERR_INVALID, "%s: a step state needs the window buffers and a capacity in [1,%d]", who, kMaxRecent);
     if (!aligned16(a.kp) || !aligned16(a.vp) || (has_meta && layout != kStructInt4 && (!aligned16(a.km) || !aligned16(a.vm))))
         return fail(RESKV_ERR_INVALID, "%s: payload and metadata pointers must be 16-byte aligned", who);
-    if ((reinterpret_cast<uintptr_t>(a.kc) & 3u) || (reinterpret_cast<uintptr_t>(a.q) & 1u))
-        return fail(RESKV_ERR_INVALID, "%s: misaligned centroid or query pointer", who);
+    if (!aligned16(a.kc) || (reinterpret_cast<uintptr_t>(a.q) & 1u))
+        return fail(RESKV_ERR_INVALID, "%s: misaligned centroid (16 bytes) or query pointer", who);
     const bool has_recent = a.recent_tokens > 0;
     if (a.recent_tokens < 0 || (has_recent && (!a.rq || !a.rk || !a.rv)))
         return fail(RESKV_ERR_INVALID, "%s: recent window needs rotated q, rotated k and v", who);

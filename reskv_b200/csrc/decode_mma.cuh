@@ -451,10 +451,13 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
             }
         }
         const __half* src = p.kc + static_cast<size_t>(unit) * p.ck * kHeadDim;
-        for (int idx = tid; idx < p.ck * (kHeadDim / 2); idx += kThreadsM) {
-            const int row = idx / (kHeadDim / 2), d = (idx % (kHeadDim / 2)) * 2;
-            const float2 v = __half22float2(*reinterpret_cast<const __half2*>(src + row * kHeadDim + d));
-            *reinterpret_cast<float2*>(kc_s + row * kCenStride + cen_index(d)) = v;
+        for (int idx = tid; idx < p.ck * (kHeadDim / 8); idx += kThreadsM) {  // 8 coordinates per step
+            const int row = idx / (kHeadDim / 8), d = (idx % (kHeadDim / 8)) * 8;
+            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + row * kHeadDim + d));
+            const __half2* h = reinterpret_cast<const __half2*>(&raw);
+            const float2 v0 = __half22float2(h[0]), v1 = __half22float2(h[1]), v2 = __half22float2(h[2]), v3 = __half22float2(h[3]);
+            *reinterpret_cast<float4*>(kc_s + row * kCenStride + cen_index(d)) = make_float4(v0.x, v0.y, v1.x, v1.y);
+            *reinterpret_cast<float4*>(kc_s + row * kCenStride + cen_index(d + 4)) = make_float4(v2.x, v2.y, v3.x, v3.y);
         }
     }
 
