@@ -273,9 +273,13 @@ __global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const Kmean
             const __half* xr = xu + static_cast<size_t>(t0 + r) * kHeadDim;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const long long fx = static_cast<long long>(__half2float(xr[lane + 32 * i]) * kFix);  // exact
-                atomicAdd(&lo_s[c * kHeadDim + lane + 32 * i], static_cast<int>(fx & 0xfffff));
-                atomicAdd(&hi_s[c * kHeadDim + lane + 32 * i], static_cast<int>(fx >> 20));
+                // x * 2^24 is an integer below 2^41: split it, exactly, into hi * 2^20 + lo with both
+                // parts carrying the sign of x (|lo| < 2^20, |hi| < 2^21)
+                const float fx = __half2float(xr[lane + 32 * i]) * kFix;
+                const float hi = truncf(fx * (1.0f / 1048576.0f));
+                const float lo = fmaf(hi, -1048576.0f, fx);
+                atomicAdd(&lo_s[c * kHeadDim + lane + 32 * i], __float2int_rz(lo));
+                atomicAdd(&hi_s[c * kHeadDim + lane + 32 * i], __float2int_rz(hi));
             }
             if (lane == 0) atomicAdd(&cnt_s[c], 1);
         }
@@ -284,7 +288,7 @@ __global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const Kmean
     long long* sums_g = p.sums + static_cast<size_t>(unit) * p.clusters * kHeadDim;
     for (int i = tid; i < p.clusters * kHeadDim; i += kThreads) {
         if (cnt_s[i / kHeadDim] > 0) {
-            const long long v = (static_cast<long long>(hi_s[i]) << 20) + lo_s[i];
+            const long long v = static_cast<long long>(hi_s[i]) * 1048576LL + lo_s[i];
             atomicAdd(reinterpret_cast<unsigned long long*>(sums_g + i), static_cast<unsigned long long>(v));
         }
     }
