@@ -518,7 +518,7 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
     if (ntiles > 0) write_query(0);
 
     // ---- per-warp running state ---------------------------------------------------------------
-    float acc[8][4];          // O^T: m-block i -> coordinates 16g+i (c0,c1) and 16g+8+i (c2,c3); heads 2q, 2q+1
+    float acc[8][4];          // O^T: m-block i -> coordinates 16g+2i (c0,c1) and 16g+2i+1 (c2,c3); heads 2q, 2q+1
     float m_used[2], l_part[2];
 #pragma unroll
     for (int i = 0; i < 8; ++i)
@@ -674,30 +674,6 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i) sc[i] += sc2[i] + sc3[i];
-            // ================= values: tokens 2q, 2q+1, 2q+8, 2q+9; coordinates [16g, 16g+16) =================
-            uint32_t v01[16], v23[16];  // (token 2q | token 2q+1 << 16), (2q+8 | 2q+9 << 16) per coordinate
-            {
-                const unsigned char* pv_bytes = reinterpret_cast<const unsigned char*>(pre_v);
-                const int r0 = 2 * qd, r1 = 2 * qd + 1, r2 = 2 * qd + 8, r3 = 2 * qd + 9;
-                Field f0 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r0, g, r0 < nvalid);
-                Field f1 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r1, g, r1 < nvalid);
-                Field f2 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r2, g, r2 < nvalid);
-                Field f3 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r3, g, r3 < nvalid);
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
-                    uint32_t h0[4], h1[4], h2[4], h3[4];
-                    f0.bits4(ks, h0);
-                    f1.bits4(ks, h1);
-                    f2.bits4(ks, h2);
-                    f3.bits4(ks, h3);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        v01[4 * ks + e] = h0[e] | (h1[e] << 16);
-                        v23[4 * ks + e] = h2[e] | (h3[e] << 16);
-                    }
-                }
-            }
-
             // sc: c0,c1 = (token g, heads 2q, 2q+1), c2,c3 = (token g+8, ...), log2 domain
             if (!okA) sc[0] = sc[1] = -INFINITY;
             if (!okB) sc[2] = sc[3] = -INFINITY;
@@ -768,9 +744,29 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
                 pb1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p23));
             }
 
-            // O^T += Vres^T . P
+            // O^T += Vres^T . P.  Values: tokens 2q, 2q+1, 2q+8, 2q+9 of the block, coordinates [16g, 16g+16);
+            // m-block i holds coordinates 16g + 2i (rows g) and 16g + 2i + 1 (rows g + 8), so that the MMAs
+            // follow the field walks two coordinates at a time
+            {
+                const unsigned char* pv_bytes = reinterpret_cast<const unsigned char*>(pre_v);
+                const int r0 = 2 * qd, r1 = 2 * qd + 1, r2 = 2 * qd + 8, r3 = 2 * qd + 9;
+                Field f0 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r0, g, r0 < nvalid);
+                Field f1 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r1, g, r1 < nvalid);
+                Field f2 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r2, g, r2 < nvalid);
+                Field f3 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r3, g, r3 < nvalid);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) mma_16816(acc[i], v01[i], v01[8 + i], v23[i], v23[8 + i], pb0, pb1);
+                for (int ks = 0; ks < 4; ++ks) {
+                    uint32_t h0[4], h1[4], h2[4], h3[4];
+                    f0.bits4(ks, h0);
+                    f1.bits4(ks, h1);
+                    f2.bits4(ks, h2);
+                    f3.bits4(ks, h3);
+                    mma_16816(acc[2 * ks], h0[0] | (h1[0] << 16), h0[1] | (h1[1] << 16), h2[0] | (h3[0] << 16),
+                              h2[1] | (h3[1] << 16), pb0, pb1);
+                    mma_16816(acc[2 * ks + 1], h0[2] | (h1[2] << 16), h0[3] | (h1[3] << 16), h2[2] | (h3[2] << 16),
+                              h2[3] | (h3[3] << 16), pb0, pb1);
+                }
+            }
             __syncwarp();  // rank-base table is rewritten next tile
         }
         if (it + 1 < ntiles) write_query(it + 1);
@@ -805,8 +801,8 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
             float* dst = red_acc + (warp * GQA + h) * kHeadDim + 16 * g;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                dst[i] = acc[i][u] * scale;
-                dst[8 + i] = acc[i][2 + u] * scale;
+                dst[2 * i] = acc[i][u] * scale;
+                dst[2 * i + 1] = acc[i][2 + u] * scale;
             }
             if (qd * 2 + u < GQA) {
                 float* bdst = beta_s + (warp * GQA + h) * kMaxClusters + g;
