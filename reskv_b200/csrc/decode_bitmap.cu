@@ -448,15 +448,49 @@ struct MergeParams {
 
 constexpr int kMergeThreads = 128;
 constexpr int kMaxRecent = 1024;  // recent tokens whose scores fit the shared buffer
+constexpr int kRecentChunk = 32;  // recent tokens staged in shared memory at a time
 
-// One CTA per query head; thread d owns output coordinate d.
-__global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const MergeParams p) {
-    __shared__ float beta_s[kMaxClusters];
-    __shared__ float sc_s[kMaxRecent];
-    __shared__ float red[kMergeThreads / 32];
-    const int fq = blockIdx.x, d = threadIdx.x, lane = d & 31, warp = d >> 5;
-    const int b = fq / p.nh, head = fq % p.nh;
-    const int unit = b * p.kh + head / (p.nh / p.kh);
+// rows x 128 FP16 values, global -> shared, 16 bytes per thread and copy (all in flight at once)
+__device__ __forceinline__ void stage_rows(__half* dst, const __half* src, int rows, int tid, int threads) {
+    for (int i = tid; i < rows * (kHeadDim / 8); i += threads) cp_async16(dst + i * 8, src + i * 8);
+}
+
+// dynamic shared memory of the merge kernel: value centroids, one chunk of recent keys and of recent
+// values (shared by the unit's query heads), recent scores per head
+size_t merge_smem_bytes(int cv, int gqa, int recent_max) {
+    return (static_cast<size_t>(cv) + 2 * kRecentChunk) * kHeadDim * sizeof(__half) +
+           static_cast<size_t>(gqa) * ((recent_max + 3) / 4 * 4) * sizeof(float);
+}
+
+// One CTA per (sequence, KV head) unit, 128 threads per query head of the unit; thread (h, d) owns
+// output coordinate d of head h.  Everything that is read with a stride or by several heads (value
+// centroids, recent keys and values) is staged in shared memory by 16-byte asynchronous copies
+// issued up front, so the kernel pays a few memory round trips instead of one per centroid and
+// per recent token.
+__global__ void __launch_bounds__(1024) decode_merge_kernel(const MergeParams p, int recent_max) {
+    extern __shared__ __align__(16) unsigned char merge_smem[];
+    __shared__ float beta_s[8][kMaxClusters];
+    __shared__ float red[8][kMergeThreads / 32];
+    const int gqa = p.nh / p.kh, threads = gqa * kMergeThreads;
+    const int unit = blockIdx.x, tid = threadIdx.x;
+    const int h = tid / kMergeThreads, d = tid % kMergeThreads, lane = d & 31, warp = d >> 5;
+    const int fq = unit * gqa + h;  // (b * kh + hkv) * gqa + h == b * nh + hkv * gqa + h
+    const int sc_stride = (recent_max + 3) / 4 * 4;
+    __half* vc_s = reinterpret_cast<__half*>(merge_smem);
+    __half* rk_s = vc_s + static_cast<size_t>(p.cv) * kHeadDim;
+    __half* rv_s = rk_s + kRecentChunk * kHeadDim;
+    float* sc_s = reinterpret_cast<float*>(rv_s + kRecentChunk * kHeadDim) + h * sc_stride;
+    const int tr = p.dyn ? min(p.dyn[1], recent_max) : p.tr;
+    const bool dot_scores = tr > 0 && !p.rscores;
+    const __half* rk_g = p.rk ? p.rk + static_cast<size_t>(unit) * p.recent_cap * kHeadDim : nullptr;
+    const __half* rv_g = p.rv ? p.rv + static_cast<size_t>(unit) * p.recent_cap * kHeadDim : nullptr;
+
+    // group 0: value centroids + first chunk of recent keys; group 1: first chunk of recent values
+    if (p.splits > 0) stage_rows(vc_s, p.vc + static_cast<size_t>(unit) * p.cv * kHeadDim, p.cv, tid, threads);
+    if (dot_scores) stage_rows(rk_s, rk_g, min(tr, kRecentChunk), tid, threads);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    if (tr > 0) stage_rows(rv_s, rv_g, min(tr, kRecentChunk), tid, threads);
+    asm volatile("cp.async.commit_group;" ::: "memory");
 
     // compressed part: numerator `num`, max `m2` (log2 domain), sum `l`
     float m2, l, num;
@@ -467,6 +501,7 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Merge
         for (int s = 1; s < p.splits; ++s) m2 = fmaxf(m2, pm[s]);
         l = 0.f, num = 0.f;
         float bsum = 0.f;
+#pragma unroll 4
         for (int s = 0; s < p.splits; ++s) {
             const float w = (pm[s] == -INFINITY) ? 0.f : fast_exp2(pm[s] - m2);
             l += pl[s] * w;
@@ -474,10 +509,7 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Merge
             num += p.ws_delta[row * kHeadDim + d] * w;
             if (d < p.cv) bsum += p.ws_beta[row * kMaxClusters + d] * w;
         }
-        if (d < kMaxClusters) beta_s[d] = (d < p.cv) ? bsum : 0.f;
-        __syncthreads();
-        const __half* vc = p.vc + static_cast<size_t>(unit) * p.cv * kHeadDim + d;
-        for (int c = 0; c < p.cv; ++c) num = fmaf(beta_s[c], __half2float(vc[c * kHeadDim]), num);
+        if (d < kMaxClusters) beta_s[h][d] = (d < p.cv) ? bsum : 0.f;
         if (d == 0) {
             if (p.out_m) p.out_m[fq] = m2 * kLn2;
             if (p.out_l) p.out_l[fq] = l;
@@ -487,8 +519,13 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Merge
         l = p.ws_l[fq];
         num = __half2float(p.comp_out[static_cast<size_t>(fq) * kHeadDim + d]) * l;
     }
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();  // beta_s, vc_s and the first key chunk are in place
+    if (p.splits > 0) {
+#pragma unroll 8
+        for (int c = 0; c < p.cv; ++c) num = fmaf(beta_s[h][c], __half2float(vc_s[c * kHeadDim + d]), num);
+    }
 
-    const int tr = p.dyn ? min(p.dyn[1], kMaxRecent) : p.tr;
     if (tr > 0) {
         // scores of the recent tokens (log2 domain) into shared memory
         if (p.rscores) {
@@ -500,37 +537,73 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Merge
 #pragma unroll
             for (int i = 0; i < 4; ++i) qv[i] = __half2float(qrow[lane + 32 * i]);
             const float mul = p.scaling * kLog2e;
-            for (int t = warp; t < tr; t += kMergeThreads / 32) {
-                const __half* krow = p.rk + (static_cast<size_t>(unit) * p.recent_cap + t) * kHeadDim;
-                float dot = 0.f;
+            for (int c0 = 0; c0 < tr; c0 += kRecentChunk) {
+                const int n = min(kRecentChunk, tr - c0);
+                if (c0 > 0) {  // later chunks: plain staging, one round trip each
+                    __syncthreads();
+                    stage_rows(rk_s, rk_g + static_cast<size_t>(c0) * kHeadDim, n, tid, threads);
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                    asm volatile("cp.async.wait_group 0;" ::: "memory");
+                    __syncthreads();
+                }
+                for (int t = warp; t < n; t += kMergeThreads / 32) {
+                    const __half* krow = rk_s + t * kHeadDim;
+                    float dot = 0.f;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) dot = fmaf(qv[i], __half2float(krow[lane + 32 * i]), dot);
+                    for (int i = 0; i < 4; ++i) dot = fmaf(qv[i], __half2float(krow[lane + 32 * i]), dot);
 #pragma unroll
-                for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-                if (lane == 0) sc_s[t] = dot * mul;
+                    for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+                    if (lane == 0) sc_s[c0 + t] = dot * mul;
+                }
             }
         }
-        __syncthreads();
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();  // scores and the first value chunk are in place
         float rm = -INFINITY;
         for (int t = d; t < tr; t += kMergeThreads) rm = fmaxf(rm, sc_s[t]);
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) rm = fmaxf(rm, __shfl_xor_sync(0xffffffffu, rm, off));
-        if (lane == 0) red[warp] = rm;
+        if (lane == 0) red[h][warp] = rm;
         __syncthreads();
-        rm = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+        rm = fmaxf(fmaxf(red[h][0], red[h][1]), fmaxf(red[h][2], red[h][3]));
         const float jm = fmaxf(rm, m2);
         const float cw = (m2 == -INFINITY) ? 0.f : fast_exp2(m2 - jm);
         float rnum = 0.f, rl = 0.f;
-        const __half* vrow = p.rv + static_cast<size_t>(unit) * p.recent_cap * kHeadDim + d;
-        for (int t = 0; t < tr; ++t) {
-            const float w = fast_exp2(sc_s[t] - jm);
-            rl += w;
-            rnum = fmaf(w, __half2float(vrow[static_cast<size_t>(t) * kHeadDim]), rnum);
+        for (int c0 = 0; c0 < tr; c0 += kRecentChunk) {
+            const int n = min(kRecentChunk, tr - c0);
+            if (c0 > 0) {
+                __syncthreads();
+                stage_rows(rv_s, rv_g + static_cast<size_t>(c0) * kHeadDim, n, tid, threads);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                __syncthreads();
+            }
+#pragma unroll 8
+            for (int t = 0; t < n; ++t) {
+                const float w = fast_exp2(sc_s[c0 + t] - jm);
+                rl += w;
+                rnum = fmaf(w, __half2float(rv_s[t * kHeadDim + d]), rnum);
+            }
         }
         num = num * cw + rnum;
         l = l * cw + rl;
     }
     p.out[static_cast<size_t>(fq) * kHeadDim + d] = __float2half_rn(num / fmaxf(l, 1e-20f));
+}
+
+// one CTA per unit with 128 threads per query head of the unit
+int launch_merge(const MergeParams& mp, int units, int recent_max, cudaStream_t s) {
+    const int gqa = mp.nh / mp.kh;
+    if (gqa < 1 || gqa > 8) return fail(RESKV_ERR_INVALID, "merge: at most 8 query heads per KV head");
+    const size_t smem = merge_smem_bytes(mp.splits > 0 ? mp.cv : 0, gqa, recent_max);
+    if (smem > 48 * 1024) {
+        if (int rc = check_cuda(cudaFuncSetAttribute(decode_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     static_cast<int>(smem)),
+                                "cudaFuncSetAttribute(decode_merge)"))
+            return rc;
+    }
+    decode_merge_kernel<<<units, gqa * kMergeThreads, smem, s>>>(mp, recent_max);
+    return check_cuda(cudaGetLastError(), "decode_merge launch");
 }
 
 template <int GQA, class L, int CVS>
@@ -695,8 +768,10 @@ int decode_common(const DecodeArgs& a, LayoutId layout, bool has_meta, bool has_
         return fail(RESKV_ERR_INVALID, "%s: a step state needs the window buffers and a capacity in [1,%d]", who, kMaxRecent);
     if (!aligned16(a.kp) || !aligned16(a.vp) || (has_meta && layout != kStructInt4 && (!aligned16(a.km) || !aligned16(a.vm))))
         return fail(RESKV_ERR_INVALID, "%s: payload and metadata pointers must be 16-byte aligned", who);
-    if (!aligned16(a.kc) || (reinterpret_cast<uintptr_t>(a.q) & 1u))
+    if (!aligned16(a.kc) || !aligned16(a.vc) || (reinterpret_cast<uintptr_t>(a.q) & 1u))
         return fail(RESKV_ERR_INVALID, "%s: misaligned centroid (16 bytes) or query pointer", who);
+    if ((a.rk && !aligned16(a.rk)) || (a.rv && !aligned16(a.rv)))
+        return fail(RESKV_ERR_INVALID, "%s: recent keys and values must be 16-byte aligned", who);
     const bool has_recent = a.recent_tokens > 0;
     if (a.recent_tokens < 0 || (has_recent && (!a.rq || !a.rk || !a.rv)))
         return fail(RESKV_ERR_INVALID, "%s: recent window needs rotated q, rotated k and v", who);
@@ -755,8 +830,7 @@ int decode_common(const DecodeArgs& a, LayoutId layout, bool has_meta, bool has_
     mp.kh = a.kv_heads, mp.nh = a.q_heads, mp.splits = splits, mp.cv = a.cv, mp.tr = a.recent_tokens;
     mp.scaling = a.scaling;
     mp.dyn = a.dyn, mp.recent_cap = a.dyn ? a.recent_cap : a.recent_tokens;
-    decode_merge_kernel<<<a.batch * a.q_heads, kMergeThreads, 0, s>>>(mp);
-    return check_cuda(cudaGetLastError(), "decode_merge launch");
+    return launch_merge(mp, units, a.dyn ? a.recent_cap : a.recent_tokens, s);
 }
 }  // namespace
 
@@ -916,6 +990,8 @@ static int merge_recent_common(const void* comp_out, const float* comp_m, const 
     if (recent_tokens < 1) return fail(RESKV_ERR_INVALID, "%s: recent_tokens must be positive", who);
     if (recent_tokens > kMaxRecent)
         return fail(RESKV_ERR_LIMIT, "%s: at most %d recent tokens, got %d", who, kMaxRecent, recent_tokens);
+    if ((rk && !aligned16(rk)) || !aligned16(rv))
+        return fail(RESKV_ERR_INVALID, "%s: recent keys and values must be 16-byte aligned", who);
     MergeParams mp{};
     mp.ws_m = comp_m, mp.ws_l = comp_l;
     mp.comp_out = static_cast<const __half*>(comp_out);
@@ -926,8 +1002,7 @@ static int merge_recent_common(const void* comp_out, const float* comp_m, const 
     mp.out = static_cast<__half*>(merged);
     mp.kh = kv_heads, mp.nh = q_heads, mp.splits = 0, mp.tr = recent_tokens, mp.scaling = scaling;
     mp.recent_cap = recent_tokens;
-    decode_merge_kernel<<<batch * q_heads, kMergeThreads, 0, static_cast<cudaStream_t>(stream)>>>(mp);
-    return check_cuda(cudaGetLastError(), "merge_recent launch");
+    return launch_merge(mp, batch * kv_heads, recent_tokens, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int reskv_merge_recent_scores(const void* comp_out, const float* comp_m, const float* comp_l,
