@@ -64,6 +64,33 @@ def test_matches_oracle_over_lengths(t, nnz):
     assert_attention_close(out, oracle_attention(q, kc, vc, position=t + 3))
 
 
+def test_reference_cpu_configuration_at_full_size():
+    """One sequence of 8 KV heads at context 8192 as the reference's CPU case sets it up: 4 sink
+    tokens kept dense (start_position = 4), 8128 compressed tokens at sparsity 0.5, the remaining 60
+    tokens plus the sinks in the dense segment."""
+    t, sinks, dense = 8128, 4, 60
+    q, kc, vc = _case(1, 8, 4, t, 64, seed=21)
+    pos = sinks + t + dense - 1
+    freq = (500000.0 ** (-torch.arange(64).float() / 64)).float()
+    qr = torch.from_numpy(oatt.rotate(np16(q), np.array([pos]), np16(freq))).half()
+    g = torch.Generator().manual_seed(22)
+    kr = (torch.randn(1, 8, sinks + dense, 128, generator=g) * 0.5).half()  # rotated sink + window keys
+    vr = (torch.randn(1, 8, sinks + dense, 128, generator=g) * 0.5).half()
+    kw = dict(position=pos, start_position=sinks, recent=(qr, kr, vr))
+    out = _run(q, kc, vc, 64, **kw)
+    assert_attention_close(out, oracle_attention(q, kc, vc, **kw))
+
+
+@pytest.mark.parametrize("nnz", [32, 64])
+def test_long_context_head(nnz):
+    """65 472 compressed tokens (the 64K-context case): positions far from the query, 1023 tiles,
+    split-K over many CTAs."""
+    t = 65472
+    q, kc, vc = _case(1, 1, 4, t, nnz, seed=31 + nnz)
+    out = _run(q, kc, vc, nnz, position=t + 63)
+    assert_attention_close(out, oracle_attention(q, kc, vc, position=t + 63))
+
+
 @pytest.mark.parametrize("gqa", [1, 4, 8])
 @pytest.mark.parametrize("clusters", [1, 32, 33, 64])
 def test_head_ratios_and_centroid_counts(gqa, clusters):
