@@ -568,7 +568,7 @@ def run_gpu(a):
                     "h2d_bytes_per_step": int(host_q[0].nbytes + host_k[0].nbytes + host_v[0].nbytes),
                     "d2h_bytes_per_step": int(host_out.nbytes)},
             "gpu_launches": launches,
-            "roofline": {"bound": "hbm", "kernel": "decode_bitmap_mma_kernel (split-K partial pass of one attention call; "
+            "roofline": {"bound": "hbm", "kernel": "mma::decode_mma_kernel<4, LayoutMmaBitmap<nnz>> (split-K partial pass of one attention call; "
                                                    "CUDA events recorded around the launch inside the library)",
                          "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                          "frac": achieved / peak, "frac_of_8000": achieved / 8000.0,
