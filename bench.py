@@ -299,6 +299,8 @@ PLANS = (  # (name, sparsity, bits, layout, K+V bytes per compressed token and K
     ("int4_unstructured_s050", 0.5, 4, "unstructured", 134),
     ("int2_unstructured_s050", 0.5, 2, "unstructured", 70),
     ("int4_structured_1of4", 0.75, 4, "structured", 54),
+    ("int4_compact_s050", 0.5, 4, "compact", 102),   # bitmap + codes of the retained coordinates (not in the reference)
+    ("int4_compact_s075", 0.75, 4, "compact", 70),
 )
 
 

@@ -96,6 +96,7 @@ int reskv_decode_bitmap_fp16(const void* q, const void* k_centroids, const void*
 #define RESKV_LAYOUT_UNSTRUCTURED 0
 #define RESKV_LAYOUT_TILED 1
 #define RESKV_LAYOUT_STRUCTURED 2
+#define RESKV_LAYOUT_COMPACT 3 /* reskv_decode_step only; see reskv_decode_compact */
 
 int reskv_decode_packed(int layout, int bits, const void* q, const void* k_centroids, const void* k_ids,
                         const void* k_payload, const void* k_meta, const void* k_scale, const void* v_centroids,
@@ -104,6 +105,28 @@ int reskv_decode_packed(int layout, int bits, const void* q, const void* k_centr
                         int start_pos, int pos_q, float rope_theta, const float* inv_freq, float scaling, int splits,
                         const void* recent_q, const void* recent_k, const void* recent_v, int recent_tokens,
                         void* workspace, size_t workspace_bytes, void* out, float* out_m, float* out_l, void* stream);
+
+/* ---- compact quantised residuals --------------------------------------------------------
+ * No counterpart in the reference: its unstructured INT4 / INT2 layout stores all 128
+ * coordinates of a token (discarded ones as 0).  The compact layout keeps the MSB-first
+ * bitmap of the unstructured FP16 layout (i64 [.., 2]) and stores only the codes of the
+ * nnz retained coordinates, in ascending coordinate order: words i32 [.., nnz*bits/32],
+ * code of rank r at bit (r % (32/bits)) * bits of word r / (32/bits); scale f16 [..].
+ * Selection, scale and codes are those of reskv_encode_quantized.  Supported: bits 4 with
+ * nnz 64 or 32 (51 or 35 bytes per token and tensor instead of 67), bits 2 with nnz 64.
+ * reskv_decode_compact takes the arguments of reskv_decode_packed with (bits, nnz) in
+ * place of (layout, bits). */
+int reskv_encode_compact(const void* x, const void* centroids, const int32_t* ids, int batch, int kv_heads, int tokens,
+                         int64_t x_tok_stride, int clusters, int nnz, int bits, void* words, void* bitmap, void* scale,
+                         int64_t out_tok_stride, void* stream);
+
+int reskv_decode_compact(int bits, int nnz, const void* q, const void* k_centroids, const void* k_ids,
+                         const void* k_payload, const void* k_bitmap, const void* k_scale, const void* v_centroids,
+                         const void* v_ids, const void* v_payload, const void* v_bitmap, const void* v_scale, int batch,
+                         int kv_heads, int q_heads, int tokens, int64_t tok_stride, int k_clusters, int v_clusters,
+                         int start_pos, int pos_q, float rope_theta, const float* inv_freq, float scaling, int splits,
+                         const void* recent_q, const void* recent_k, const void* recent_v, int recent_tokens,
+                         void* workspace, size_t workspace_bytes, void* out, float* out_m, float* out_l, void* stream);
 
 /* ---- decode steps that can be captured in a CUDA graph --------------------------------
  * No counterpart in the reference (its decode loop is eager Python,
@@ -116,8 +139,8 @@ int reskv_decode_packed(int layout, int bits, const void* q, const void* k_centr
  * (f16 [B*KH,window_capacity,128]); reskv_decode_step is reskv_decode_bitmap_fp16 /
  * reskv_decode_packed with the query position, the window length and -- when
  * step_state[2] >= 0 -- the compressed token count read from step_state inside the
- * kernels (layout UNSTRUCTURED with bits 16 selects the bitmap kernels, nnz = payload
- * width; `tokens` then only sizes the split count and is what the kernels use when
+ * kernels (layout UNSTRUCTURED with bits 16 selects the bitmap kernels, nnz = retained
+ * coordinates per token, read for the bitmap and the compact layouts; `tokens` then only sizes the split count and is what the kernels use when
  * step_state[2] < 0; a count above tok_stride is cut to tok_stride; with 8-byte
  * metadata rows the count must keep the parity of `tokens`); reskv_step_advance adds
  * to the first two numbers.  A graph that holds "advance(0, 1), then per layer append +

@@ -139,9 +139,33 @@ def encode_quantized(x, centroids, ids, nnz: int, bits: int):
     return words.astype(np.uint32).view(np.int32), h
 
 
+def encode_compact(x, centroids, ids, nnz: int, bits: int):
+    """-> ``(words i32 [B,H,T,nnz*bits/32], bitmap i64 [B,H,T,2], scale f16 [B,H,T])``.
+
+    Same selection, scale and codes as ``encode_quantized``; only the kept
+    coordinates are stored (ascending coordinate order) next to the MSB-first
+    bitmap of the unstructured FP16 layout.  No counterpart in the reference.
+    """
+    qmax = (1 << (bits - 1)) - 1
+    r32 = residual_fp32(x, centroids, ids)
+    mask = topk_mask(_keys(r32), nnz)
+    amax = np.where(mask, np.abs(r32), np.float32(0)).max(-1).astype(np.float32)
+    h = np.where(amax > 0, amax / np.float32(qmax), np.float32(1.0)).astype(np.float32).astype(np.float16)
+    q = np.clip(np.rint(r32 / h.astype(np.float32)[..., None]), -qmax, qmax).astype(np.int64) & ((1 << bits) - 1)
+    order = np.argsort(~mask, axis=-1, kind="stable")[..., :nnz]  # kept coordinates, ascending
+    codes = np.take_along_axis(q, order, axis=-1)
+    per = 32 // bits
+    words = (codes.reshape(*codes.shape[:-1], nnz // per, per) << (np.arange(per) * bits)).sum(-1)
+    weights = np.uint64(1) << (np.uint64(63) - np.arange(64, dtype=np.uint64))
+    bitmap = (mask.reshape(*mask.shape[:-1], 2, 64).astype(np.uint64) * weights).sum(-1, dtype=np.uint64)
+    return words.astype(np.uint32).view(np.int32), bitmap.view(np.int64), h
+
+
 def encode(layout: str, bits: int, nnz: int, x, centroids, ids):
     """Dispatch by plan -> ``(payload, metadata or None, scale or None)``
     (compression.py:72-101)."""
+    if layout == "compact":
+        return encode_compact(x, centroids, ids, nnz, bits)
     if bits == 16 and layout == "unstructured":
         p, m = encode_unstructured_fp16(x, centroids, ids, nnz)
         return p, m, None

@@ -56,6 +56,25 @@ def residual_quantized(words: np.ndarray, scale: np.ndarray, bits: int) -> np.nd
     return q.astype(np.float32) * scale.astype(np.float32)[..., None]
 
 
+def residual_compact(words: np.ndarray, bitmap: np.ndarray, scale: np.ndarray, bits: int) -> np.ndarray:
+    """Compact quantised layout (no counterpart in the reference): the MSB-first
+    bitmap of the unstructured FP16 layout says which coordinates are kept, the
+    words hold the codes of the kept coordinates only, in ascending coordinate
+    order, code ``i`` at bit ``(i % per) * bits`` of word ``i // per`` with
+    ``per = 32 // bits``; codes and scale are those of the unstructured
+    quantised layout."""
+    per = 32 // bits
+    shifts = np.arange(per) * bits
+    q = (_u32(words)[..., None] >> shifts) & ((1 << bits) - 1)
+    q = q.reshape(*words.shape[:-1], words.shape[-1] * per)
+    sign = 1 << (bits - 1)
+    q = ((q ^ sign) - sign).astype(np.float32)
+    kept = mask_unstructured_fp16(bitmap)
+    rank = np.cumsum(kept, axis=-1) - 1
+    vals = np.take_along_axis(q, np.clip(rank, 0, q.shape[-1] - 1), axis=-1)
+    return np.where(kept, vals, np.float32(0)) * scale.astype(np.float32)[..., None]
+
+
 def residual_structured_int4(packed: np.ndarray, meta: np.ndarray, scale: np.ndarray) -> np.ndarray:
     """1-of-4 INT4: 32 signed nibbles, 32 two-bit in-group indices
     (reference.py:27-36)."""
@@ -97,6 +116,8 @@ def residual_tiled_fp16(payload: np.ndarray, meta: np.ndarray) -> np.ndarray:
 
 def residual(layout: str, bits: int, payload, metadata, scale) -> np.ndarray:
     """Dense float32 residual ``[B,H,T,128]`` of any layout."""
+    if layout == "compact":
+        return residual_compact(payload, metadata, scale, bits)
     if layout == "unstructured" and bits != 16:
         return residual_quantized(payload, scale, bits)
     if layout == "unstructured":

@@ -77,6 +77,9 @@ def attention(
         else:
             fn = ext.decode_structured_int4 if plan.bits == 4 else ext.decode_structured_fp16
             result = fn(q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, *suffix, False, plan.splits, freq, fused)
+    elif plan.layout == "compact":
+        result = ext.decode_compact(q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, *suffix, plan.bits, plan.splits, freq,
+                                    fused)
     elif plan.layout == "unstructured":
         result = ext.decode_quantized(q, kc, ki, kp, ks, vc, vi, vp, vs, *suffix, plan.bits, plan.bits, plan.splits,
                                       freq, fused)

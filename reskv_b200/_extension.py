@@ -49,6 +49,11 @@ SIGNATURES = {
         _I,
         [_P] * 9 + [_I, _I, _I, _I, _L, _I, _I, _I, _I, _I, _F, _P, _F, _I, _P, _P, _P, _I, _P, _P, _P, _P],
     ),
+    "reskv_encode_compact": (_I, [_P, _P, _P, _I, _I, _I, _L, _I, _I, _I, _P, _P, _P, _L, _P]),
+    "reskv_decode_compact": (
+        _I,
+        [_I, _I] + [_P] * 11 + [_I, _I, _I, _I, _L, _I, _I, _I, _I, _F, _P, _F, _I, _P, _P, _P, _I, _P, _Z, _P, _P, _P, _P],
+    ),
     "reskv_window_append": (_I, [_P] * 6 + [_I, _I, _I, _P, _P]),
     "reskv_decode_step": (
         _I,
@@ -169,6 +174,17 @@ class CompressionOps(_Ops):
                                               bits, words.data_ptr(), scale.data_ptr(), t, _stream(x.device)))
         return words, scale
 
+    def compress_compact(self, x, centroids, ids, nnz, bits):
+        """Compact quantised layout (not in the reference): ``(words i32 [B,H,T,nnz*bits/32],
+        bitmap i64 [B,H,T,2], scale f16 [B,H,T])``."""
+        b, h, t, c = self._dims(x, centroids, ids)
+        words = torch.empty((b, h, t, nnz * bits // 32), dtype=torch.int32, device=x.device)
+        bitmap = torch.empty((b, h, t, 2), dtype=torch.int64, device=x.device)
+        scale = torch.empty((b, h, t), dtype=torch.float16, device=x.device)
+        check(self.lib.reskv_encode_compact(x.data_ptr(), centroids.data_ptr(), ids.data_ptr(), b, h, t, t, c, nnz, bits,
+                                            words.data_ptr(), bitmap.data_ptr(), scale.data_ptr(), t, _stream(x.device)))
+        return words, bitmap, scale
+
     def compress_structured_int4(self, x, centroids, ids):
         b, h, t, c = self._dims(x, centroids, ids)
         packed = torch.empty((b, h, t, 4), dtype=torch.int32, device=x.device)
@@ -214,15 +230,15 @@ def _token_stride(rows: torch.Tensor, width: int) -> int:
     return rows.stride(0) // width
 
 
-LAYOUT_UNSTRUCTURED, LAYOUT_TILED, LAYOUT_STRUCTURED = 0, 1, 2
+LAYOUT_UNSTRUCTURED, LAYOUT_TILED, LAYOUT_STRUCTURED, LAYOUT_COMPACT = 0, 1, 2, 3
 
 
 def _decode(lib, layout, bits, q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, kh, nh, start_pos, pos_q, rope_theta, scale,
             splits, inv_freq, return_stats=True, recent=None):
     """Allocate outputs and scratch, call the decode entry point of a layout.
 
-    ``layout is None`` selects the unstructured FP16 bitmap kernel, otherwise
-    ``reskv_decode_packed``.  ``recent = (q_rot [B*nh,128], k_rot, v [B,kh,Tr,128])``
+    ``layout is None`` selects the unstructured FP16 bitmap kernel, ``LAYOUT_COMPACT``
+    ``reskv_decode_compact``, anything else ``reskv_decode_packed``.  ``recent = (q_rot [B*nh,128], k_rot, v [B,kh,Tr,128])``
     folds a dense window into the same launch pair.
     """
     bnh = q.shape[0]
@@ -252,6 +268,10 @@ def _decode(lib, layout, bits, q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, kh, nh
         rc = lib.reskv_decode_bitmap_fp16(q.data_ptr(), kc.data_ptr(), ki.data_ptr(), kp.data_ptr(), km.data_ptr(),
                                           vc.data_ptr(), vi.data_ptr(), vp.data_ptr(), vm.data_ptr(), *tail, width,
                                           *rest)
+    elif layout == LAYOUT_COMPACT:
+        rc = lib.reskv_decode_compact(bits, width * 32 // bits, q.data_ptr(), kc.data_ptr(), ki.data_ptr(), kp.data_ptr(),
+                                      _ptr(km), _ptr(ks), vc.data_ptr(), vi.data_ptr(), vp.data_ptr(), _ptr(vm),
+                                      _ptr(vs), *tail, *rest)
     else:
         rc = lib.reskv_decode_packed(layout, bits, q.data_ptr(), kc.data_ptr(), ki.data_ptr(), kp.data_ptr(),
                                      _ptr(km), _ptr(ks), vc.data_ptr(), vi.data_ptr(), vp.data_ptr(), _ptr(vm),
@@ -315,6 +335,12 @@ class AttentionOps(_Ops):
             raise ValueError("decode_quantized expects equal key and value bit widths of 2 or 4")
         return _decode(self.lib, LAYOUT_UNSTRUCTURED, k_bits, q, kc, ki, kp, None, ks, vc, vi, vp, None, vs, kh, nh,
                        start_pos, pos_q, rope_theta, scale, splits, inv_freq, True, recent)
+
+    def decode_compact(self, q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, kh, nh, start_pos, pos_q, rope_theta, scale,
+                       bits, splits=0, inv_freq=None, recent=None):
+        """Compact quantised layout (not in the reference): bitmap + codes of the retained coordinates."""
+        return _decode(self.lib, LAYOUT_COMPACT, bits, q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, kh, nh, start_pos,
+                       pos_q, rope_theta, scale, splits, inv_freq, True, recent)
 
     def merge_recent(self, out, m, l, q_rope, k_recent, v_recent, kh, nh, scale):
         b = out.shape[0] // nh

@@ -70,7 +70,9 @@ def _encode(x, centers, ids, plan: KernelPlan, *, value=False):
     x = x.contiguous()
     ops = _ops(x)
     metadata = scale = None
-    if plan.bits == 16 and plan.layout == "unstructured":
+    if plan.layout == "compact":
+        payload, metadata, scale = ops.compress_compact(x, centers, ids, plan.nnz, plan.bits)
+    elif plan.bits == 16 and plan.layout == "unstructured":
         payload, metadata = ops.compress_bitmap_fp16(x, centers, ids, plan.nnz)
     elif plan.bits == 16:
         payload, metadata = ops.compress_fp16(x, centers, ids, plan.nnz, plan.layout == "structured")

@@ -24,7 +24,9 @@ from __future__ import annotations
 
 from dataclasses import asdict, dataclass, fields
 
-_LAYOUTS = ("unstructured", "tiled", "structured")
+_LAYOUTS = ("unstructured", "tiled", "structured", "compact")
+# "compact" has no counterpart in the reference: quantised residuals stored as bitmap + packed codes
+# of the retained coordinates only (the reference's unstructured quantised layout stores all 128).
 _FUSIONS = ("per_token", "deferred")
 
 
@@ -106,6 +108,9 @@ class KernelPlan:
         elif self.layout == "tiled":
             if (self.bits, self.nnz, self.centroid_fusion) != (16, 64, "per_token"):
                 raise ValueError("invalid tiled residual configuration")
+        elif self.layout == "compact":
+            if self.bits == 16 or self.nnz * self.bits < 128 or self.centroid_fusion != "per_token":
+                raise ValueError("invalid compact residual configuration")
         else:
             wanted = "deferred" if self.bits == 16 else "per_token"
             if self.centroid_fusion != wanted:
@@ -187,6 +192,8 @@ class ResKVKernelConfig:
             raise ValueError("structured layout requires sparsity=0.75 and bits=4 or 16")
         if self.layout == "tiled" and (self.bits, self.sparsity) != (16, 0.5):
             raise ValueError("tiled masks support only FP16 residuals at sparsity 0.5")
+        if self.layout == "compact" and (self.bits == 16 or (self.bits == 2 and self.sparsity != 0.5)):
+            raise ValueError("compact layout stores INT4 residuals, or INT2 residuals at sparsity 0.5")
 
     @property
     def keep_ratio(self) -> float:
@@ -212,13 +219,15 @@ class ResKVKernelConfig:
         fusion = self.centroid_fusion
         if fusion == "auto":
             per_token = (
-                layout == "tiled"
+                layout in ("tiled", "compact")
                 or (layout == "unstructured" and self.bits != 16)
                 or (layout == "structured" and batch_size <= 2)
             )
             fusion = "per_token" if per_token else "deferred"
         if layout == "tiled" and fusion != "per_token":
             raise ValueError("tiled masks require per_token centroid fusion")
+        if layout == "compact" and fusion != "per_token":
+            raise ValueError("compact quantized caches require per_token centroid fusion")
         if layout == "unstructured":
             if self.bits == 16 and fusion != "deferred":
                 raise ValueError("unstructured FP16 requires deferred centroid fusion")

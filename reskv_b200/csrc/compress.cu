@@ -158,6 +158,61 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) encode_quantized_kernel(con
     }
 }
 
+// ---- compact quantised: bitmap + codes of the retained coordinates only ---------------
+// Same selection, scale and codes as encode_quantized_kernel; code of rank r (ascending
+// coordinate) at bit (r % kPer) * BITS of word r / kPer.
+template <int BITS>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) encode_compact_kernel(const EncodeParams p) {
+    constexpr int kQmax = (1 << (BITS - 1)) - 1;
+    constexpr int kPer = 32 / BITS;
+    __shared__ uint32_t scratch[kWarpsPerCta][8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwords = p.nnz / kPer;
+    const long long rows = static_cast<long long>(p.units) * p.tokens;
+    for (long long row = static_cast<long long>(blockIdx.x) * kWarpsPerCta + warp; row < rows;
+         row += static_cast<long long>(gridDim.x) * kWarpsPerCta) {
+        const int unit = static_cast<int>(row / p.tokens), t = static_cast<int>(row % p.tokens);
+        const Residual res = load_residual(p, unit, t, lane);
+        bool keep[4];
+        uint32_t vote[4];
+        select_topk(res.key, p.nnz, lane, keep, vote);
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) amax = fmaxf(amax, keep[i] ? fabsf(res.r[i]) : 0.f);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, off));
+        const __half hs = amax > 0.f ? __float2half_rn(__fdiv_rn(amax, static_cast<float>(kQmax))) : __float2half_rn(1.f);
+        const float s = __half2float(hs);
+        if (lane < 8) scratch[warp][lane] = 0u;
+        __syncwarp();
+        const uint32_t below = (1u << lane) - 1u;
+        int base = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (keep[i]) {
+                const float f = rintf(__fdiv_rn(res.r[i], s));
+                const int q = static_cast<int>(fminf(fmaxf(f, -static_cast<float>(kQmax)), static_cast<float>(kQmax)));
+                const int r = base + __popc(vote[i] & below);
+                atomicOr(&scratch[warp][r / kPer], (static_cast<uint32_t>(q) & ((1u << BITS) - 1u)) << ((r % kPer) * BITS));
+            }
+            base += __popc(vote[i]);
+        }
+        __syncwarp();
+        const size_t orow = static_cast<size_t>(unit) * p.out_stride + t;
+        if (lane < nwords) static_cast<int32_t*>(p.payload)[orow * nwords + lane] = static_cast<int32_t>(scratch[warp][lane]);
+        if (lane == 0) {
+            uint4 bm;  // word w of the bitmap: coordinate d at bit 63 - d % 64
+            bm.y = __brev(vote[0]);
+            bm.x = __brev(vote[1]);
+            bm.w = __brev(vote[2]);
+            bm.z = __brev(vote[3]);
+            static_cast<uint4*>(p.meta)[orow] = bm;
+            p.scale[orow] = hs;
+        }
+        __syncwarp();
+    }
+}
+
 // ---- tiled (mask) / structured 4:16 (indices) FP16 -----------------------------------
 // Tile j = coordinates 16j..16j+15 = half-warp (j % 2) of owned coordinate i = j / 2.
 template <bool STRUCT>
@@ -309,6 +364,27 @@ extern "C" int reskv_encode_quantized(const void* x, const void* centroids, cons
     else
         encode_quantized_kernel<2><<<grid_for(rows), kWarpsPerCta * 32, 0, s>>>(p);
     return check_cuda(cudaGetLastError(), "encode_quantized launch");
+}
+
+extern "C" int reskv_encode_compact(const void* x, const void* centroids, const int32_t* ids, int batch, int kv_heads,
+                                    int tokens, int64_t x_tok_stride, int clusters, int nnz, int bits, void* words,
+                                    void* bitmap, void* scale, int64_t out_tok_stride, void* stream) {
+    if (int rc = check_common("encode_compact", x, centroids, ids, words, batch, kv_heads, tokens, x_tok_stride,
+                              clusters, out_tok_stride))
+        return rc;
+    if (!scale || !bitmap) return fail(RESKV_ERR_INVALID, "encode_compact: null bitmap or scale pointer");
+    if (nnz != 32 && nnz != 64) return fail(RESKV_ERR_INVALID, "encode_compact: nnz must be 32 or 64, got %d", nnz);
+    if (bits != 2 && bits != 4) return fail(RESKV_ERR_INVALID, "encode_compact: bits must be 2 or 4, got %d", bits);
+    if (nnz * bits < 128) return fail(RESKV_ERR_INVALID, "encode_compact: rows below 16 bytes (nnz %d, %d bits) are not supported", nnz, bits);
+    EncodeParams p{static_cast<const __half*>(x), static_cast<const __half*>(centroids), ids, words, bitmap,
+                   static_cast<__half*>(scale), x_tok_stride, out_tok_stride, batch * kv_heads, tokens, clusters, nnz};
+    const long long rows = static_cast<long long>(p.units) * tokens;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (bits == 4)
+        encode_compact_kernel<4><<<grid_for(rows), kWarpsPerCta * 32, 0, s>>>(p);
+    else
+        encode_compact_kernel<2><<<grid_for(rows), kWarpsPerCta * 32, 0, s>>>(p);
+    return check_cuda(cudaGetLastError(), "encode_compact launch");
 }
 
 extern "C" int reskv_encode_tiled_fp16(const void* x, const void* centroids, const int32_t* ids, int batch,

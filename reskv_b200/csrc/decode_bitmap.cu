@@ -644,7 +644,7 @@ int g_variant = 0;
 // optional events recorded right before / after the partial kernel (profiling aid)
 cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;
 
-enum LayoutId { kBitmap32, kBitmap64, kQuant4, kQuant2, kTiled64, kStruct32, kStructInt4 };
+enum LayoutId { kBitmap32, kBitmap64, kQuant4, kQuant2, kTiled64, kStruct32, kStructInt4, kCompact4x64, kCompact4x32, kCompact2x64 };
 
 template <int GQA>
 int dispatch_layout(const DecodeParams& p, LayoutId layout, int units, cudaStream_t s) {
@@ -663,6 +663,12 @@ int dispatch_layout(const DecodeParams& p, LayoutId layout, int units, cudaStrea
         case kStruct32:
             return g_variant == 0 ? launch_packed_mma(p, 3, GQA, units, s)
                                   : launch_simt<GQA, LayoutTiled<32, true>>(p, units, s);
+        case kCompact4x64:
+        case kCompact4x32:
+        case kCompact2x64:
+            if (g_variant != 0)
+                return fail(RESKV_ERR_INVALID, "the compact quantised layout has no warp-per-token kernel");
+            return launch_packed_mma(p, 5 + (layout - kCompact4x64), GQA, units, s);
         default: {
             // 8-byte metadata rows can only be bulk-copied when every tile starts 16-byte aligned
             const bool bulk_ok = p.tokens % 2 == 0 && p.tok_stride % 2 == 0 && aligned16(p.kb) && aligned16(p.vb);
@@ -880,6 +886,32 @@ extern "C" int reskv_decode_packed(int layout, int bits, const void* q, const vo
     return decode_common(a, id, meta, scale, "decode_packed");
 }
 
+extern "C" int reskv_decode_compact(int bits, int nnz, const void* q, const void* k_centroids, const void* k_ids,
+                                    const void* k_payload, const void* k_bitmap, const void* k_scale,
+                                    const void* v_centroids, const void* v_ids, const void* v_payload,
+                                    const void* v_bitmap, const void* v_scale, int batch, int kv_heads, int q_heads,
+                                    int tokens, int64_t tok_stride, int k_clusters, int v_clusters, int start_pos,
+                                    int pos_q, float rope_theta, const float* inv_freq, float scaling, int splits,
+                                    const void* recent_q, const void* recent_k, const void* recent_v, int recent_tokens,
+                                    void* workspace, size_t workspace_bytes_given, void* out, float* out_m,
+                                    float* out_l, void* stream) {
+    LayoutId id;
+    if (bits == 4 && nnz == 64) {
+        id = kCompact4x64;
+    } else if (bits == 4 && nnz == 32) {
+        id = kCompact4x32;
+    } else if (bits == 2 && nnz == 64) {
+        id = kCompact2x64;
+    } else {
+        return fail(RESKV_ERR_INVALID, "decode_compact: no kernel for %d retained %d-bit codes per token", nnz, bits);
+    }
+    const DecodeArgs a{q, k_centroids, k_ids, k_payload, k_bitmap, k_scale, v_centroids, v_ids, v_payload, v_bitmap,
+                       v_scale, batch, kv_heads, q_heads, tokens, tok_stride, k_clusters, v_clusters, start_pos, pos_q,
+                       rope_theta, inv_freq, scaling, splits, recent_q, recent_k, recent_v, recent_tokens, workspace,
+                       workspace_bytes_given, out, out_m, out_l, stream};
+    return decode_common(a, id, true, true, "decode_compact");
+}
+
 extern "C" int reskv_decode_step(int layout, int bits, int nnz, const void* q, const void* k_centroids,
                                  const void* k_ids, const void* k_payload, const void* k_meta, const void* k_scale,
                                  const void* v_centroids, const void* v_ids, const void* v_payload,
@@ -902,6 +934,10 @@ extern "C" int reskv_decode_step(int layout, int bits, int nnz, const void* q, c
         id = kStruct32;
     } else if (layout == RESKV_LAYOUT_STRUCTURED && bits == 4) {
         id = kStructInt4, scale = true;
+    } else if (layout == RESKV_LAYOUT_COMPACT && bits == 4 && (nnz == 64 || nnz == 32)) {
+        id = nnz == 64 ? kCompact4x64 : kCompact4x32, scale = true;
+    } else if (layout == RESKV_LAYOUT_COMPACT && bits == 2 && nnz == 64) {
+        id = kCompact2x64, scale = true;
     } else {
         return fail(RESKV_ERR_INVALID, "decode_step: no kernel for layout %d with %d-bit residuals (nnz %d)", layout, bits, nnz);
     }

@@ -7,7 +7,8 @@ namespace reskv {
 
 struct DecodeParams;
 // Launches the tensor-core partial kernel of a non-bitmap layout (decode_packed_mma.cu).
-// layout: 0 = INT4, 1 = INT2 (unstructured), 2 = tiled FP16, 3 = structured FP16, 4 = structured INT4.
+// layout: 0 = INT4, 1 = INT2 (unstructured), 2 = tiled FP16, 3 = structured FP16, 4 = structured INT4,
+// 5 / 6 = compact INT4 with 64 / 32 codes, 7 = compact INT2 with 64 codes.
 int launch_packed_mma(const DecodeParams& p, int layout, int gqa, int units, cudaStream_t stream);
 
 namespace {

@@ -305,6 +305,70 @@ struct LayoutMmaQuant {
     }
 };
 
+// Compact quantised layout: a 16-bit keep mask like the FP16 bitmap layout, but the field's retained
+// coordinates are BITS-wide codes inside the token's packed row.  At most 16 codes of 4 bits: the
+// field's codes fit one 64-bit window, fetched once (three aligned words, funnel-shifted to the
+// field's first code) and consumed from the low end.  A code enters arithmetic as the FP16 number
+// 1024 + (code ^ sign), i.e. bits 0x6400 | (code ^ sign); the offset 1024 + sign is removed by the
+// consumer (key side: folded into the FP32 accumulator start; value side: one HADD2 per pair).
+template <int BITS>
+struct CompactField {
+    static constexpr uint32_t kSign = 1u << (BITS - 1);
+    static constexpr uint32_t kZero = 0x6400u | kSign;  // FP16 bits of the value that stands for code 0
+    uint32_t mask, lo, hi;
+    __device__ __forceinline__ uint32_t next() {  // FP16 bits of the next retained code; advances the window
+        const uint32_t h = ((lo & ((1u << BITS) - 1u)) ^ kZero);
+        lo = __funnelshift_r(lo, hi, BITS);
+        hi >>= BITS;
+        return h;
+    }
+    __device__ __forceinline__ void add4(int ks, float (&k)[4], unsigned short scale) {
+        // k += code * scale for retained coordinates (code = h - (1024 + sign), exact in FP16)
+        const __half off = __float2half_rn(1024.f + static_cast<float>(kSign));
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (mask & (0x8000u >> (4 * ks + e))) {
+                const __half code = __hsub(__ushort_as_half(static_cast<unsigned short>(next())), off);
+                k[e] = fma_f16_f16_f32(__half_as_ushort(code), scale, k[e]);
+            }
+        }
+    }
+    __device__ __forceinline__ void bits4(int ks, uint32_t (&h)[4]) {
+        uint32_t raw[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) raw[e] = (mask & (0x8000u >> (4 * ks + e))) ? next() : kZero;
+        // remove the offset exactly: values are integers in [-8, 7]
+        const __half2 off = __float2half2_rn(-(1024.f + static_cast<float>(kSign)));
+        const uint32_t p01 = raw[0] | (raw[1] << 16), p23 = raw[2] | (raw[3] << 16);
+        const __half2 r01 = __hadd2(*reinterpret_cast<const __half2*>(&p01), off);
+        const __half2 r23 = __hadd2(*reinterpret_cast<const __half2*>(&p23), off);
+        const uint32_t q01 = *reinterpret_cast<const uint32_t*>(&r01), q23 = *reinterpret_cast<const uint32_t*>(&r23);
+        h[0] = q01 & 0xffffu, h[1] = q01 >> 16, h[2] = q23 & 0xffffu, h[3] = q23 >> 16;
+    }
+};
+
+template <int BITS, int NNZ>
+struct LayoutMmaCompact {
+    static constexpr int kPayloadBytes = NNZ * BITS / 8, kMetaBytes = 16, kPad = 0;
+    static constexpr bool kScale = true, kPrefix = true, kScaleP = true;
+    static_assert(kPayloadBytes % 16 == 0, "packed rows must be whole 16-byte pieces");
+    using Field = CompactField<BITS>;
+    __device__ static __forceinline__ Field field(const unsigned char* pay, const unsigned char* meta,
+                                                  const unsigned char* pre, int tok, int f, bool ok) {
+        Field fd;
+        fd.mask = ok ? *reinterpret_cast<const unsigned short*>(meta + tok * 16 + field_offset(f)) : 0u;
+        // first code of the field = rank base * BITS bits into the row; words past the row's end are
+        // never consumed (a field holds at most popcount(mask) codes), so their index is clamped
+        constexpr int kWords = kPayloadBytes / 4;
+        const uint32_t* row = reinterpret_cast<const uint32_t*>(pay + tok * kPayloadBytes);
+        const int bit = pre[(tok & 15) * 8 + f] * BITS, w = bit >> 5, sh = bit & 31;
+        const uint32_t w0 = row[min(w, kWords - 1)], w1 = row[min(w + 1, kWords - 1)], w2 = row[min(w + 2, kWords - 1)];
+        fd.lo = __funnelshift_r(w0, w1, sh);
+        fd.hi = __funnelshift_r(w1, w2, sh);
+        return fd;
+    }
+};
+
 // 1-of-4 structured INT4: per 4-coordinate group one signed nibble and a 2-bit position.
 struct StructInt4Field {
     uint32_t c01, c23;  // the field's four group codes as FP16 pairs

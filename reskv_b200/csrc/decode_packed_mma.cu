@@ -1,5 +1,5 @@
 // Tensor-core partial decode kernels for the layouts other than the unstructured FP16 bitmap:
-// unstructured INT4 / INT2, tiled FP16, 4:16 structured FP16, 1-of-4 structured INT4.
+// unstructured INT4 / INT2, tiled FP16, 4:16 structured FP16, 1-of-4 structured INT4, compact INT4 / INT2.
 // Same kernel template as the bitmap layout (decode_mma.cuh); only the field policy differs.
 #include "decode_common.cuh"
 
@@ -26,6 +26,9 @@ int by_layout(const DecodeParams& p, int layout, int units, cudaStream_t s) {
         case 1: return launch<GQA, mma::LayoutMmaQuant<2>>(p, units, s);
         case 2: return launch<GQA, mma::LayoutMmaTiled<64, false>>(p, units, s);
         case 3: return launch<GQA, mma::LayoutMmaTiled<32, true>>(p, units, s);
+        case 5: return launch<GQA, mma::LayoutMmaCompact<4, 64>>(p, units, s);
+        case 6: return launch<GQA, mma::LayoutMmaCompact<4, 32>>(p, units, s);
+        case 7: return launch<GQA, mma::LayoutMmaCompact<2, 64>>(p, units, s);
         default: return launch<GQA, mma::LayoutMmaStructInt4>(p, units, s);
     }
 }

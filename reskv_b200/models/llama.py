@@ -235,7 +235,8 @@ class ResKVLlama:
     # which the compressed segment is fixed) and replayed: query position and window length live in
     # a device-side step state that the append / decode kernels read and a final kernel advances.
     def _step_body(self, tok):
-        from .._extension import LAYOUT_UNSTRUCTURED, LAYOUT_STRUCTURED, LAYOUT_TILED, _stream, check, library
+        from .._extension import (LAYOUT_COMPACT, LAYOUT_STRUCTURED, LAYOUT_TILED, LAYOUT_UNSTRUCTURED, _stream, check,
+                                  library)
 
         lib = library()
         b = tok.shape[0]
@@ -280,11 +281,12 @@ class ResKVLlama:
                 _, ki, kp, km, ks = key._native
                 _, vi, vp, vm, vs = val._native
                 kc, vc = self._centroids[index]
-                layout = {"unstructured": LAYOUT_UNSTRUCTURED, "tiled": LAYOUT_TILED, "structured": LAYOUT_STRUCTURED}[plan.layout]
+                layout = {"unstructured": LAYOUT_UNSTRUCTURED, "tiled": LAYOUT_TILED, "structured": LAYOUT_STRUCTURED,
+                          "compact": LAYOUT_COMPACT}[plan.layout]
                 att = half(b, self.h_q * 128)
                 # token count and centroid tables are read from the step state / fixed-shape tables,
                 # so the captured launch stays valid when a group is compressed between replays
-                check(lib.reskv_decode_step(layout, plan.bits, kp.shape[2], q_raw.data_ptr(), kc.data_ptr(), ki.data_ptr(),
+                check(lib.reskv_decode_step(layout, plan.bits, plan.nnz, q_raw.data_ptr(), kc.data_ptr(), ki.data_ptr(),
                                             kp.data_ptr(), ptr(km), ptr(ks), vc.data_ptr(), vi.data_ptr(), vp.data_ptr(),
                                             ptr(vm), ptr(vs), b, self.h_kv, self.h_q, key.seq_len, key.token_stride,
                                             kc.shape[1], vc.shape[1], 0, float(self.shape.rope_theta),

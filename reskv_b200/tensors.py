@@ -43,14 +43,16 @@ def payload_width(plan: KernelPlan) -> int:
     """Last-axis length of ``payload`` for ``plan`` (reference tensors.py:58-64)."""
     if plan.bits == 16:
         return plan.nnz
+    if plan.layout == "compact":
+        return plan.nnz * plan.bits // 32  # codes of the retained coordinates only
     return 4 if plan.layout == "structured" else 4 * plan.bits
 
 
 def metadata_spec(plan: KernelPlan):
     """``(words, dtype)`` of ``metadata`` for ``plan``, or ``None`` when unused."""
-    if plan.bits != 16 and plan.layout != "structured":
+    if plan.bits != 16 and plan.layout not in ("structured", "compact"):
         return None
-    if plan.layout == "unstructured":
+    if plan.layout in ("unstructured", "compact"):
         return 2, torch.int64
     return (2 if plan.bits == 4 else 4), torch.int32
 

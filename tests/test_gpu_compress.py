@@ -14,14 +14,15 @@ DEV = "cuda"
 
 PLANS = [("unstructured", 16, 32), ("unstructured", 16, 64), ("tiled", 16, 64), ("structured", 16, 32),
          ("structured", 4, 32), ("unstructured", 4, 32), ("unstructured", 4, 64), ("unstructured", 2, 32),
-         ("unstructured", 2, 64)]
+         ("unstructured", 2, 64), ("compact", 4, 64), ("compact", 4, 32), ("compact", 2, 64)]
+REFERENCE_PLANS = [p for p in PLANS if p[0] != "compact"]  # layouts the reference has (and the fixtures cover)
 
 
 def _plan(layout, bits, nnz):
     from reskv_b200.config import KernelPlan
 
     fusion = {"unstructured": "deferred" if bits == 16 else "per_token", "tiled": "per_token",
-              "structured": "deferred"}[layout]
+              "structured": "deferred", "compact": "per_token"}[layout]
     return KernelPlan(layout, fusion, bits, nnz, 4, 0)
 
 
@@ -63,7 +64,7 @@ def test_bit_exact_on_cluster_mixture(layout, bits, nnz, shape):
     _assert_same(ct, oenc.encode(layout, bits, nnz, np16(x), np16(cen), np16(ids)))
 
 
-@pytest.mark.parametrize("layout,bits,nnz", PLANS)
+@pytest.mark.parametrize("layout,bits,nnz", REFERENCE_PLANS)
 def test_golden_inputs_and_reference_decoder(golden, layout, bits, nnz):
     """Same inputs as the fixtures: packed output equals what the reference's
     own decoder was given, so its dense reconstruction is reproduced exactly."""
@@ -110,6 +111,23 @@ def test_ties_zeros_and_extremes(layout, bits, nnz):
         x, ids = x[:, :, :-1].contiguous(), ids[:, :, :-1].contiguous()
     ct = _encode_cuda(x, cen, ids, layout, bits, nnz)
     _assert_same(ct, oenc.encode(layout, bits, nnz, np16(x), np16(cen), np16(ids)))
+
+
+@pytest.mark.parametrize("bits,nnz", [(4, 64), (4, 32), (2, 64)])
+def test_compact_layout_holds_the_codes_of_the_quantised_layout(bits, nnz):
+    """The compact layout stores the same codes as the unstructured quantised layout, kept
+    coordinates only: both decode to the same dense residual, in 16 + nnz*bits/8 bytes per token."""
+    from reskv_b200.synthetic import gaussian, mixture
+
+    x = mixture(2, 2, 200, seed=5)
+    cen = gaussian(2, 2, 16, 128, seed=6)
+    ids = torch.randint(16, (2, 2, 200), generator=torch.Generator().manual_seed(7), dtype=torch.int32)
+    compact = _encode_cuda(x, cen, ids, "compact", bits, nnz)
+    full = _encode_cuda(x, cen, ids, "unstructured", bits, nnz)
+    a = olay.residual("compact", bits, np16(compact.payload), np16(compact.metadata), np16(compact.scale))
+    b = olay.residual("unstructured", bits, np16(full.payload), None, np16(full.scale))
+    assert np.array_equal(a, b)
+    assert compact.payload.shape[-1] * 4 == nnz * bits // 8 and compact.metadata.shape[-1] == 2
 
 
 def test_out_of_range_ids_are_rejected():
