@@ -50,7 +50,7 @@ UNIT = "tok/s (one decoder attention layer: cache update + fused compressed atte
 # (profiles/), keyed by workload name; None until a capture exists.
 NCU_TRAFFIC_BYTES = {
     # profiles/decode_bitmap_mma_b32_ctx8192_s075.md: dram__bytes_read.sum + dram__bytes_write.sum of one launch
-    "llama31-8b-layer attn decode ctx8192 b32 s0.75 fp16 unstructured": 339.5e6 + 8.4e6,
+    "llama31-8b-layer attn decode ctx8192 b32 s0.75 fp16 unstructured": 339.6e6 + 8.0e6,
 }
 
 
