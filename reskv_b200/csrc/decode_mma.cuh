@@ -222,13 +222,17 @@ struct LayoutMmaTiled {
     using Field = WalkField;
     __device__ static __forceinline__ Field field(const unsigned char* pay, const unsigned char* meta,
                                                   const unsigned char*, int tok, int f, bool ok) {
-        uint32_t code = ok ? *reinterpret_cast<const unsigned short*>(meta + tok * 16 + 2 * f) : 0u;
-        if constexpr (INDEXED) {
-            const uint32_t c = code;
-            code = ok ? ((1u << (c & 15u)) | (1u << ((c >> 4) & 15u)) | (1u << ((c >> 8) & 15u)) | (1u << (c >> 12))) : 0u;
-        }
+        const uint32_t code = ok ? *reinterpret_cast<const unsigned short*>(meta + tok * 16 + 2 * f) : 0u;
         Field fd;
-        fd.mask = __brev(code) >> 16;  // LSB-first -> bit 15 = first coordinate
+        if constexpr (INDEXED) {
+            // four in-tile indices -> keep mask with bit 15 = first coordinate
+            const uint32_t c = code;
+            fd.mask = ok ? ((0x8000u >> (c & 15u)) | (0x8000u >> ((c >> 4) & 15u)) | (0x8000u >> ((c >> 8) & 15u)) |
+                            (0x8000u >> (c >> 12)))
+                         : 0u;
+        } else {
+            fd.mask = __brev(code) >> 16;  // LSB-first -> bit 15 = first coordinate
+        }
         fd.ptr = reinterpret_cast<const __half*>(pay + tok * (kPayloadBytes + kPad)) + f * (NNZ / 8);
         return fd;
     }
