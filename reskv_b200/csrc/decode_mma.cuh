@@ -27,7 +27,15 @@
 // once per 64-token tile (by all threads, incrementally) into MMA B-fragment
 // order.  Softmax keeps a lazily updated running maximum per head (rescale only
 // when it grows by more than 2^8), P is rounded to FP16 once and that rounded
-// value is used for the sum, the cluster masses and the PV product alike.
+// value is used for the sum, the cluster masses and the PV product alike.  The
+// cluster masses beta[value cluster][head] are a third contraction on the same P,
+// onehot(value id)^T . P (one-hot rows from a packed FP16 compare of the ids), and
+// the PV MMAs follow the value walks two coordinates at a time.
+//
+// Staging: metadata by one bulk copy per tile, payload rows of the sparse FP16
+// layouts by 16-byte cp.async pieces of all threads into rows padded by 16 bytes
+// (lanes that walk the same field of different tokens then start in different
+// banks); one mbarrier per ring slot counts both, every wait on it is bounded.
 //
 // Precision: a single FP16 rounding of the rotated key is not enough (outlier
 // channels put the score error at ~1e-3, ten times the output tolerance on short
