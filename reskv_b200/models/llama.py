@@ -87,7 +87,7 @@ class ResKVLlama:
     """
 
     def __init__(self, shape: LlamaShape = LlamaShape(), kernel_config: ResKVKernelConfig | None = None, *,
-                 cache: str = "reskv", device="cuda", seed: int = 0, group=None, prefill_chunk: int = 16384):
+                 cache: str = "reskv", device="cuda", seed: int = 0, group=None, prefill_chunk: int = 65536):
         if cache not in ("reskv", "dense"):
             raise ValueError("cache must be 'reskv' or 'dense'")
         self.shape, self.cache_kind, self.device = shape, cache, torch.device(device)
@@ -166,29 +166,45 @@ class ResKVLlama:
     # -- prefill / decode ----------------------------------------------------------------------
     @torch.no_grad()
     def prefill(self, ids: torch.Tensor, reserve: int = 0) -> torch.Tensor:
-        """Run the prompt ``ids [B, T]``; builds the caches; returns last-token logits."""
+        """Run the prompt ``ids [B, T]``; builds the caches; returns last-token logits.
+
+        Norms, projections, RoPE and the dense causal attention run over slices of the batch (at most
+        ``prefill_chunk`` tokens at a time) so that their FP32 temporaries stay small at long contexts;
+        the cache of a layer receives the whole batch at once."""
         b, t = ids.shape
         cos, sin = self._trig(0, t)
         x = self.embed[ids]
         self.caches = []
+        rows = max(1, self.prefill_chunk // t)  # sequences per slice
+        half = dict(dtype=torch.float16, device=self.device)
         for layer in self.layers:
-            q, k, v = self._qkv(layer, x)
-            qr, kr = _rope(q, cos, sin), _rope(k, cos, sin)
-            att = F.scaled_dot_product_attention(qr, kr, v, is_causal=t > 1, enable_gqa=True, scale=self.scaling)
+            k_raw = torch.empty((b, self.h_kv, t, 128), **half)
+            k_rot, v_all = torch.empty_like(k_raw), torch.empty_like(k_raw)
+            att = torch.empty((b, t, self.h_q * 128), **half)
+            for i in range(0, b, rows):
+                q, k, v = self._qkv(layer, x[i:i + rows])
+                qr, kr = _rope(q, cos, sin), _rope(k, cos, sin)
+                out = F.scaled_dot_product_attention(qr, kr, v, is_causal=t > 1, enable_gqa=True, scale=self.scaling)
+                att[i:i + rows] = out.transpose(1, 2).reshape(-1, t, self.h_q * 128)
+                k_raw[i:i + rows], k_rot[i:i + rows], v_all[i:i + rows] = k, kr, v
+                del q, k, v, qr, kr, out
             if self.cache_kind == "reskv":
                 cache = ResKVLayerCache(self.kernel_config)
-                cache.update(kr, v, {"raw_keys": k.contiguous()})
+                cache.update(k_rot, v_all, {"raw_keys": k_raw})
                 if reserve and cache.compressed is not None:
                     total = cache.compressed.seq_len + reserve
                     cache.compressed.key = cache.compressed.key.reserve(total)
                     cache.compressed.value = cache.compressed.value.reserve(total)
             else:
                 cache = _DenseLayerCache(b, self.h_kv, t + reserve, self.device)
-                cache.append(kr, v)
+                cache.append(k_rot, v_all)
             self.caches.append(cache)
-            del qr, kr, q, k, v
-            x = x + self._all_reduce(F.linear(att.transpose(1, 2).reshape(b, t, -1), layer["wo"]))
-            x = x + self._mlp(layer, _rms_norm(x, layer["norm2"], self.shape.rms_eps))
+            del k_raw, k_rot, v_all
+            for i in range(0, b, rows):
+                x[i:i + rows] += self._all_reduce(F.linear(att[i:i + rows], layer["wo"]))
+            del att
+            for i in range(0, b, rows):
+                x[i:i + rows] += self._mlp(layer, _rms_norm(x[i:i + rows], layer["norm2"], self.shape.rms_eps))
         self.length = t
         return self._logits(x[:, -1:])
 
