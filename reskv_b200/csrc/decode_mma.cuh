@@ -188,8 +188,16 @@ __device__ __forceinline__ float h2f_bits(uint32_t bits) {
 // Sparse FP16 layouts: a 16-bit keep mask (bit 15 = first coordinate) and a pointer to the
 // field's first retained value; retained values are consecutive in the payload row.
 struct WalkField {
+    static constexpr bool kSlotwise = true;  // offers add1 / bits1: callers interleave the walks of several fields
     uint32_t mask;
     const __half* ptr;
+    __device__ __forceinline__ void add1(int slot, float& k) {
+        if (mask & (0x8000u >> slot)) {
+            k = add_f16_f32(*reinterpret_cast<const unsigned short*>(ptr), k);
+            ++ptr;
+        }
+    }
+    __device__ __forceinline__ uint32_t bits1(int slot) { return walk16(mask, slot, ptr); }
     __device__ __forceinline__ void add4(int ks, float (&k)[4], unsigned short) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -266,6 +274,7 @@ __device__ __forceinline__ uint32_t codes_to_h2(uint32_t x) {
 // residual = code * scale (scale FP16 per token).
 template <int BITS>
 struct QuantField {
+    static constexpr bool kSlotwise = false;
     uint32_t w0, w1;
     // codes of coordinates 4 ks + {0,1} and 4 ks + {2,3} as FP16 pairs
     __device__ __forceinline__ void pairs(int ks, uint32_t& p01, uint32_t& p23) const {
@@ -325,6 +334,7 @@ struct LayoutMmaQuant {
 // consumer (key side: folded into the FP32 accumulator start; value side: one HADD2 per pair).
 template <int BITS>
 struct CompactField {
+    static constexpr bool kSlotwise = false;
     static constexpr uint32_t kSign = 1u << (BITS - 1);
     static constexpr uint32_t kZero = 0x6400u | kSign;  // FP16 bits of the value that stands for code 0
     uint32_t mask, lo, hi;
@@ -383,6 +393,7 @@ struct LayoutMmaCompact {
 
 // 1-of-4 structured INT4: per 4-coordinate group one signed nibble and a 2-bit position.
 struct StructInt4Field {
+    static constexpr bool kSlotwise = false;
     uint32_t c01, c23;  // the field's four group codes as FP16 pairs
     uint32_t sel;       // four 2-bit in-group positions
     __device__ __forceinline__ unsigned short code(int ks) const {
@@ -705,10 +716,21 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
                 const float4 bl = *reinterpret_cast<const float4*>(cB + cu), bh = *reinterpret_cast<const float4*>(cB + 64 + cu);
                 float kAl[4] = {al.x, al.y, al.z, al.w}, kAh[4] = {ah.x, ah.y, ah.z, ah.w};
                 float kBl[4] = {bl.x, bl.y, bl.z, bl.w}, kBh[4] = {bh.x, bh.y, bh.z, bh.w};
-                fAl.add4(ks, kAl, kscA);
-                fAh.add4(ks, kAh, kscA);
-                fBl.add4(ks, kBl, kscB);
-                fBh.add4(ks, kBh, kscB);
+                if constexpr (Field::kSlotwise) {
+                    // the four walks advance together, one coordinate each at a time
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        fAl.add1(4 * ks + e, kAl[e]);
+                        fAh.add1(4 * ks + e, kAh[e]);
+                        fBl.add1(4 * ks + e, kBl[e]);
+                        fBh.add1(4 * ks + e, kBh[e]);
+                    }
+                } else {
+                    fAl.add4(ks, kAl, kscA);
+                    fAh.add4(ks, kAh, kscA);
+                    fBl.add4(ks, kBl, kscB);
+                    fBh.add4(ks, kBh, kscB);
+                }
                 float rAl[4], rAh[4], rBl[4], rBh[4];
 #pragma unroll
                 for (int e2 = 0; e2 < 2; ++e2) {
@@ -833,10 +855,20 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
                     uint32_t h0[4], h1[4], h2[4], h3[4];
-                    f0.bits4(ks, h0);
-                    f1.bits4(ks, h1);
-                    f2.bits4(ks, h2);
-                    f3.bits4(ks, h3);
+                    if constexpr (Field::kSlotwise) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            h0[e] = f0.bits1(4 * ks + e);
+                            h1[e] = f1.bits1(4 * ks + e);
+                            h2[e] = f2.bits1(4 * ks + e);
+                            h3[e] = f3.bits1(4 * ks + e);
+                        }
+                    } else {
+                        f0.bits4(ks, h0);
+                        f1.bits4(ks, h1);
+                        f2.bits4(ks, h2);
+                        f3.bits4(ks, h3);
+                    }
                     mma_16816(acc[2 * ks], h0[0] | (h1[0] << 16), h0[1] | (h1[1] << 16), h2[0] | (h3[0] << 16),
                               h2[1] | (h3[1] << 16), pb0, pb1);
                     mma_16816(acc[2 * ks + 1], h0[2] | (h1[2] << 16), h0[3] | (h1[3] << 16), h2[2] | (h3[2] << 16),
