@@ -711,6 +711,14 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
             for (int ks = 0; ks < 4; ++ks) {
                 // four coordinates 16q + 4ks .. +3 and their partners + 64, both tokens:
                 // k = centroid (+ residual where the bitmap bit is set)
+                // query fragments of k-step ks (low half of the head) and ks + 4 (high half), requested first
+                uint2 qh_l = make_uint2(0u, 0u), qh_h = qh_l, ql_l = qh_l, ql_h = qh_l;
+                if (q_on) {
+                    qh_l = *reinterpret_cast<const uint2*>(qbuf + 4 * ks);
+                    qh_h = *reinterpret_cast<const uint2*>(qbuf + 64 + 4 * ks);
+                    ql_l = *reinterpret_cast<const uint2*>(qbuf + GQA * kQStride + 4 * ks);
+                    ql_h = *reinterpret_cast<const uint2*>(qbuf + GQA * kQStride + 64 + 4 * ks);
+                }
                 const int cu = (ks ^ cen_swz) * 4;
                 const float4 al = *reinterpret_cast<const float4*>(cA + cu), ah = *reinterpret_cast<const float4*>(cA + 64 + cu);
                 const float4 bl = *reinterpret_cast<const float4*>(cB + cu), bh = *reinterpret_cast<const float4*>(cB + 64 + cu);
@@ -745,14 +753,6 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
                     rBh[e] = kBh[e] * tb.x + kBl[e] * tb.y;
                     rBl[e + 1] = kBl[e + 1] * tb.z - kBh[e + 1] * tb.w;
                     rBh[e + 1] = kBh[e + 1] * tb.z + kBl[e + 1] * tb.w;
-                }
-                // k-step ks (low half of the head) and ks + 4 (high half)
-                uint2 qh_l = make_uint2(0u, 0u), qh_h = qh_l, ql_l = qh_l, ql_h = qh_l;
-                if (q_on) {
-                    qh_l = *reinterpret_cast<const uint2*>(qbuf + 4 * ks);
-                    qh_h = *reinterpret_cast<const uint2*>(qbuf + 64 + 4 * ks);
-                    ql_l = *reinterpret_cast<const uint2*>(qbuf + GQA * kQStride + 4 * ks);
-                    ql_h = *reinterpret_cast<const uint2*>(qbuf + GQA * kQStride + 64 + 4 * ks);
                 }
                 uint32_t a0, a1, a2, a3, l0, l1, l2, l3;
                 split_h2(rAl[0], rAl[1], a0, l0);
