@@ -772,6 +772,15 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i) sc[i] += sc2[i] + sc3[i];
+            // value fields of tokens 2q, 2q+1, 2q+8, 2q+9, coordinates [16g, 16g+16): set up before the softmax so
+            // that their mask and rank-base loads are in flight during it
+            const unsigned char* pv_bytes = reinterpret_cast<const unsigned char*>(pre_v);
+            const int r0 = 2 * qd, r1 = 2 * qd + 1, r2 = 2 * qd + 8, r3 = 2 * qd + 9;
+            Field f0 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r0, g, r0 < nvalid);
+            Field f1 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r1, g, r1 < nvalid);
+            Field f2 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r2, g, r2 < nvalid);
+            Field f3 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r3, g, r3 < nvalid);
+
             // sc: c0,c1 = (token g, heads 2q, 2q+1), c2,c3 = (token g+8, ...), log2 domain
             if (!okA) sc[0] = sc[1] = -INFINITY;
             if (!okB) sc[2] = sc[3] = -INFINITY;
@@ -846,12 +855,6 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
             // m-block i holds coordinates 16g + 2i (rows g) and 16g + 2i + 1 (rows g + 8), so that the MMAs
             // follow the field walks two coordinates at a time
             {
-                const unsigned char* pv_bytes = reinterpret_cast<const unsigned char*>(pre_v);
-                const int r0 = 2 * qd, r1 = 2 * qd + 1, r2 = 2 * qd + 8, r3 = 2 * qd + 9;
-                Field f0 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r0, g, r0 < nvalid);
-                Field f1 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r1, g, r1 < nvalid);
-                Field f2 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r2, g, r2 < nvalid);
-                Field f3 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r3, g, r3 < nvalid);
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
                     uint32_t h0[4], h1[4], h2[4], h3[4];
