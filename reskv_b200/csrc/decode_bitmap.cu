@@ -457,9 +457,10 @@ __device__ __forceinline__ void stage_rows(__half* dst, const __half* src, int r
 
 // dynamic shared memory of the merge kernel: value centroids, one chunk of recent keys and of recent
 // values (shared by the unit's query heads), recent scores per head
+constexpr int kMergePartStride = kHeadDim + kMaxClusters + 4;
 size_t merge_smem_bytes(int cv, int gqa, int recent_max) {
     return (static_cast<size_t>(cv) + 2 * kRecentChunk) * kHeadDim * sizeof(__half) +
-           static_cast<size_t>(gqa) * ((recent_max + 3) / 4 * 4) * sizeof(float);
+           static_cast<size_t>(gqa) * ((kMergeThreads / 32) * kMergePartStride + (recent_max + 3) / 4 * 4) * sizeof(float);
 }
 
 // One CTA per (sequence, KV head) unit, 128 threads per query head of the unit; thread (h, d) owns
@@ -471,6 +472,7 @@ __global__ void __launch_bounds__(1024) decode_merge_kernel(const MergeParams p,
     extern __shared__ __align__(16) unsigned char merge_smem[];
     __shared__ float beta_s[8][kMaxClusters];
     __shared__ float red[8][kMergeThreads / 32];
+    constexpr int kPartStride = kMergePartStride;  // per (head, warp): delta, cluster masses, max, sum
     const int gqa = p.nh / p.kh, threads = gqa * kMergeThreads;
     const int unit = blockIdx.x, tid = threadIdx.x;
     const int h = tid / kMergeThreads, d = tid % kMergeThreads, lane = d & 31, warp = d >> 5;
@@ -479,7 +481,8 @@ __global__ void __launch_bounds__(1024) decode_merge_kernel(const MergeParams p,
     __half* vc_s = reinterpret_cast<__half*>(merge_smem);
     __half* rk_s = vc_s + static_cast<size_t>(p.cv) * kHeadDim;
     __half* rv_s = rk_s + kRecentChunk * kHeadDim;
-    float* sc_s = reinterpret_cast<float*>(rv_s + kRecentChunk * kHeadDim) + h * sc_stride;
+    float* part_s = reinterpret_cast<float*>(rv_s + kRecentChunk * kHeadDim);  // [gqa][4 warps][kPartStride]
+    float* sc_s = part_s + gqa * (kMergeThreads / 32) * kPartStride + h * sc_stride;
     const int tr = p.dyn ? min(p.dyn[1], recent_max) : p.tr;
     const bool dot_scores = tr > 0 && !p.rscores;
     const __half* rk_g = p.rk ? p.rk + static_cast<size_t>(unit) * p.recent_cap * kHeadDim : nullptr;
@@ -495,19 +498,47 @@ __global__ void __launch_bounds__(1024) decode_merge_kernel(const MergeParams p,
     // compressed part: numerator `num`, max `m2` (log2 domain), sum `l`
     float m2, l, num;
     if (p.splits > 0) {
+        // The four warps of a head share the splits (warp w takes splits w, w + 4, ...) and read each
+        // partial row with 16-byte loads (lane: coordinates 4 lane .. 4 lane + 3; lanes 0..15 also four
+        // cluster masses), so all loads of a warp are in flight together; the four partial results are
+        // combined through shared memory.
         const float* pm = p.ws_m + static_cast<size_t>(fq) * p.splits;
         const float* pl = p.ws_l + static_cast<size_t>(fq) * p.splits;
-        m2 = pm[0];
-        for (int s = 1; s < p.splits; ++s) m2 = fmaxf(m2, pm[s]);
+        float wm = -INFINITY;
+        for (int s = warp; s < p.splits; s += kMergeThreads / 32) wm = fmaxf(wm, pm[s]);
+        float wl = 0.f;
+        float4 wn = make_float4(0.f, 0.f, 0.f, 0.f), wb = wn;
+#pragma unroll 4
+        for (int s = warp; s < p.splits; s += kMergeThreads / 32) {
+            const float w = (pm[s] == -INFINITY) ? 0.f : fast_exp2(pm[s] - wm);
+            const size_t row = static_cast<size_t>(fq) * p.splits + s;
+            const float4 dv = *reinterpret_cast<const float4*>(p.ws_delta + row * kHeadDim + 4 * lane);
+            wl += pl[s] * w;
+            wn.x += dv.x * w, wn.y += dv.y * w, wn.z += dv.z * w, wn.w += dv.w * w;
+            if (lane < kMaxClusters / 4) {
+                const float4 bv = *reinterpret_cast<const float4*>(p.ws_beta + row * kMaxClusters + 4 * lane);
+                wb.x += bv.x * w, wb.y += bv.y * w, wb.z += bv.z * w, wb.w += bv.w * w;
+            }
+        }
+        float* slot = part_s + (h * (kMergeThreads / 32) + warp) * kPartStride;  // [delta 128 | beta 64 | m | l]
+        *reinterpret_cast<float4*>(slot + 4 * lane) = wn;
+        if (lane < kMaxClusters / 4) *reinterpret_cast<float4*>(slot + kHeadDim + 4 * lane) = wb;
+        if (lane == 0) slot[kHeadDim + kMaxClusters] = wm, slot[kHeadDim + kMaxClusters + 1] = wl;
+        __syncthreads();
+        const float* mine = part_s + h * (kMergeThreads / 32) * kPartStride;
+        m2 = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kMergeThreads / 32; ++w) m2 = fmaxf(m2, mine[w * kPartStride + kHeadDim + kMaxClusters]);
         l = 0.f, num = 0.f;
         float bsum = 0.f;
-#pragma unroll 4
-        for (int s = 0; s < p.splits; ++s) {
-            const float w = (pm[s] == -INFINITY) ? 0.f : fast_exp2(pm[s] - m2);
-            l += pl[s] * w;
-            const size_t row = static_cast<size_t>(fq) * p.splits + s;
-            num += p.ws_delta[row * kHeadDim + d] * w;
-            if (d < p.cv) bsum += p.ws_beta[row * kMaxClusters + d] * w;
+#pragma unroll
+        for (int w = 0; w < kMergeThreads / 32; ++w) {
+            const float* ps = mine + w * kPartStride;
+            const float pmw = ps[kHeadDim + kMaxClusters];
+            const float sc = (pmw == -INFINITY) ? 0.f : fast_exp2(pmw - m2);
+            l += ps[kHeadDim + kMaxClusters + 1] * sc;
+            num += ps[d] * sc;
+            if (d < p.cv) bsum += ps[kHeadDim + d] * sc;
         }
         if (d < kMaxClusters) beta_s[h][d] = (d < p.cv) ? bsum : 0.f;
         if (d == 0) {
@@ -805,10 +836,11 @@ int decode_common(const DecodeArgs& a, LayoutId layout, bool has_meta, bool has_
     p.vid = static_cast<const int8_t*>(a.vid);
     p.vp = a.vp, p.vb = a.vm;
     p.ks = static_cast<const __half*>(a.ks), p.vs = static_cast<const __half*>(a.vs);
-    p.ws_m = wsf;
-    p.ws_l = wsf + rows;
-    p.ws_delta = wsf + 2 * rows;
-    p.ws_beta = wsf + 2 * rows + rows * kHeadDim;
+    // the two wide arrays first: their rows stay 16-byte aligned for any row count
+    p.ws_delta = wsf;
+    p.ws_beta = wsf + rows * kHeadDim;
+    p.ws_m = wsf + rows * (kHeadDim + kMaxClusters);
+    p.ws_l = p.ws_m + rows;
     p.status = static_cast<uint32_t*>(a.workspace);
     p.inv_freq = a.inv_freq;
     p.tok_stride = a.tok_stride;
