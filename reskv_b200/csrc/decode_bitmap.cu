@@ -495,6 +495,14 @@ __global__ void __launch_bounds__(1024) decode_merge_kernel(const MergeParams p,
     if (tr > 0) stage_rows(rv_s, rv_g, min(tr, kRecentChunk), tid, threads);
     asm volatile("cp.async.commit_group;" ::: "memory");
 
+    // rotated query of this head, requested together with everything else the kernel reads
+    float qv[4] = {0.f, 0.f, 0.f, 0.f};
+    if (dot_scores) {
+        const __half* qrow = p.rq + static_cast<size_t>(fq) * kHeadDim;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) qv[i] = __half2float(qrow[lane + 32 * i]);
+    }
+
     // compressed part: numerator `num`, max `m2` (log2 domain), sum `l`
     float m2, l, num;
     if (p.splits > 0) {
@@ -563,10 +571,6 @@ __global__ void __launch_bounds__(1024) decode_merge_kernel(const MergeParams p,
             for (int t = d; t < tr; t += kMergeThreads)
                 sc_s[t] = p.rscores[static_cast<size_t>(fq) * tr + t] * kLog2e;
         } else {
-            const __half* qrow = p.rq + static_cast<size_t>(fq) * kHeadDim;
-            float qv[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) qv[i] = __half2float(qrow[lane + 32 * i]);
             const float mul = p.scaling * kLog2e;
             for (int c0 = 0; c0 < tr; c0 += kRecentChunk) {
                 const int n = min(kRecentChunk, tr - c0);
