@@ -1,0 +1,5 @@
+"""Alias: this module is replaced by ``reskv_b200.cache`` on import."""
+import importlib
+import sys
+
+sys.modules[__name__] = importlib.import_module("reskv_b200.cache")

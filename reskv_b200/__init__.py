@@ -9,7 +9,7 @@ on first use.
 from .config import KernelPlan, ResKVConfig, ResKVKernelConfig
 
 __version__ = "0.1.0"
-__all__ = ["ResKVKernelConfig", "ResKVConfig", "KernelPlan", "compress", "attention"]
+__all__ = ["ResKVKernelConfig", "ResKVForCausalLM", "ResKVConfig", "KernelPlan", "compress", "attention"]
 
 
 def __getattr__(name):
@@ -21,4 +21,8 @@ def __getattr__(name):
         from ._attention import attention
 
         return attention
+    if name == "ResKVForCausalLM":  # needs transformers: imported on first use (reference __init__.py:18-21)
+        from .models.hf_llama import ResKVForCausalLM
+
+        return ResKVForCausalLM
     raise AttributeError(name)
