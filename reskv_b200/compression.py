@@ -17,15 +17,17 @@ from .tensors import CompressedKV, CompressedTensor
 _INT_DTYPES = (torch.int8, torch.int16, torch.int32, torch.int64)
 
 
-def _validate(x: torch.Tensor):
-    if x.ndim != 4 or x.shape[-1] != 128 or not x.is_cuda or x.dtype != torch.float16:
-        raise ValueError("expected FP16 CUDA tensor [batch, kv_heads, tokens, 128]")
-    if min(x.shape[:3]) < 1:
-        raise ValueError("batch, head and token dimensions must be nonempty")
+def _require_kv(x, role: str) -> None:
+    """K or V as the kernels read it: FP16, on a CUDA device, ``[B, H, T, 128]``, no empty axis."""
+    layout_ok = isinstance(x, torch.Tensor) and x.ndim == 4 and x.shape[-1] == 128
+    if not (layout_ok and x.is_cuda and x.dtype == torch.float16):
+        raise ValueError(f"{role}: expected FP16 CUDA tensor [batch, kv_heads, tokens, 128]")
+    if 0 in x.shape[:3]:
+        raise ValueError(f"{role}: batch, head and token dimensions must be nonempty")
 
 
 def _ops(x: torch.Tensor):
-    return load_extension("compression", device_index=x.device.index or 0)
+    return load_extension("compression", device_index=x.device.index)
 
 
 @torch.no_grad()
@@ -45,7 +47,7 @@ def cluster(x: torch.Tensor, count: int = 32, iterations: int = 10, *, value: bo
     ``T < count`` on the K path the surplus centres repeat tokens instead of
     adding jitter from the global RNG.
     """
-    _validate(x)
+    _require_kv(x, "cluster input")
     t = x.shape[2]
     if value:
         count = min(count, t)
@@ -83,6 +85,51 @@ def _encode(x, centers, ids, plan: KernelPlan, *, value=False):
     return CompressedTensor(centers, ids, payload, metadata, scale, plan)
 
 
+def _plan_for(config: ResKVKernelConfig, previous, plan, batch: int) -> KernelPlan:
+    """The plan the new tokens are packed with: the caller's, else the existing cache's, else the
+    configuration's own choice for this batch.  It has to describe the same format as ``config``."""
+    if plan is None:
+        plan = previous.key.plan if previous is not None else config.resolve(batch)
+    asked = {"layout": config.layout, "centroid fusion": config.centroid_fusion}
+    got = {"layout": plan.layout, "centroid fusion": plan.centroid_fusion}
+    if (plan.bits, plan.nnz) != (config.bits, int(128 * config.keep_ratio)):
+        raise ValueError("compression plan and configuration disagree")
+    for what, want in asked.items():
+        if want != "auto" and got[what] != want:
+            raise ValueError(f"compression plan violates the requested {what}")
+    if plan.fixed_shift is not (config.softmax_mode == "fixed_shift"):
+        raise ValueError("compression plan and softmax configuration disagree")
+    return plan
+
+
+def _check_previous(previous: CompressedKV, key: torch.Tensor, limit: int) -> None:
+    """An existing cache can take the new group only if it belongs to the same sequences and heads,
+    lives on the same device and its centroid tables respect the configured limit."""
+    tables = (previous.key.centroids, previous.value.centroids)
+    same_units = previous.key.cluster_ids.shape[:2] == key.shape[:2]
+    if not same_units or tables[0].device != key.device:
+        raise ValueError("previous cache has incompatible dimensions or device")
+    if any(t.shape[2] > limit for t in tables):
+        raise ValueError("previous cache exceeds the configured centroid limit")
+
+
+def _check_external(centres, ids, key: torch.Tensor, limit: int) -> None:
+    """One side of ``clustering=``: a centroid table ``[B,H,C,128]`` with ``1 <= C <= limit`` and integer
+    ids ``[B,H,T]`` inside ``[0, C)``, both next to K / V."""
+    if centres.ndim != 4 or tuple(centres.shape[:2]) != tuple(key.shape[:2]) or centres.shape[-1] != 128:
+        raise ValueError("external centers must have shape [B,H,C,128]")
+    count = centres.shape[2]
+    if count < 1 or count > limit or ids.shape != key.shape[:3]:
+        raise ValueError("external clustering has incompatible sizes")
+    if {centres.device, ids.device} != {key.device}:
+        raise ValueError("external clustering must share the K/V device")
+    if ids.dtype not in _INT_DTYPES:
+        raise ValueError("cluster IDs must be integer tensors")
+    lo, hi = torch.aminmax(ids)
+    if int(lo) < 0 or int(hi) >= count:
+        raise ValueError("external cluster IDs are out of range")
+
+
 @torch.no_grad()
 def compress(
     key: torch.Tensor,
@@ -100,51 +147,33 @@ def compress(
     clustering, ``previous`` extends an existing cache (its centroid tables grow
     by one group mean until ``config.max_clusters``).
     """
-    config = ResKVKernelConfig() if config is None else config
-    if not isinstance(config, ResKVKernelConfig):
+    if config is None:
+        config = ResKVKernelConfig()
+    elif not isinstance(config, ResKVKernelConfig):
         raise TypeError("compress requires ResKVKernelConfig; ResKVConfig is for accuracy evaluation")
-    _validate(key)
-    _validate(value)
+    _require_kv(key, "key")
+    _require_kv(value, "value")
     if key.shape != value.shape or key.device != value.device:
         raise ValueError("K and V must have identical shapes and devices")
-    plan = plan or (previous.key.plan if previous else config.resolve(key.shape[0]))
-    if plan.bits != config.bits or plan.nnz != int(128 * config.keep_ratio):
-        raise ValueError("compression plan and configuration disagree")
-    if config.layout != "auto" and plan.layout != config.layout:
-        raise ValueError("compression plan violates the requested layout")
-    if config.centroid_fusion != "auto" and plan.centroid_fusion != config.centroid_fusion:
-        raise ValueError("compression plan violates the requested centroid fusion")
-    if plan.fixed_shift != (config.softmax_mode == "fixed_shift"):
-        raise ValueError("compression plan and softmax configuration disagree")
+    plan = _plan_for(config, previous, plan, key.shape[0])
     if previous is not None:
-        pk = previous.key
-        if pk.cluster_ids.shape[:2] != key.shape[:2] or pk.centroids.device != key.device:
-            raise ValueError("previous cache has incompatible dimensions or device")
-        if max(pk.centroids.shape[2], previous.value.centroids.shape[2]) > config.max_clusters:
-            raise ValueError("previous cache exceeds the configured centroid limit")
-    if clustering is not None and previous is not None:
-        raise ValueError("provide clustering or previous, not both")
+        _check_previous(previous, key, config.max_clusters)
+        if clustering is not None:
+            raise ValueError("provide clustering or previous, not both")
     if clustering is not None:
-        (kc, ki), (vc, vi) = clustering
-        for centers, ids in ((kc, ki), (vc, vi)):
-            if centers.ndim != 4 or centers.shape[:2] != key.shape[:2] or centers.shape[-1] != 128:
-                raise ValueError("external centers must have shape [B,H,C,128]")
-            if not 1 <= centers.shape[2] <= config.max_clusters or ids.shape != key.shape[:3]:
-                raise ValueError("external clustering has incompatible sizes")
-            if centers.device != key.device or ids.device != key.device:
-                raise ValueError("external clustering must share the K/V device")
-            if ids.dtype not in _INT_DTYPES:
-                raise ValueError("cluster IDs must be integer tensors")
-            if bool(((ids < 0) | (ids >= centers.shape[2])).any()):
-                raise ValueError("external cluster IDs are out of range")
-    elif previous is not None:
-        kc, ki = _incremental_cluster(key, previous.key.centroids, config)
-        vc, vi = _incremental_cluster(value, previous.value.centroids, config, value=True)
-    else:
-        kc, ki = cluster(key, config.num_clusters, config.kmeans_iterations)
-        vc, vi = cluster(value, config.num_clusters, config.kmeans_iterations, value=True)
-    k = _encode(key, kc, ki, plan)
-    v = _encode(value, vc, vi, plan, value=True)
-    if previous is not None:
-        k, v = previous.key.append(k), previous.value.append(v)
-    return CompressedKV(k, v)
+        for centres, ids in clustering:
+            _check_external(centres, ids, key, config.max_clusters)
+
+    packed = []
+    for side, x in enumerate((key, value)):  # 0 = K, 1 = V
+        is_value = side == 1
+        if clustering is not None:
+            centres, ids = clustering[side]
+        elif previous is not None:
+            grown = (previous.key, previous.value)[side].centroids
+            centres, ids = _incremental_cluster(x, grown, config, value=is_value)
+        else:
+            centres, ids = cluster(x, config.num_clusters, config.kmeans_iterations, value=is_value)
+        new = _encode(x, centres, ids, plan, value=is_value)
+        packed.append(new if previous is None else (previous.key, previous.value)[side].append(new))
+    return CompressedKV(*packed)
