@@ -71,6 +71,10 @@ class CompressedTensor:
     # Backing buffers [B,H,capacity,...] of (ids, payload, metadata, scale); the
     # public fields are their leading ``T`` tokens.
     _buffers: tuple = field(default=(), init=False, repr=False)
+    # One-element list shared by every window over the same ``_buffers``: the number of tokens that
+    # some window has already written there.  A window shorter than that has a sibling that appended
+    # first, so its own ``append`` must not write into the shared buffers (it copies instead).
+    _live: list = field(default=None, init=False, repr=False)
 
     def __post_init__(self):
         c, ids, p = self.centroids, self.cluster_ids, self.payload
@@ -118,6 +122,7 @@ class CompressedTensor:
             self.metadata = self.metadata.contiguous() if self.metadata is not None else None
             self.scale = self.scale.contiguous() if self.scale is not None else None
             self._buffers = (self.cluster_ids, self.payload, self.metadata, self.scale)
+            self._live = [n]
         cap = self._buffers[0].shape[2]
 
         def rows(buf):
@@ -132,12 +137,14 @@ class CompressedTensor:
         )
 
     @classmethod
-    def _window(cls, centroids, buffers, length, plan) -> "CompressedTensor":
-        """Tensor over the first ``length`` tokens of capacity ``buffers``."""
+    def _window(cls, centroids, buffers, length, plan, live=None) -> "CompressedTensor":
+        """Tensor over the first ``length`` tokens of capacity ``buffers``; ``live`` is the written-length
+        marker of those buffers (a fresh one when they are new)."""
         self = cls.__new__(cls)
         self.centroids = centroids
         self.plan = plan
         self._buffers = tuple(buffers)
+        self._live = [length] if live is None else live
         views = [buf[:, :, :length] if buf is not None else None for buf in buffers]
         self.cluster_ids, self.payload, self.metadata, self.scale = views
         self._native = ()
@@ -161,14 +168,25 @@ class CompressedTensor:
 
     @property
     def nbytes(self) -> int:
+        """Bytes of the backing storages, i.e. of the *capacity* (up to twice the live data after an
+        ``append`` grew the buffers); ``live_nbytes`` counts the live tokens only."""
         return _storage_bytes(self.tensors)
 
+    @property
+    def live_nbytes(self) -> int:
+        """Bytes the live tokens occupy (what the reference's ``nbytes`` reports for its exactly sized
+        tensors, reskv/tensors.py:121-132): centroid table plus ``seq_len`` rows of every per-token tensor."""
+        views = (self.centroids, self.cluster_ids, self.payload, self.metadata, self.scale)
+        return sum(v.numel() * v.element_size() for v in views if v is not None)
+
     # -- updates ----------------------------------------------------------
-    def reserve(self, capacity: int) -> "CompressedTensor":
-        """Same tokens over buffers that hold at least ``capacity`` tokens."""
+    def reserve(self, capacity: int, *, copy: bool = False) -> "CompressedTensor":
+        """Same tokens over buffers that hold at least ``capacity`` tokens (``copy=True``: over new
+        buffers even when the present ones are large enough)."""
         n = self.seq_len
-        if self.token_stride >= capacity:
+        if self.token_stride >= capacity and not copy:
             return self
+        capacity = max(capacity, n)
         b, h = self.cluster_ids.shape[:2]
         grown = []
         for view in (self.cluster_ids, self.payload, self.metadata, self.scale):
@@ -188,17 +206,24 @@ class CompressedTensor:
         ``other`` behind the live tokens of ``self``'s buffers and returns a
         longer window over the same memory; only a full buffer is reallocated
         (to twice the needed length).  ``self`` stays valid: its tokens are not
-        touched.
+        touched.  Appending twice to the same tensor (two continuations of one
+        prefix) is as functional as the reference's ``torch.cat``: the second
+        append finds the slots behind ``self`` taken by the first and writes into
+        a copy, so both results stay intact.
         """
         if self.plan != other.plan:
             raise ValueError("cannot concatenate different cache plans")
         n, total = self.seq_len, self.seq_len + other.seq_len
-        base = self if self.token_stride >= total else self.reserve(max(2 * total, 256))
+        taken = self._live[0] != n  # a sibling window already appended behind these tokens
+        base = self
+        if taken or self.token_stride < total:
+            base = self.reserve(max(2 * total, 256) if self.token_stride < total else self.token_stride, copy=taken)
         news = (other.cluster_ids, other.payload, other.metadata, other.scale)
         for buf, new in zip(base._buffers, news):
             if buf is not None:
                 buf[:, :, n:total].copy_(new)
-        return CompressedTensor._window(other.centroids, base._buffers, total, self.plan)
+        base._live[0] = total
+        return CompressedTensor._window(other.centroids, base._buffers, total, self.plan, base._live)
 
     def index_select(self, index: torch.Tensor) -> "CompressedTensor":
         def take(t):

@@ -1,0 +1,53 @@
+"""Container behaviour that needs no GPU: appends over shared capacity buffers."""
+
+import torch
+
+from reskv_b200.config import KernelPlan
+from reskv_b200.tensors import CompressedTensor
+
+
+def _tensor(t, seed, centroids=4):
+    g = torch.Generator().manual_seed(seed)
+    plan = KernelPlan("unstructured", "deferred", 16, 32, 2, 0)
+    return CompressedTensor(
+        torch.randn(1, 2, centroids, 128, generator=g).half(),
+        torch.randint(centroids, (1, 2, t), generator=g, dtype=torch.int32),
+        torch.randn(1, 2, t, 32, generator=g).half(),
+        torch.randint(-(2 ** 62), 2 ** 62, (1, 2, t, 2), generator=g, dtype=torch.int64),
+        None, plan)
+
+
+def _cat(a, b):
+    return [torch.cat((x, y), 2) for x, y in ((a.cluster_ids, b.cluster_ids), (a.payload, b.payload),
+                                              (a.metadata, b.metadata))]
+
+
+def _same(t, want):
+    return all(torch.equal(x, y) for x, y in zip((t.cluster_ids, t.payload, t.metadata), want))
+
+
+def test_two_appends_from_one_parent_do_not_overwrite_each_other():
+    parent, first, second, third = _tensor(100, 1), _tensor(64, 2), _tensor(64, 3), _tensor(64, 4)
+    want_a, want_b = _cat(parent, first), _cat(parent, second)
+    a = parent.append(first)      # grows the buffers, writes slots [100, 164)
+    b = parent.append(second)     # parent's buffers are its own 100 tokens: new buffers again
+    assert _same(a, want_a) and _same(b, want_b)
+    # both continue in place over their own buffers ...
+    a2 = a.append(third)
+    assert a2.payload.data_ptr() == a.payload.data_ptr() and _same(a, want_a)
+    # ... and a second continuation of `a` (whose slots behind 164 are now taken by a2) is copied
+    a3 = a.append(second)
+    assert a3.payload.data_ptr() != a.payload.data_ptr()
+    want_a2 = [torch.cat((x, y), 2) for x, y in zip(want_a, (third.cluster_ids, third.payload, third.metadata))]
+    want_a3 = [torch.cat((x, y), 2) for x, y in zip(want_a, (second.cluster_ids, second.payload, second.metadata))]
+    assert _same(a2, want_a2) and _same(a3, want_a3) and _same(b, want_b)
+    assert torch.equal(a3.centroids, second.centroids)  # the newer centroid table wins
+
+
+def test_capacity_and_live_bytes():
+    parent = _tensor(100, 5)
+    grown = parent.append(_tensor(64, 6))
+    per_token = 1 + 32 * 2 + 16
+    assert grown.live_nbytes == 2 * 4 * 128 * 2 + 2 * 164 * per_token
+    assert grown.nbytes >= grown.live_nbytes and grown.token_stride >= 2 * 164
+    assert parent.live_nbytes == 2 * 4 * 128 * 2 + 2 * 100 * per_token
