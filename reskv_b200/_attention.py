@@ -12,6 +12,7 @@ from __future__ import annotations
 import torch
 
 from ._extension import load_extension
+from .config import _reference_schedule
 from .tensors import CompressedKV
 
 
@@ -50,7 +51,7 @@ def attention(
         raise ValueError("query position precedes compressed tokens")
     plan = cache.key.plan
     family = "attention" if plan.centroid_fusion == "per_token" else "cluster_mass"
-    ext = load_extension(family, plan, query.device.index or 0)
+    ext = load_extension(family, plan, query.device.index)
     q = query.reshape(b * nh, 128).contiguous()
     kc, ki, kp, km, ks = cache.key._native
     vc, vi, vp, vm, vs = cache.value._native
@@ -67,23 +68,29 @@ def attention(
             raise ValueError("recent Q/K/V shapes do not match the compressed cache")
         if any(x.device != query.device or x.dtype != torch.float16 for x in recent):
             raise ValueError("recent tensors must be FP16 on the query device")
+    # A plan from ``resolve()`` carries the split count of the reference's schedule table, which was tuned
+    # for other kernels on another GPU: such a plan gets this library's own schedule (0).  A split count that
+    # differs from the table entry was chosen by the caller and is passed on.
+    splits = plan.splits
+    if plan.layout != "compact" and splits == _reference_schedule(plan.layout, plan.centroid_fusion, plan.bits, b)[1]:
+        splits = 0
     suffix = (kh, nh, int(start_position), int(position), float(rope_theta), scale)
     fused = (qr.reshape(b * nh, 128), kr, vr) if has_recent else None
     # every decode op takes the dense window as an extra argument and folds it into its
     # merge kernel, so no separate merge_recent launch (or bmm) is needed here
     if plan.centroid_fusion == "deferred":
         if plan.layout == "unstructured":
-            result = ext.decode_fp16(q, kc, ki, kp, km, vc, vi, vp, vm, *suffix, False, plan.splits, freq, fused)
+            result = ext.decode_fp16(q, kc, ki, kp, km, vc, vi, vp, vm, *suffix, False, splits, freq, fused)
         else:
             fn = ext.decode_structured_int4 if plan.bits == 4 else ext.decode_structured_fp16
-            result = fn(q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, *suffix, False, plan.splits, freq, fused)
+            result = fn(q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, *suffix, False, splits, freq, fused)
     elif plan.layout == "compact":
-        result = ext.decode_compact(q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, *suffix, plan.bits, plan.splits, freq,
+        result = ext.decode_compact(q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, *suffix, plan.bits, splits, freq,
                                     fused)
     elif plan.layout == "unstructured":
-        result = ext.decode_quantized(q, kc, ki, kp, ks, vc, vi, vp, vs, *suffix, plan.bits, plan.bits, plan.splits,
+        result = ext.decode_quantized(q, kc, ki, kp, ks, vc, vi, vp, vs, *suffix, plan.bits, plan.bits, splits,
                                       freq, fused)
     else:
         fn = ext.decode_int4 if plan.bits == 4 else ext.decode_fp16
-        result = fn(q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, *suffix, plan.splits, freq, fused)
+        result = fn(q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, *suffix, splits, freq, fused)
     return result[0].reshape(b, nh, 1, 128)

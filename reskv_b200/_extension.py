@@ -123,26 +123,69 @@ def _stream(device: torch.device) -> int:
 _CHECK_STATUS = os.environ.get("RESKV_CHECK_STATUS") == "1"
 
 
+def device_index_of(device) -> int:
+    """Ordinal of a CUDA device; an index-less ``cuda`` device means the current one."""
+    index = torch.device(device).index if not isinstance(device, int) else device
+    return torch.cuda.current_device() if index is None else int(index)
+
+
+class BoundLibrary:
+    """The native library with one CUDA device made current around every call.
+
+    The C entry points launch on the current device and cache per-device facts
+    (SM count, kernel attributes, built-in scratch) against it, like the reference's
+    ops do under ``CUDAGuard(tensor.device())`` (cluster_mass.cu:1187, attention.cu:684,
+    compression.cu:396).  Tensors of ``cuda:1`` used while ``cuda:0`` is current would
+    otherwise be handed to a launch on the wrong GPU.
+    """
+
+    def __init__(self, lib: ctypes.CDLL, device_index: int):
+        self._lib, self._index = lib, int(device_index)
+
+    def __getattr__(self, name):
+        fn, index = getattr(self._lib, name), self._index
+
+        def call(*args):
+            if torch.cuda.current_device() == index:
+                return fn(*args)
+            with torch.cuda.device(index):
+                return fn(*args)
+
+        self.__dict__[name] = call
+        return call
+
+
+def bound_library(device) -> BoundLibrary:
+    """``library()`` bound to ``device`` (a ``torch.device``, tensor device or ordinal)."""
+    return BoundLibrary(library(), device_index_of(device))
+
+
+def _same_device(device_index: int, *tensors) -> None:
+    for t in tensors:
+        if t is not None and (not t.is_cuda or device_index_of(t.device) != device_index):
+            raise ValueError(f"all tensors of this call must live on cuda:{device_index}, got one on {t.device}")
+
+
 class _Ops:
     """Base of the operator tables: remembers the plan and device of the load."""
 
     def __init__(self, plan: KernelPlan | None, device_index: int):
         self.plan = plan
         self.device = torch.device("cuda", device_index)
-        self.lib = library()
+        self.lib = BoundLibrary(library(), device_index)
 
 
 class CompressionOps(_Ops):
     """``compression`` family (reference pybind module compression.cu:508-512)."""
 
-    @staticmethod
-    def _dims(x, centroids, ids):
+    def _dims(self, x, centroids, ids):
         if x.dtype != torch.float16 or centroids.dtype != torch.float16 or ids.dtype != torch.int32:
             raise ValueError("compression ops expect FP16 x/centroids and int32 ids")
         if x.ndim != 4 or centroids.ndim != 4 or ids.ndim != 3 or x.shape[3] != 128 or centroids.shape[3] != 128:
             raise ValueError("compression ops expect x[B,H,T,128], centroids[B,H,C,128], ids[B,H,T]")
         if not (x.is_contiguous() and centroids.is_contiguous() and ids.is_contiguous()):
             raise ValueError("compression ops expect contiguous tensors")
+        _same_device(self.device.index, x, centroids, ids)
         b, h, t, _ = x.shape
         return b, h, t, centroids.shape[2]
 
@@ -199,6 +242,7 @@ class CompressionOps(_Ops):
         """Lloyd clustering -> (centroids f16 [B,H,C,128], ids i32 [B,H,T])."""
         if x.dtype != torch.float16 or x.ndim != 4 or x.shape[3] != 128 or not x.is_contiguous():
             raise ValueError("kmeans expects contiguous FP16 x[B,H,T,128]")
+        _same_device(self.device.index, x)
         b, h, t, _ = x.shape
         need = self.lib.reskv_kmeans_workspace_bytes(b, h, count)
         if need == 0:
@@ -212,6 +256,7 @@ class CompressionOps(_Ops):
 
     def kmeans_incremental(self, x, centroids, append):
         """Decode-time step -> (centroids f16 [B,H,C or C+1,128], ids i32 [B,H,T])."""
+        _same_device(self.device.index, x, centroids)
         b, h, t, _ = x.shape
         old = centroids.shape[2]
         new = old + int(bool(append))
@@ -241,6 +286,7 @@ def _decode(lib, layout, bits, q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, kh, nh
     ``reskv_decode_compact``, anything else ``reskv_decode_packed``.  ``recent = (q_rot [B*nh,128], k_rot, v [B,kh,Tr,128])``
     folds a dense window into the same launch pair.
     """
+    _same_device(lib._index, q, kc, ki, kp, km, ks, vc, vi, vp, vm, vs, inv_freq, *(recent or ()))
     bnh = q.shape[0]
     b = bnh // nh
     t, width = kp.shape[1], kp.shape[2]
@@ -306,6 +352,7 @@ class ClusterMassOps(_Ops):
                        pos_q, rope_theta, scale, splits, inv_freq, return_stats, recent)
 
     def merge_recent(self, out, m, l, scores, v_recent, kh, nh):
+        _same_device(self.device.index, out, m, l, scores, v_recent)
         b = out.shape[0] // nh
         merged = torch.empty_like(out)
         check(self.lib.reskv_merge_recent_scores(out.data_ptr(), m.data_ptr(), l.data_ptr(), scores.data_ptr(),
@@ -343,6 +390,7 @@ class AttentionOps(_Ops):
                        pos_q, rope_theta, scale, splits, inv_freq, True, recent)
 
     def merge_recent(self, out, m, l, q_rope, k_recent, v_recent, kh, nh, scale):
+        _same_device(self.device.index, out, m, l, q_rope, k_recent, v_recent)
         b = out.shape[0] // nh
         merged = torch.empty_like(out)
         check(self.lib.reskv_merge_recent_qk(out.data_ptr(), m.data_ptr(), l.data_ptr(), q_rope.data_ptr(),
@@ -354,8 +402,16 @@ class AttentionOps(_Ops):
 _TABLES = {"compression": CompressionOps, "attention": AttentionOps, "cluster_mass": ClusterMassOps}
 
 
+def load_extension(family: str, plan: KernelPlan | None = None, device_index: int | None = 0):
+    """Operator table of one kernel family (reference _extension.py:14-61); ``device_index=None``
+    means the current CUDA device.  See ``_load_extension`` for what is (not) built."""
+    if device_index is None and family in _FAMILIES and torch.cuda.is_available():
+        device_index = torch.cuda.current_device()
+    return _load_extension(family, plan, device_index)
+
+
 @lru_cache(maxsize=32)
-def load_extension(family: str, plan: KernelPlan | None = None, device_index: int = 0):
+def _load_extension(family: str, plan: KernelPlan | None = None, device_index: int | None = 0):
     """Operator table of one kernel family (reference _extension.py:14-61).
 
     Unlike the reference nothing is compiled here: the plan only selects

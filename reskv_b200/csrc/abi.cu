@@ -21,6 +21,27 @@ int check_cuda(cudaError_t e, const char* what) {
     return fail(RESKV_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
 }
 
+int check_device_pointer(const void* ptr, const char* who, const char* what) {
+    cudaPointerAttributes attr{};
+    const cudaError_t e = cudaPointerGetAttributes(&attr, ptr);
+    if (e != cudaSuccess) {
+        cudaGetLastError();  // the failed query must not poison later calls
+        return fail(RESKV_ERR_INVALID, "%s: %s is not memory a CUDA device can be asked about (%s)", who, what,
+                    cudaGetErrorString(e));
+    }
+    if (attr.type == cudaMemoryTypeManaged) return RESKV_OK;
+    if (attr.type != cudaMemoryTypeDevice)
+        return fail(RESKV_ERR_INVALID, "%s: %s must be device memory, got a host pointer", who, what);
+    int dev = -1;
+    if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+    if (attr.device != dev)
+        return fail(RESKV_ERR_INVALID,
+                    "%s: %s lives on device %d but device %d is current; make the tensors' device current "
+                    "(cudaSetDevice) before the call",
+                    who, what, attr.device, dev);
+    return RESKV_OK;
+}
+
 int sm_count() {
     static int cached[64] = {0};
     int dev = 0;

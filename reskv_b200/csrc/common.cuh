@@ -23,6 +23,11 @@ int check_cuda(cudaError_t e, const char* what);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Every entry point launches on the CURRENT device (as the stream it is given must belong to it): `ptr` has to be
+// memory of that device (or managed memory).  A host pointer or another GPU's memory is refused with
+// RESKV_ERR_INVALID before anything is launched -- a kernel given such a pointer would fault.
+int check_device_pointer(const void* ptr, const char* who, const char* what);
+
 // Number of SMs of the current device (cached per device).
 int sm_count();
 

@@ -317,7 +317,8 @@ int check_common(const char* who, const void* x, const void* cen, const void* id
     if (batch < 1 || kv_heads < 1 || tokens < 1) return fail(RESKV_ERR_INVALID, "%s: batch, heads and tokens must be positive", who);
     if (clusters < 1 || clusters > kMaxClusters) return fail(RESKV_ERR_INVALID, "%s: centroid count must be in [1,64]", who);
     if (x_stride < tokens || out_stride < tokens) return fail(RESKV_ERR_INVALID, "%s: token stride smaller than token count", who);
-    return RESKV_OK;
+    if (int rc = check_device_pointer(x, who, "x")) return rc;
+    return check_device_pointer(payload, who, "payload");
 }
 
 int grid_for(long long rows) {

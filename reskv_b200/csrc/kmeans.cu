@@ -396,6 +396,8 @@ extern "C" int reskv_kmeans(const void* x, int batch, int kv_heads, int tokens, 
     const size_t need = kmeans_ws_bytes(units, clusters);
     if (!workspace || workspace_bytes < need)
         return fail(RESKV_ERR_WORKSPACE, "kmeans: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    if (int rc = check_device_pointer(x, "kmeans", "x")) return rc;
+    if (int rc = check_device_pointer(centroids, "kmeans", "centroids")) return rc;
     const size_t per = static_cast<size_t>(units) * clusters * kHeadDim;
     KmeansParams p{};
     p.x = static_cast<const __half*>(x);
@@ -436,6 +438,8 @@ extern "C" int reskv_kmeans_incremental(const void* x, int batch, int kv_heads, 
                                         const void* old_centroids, int old_clusters, void* new_centroids,
                                         int new_clusters, int32_t* ids, void* stream) {
     if (!x || !old_centroids || !new_centroids || !ids) return fail(RESKV_ERR_INVALID, "kmeans_incremental: null tensor pointer");
+    if (int rc = check_device_pointer(x, "kmeans_incremental", "x")) return rc;
+    if (int rc = check_device_pointer(new_centroids, "kmeans_incremental", "new_centroids")) return rc;
     if (batch < 1 || kv_heads < 1 || tokens < 1) return fail(RESKV_ERR_INVALID, "kmeans_incremental: batch, heads and tokens must be positive");
     if (old_clusters < 1 || new_clusters > kMaxClusters || (new_clusters != old_clusters && new_clusters != old_clusters + 1))
         return fail(RESKV_ERR_INVALID, "kmeans_incremental: centre counts must satisfy 1 <= old <= new <= old + 1 <= 64");

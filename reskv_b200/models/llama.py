@@ -251,10 +251,10 @@ class ResKVLlama:
     # which the compressed segment is fixed) and replayed: query position and window length live in
     # a device-side step state that the append / decode kernels read and a final kernel advances.
     def _step_body(self, tok):
-        from .._extension import (LAYOUT_COMPACT, LAYOUT_STRUCTURED, LAYOUT_TILED, LAYOUT_UNSTRUCTURED, _stream, check,
-                                  library)
+        from .._extension import (LAYOUT_COMPACT, LAYOUT_STRUCTURED, LAYOUT_TILED, LAYOUT_UNSTRUCTURED, _stream,
+                                  bound_library, check)
 
-        lib = library()
+        lib = bound_library(self.device)  # every launch below runs with the model's device current
         b = tok.shape[0]
         d = self.shape.hidden
         stream = _stream(self.device)
@@ -306,7 +306,7 @@ class ResKVLlama:
                                             kp.data_ptr(), ptr(km), ptr(ks), vc.data_ptr(), vi.data_ptr(), vp.data_ptr(),
                                             ptr(vm), ptr(vs), b, self.h_kv, self.h_q, key.seq_len, key.token_stride,
                                             kc.shape[1], vc.shape[1], 0, float(self.shape.rope_theta),
-                                            self.inv_freq.data_ptr(), float(self.scaling), plan.splits, q_rot.data_ptr(),
+                                            self.inv_freq.data_ptr(), float(self.scaling), 0, q_rot.data_ptr(),
                                             cache.keys.data_ptr(), cache.values.data_ptr(), cap, state,
                                             self._workspace.data_ptr(), self._workspace.numel(), att.data_ptr(), stream),
                       launches=2)

@@ -78,3 +78,41 @@ def test_package_import_is_light():
          "assert reskv_b200.ResKVKernelConfig().bits == 16; assert reskv_b200.ResKVConfig().bits == 16; "
          "assert 'torch' not in sys.modules"],
         check=True, cwd=ROOT)
+
+
+def test_pointers_that_are_not_memory_of_the_current_device_are_refused():
+    """Every entry point launches on the current device: host memory (here) or another GPU's memory is
+    turned down with RESKV_ERR_INVALID before anything is launched."""
+    import numpy as np
+
+    from reskv_b200._extension import ERR_INVALID, library
+
+    lib = library()
+    t, nnz = 64, 32
+    host = {name: np.zeros(shape, dtype) for name, shape, dtype in (
+        ("q", (4, 128), np.float16), ("cen", (1, 32, 128), np.float16), ("ids", (1, t), np.int8),
+        ("pay", (1, t, nnz), np.float16), ("bm", (1, t, 2), np.int64), ("ws", (1 << 20,), np.uint8),
+        ("out", (4, 128), np.float16))}
+    ptr = {k: v.ctypes.data for k, v in host.items()}
+    assert all(p % 16 == 0 for p in ptr.values())
+    rc = lib.reskv_decode_bitmap_fp16(ptr["q"], ptr["cen"], ptr["ids"], ptr["pay"], ptr["bm"], ptr["cen"], ptr["ids"],
+                                      ptr["pay"], ptr["bm"], 1, 1, 4, t, t, 32, 32, nnz, 0, t, 500000.0, None, 0.088, 0,
+                                      None, None, None, 0, ptr["ws"], host["ws"].size, ptr["out"], None, None, None)
+    assert rc == ERR_INVALID
+    assert b"decode_bitmap_fp16: q" in lib.reskv_last_error()
+    x = np.zeros((1, 1, t, 128), np.float16)
+    ids = np.zeros((1, 1, t), np.int32)
+    rc = lib.reskv_encode_bitmap_fp16(x.ctypes.data, ptr["cen"], ids.ctypes.data, 1, 1, t, t, 32, nnz, ptr["pay"],
+                                      ptr["bm"], t, None)
+    assert rc == ERR_INVALID and b"x" in lib.reskv_last_error()
+
+
+def test_operator_tables_refuse_tensors_of_another_device():
+    import torch
+
+    from reskv_b200._extension import _same_device, device_index_of
+
+    assert device_index_of(torch.device("cuda", 3)) == 3 and device_index_of(2) == 2
+    with pytest.raises(ValueError, match="must live on cuda:0"):
+        _same_device(0, torch.zeros(1))
+    _same_device(0, None)
