@@ -38,6 +38,7 @@ extern "C" {
 /* Bits of the 32-bit status word a kernel ORs into workspace[0] when something
  * went wrong on the device (read it after synchronising the stream). */
 #define RESKV_STATUS_WAIT_TIMEOUT 1u /* a bounded wait on an async copy ran out */
+#define RESKV_STATUS_STATE_RANGE 2u  /* a device-side count or slot index was out of range and got clamped / skipped */
 
 /* Message of the last failure on the calling thread ("" if none). */
 const char* reskv_last_error(void);

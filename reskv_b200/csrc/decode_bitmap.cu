@@ -518,7 +518,8 @@ __global__ void __launch_bounds__(1024) decode_merge_kernel(const MergeParams p,
         float4 wn = make_float4(0.f, 0.f, 0.f, 0.f), wb = wn;
 #pragma unroll 4
         for (int s = warp; s < p.splits; s += kMergeThreads / 32) {
-            const float w = (pm[s] == -INFINITY) ? 0.f : fast_exp2(pm[s] - wm);
+            if (pm[s] == -INFINITY) continue;  // empty slot: its delta / beta rows were never written
+            const float w = fast_exp2(pm[s] - wm);
             const size_t row = static_cast<size_t>(fq) * p.splits + s;
             const float4 dv = *reinterpret_cast<const float4*>(p.ws_delta + row * kHeadDim + 4 * lane);
             wl += pl[s] * w;
@@ -626,14 +627,29 @@ __global__ void __launch_bounds__(1024) decode_merge_kernel(const MergeParams p,
     p.out[static_cast<size_t>(fq) * kHeadDim + d] = __float2half_rn(num / fmaxf(l, 1e-20f));
 }
 
+// cudaFuncSetAttribute(max dynamic shared memory) once per kernel instance and device, not per call.
+// `done` is a per-instantiation bit mask over device ordinals (< 64); a race between host threads only
+// repeats the idempotent call.
+template <class Kernel>
+int allow_smem(Kernel kern, size_t smem, unsigned long long& done, const char* what) {
+    int dev = 0;
+    if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+    const bool tracked = dev >= 0 && dev < 64;
+    if (tracked && (done >> dev & 1ull)) return RESKV_OK;
+    if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)), what))
+        return rc;
+    if (tracked) done |= 1ull << dev;
+    return RESKV_OK;
+}
+
 // one CTA per unit with 128 threads per query head of the unit
 int launch_merge(const MergeParams& mp, int units, int recent_max, cudaStream_t s) {
     const int gqa = mp.nh / mp.kh;
     if (gqa < 1 || gqa > 8) return fail(RESKV_ERR_INVALID, "merge: at most 8 query heads per KV head");
     const size_t smem = merge_smem_bytes(mp.splits > 0 ? mp.cv : 0, gqa, recent_max);
     if (smem > 48 * 1024) {
-        if (int rc = check_cuda(cudaFuncSetAttribute(decode_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                     static_cast<int>(smem)),
+        static unsigned long long done = 0;
+        if (int rc = allow_smem(decode_merge_kernel, merge_smem_bytes(kMaxClusters, 8, kMaxRecent), done,
                                 "cudaFuncSetAttribute(decode_merge)"))
             return rc;
     }
@@ -648,9 +664,10 @@ int launch_simt_cvs(const DecodeParams& p, int units, cudaStream_t stream) {
     const size_t red_bytes = static_cast<size_t>(kWarps) * GQA * (kHeadDim + 32 * CVS) * sizeof(float);
     if (smem < red_bytes) smem = red_bytes;
     auto kern = decode_simt_partial_kernel<GQA, L, CVS>;
-    if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 static_cast<int>(smem)),
-                            "cudaFuncSetAttribute(decode_simt_partial)"))
+    // the kernel's shared memory grows with the key centroid count: allow the maximum once
+    static unsigned long long done = 0;
+    const size_t smem_max = sizeof(Stage<L>) * kStages + static_cast<size_t>(kMaxClusters) * kHeadDim * sizeof(__half);
+    if (int rc = allow_smem(kern, smem_max > red_bytes ? smem_max : red_bytes, done, "cudaFuncSetAttribute(decode_simt_partial)"))
         return rc;
     kern<<<dim3(p.splits, units), kThreads, smem, stream>>>(p);
     return check_cuda(cudaGetLastError(), "decode_simt_partial launch");
@@ -662,15 +679,14 @@ int launch_simt(const DecodeParams& p, int units, cudaStream_t s) {
 }
 
 template <int GQA, int NNZ>
-int launch_partial_mma(const DecodeParams& p, int units, cudaStream_t stream) {
+int launch_partial_mma(const DecodeParams& p, int, cudaStream_t stream) {
     using ML = mma::LayoutMmaBitmap<NNZ>;
     const size_t smem = mma::smem_bytes<GQA, ML>(p.ck);
     auto kern = mma::decode_mma_kernel<GQA, ML>;
-    if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 static_cast<int>(smem)),
-                            "cudaFuncSetAttribute(decode_bitmap_mma)"))
+    static unsigned long long done = 0;
+    if (int rc = allow_smem(kern, mma::smem_bytes<GQA, ML>(kMaxClusters), done, "cudaFuncSetAttribute(decode_bitmap_mma)"))
         return rc;
-    kern<<<dim3(p.splits, units), mma::kThreadsM, smem, stream>>>(p);
+    kern<<<p.grid, mma::kThreadsM, smem, stream>>>(p);
     return check_cuda(cudaGetLastError(), "decode_bitmap_mma launch");
 }
 
@@ -737,6 +753,46 @@ size_t workspace_bytes(int bnh, int splits) {
     return kWsHeader + rows * (2 + kHeadDim + kMaxClusters) * sizeof(float);
 }
 
+// How a decode call is cut into partial results.
+struct PartialPlan {
+    int slots;     // partial results per query head in the workspace
+    int chunk;     // tiles per CTA
+    int grid;      // CTAs of the tensor-core kernel (the warp-per-token kernel runs slots x units)
+    int balanced;  // 1: equal share of all tiles per CTA, 0: one CTA per (unit, split)
+};
+
+// splits_req > 0 (caller's choice) or the warp-per-token kernel: fixed splits per unit.  Otherwise the balanced
+// schedule: at most two CTAs per SM, every CTA streams ceil(all tiles / CTAs) consecutive tiles, so the per-CTA
+// tables are built once per CTA and no SM idles on a partial last wave.  A unit of n tiles is then touched by at
+// most (n - 1) / chunk + 2 CTAs.  With a device-side token count (`dyn`) chunk is recomputed on the device as
+// ceil(units * n / grid), which keeps that figure below ceil(grid / units) + 1 for any n.
+PartialPlan plan_partials(int units, int tokens, int splits_req, bool tensor_core, bool dyn, int64_t tok_stride) {
+    const int tiles = (tokens + kTile - 1) / kTile;
+    PartialPlan pp{};
+    if (splits_req > 0 || !tensor_core) {
+        int splits = splits_req > 0 ? splits_req : pick_splits(units, tokens);
+        if (splits > tiles) splits = tiles;
+        const int per = (tiles + splits - 1) / splits;
+        splits = (tiles + per - 1) / per;  // drop splits that would get no tile
+        pp.slots = splits, pp.chunk = per, pp.grid = units * splits, pp.balanced = 0;
+        return pp;
+    }
+    const long long max_tiles = dyn ? (tok_stride + kTile - 1) / kTile : tiles;
+    const long long all = static_cast<long long>(units) * (dyn ? max_tiles : tiles);
+    long long grid = 2ll * sm_count();
+    if (grid > all) grid = all;
+    const long long chunk = (static_cast<long long>(units) * tiles + grid - 1) / grid;
+    if (dyn) {
+        pp.slots = static_cast<int>((grid + units - 1) / units) + 1;
+    } else {
+        grid = (static_cast<long long>(units) * tiles + chunk - 1) / chunk;  // CTAs that get tiles
+        const long long s = (tiles - 1) / chunk + 2;
+        pp.slots = static_cast<int>(s < tiles ? s : tiles);
+    }
+    pp.chunk = static_cast<int>(chunk), pp.grid = static_cast<int>(grid), pp.balanced = 1;
+    return pp;
+}
+
 }  // namespace
 }  // namespace reskv
 
@@ -762,10 +818,14 @@ extern "C" int reskv_decode_auto_splits(int batch, int kv_heads, int tokens) {
 extern "C" size_t reskv_decode_bitmap_fp16_workspace_bytes(int batch, int kv_heads, int q_heads, int tokens,
                                                            int splits) {
     if (batch < 1 || kv_heads < 1 || q_heads < 1 || tokens < 1) return 0;
-    if (splits <= 0) splits = pick_splits(batch * kv_heads, tokens);
-    const int tiles = (tokens + kTile - 1) / kTile;
-    if (splits > tiles) splits = tiles;
-    return workspace_bytes(batch * q_heads, splits);
+    // enough for either kernel variant and for a device-side token count (decode_step) up to `tokens`
+    const int units = batch * kv_heads;
+    int slots = plan_partials(units, tokens, splits, true, false, tokens).slots;
+    const int a = plan_partials(units, tokens, splits, false, false, tokens).slots;
+    const int b = plan_partials(units, tokens, splits, true, true, tokens).slots;
+    if (a > slots) slots = a;
+    if (b > slots) slots = b;
+    return workspace_bytes(batch * q_heads, slots);
 }
 
 namespace {
@@ -788,6 +848,16 @@ struct DecodeArgs {
     const int32_t* dyn = nullptr;  // device step state {pos_q, recent tokens}
     int recent_cap = 0;            // window capacity in tokens when dyn is given
 };
+
+// Which partial kernel dispatch_layout will pick for this call (its partial plan differs).
+bool tensor_core_variant(LayoutId layout, const DecodeArgs& a) {
+    if (layout == kStructInt4) {
+        const bool bulk_ok = a.tokens % 2 == 0 && a.tok_stride % 2 == 0 && aligned16(a.km) && aligned16(a.vm);
+        return g_variant == 0 && bulk_ok;
+    }
+    if (layout == kCompact4x64 || layout == kCompact4x32 || layout == kCompact2x64) return true;
+    return g_variant == 0;
+}
 
 int decode_common(const DecodeArgs& a, LayoutId layout, bool has_meta, bool has_scale, const char* who) {
     if (!a.q || !a.kc || !a.kid || !a.kp || !a.vc || !a.vid || !a.vp || !a.out)
@@ -813,6 +883,9 @@ int decode_common(const DecodeArgs& a, LayoutId layout, bool has_meta, bool has_
         return fail(RESKV_ERR_INVALID, "%s: misaligned centroid (16 bytes) or query pointer", who);
     if ((a.rk && !aligned16(a.rk)) || (a.rv && !aligned16(a.rv)))
         return fail(RESKV_ERR_INVALID, "%s: recent keys and values must be 16-byte aligned", who);
+    if (int rc = check_device_pointer(a.q, who, "q")) return rc;
+    if (int rc = check_device_pointer(a.kp, who, "k_payload")) return rc;
+    if (int rc = check_device_pointer(a.out, who, "out")) return rc;
     const bool has_recent = a.recent_tokens > 0;
     if (a.recent_tokens < 0 || (has_recent && (!a.rq || !a.rk || !a.rv)))
         return fail(RESKV_ERR_INVALID, "%s: recent window needs rotated q, rotated k and v", who);
@@ -820,12 +893,8 @@ int decode_common(const DecodeArgs& a, LayoutId layout, bool has_meta, bool has_
         return fail(RESKV_ERR_LIMIT, "%s: at most %d recent tokens, got %d", who, kMaxRecent, a.recent_tokens);
 
     const int units = a.batch * a.kv_heads;
-    const int tiles = (a.tokens + kTile - 1) / kTile;
-    int splits = a.splits;
-    if (splits <= 0) splits = pick_splits(units, a.tokens);
-    if (splits > tiles) splits = tiles;
-    const int per = (tiles + splits - 1) / splits;
-    splits = (tiles + per - 1) / per;  // drop splits that would get no tile
+    const PartialPlan pp = plan_partials(units, a.tokens, a.splits, tensor_core_variant(layout, a), a.dyn != nullptr, a.tok_stride);
+    const int splits = pp.slots, per = pp.chunk;
     const size_t need = workspace_bytes(a.batch * a.q_heads, splits);
     if (!a.workspace || a.workspace_bytes < need)
         return fail(RESKV_ERR_WORKSPACE, "%s: workspace of %zu bytes needed, %zu given", who, need, a.workspace_bytes);
@@ -852,6 +921,7 @@ int decode_common(const DecodeArgs& a, LayoutId layout, bool has_meta, bool has_
     p.start_pos = a.start_pos, p.pos_q = a.pos_q, p.splits = splits, p.tiles_per_split = per;
     p.theta = a.theta, p.scaling = a.scaling;
     p.dyn = a.dyn;
+    p.units = units, p.balanced = pp.balanced, p.grid = pp.grid;
 
     cudaStream_t s = static_cast<cudaStream_t>(a.stream);
     if (g_ev_start) cudaEventRecord(g_ev_start, s);
@@ -1027,12 +1097,8 @@ extern "C" int reskv_decode_bitmap_fp16_noalloc(const void* q, const void* k_cen
         return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16_noalloc: batch, heads and tokens must be positive");
     if (nnz != 32 && nnz != 64)
         return fail(RESKV_ERR_INVALID, "decode_bitmap_fp16_noalloc: nnz must be 32 or 64, got %d", nnz);
-    // the same split arithmetic as the allocating entry point, to size the scratch first
-    const int tiles = (tokens + kTile - 1) / kTile;
-    int eff = splits > 0 ? splits : pick_splits(batch * kv_heads, tokens);
-    if (eff > tiles) eff = tiles;
-    const int per = (tiles + eff - 1) / eff;
-    eff = (tiles + per - 1) / per;
+    // the same partial plan as the allocating entry point, to size the scratch first
+    const int eff = plan_partials(batch * kv_heads, tokens, splits, g_variant == 0, false, tok_stride).slots;
     const size_t need = workspace_bytes(batch * q_heads, eff);
     if (need > static_cast<size_t>(RESKV_NOALLOC_SCRATCH_BYTES))
         return fail(RESKV_ERR_LIMIT,

@@ -41,7 +41,12 @@ struct DecodeParams {
     const float* inv_freq;
     int64_t tok_stride;
     int kh, nh, tokens, ck, cv;
+    // splits = partial slots per query head in the workspace; tiles_per_split = tiles per CTA (see `balanced`)
     int start_pos, pos_q, splits, tiles_per_split;
+    // units = batch * kv heads.  balanced != 0: the tensor-core kernel runs a 1-D grid whose CTAs each take an
+    // equal share of all units' tiles (a CTA may finish one unit and start the next); balanced == 0: one CTA per
+    // (unit, split) with `tiles_per_split` tiles each.
+    int units, balanced, grid;  // grid = CTAs of the tensor-core kernel
     float theta, scaling;
     // optional device-resident step state {query position, dense-window tokens, compressed tokens
     // or -1, reserved}: when set it overrides pos_q, the merge kernel's recent-token count and

@@ -439,6 +439,10 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int kStages = stages_for<ML>();
     constexpr int kItems = (GQA * 32 + kThreadsM - 1) / kThreadsM;  // query items per thread
+    // With four query heads the eight columns of the score MMA hold the query's FP16 hi halves (columns
+    // 0..3) next to its lo halves (columns 4..7): one MMA per key half instead of two, the two columns of
+    // a head are added afterwards (lanes q and q ^ 2).
+    constexpr bool kPackQ = GQA == 4;
     using StageT = StageM<ML>;
     using Field = typename ML::Field;
     StageT* stages = reinterpret_cast<StageT*>(smem_raw);
@@ -453,67 +457,35 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
     __shared__ uint32_t timed_out;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, qd = lane & 3;
-    const int split = blockIdx.x, unit = blockIdx.y;
-    const int b = unit / p.kh, hkv = unit % p.kh;
     const int tokens = token_count(p);
     const int total_tiles = (tokens + kTileM - 1) / kTileM;
-    const int per_split = split_tiles(p, total_tiles);
-    const int tile_begin = split * per_split;
-    const int ntiles = max(0, min(total_tiles, tile_begin + per_split) - tile_begin);
-
-    const size_t unit_tok = static_cast<size_t>(unit) * p.tok_stride;
-    const unsigned char* km_g = static_cast<const unsigned char*>(p.kb) + unit_tok * ML::kMetaBytes;
-    const unsigned char* vm_g = static_cast<const unsigned char*>(p.vb) + unit_tok * ML::kMetaBytes;
-    const unsigned char* kp_g = static_cast<const unsigned char*>(p.kp) + unit_tok * ML::kPayloadBytes;
-    const unsigned char* vp_g = static_cast<const unsigned char*>(p.vp) + unit_tok * ML::kPayloadBytes;
-    const int8_t* kid_g = p.kid + unit_tok;
-    const int8_t* vid_g = p.vid + unit_tok;
-    const __half* ks_g = ML::kScale ? p.ks + unit_tok : nullptr;
-    const __half* vs_g = ML::kScale ? p.vs + unit_tok : nullptr;
+    // Work of the launch = the tiles of all units laid end to end, every unit padded to n_pad tiles.  CTA c
+    // takes the range [c * chunk, (c + 1) * chunk) and walks it unit by unit; the part of one unit inside
+    // the range is a *segment* and produces one partial result (slot = number of CTAs that started earlier
+    // on the same unit).  Balanced schedule: n_pad = tiles of a unit and chunk = all tiles / CTAs, so every
+    // CTA streams the same number of tiles and sets its tables up once; fixed-split schedule: chunk = tiles
+    // per split and n_pad = chunk * splits, i.e. exactly one segment per CTA.
+    int n_pad, chunk;
+    if (p.balanced) {
+        n_pad = max(total_tiles, 1);
+        chunk = p.dyn ? static_cast<int>((static_cast<long long>(p.units) * n_pad + gridDim.x - 1) / gridDim.x)
+                      : p.tiles_per_split;
+    } else {
+        chunk = max(split_tiles(p, total_tiles), 1);
+        n_pad = chunk * p.splits;
+    }
+    const long long work_total = static_cast<long long>(p.units) * n_pad;
+    long long work = static_cast<long long>(blockIdx.x) * chunk;
+    const long long work_end = min(work_total, work + chunk);
+    if (work >= work_end) return;
 
     if (tid == 0) {
         timed_out = 0;
         for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], ML::kPad ? 1 + kThreadsM : 1);
         mbar_fence_init();
     }
-    __syncthreads();
-    auto issue = [&](int tile_rel) {
-        const int t0 = (tile_begin + tile_rel) * kTileM;
-        const int n = min(kTileM, tokens - t0);
-        StageT& st = stages[tile_rel % kStages];
-        uint64_t* bar = &full_bar[tile_rel % kStages];
-        // 8-byte metadata rows stay bulk-copyable: tiles start at multiples of 64 tokens and the host
-        // selects this kernel for them only when token count and token stride are even
-        const uint32_t md_bytes = n * ML::kMetaBytes, pl_bytes = n * ML::kPayloadBytes;
-        const unsigned char* kp_src = kp_g + static_cast<size_t>(t0) * ML::kPayloadBytes;
-        const unsigned char* vp_src = vp_g + static_cast<size_t>(t0) * ML::kPayloadBytes;
-        if constexpr (ML::kPad != 0) {
-            // metadata in bulk by one thread; payload rows in 16-byte pieces by everyone, into padded rows
-            if (tid == 0) {
-                mbar_arrive_expect_tx(bar, 2 * md_bytes);
-                bulk_g2s(st.km, km_g + static_cast<size_t>(t0) * ML::kMetaBytes, md_bytes, bar);
-                bulk_g2s(st.vm, vm_g + static_cast<size_t>(t0) * ML::kMetaBytes, md_bytes, bar);
-            }
-            constexpr int kPieces = ML::kPayloadBytes / 16, kRow = ML::kPayloadBytes + ML::kPad;
-            for (int c = tid; c < n * kPieces; c += kThreadsM) {
-                const int dst = (c / kPieces) * kRow + (c % kPieces) * 16;
-                cp_async16(st.kp + dst, kp_src + c * 16);
-                cp_async16(st.vp + dst, vp_src + c * 16);
-            }
-            cp_async_arrive(bar);
-        } else if (tid == 0) {
-            mbar_arrive_expect_tx(bar, 2 * md_bytes + 2 * pl_bytes);
-            if (ML::kMetaBytes) {
-                bulk_g2s(st.km, km_g + static_cast<size_t>(t0) * ML::kMetaBytes, md_bytes, bar);
-                bulk_g2s(st.vm, vm_g + static_cast<size_t>(t0) * ML::kMetaBytes, md_bytes, bar);
-            }
-            bulk_g2s(st.kp, kp_src, pl_bytes, bar);
-            bulk_g2s(st.vp, vp_src, pl_bytes, bar);
-        }
-    };
-    for (int s = 0; s < kStages && s < ntiles; ++s) issue(s);
 
-    // ---- tables: sin/cos of (tile offset j) x (frequency i); key centroids; zeroed query rows ----
+    // ---- once per CTA: sin/cos of (tile offset j) x (frequency i) ------------------------------
     {
         const int i = tid & 63, half = tid >> 6;
         const float f = rope_freq(p.inv_freq, p.theta, i);
@@ -537,112 +509,20 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
                 s = ns, c = nc;
             }
         }
-        const __half* src = p.kc + static_cast<size_t>(unit) * p.ck * kHeadDim;
-        for (int idx = tid; idx < p.ck * (kHeadDim / 8); idx += kThreadsM) {  // 8 coordinates per step
-            const int row = idx / (kHeadDim / 8), d = (idx % (kHeadDim / 8)) * 8;
-            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + row * kHeadDim + d));
-            const __half2* h = reinterpret_cast<const __half2*>(&raw);
-            const float2 v0 = __half22float2(h[0]), v1 = __half22float2(h[1]), v2 = __half22float2(h[2]), v3 = __half22float2(h[3]);
-            *reinterpret_cast<float4*>(kc_s + row * kCenStride + cen_index(d)) = make_float4(v0.x, v0.y, v1.x, v1.y);
-            *reinterpret_cast<float4*>(kc_s + row * kCenStride + cen_index(d + 4)) = make_float4(v2.x, v2.y, v3.x, v3.y);
-        }
     }
-
-    // ---- query state: item = (head, two adjacent frequencies i2, i2 + 1) ----------------------
-    // angle (pos_q - P0) * f goes down by 64 f per tile; seeded exactly every kReseedTiles tiles
-    float q_lo[kItems][2], q_hi[kItems][2], q_f[kItems][2];
-    float st_c[kItems][2], st_s[kItems][2], dn_c[kItems][2], dn_s[kItems][2];
-    const float q_mul = p.scaling * kLog2e;
+    // query items of this thread: (head, two adjacent frequencies i2, i2 + 1); the per-tile angle step
+    // does not depend on the unit
+    float q_f[kItems][2], dn_c[kItems][2], dn_s[kItems][2];
 #pragma unroll
     for (int it = 0; it < kItems; ++it) {
-        const int item = tid + it * kThreadsM;
-        const int h = item >> 5, i2 = (item & 31) * 2;
-        const bool on = item < GQA * 32;
-        const __half* qrow = p.q + (static_cast<size_t>(b) * p.nh + hkv * GQA + (on ? h : 0)) * kHeadDim;
+        const int i2 = ((tid + it * kThreadsM) & 31) * 2;
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-            q_lo[it][u] = on ? __half2float(qrow[i2 + u]) * q_mul : 0.f;
-            q_hi[it][u] = on ? __half2float(qrow[i2 + u + 64]) * q_mul : 0.f;
             q_f[it][u] = rope_freq(p.inv_freq, p.theta, i2 + u);
             sincosf(static_cast<float>(kTileM) * q_f[it][u], &dn_s[it][u], &dn_c[it][u]);
-            st_c[it][u] = 1.f, st_s[it][u] = 0.f;
         }
     }
-
-    auto write_query = [&](int tile_rel) {
-        // Qt = R(pos_q - P0) q  for the tile that starts at token t0, as FP16 hi + lo
-        const int t0 = (tile_begin + tile_rel) * kTileM;
-        __half* base = qf + (tile_rel & 1) * (kQSets * GQA * kQStride);
-#pragma unroll
-        for (int it = 0; it < kItems; ++it) {
-            const int item = tid + it * kThreadsM;
-            if (item >= GQA * 32) continue;
-            const int h = item >> 5, i2 = (item & 31) * 2;
-            float lo[2], hi[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                if (tile_rel % kReseedTiles == 0) {
-                    const float delta = static_cast<float>(query_position(p) - (p.start_pos + t0));
-                    sincosf(delta * q_f[it][u], &st_s[it][u], &st_c[it][u]);
-                }
-                const float c = st_c[it][u], s = st_s[it][u];
-                lo[u] = q_lo[it][u] * c - q_hi[it][u] * s;
-                hi[u] = q_hi[it][u] * c + q_lo[it][u] * s;
-                // next tile: angle - 64 f
-                st_c[it][u] = c * dn_c[it][u] + s * dn_s[it][u];
-                st_s[it][u] = s * dn_c[it][u] - c * dn_s[it][u];
-            }
-            const __half2 lo_h = __floats2half2_rn(lo[0], lo[1]), hi_h = __floats2half2_rn(hi[0], hi[1]);
-            const float2 lo_f = __half22float2(lo_h), hi_f = __half22float2(hi_h);
-            __half* row_hi = base + h * kQStride;
-            __half* row_lo = base + (GQA + h) * kQStride;
-            *reinterpret_cast<__half2*>(row_hi + i2) = lo_h;
-            *reinterpret_cast<__half2*>(row_hi + i2 + 64) = hi_h;
-            *reinterpret_cast<__half2*>(row_lo + i2) = __floats2half2_rn(lo[0] - lo_f.x, lo[1] - lo_f.y);
-            *reinterpret_cast<__half2*>(row_lo + i2 + 64) = __floats2half2_rn(hi[0] - hi_f.x, hi[1] - hi_f.y);
-        }
-    };
-    if (ntiles > 0) write_query(0);
-
-    // ---- per-warp running state ---------------------------------------------------------------
-    float acc[8][4];          // O^T: m-block i -> coordinates 16g+2i (c0,c1) and 16g+2i+1 (c2,c3); heads 2q, 2q+1
-    float m_used[2], l_part[2];
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-    m_used[0] = m_used[1] = -INFINITY;
-    l_part[0] = l_part[1] = 0.f;
-    // cluster mass beta[value cluster][head] of this warp's tokens, accumulated by the tensor cores as
-    // onehot(value id)^T . P: rows = clusters 16 mb + g (+ 8), columns = heads 2q, 2q + 1
-    float bacc[4][4];
-#pragma unroll
-    for (int mb = 0; mb < 4; ++mb) bacc[mb][0] = bacc[mb][1] = bacc[mb][2] = bacc[mb][3] = 0.f;
-    uint2* pre_k = pre + warp * 32;
-    uint2* pre_v = pre_k + 16;
-
-    // cluster ids (and FP16 scales) of this warp's 16 tokens of the next tile: lanes 0..15 hold the
-    // key side of token `lane`, lanes 16..31 the value side of token `lane - 16`
-    auto load_ids = [&](int tile_rel, int& id, uint32_t& scale) {
-        const int t = (tile_begin + tile_rel) * kTileM + warp * 16 + (lane & 15);
-        id = 0, scale = 0u;
-        if (tile_rel < ntiles && t < tokens) {
-            // volatile: issue the loads here, a whole tile ahead of their use, instead of letting the
-            // compiler sink them next to the consumer
-            const int8_t* src = ((lane < 16) ? kid_g : vid_g) + t;
-            asm volatile("ld.global.nc.s8 %0, [%1];" : "=r"(id) : "l"(src));
-            if constexpr (ML::kScale) {
-                const __half* ssrc = ((lane < 16) ? ks_g : vs_g) + t;
-                unsigned short h;
-                asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(h) : "l"(ssrc));
-                scale = h;
-            }
-        }
-    };
-    int ids_next;
-    uint32_t scl_next;
-    load_ids(0, ids_next, scl_next);
-    __syncthreads();  // tables and first query tile ready
+    __syncthreads();  // barriers initialised, sin/cos table complete
 
     // sin/cos of this lane's two rows (tile offsets 16 warp + g and + 8) and 16 frequencies: the
     // same in every tile, so they live in registers for the whole kernel
@@ -670,290 +550,485 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
         }
     }
 
+    const float q_mul = p.scaling * kLog2e;
+    uint2* pre_k = pre + warp * 32;
+    uint2* pre_v = pre_k + 16;
+    uint32_t ring = 0;  // tiles issued / consumed so far by this CTA (ring slot and barrier phase follow it)
     bool lost = false;
-    for (int it = 0; it < ntiles; ++it) {
-        const int t0 = (tile_begin + it) * kTileM;
-        const int ids_cur = ids_next;
-        const uint32_t scl_cur = scl_next;
-        load_ids(it + 1, ids_next, scl_next);
-        if (!mbar_wait(&full_bar[it % kStages], (it / kStages) & 1)) lost = true;
-        const StageT& st = stages[it % kStages];
-        const int nvalid = min(16, tokens - (t0 + warp * 16));  // valid tokens of this warp's block
-        if (nvalid > 0) {
-            if constexpr (ML::kPrefix) {
-                // rank bases of the block's 16 key bitmaps (lanes 0..15) and value bitmaps (16..31)
-                const int tok = warp * 16 + (lane & 15);
-                const uint4 bm = reinterpret_cast<const uint4*>((lane < 16) ? st.km : st.vm)[tok];
-                pre_k[lane] = rank_bases(bm);  // pre_v == pre_k + 16
-                __syncwarp();
-            }
+    bool first_segment = true;
 
-            // ================= keys: rows g and g + 8 of the block =================
-            const int tokA = warp * 16 + g, tokB = tokA + 8;
-            const bool okA = g < nvalid, okB = g + 8 < nvalid;
-            const int kidA = min(max(__shfl_sync(0xffffffffu, ids_cur, g), 0), p.ck - 1);
-            const int kidB = min(max(__shfl_sync(0xffffffffu, ids_cur, g + 8), 0), p.ck - 1);
-            const unsigned char* pk_bytes = reinterpret_cast<const unsigned char*>(pre_k);
-            Field fAl = ML::field(st.kp, st.km, pk_bytes, tokA, qd, okA), fAh = ML::field(st.kp, st.km, pk_bytes, tokA, 4 + qd, okA);
-            Field fBl = ML::field(st.kp, st.km, pk_bytes, tokB, qd, okB), fBh = ML::field(st.kp, st.km, pk_bytes, tokB, 4 + qd, okB);
-            const unsigned short kscA = static_cast<unsigned short>(__shfl_sync(0xffffffffu, scl_cur, g));
-            const unsigned short kscB = static_cast<unsigned short>(__shfl_sync(0xffffffffu, scl_cur, g + 8));
-            // FP32 centroid rows; the lane's low field starts at 16q, its partner field at 64 + 16q
-            const float* cA = kc_s + kidA * kCenStride + 16 * qd;
-            const float* cB = kc_s + kidB * kCenStride + 16 * qd;
-            const int cen_swz = (qd >> 1) & 1;  // 16-byte unit swap of this lane's fields
-            const __half* qbuf = qf + (it & 1) * (kQSets * GQA * kQStride) + g * kQStride + 16 * qd;
-            const bool q_on = g < GQA;  // rows of the B operand beyond the real heads are zero
+    while (work < work_end) {
+        // ---- the segment: unit, its tile range, its partial slot --------------------------------
+        const int unit = static_cast<int>(work / n_pad);
+        const int t_pad = static_cast<int>(work - static_cast<long long>(unit) * n_pad);
+        const int len = static_cast<int>(min(static_cast<long long>(n_pad - t_pad), work_end - work));
+        const int tile_begin = min(t_pad, total_tiles);
+        const int ntiles = max(0, min(total_tiles, t_pad + len) - tile_begin);
+        const int slot = static_cast<int>(blockIdx.x) - static_cast<int>((static_cast<long long>(unit) * n_pad) / chunk);
+        const bool closes_unit = t_pad + len == n_pad;
+        work += len;
+        const int b = unit / p.kh, hkv = unit % p.kh;
 
-            // three independent accumulators (hi.hi, hi.lo, lo.hi) keep the MMA dependency chains short
-            float sc[4] = {0.f, 0.f, 0.f, 0.f}, sc2[4] = {0.f, 0.f, 0.f, 0.f}, sc3[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-                // four coordinates 16q + 4ks .. +3 and their partners + 64, both tokens:
-                // k = centroid (+ residual where the bitmap bit is set)
-                // query fragments of k-step ks (low half of the head) and ks + 4 (high half), requested first
-                uint2 qh_l = make_uint2(0u, 0u), qh_h = qh_l, ql_l = qh_l, ql_h = qh_l;
-                if (q_on) {
-                    qh_l = *reinterpret_cast<const uint2*>(qbuf + 4 * ks);
-                    qh_h = *reinterpret_cast<const uint2*>(qbuf + 64 + 4 * ks);
-                    ql_l = *reinterpret_cast<const uint2*>(qbuf + GQA * kQStride + 4 * ks);
-                    ql_h = *reinterpret_cast<const uint2*>(qbuf + GQA * kQStride + 64 + 4 * ks);
+        const size_t unit_tok = static_cast<size_t>(unit) * p.tok_stride;
+        const unsigned char* km_g = static_cast<const unsigned char*>(p.kb) + unit_tok * ML::kMetaBytes;
+        const unsigned char* vm_g = static_cast<const unsigned char*>(p.vb) + unit_tok * ML::kMetaBytes;
+        const unsigned char* kp_g = static_cast<const unsigned char*>(p.kp) + unit_tok * ML::kPayloadBytes;
+        const unsigned char* vp_g = static_cast<const unsigned char*>(p.vp) + unit_tok * ML::kPayloadBytes;
+        const int8_t* kid_g = p.kid + unit_tok;
+        const int8_t* vid_g = p.vid + unit_tok;
+        const __half* ks_g = ML::kScale ? p.ks + unit_tok : nullptr;
+        const __half* vs_g = ML::kScale ? p.vs + unit_tok : nullptr;
+
+        // the previous segment's epilogue still reads the stage memory and the centroid table
+        if (!first_segment) __syncthreads();
+        first_segment = false;
+
+        auto issue = [&](int tile_rel) {
+            const int t0 = (tile_begin + tile_rel) * kTileM;
+            const int n = min(kTileM, tokens - t0);
+            const uint32_t ring_slot = (ring + tile_rel) % kStages;
+            StageT& st = stages[ring_slot];
+            uint64_t* bar = &full_bar[ring_slot];
+            // 8-byte metadata rows stay bulk-copyable: tiles start at multiples of 64 tokens and the host
+            // selects this kernel for them only when token count and token stride are even
+            const uint32_t md_bytes = n * ML::kMetaBytes, pl_bytes = n * ML::kPayloadBytes;
+            const unsigned char* kp_src = kp_g + static_cast<size_t>(t0) * ML::kPayloadBytes;
+            const unsigned char* vp_src = vp_g + static_cast<size_t>(t0) * ML::kPayloadBytes;
+            if constexpr (ML::kPad != 0) {
+                // metadata in bulk by one thread; payload rows in 16-byte pieces by everyone, into padded rows
+                if (tid == 0) {
+                    mbar_arrive_expect_tx(bar, 2 * md_bytes);
+                    bulk_g2s(st.km, km_g + static_cast<size_t>(t0) * ML::kMetaBytes, md_bytes, bar);
+                    bulk_g2s(st.vm, vm_g + static_cast<size_t>(t0) * ML::kMetaBytes, md_bytes, bar);
                 }
-                const int cu = (ks ^ cen_swz) * 4;
-                const float4 al = *reinterpret_cast<const float4*>(cA + cu), ah = *reinterpret_cast<const float4*>(cA + 64 + cu);
-                const float4 bl = *reinterpret_cast<const float4*>(cB + cu), bh = *reinterpret_cast<const float4*>(cB + 64 + cu);
-                float kAl[4] = {al.x, al.y, al.z, al.w}, kAh[4] = {ah.x, ah.y, ah.z, ah.w};
-                float kBl[4] = {bl.x, bl.y, bl.z, bl.w}, kBh[4] = {bh.x, bh.y, bh.z, bh.w};
-                if constexpr (Field::kSlotwise) {
-                    // the four walks advance together, one coordinate each at a time
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        fAl.add1(4 * ks + e, kAl[e]);
-                        fAh.add1(4 * ks + e, kAh[e]);
-                        fBl.add1(4 * ks + e, kBl[e]);
-                        fBh.add1(4 * ks + e, kBh[e]);
-                    }
-                } else {
-                    fAl.add4(ks, kAl, kscA);
-                    fAh.add4(ks, kAh, kscA);
-                    fBl.add4(ks, kBl, kscB);
-                    fBh.add4(ks, kBh, kscB);
+                constexpr int kPieces = ML::kPayloadBytes / 16, kRow = ML::kPayloadBytes + ML::kPad;
+                for (int c = tid; c < n * kPieces; c += kThreadsM) {
+                    const int dst = (c / kPieces) * kRow + (c % kPieces) * 16;
+                    cp_async16(st.kp + dst, kp_src + c * 16);
+                    cp_async16(st.vp + dst, vp_src + c * 16);
                 }
-                float rAl[4], rAh[4], rBl[4], rBh[4];
-#pragma unroll
-                for (int e2 = 0; e2 < 2; ++e2) {
-                    const float4 ta = trA_r[ks * 2 + e2];  // (cos, sin) of two neighbouring frequencies
-                    const float4 tb = trB_r[ks * 2 + e2];
-                    const int e = 2 * e2;
-                    rAl[e] = kAl[e] * ta.x - kAh[e] * ta.y;
-                    rAh[e] = kAh[e] * ta.x + kAl[e] * ta.y;
-                    rAl[e + 1] = kAl[e + 1] * ta.z - kAh[e + 1] * ta.w;
-                    rAh[e + 1] = kAh[e + 1] * ta.z + kAl[e + 1] * ta.w;
-                    rBl[e] = kBl[e] * tb.x - kBh[e] * tb.y;
-                    rBh[e] = kBh[e] * tb.x + kBl[e] * tb.y;
-                    rBl[e + 1] = kBl[e + 1] * tb.z - kBh[e + 1] * tb.w;
-                    rBh[e + 1] = kBh[e + 1] * tb.z + kBl[e + 1] * tb.w;
+                cp_async_arrive(bar);
+            } else if (tid == 0) {
+                mbar_arrive_expect_tx(bar, 2 * md_bytes + 2 * pl_bytes);
+                if (ML::kMetaBytes) {
+                    bulk_g2s(st.km, km_g + static_cast<size_t>(t0) * ML::kMetaBytes, md_bytes, bar);
+                    bulk_g2s(st.vm, vm_g + static_cast<size_t>(t0) * ML::kMetaBytes, md_bytes, bar);
                 }
-                uint32_t a0, a1, a2, a3, l0, l1, l2, l3;
-                split_h2(rAl[0], rAl[1], a0, l0);
-                split_h2(rBl[0], rBl[1], a1, l1);
-                split_h2(rAl[2], rAl[3], a2, l2);
-                split_h2(rBl[2], rBl[3], a3, l3);
-                mma_16816(sc, a0, a1, a2, a3, qh_l.x, qh_l.y);
-                mma_16816(sc2, a0, a1, a2, a3, ql_l.x, ql_l.y);
-                mma_16816(sc3, l0, l1, l2, l3, qh_l.x, qh_l.y);
-                split_h2(rAh[0], rAh[1], a0, l0);
-                split_h2(rBh[0], rBh[1], a1, l1);
-                split_h2(rAh[2], rAh[3], a2, l2);
-                split_h2(rBh[2], rBh[3], a3, l3);
-                mma_16816(sc, a0, a1, a2, a3, qh_h.x, qh_h.y);
-                mma_16816(sc2, a0, a1, a2, a3, ql_h.x, ql_h.y);
-                mma_16816(sc3, l0, l1, l2, l3, qh_h.x, qh_h.y);
+                bulk_g2s(st.kp, kp_src, pl_bytes, bar);
+                bulk_g2s(st.vp, vp_src, pl_bytes, bar);
             }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) sc[i] += sc2[i] + sc3[i];
-            // value fields of tokens 2q, 2q+1, 2q+8, 2q+9, coordinates [16g, 16g+16): set up before the softmax so
-            // that their mask and rank-base loads are in flight during it
-            const unsigned char* pv_bytes = reinterpret_cast<const unsigned char*>(pre_v);
-            const int r0 = 2 * qd, r1 = 2 * qd + 1, r2 = 2 * qd + 8, r3 = 2 * qd + 9;
-            Field f0 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r0, g, r0 < nvalid);
-            Field f1 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r1, g, r1 < nvalid);
-            Field f2 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r2, g, r2 < nvalid);
-            Field f3 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r3, g, r3 < nvalid);
+        };
+        for (int s = 0; s < kStages && s < ntiles; ++s) issue(s);
 
-            // sc: c0,c1 = (token g, heads 2q, 2q+1), c2,c3 = (token g+8, ...), log2 domain
-            if (!okA) sc[0] = sc[1] = -INFINITY;
-            if (!okB) sc[2] = sc[3] = -INFINITY;
-
-            // ================= softmax (lazy running maximum) =================
-            float mt[2] = {fmaxf(sc[0], sc[2]), fmaxf(sc[1], sc[3])};
-#pragma unroll
-            for (int off = 4; off < 32; off <<= 1) {
-                mt[0] = fmaxf(mt[0], __shfl_xor_sync(0xffffffffu, mt[0], off));
-                mt[1] = fmaxf(mt[1], __shfl_xor_sync(0xffffffffu, mt[1], off));
+        // ---- per unit: key centroids (FP32, swizzled rows) ---------------------------------------
+        {
+            const __half* src = p.kc + static_cast<size_t>(unit) * p.ck * kHeadDim;
+            for (int idx = tid; idx < p.ck * (kHeadDim / 8); idx += kThreadsM) {  // 8 coordinates per step
+                const int row = idx / (kHeadDim / 8), d = (idx % (kHeadDim / 8)) * 8;
+                const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + row * kHeadDim + d));
+                const __half2* h = reinterpret_cast<const __half2*>(&raw);
+                const float2 v0 = __half22float2(h[0]), v1 = __half22float2(h[1]), v2 = __half22float2(h[2]), v3 = __half22float2(h[3]);
+                *reinterpret_cast<float4*>(kc_s + row * kCenStride + cen_index(d)) = make_float4(v0.x, v0.y, v1.x, v1.y);
+                *reinterpret_cast<float4*>(kc_s + row * kCenStride + cen_index(d + 4)) = make_float4(v2.x, v2.y, v3.x, v3.y);
             }
-            const bool grow = mt[0] > m_used[0] + kRescaleThreshold || mt[1] > m_used[1] + kRescaleThreshold;
-            if (__any_sync(0xffffffffu, grow)) {
-                float alpha[2];
+        }
+
+        // ---- query state: angle (pos_q - P0) * f goes down by 64 f per tile; seeded exactly every
+        // kReseedTiles tiles ------------------------------------------------------------------------
+        float q_lo[kItems][2], q_hi[kItems][2], st_c[kItems][2], st_s[kItems][2];
+#pragma unroll
+        for (int it = 0; it < kItems; ++it) {
+            const int item = tid + it * kThreadsM;
+            const int h = item >> 5, i2 = (item & 31) * 2;
+            const bool on = item < GQA * 32;
+            const __half* qrow = p.q + (static_cast<size_t>(b) * p.nh + hkv * GQA + (on ? h : 0)) * kHeadDim;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                q_lo[it][u] = on ? __half2float(qrow[i2 + u]) * q_mul : 0.f;
+                q_hi[it][u] = on ? __half2float(qrow[i2 + u + 64]) * q_mul : 0.f;
+                st_c[it][u] = 1.f, st_s[it][u] = 0.f;
+            }
+        }
+
+        auto write_query = [&](int tile_rel) {
+            // Qt = R(pos_q - P0) q  for the tile that starts at token t0, as FP16 hi + lo
+            const int t0 = (tile_begin + tile_rel) * kTileM;
+            __half* base = qf + (tile_rel & 1) * (kQSets * GQA * kQStride);
+#pragma unroll
+            for (int it = 0; it < kItems; ++it) {
+                const int item = tid + it * kThreadsM;
+                if (item >= GQA * 32) continue;
+                const int h = item >> 5, i2 = (item & 31) * 2;
+                float lo[2], hi[2];
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
-                    const float m_new = fmaxf(m_used[u], mt[u]);
-                    alpha[u] = (m_used[u] == -INFINITY) ? 0.f : fast_exp2(m_used[u] - m_new);
-                    m_used[u] = m_new;
-                    l_part[u] *= alpha[u];
-                }
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    acc[i][0] *= alpha[0], acc[i][2] *= alpha[0];
-                    acc[i][1] *= alpha[1], acc[i][3] *= alpha[1];
-                }
-#pragma unroll
-                for (int mb = 0; mb < 4; ++mb) {
-                    bacc[mb][0] *= alpha[0], bacc[mb][2] *= alpha[0];
-                    bacc[mb][1] *= alpha[1], bacc[mb][3] *= alpha[1];
-                }
-            }
-            float pr[4];
-            pr[0] = fast_exp2(sc[0] - m_used[0]), pr[1] = fast_exp2(sc[1] - m_used[1]);
-            pr[2] = fast_exp2(sc[2] - m_used[0]), pr[3] = fast_exp2(sc[3] - m_used[1]);
-            __half2 p01 = __floats2half2_rn(pr[0], pr[1]), p23 = __floats2half2_rn(pr[2], pr[3]);
-            const float2 p01f = __half22float2(p01), p23f = __half22float2(p23);
-            l_part[0] += p01f.x + p23f.x;
-            l_part[1] += p01f.y + p23f.y;
-            // P as B operand (tokens x heads): transpose the two 8x8 halves
-            uint32_t pb0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p01));
-            uint32_t pb1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p23));
-            {
-                // cluster mass: one-hot rows A[c][t] = (value id of token t == c), built two tokens at a
-                // time by a packed FP16 compare; tokens beyond the end have p = 0
-                const int w0 = __shfl_sync(0xffffffffu, ids_cur, 16 + 2 * qd), w1 = __shfl_sync(0xffffffffu, ids_cur, 17 + 2 * qd);
-                const int w2 = __shfl_sync(0xffffffffu, ids_cur, 24 + 2 * qd), w3 = __shfl_sync(0xffffffffu, ids_cur, 25 + 2 * qd);
-                const __half2 gg = __half2half2(__int2half_rn(g));
-                const __half2 d01 = __hsub2(__halves2half2(__int2half_rn(w0), __int2half_rn(w1)), gg);
-                const __half2 d23 = __hsub2(__halves2half2(__int2half_rn(w2), __int2half_rn(w3)), gg);
-#pragma unroll
-                for (int mb = 0; mb < 4; ++mb) {
-                    if (16 * mb < p.cv) {
-                        const __half2 lo = __float2half2_rn(16.f * mb), hi = __float2half2_rn(16.f * mb + 8.f);
-                        const __half2 a0 = __heq2(d01, lo), a1 = __heq2(d01, hi), a2 = __heq2(d23, lo), a3 = __heq2(d23, hi);
-                        mma_16816(bacc[mb], *reinterpret_cast<const uint32_t*>(&a0), *reinterpret_cast<const uint32_t*>(&a1),
-                                  *reinterpret_cast<const uint32_t*>(&a2), *reinterpret_cast<const uint32_t*>(&a3), pb0, pb1);
+                    if (tile_rel % kReseedTiles == 0) {
+                        const float delta = static_cast<float>(query_position(p) - (p.start_pos + t0));
+                        sincosf(delta * q_f[it][u], &st_s[it][u], &st_c[it][u]);
                     }
+                    const float c = st_c[it][u], s = st_s[it][u];
+                    lo[u] = q_lo[it][u] * c - q_hi[it][u] * s;
+                    hi[u] = q_hi[it][u] * c + q_lo[it][u] * s;
+                    // next tile: angle - 64 f
+                    st_c[it][u] = c * dn_c[it][u] + s * dn_s[it][u];
+                    st_s[it][u] = s * dn_c[it][u] - c * dn_s[it][u];
+                }
+                const __half2 lo_h = __floats2half2_rn(lo[0], lo[1]), hi_h = __floats2half2_rn(hi[0], hi[1]);
+                const float2 lo_f = __half22float2(lo_h), hi_f = __half22float2(hi_h);
+                __half* row_hi = base + h * kQStride;
+                __half* row_lo = base + (GQA + h) * kQStride;
+                *reinterpret_cast<__half2*>(row_hi + i2) = lo_h;
+                *reinterpret_cast<__half2*>(row_hi + i2 + 64) = hi_h;
+                *reinterpret_cast<__half2*>(row_lo + i2) = __floats2half2_rn(lo[0] - lo_f.x, lo[1] - lo_f.y);
+                *reinterpret_cast<__half2*>(row_lo + i2 + 64) = __floats2half2_rn(hi[0] - hi_f.x, hi[1] - hi_f.y);
+            }
+        };
+        if (ntiles > 0) write_query(0);
+
+        // ---- per-warp running state -------------------------------------------------------------
+        float acc[8][4];          // O^T: m-block i -> coordinates 16g+2i (c0,c1) and 16g+2i+1 (c2,c3); heads 2q, 2q+1
+        float m_used[2], l_part[2];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+        m_used[0] = m_used[1] = -INFINITY;
+        l_part[0] = l_part[1] = 0.f;
+        // cluster mass beta[value cluster][head] of this warp's tokens, accumulated by the tensor cores as
+        // onehot(value id)^T . P: rows = clusters 16 mb + g (+ 8), columns = heads 2q, 2q + 1
+        float bacc[4][4];
+#pragma unroll
+        for (int mb = 0; mb < 4; ++mb) bacc[mb][0] = bacc[mb][1] = bacc[mb][2] = bacc[mb][3] = 0.f;
+
+        // cluster ids (and FP16 scales) of this warp's 16 tokens of the next tile: lanes 0..15 hold the
+        // key side of token `lane`, lanes 16..31 the value side of token `lane - 16`
+        auto load_ids = [&](int tile_rel, int& id, uint32_t& scale) {
+            const int t = (tile_begin + tile_rel) * kTileM + warp * 16 + (lane & 15);
+            id = 0, scale = 0u;
+            if (tile_rel < ntiles && t < tokens) {
+                // volatile: issue the loads here, a whole tile ahead of their use, instead of letting the
+                // compiler sink them next to the consumer
+                const int8_t* src = ((lane < 16) ? kid_g : vid_g) + t;
+                asm volatile("ld.global.nc.s8 %0, [%1];" : "=r"(id) : "l"(src));
+                if constexpr (ML::kScale) {
+                    const __half* ssrc = ((lane < 16) ? ks_g : vs_g) + t;
+                    unsigned short h;
+                    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(h) : "l"(ssrc));
+                    scale = h;
                 }
             }
-            if constexpr (ML::kScaleP) {
-                // quantised values enter the MMA as integer codes: their per-token scale rides on P
-                const float vsA = h2f_bits(__shfl_sync(0xffffffffu, scl_cur, 16 + g));
-                const float vsB = h2f_bits(__shfl_sync(0xffffffffu, scl_cur, 24 + g));
-                p01 = __floats2half2_rn(p01f.x * vsA, p01f.y * vsA);
-                p23 = __floats2half2_rn(p23f.x * vsB, p23f.y * vsB);
-                pb0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p01));
-                pb1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p23));
-            }
+        };
+        int ids_next;
+        uint32_t scl_next;
+        load_ids(0, ids_next, scl_next);
+        __syncthreads();  // centroid table and first query tile ready
 
-            // O^T += Vres^T . P.  Values: tokens 2q, 2q+1, 2q+8, 2q+9 of the block, coordinates [16g, 16g+16);
-            // m-block i holds coordinates 16g + 2i (rows g) and 16g + 2i + 1 (rows g + 8), so that the MMAs
-            // follow the field walks two coordinates at a time
-            {
+        for (int it = 0; it < ntiles; ++it) {
+            const int t0 = (tile_begin + it) * kTileM;
+            const int ids_cur = ids_next;
+            const uint32_t scl_cur = scl_next;
+            load_ids(it + 1, ids_next, scl_next);
+            const uint32_t ring_it = ring + it;
+            if (!mbar_wait(&full_bar[ring_it % kStages], (ring_it / kStages) & 1)) lost = true;
+            const StageT& st = stages[ring_it % kStages];
+            const int nvalid = min(16, tokens - (t0 + warp * 16));  // valid tokens of this warp's block
+            if (nvalid > 0) {
+                if constexpr (ML::kPrefix) {
+                    // rank bases of the block's 16 key bitmaps (lanes 0..15) and value bitmaps (16..31)
+                    const int tok = warp * 16 + (lane & 15);
+                    const uint4 bm = reinterpret_cast<const uint4*>((lane < 16) ? st.km : st.vm)[tok];
+                    pre_k[lane] = rank_bases(bm);  // pre_v == pre_k + 16
+                    __syncwarp();
+                }
+
+                // ================= keys: rows g and g + 8 of the block =================
+                const int tokA = warp * 16 + g, tokB = tokA + 8;
+                const bool okA = g < nvalid, okB = g + 8 < nvalid;
+                const int kidA = min(max(__shfl_sync(0xffffffffu, ids_cur, g), 0), p.ck - 1);
+                const int kidB = min(max(__shfl_sync(0xffffffffu, ids_cur, g + 8), 0), p.ck - 1);
+                const unsigned char* pk_bytes = reinterpret_cast<const unsigned char*>(pre_k);
+                Field fAl = ML::field(st.kp, st.km, pk_bytes, tokA, qd, okA), fAh = ML::field(st.kp, st.km, pk_bytes, tokA, 4 + qd, okA);
+                Field fBl = ML::field(st.kp, st.km, pk_bytes, tokB, qd, okB), fBh = ML::field(st.kp, st.km, pk_bytes, tokB, 4 + qd, okB);
+                const unsigned short kscA = static_cast<unsigned short>(__shfl_sync(0xffffffffu, scl_cur, g));
+                const unsigned short kscB = static_cast<unsigned short>(__shfl_sync(0xffffffffu, scl_cur, g + 8));
+                // FP32 centroid rows; the lane's low field starts at 16q, its partner field at 64 + 16q
+                const float* cA = kc_s + kidA * kCenStride + 16 * qd;
+                const float* cB = kc_s + kidB * kCenStride + 16 * qd;
+                const int cen_swz = (qd >> 1) & 1;  // 16-byte unit swap of this lane's fields
+                const __half* qbuf = qf + (it & 1) * (kQSets * GQA * kQStride) + g * kQStride + 16 * qd;
+                // rows of the B operand: the real heads (hi halves), then -- packed form -- their lo halves
+                const bool q_on = g < (kPackQ ? 2 * GQA : GQA);
+
+                // independent accumulators (hi.hi, hi.lo, lo.hi) keep the MMA dependency chains short
+                float sc[4] = {0.f, 0.f, 0.f, 0.f}, sc2[4] = {0.f, 0.f, 0.f, 0.f}, sc3[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
-                    uint32_t h0[4], h1[4], h2[4], h3[4];
+                    // four coordinates 16q + 4ks .. +3 and their partners + 64, both tokens:
+                    // k = centroid (+ residual where the bitmap bit is set)
+                    // query fragments of k-step ks (low half of the head) and ks + 4 (high half), requested first
+                    uint2 qh_l = make_uint2(0u, 0u), qh_h = qh_l, ql_l = qh_l, ql_h = qh_l;
+                    if (q_on) {
+                        qh_l = *reinterpret_cast<const uint2*>(qbuf + 4 * ks);
+                        qh_h = *reinterpret_cast<const uint2*>(qbuf + 64 + 4 * ks);
+                        if constexpr (!kPackQ) {
+                            ql_l = *reinterpret_cast<const uint2*>(qbuf + GQA * kQStride + 4 * ks);
+                            ql_h = *reinterpret_cast<const uint2*>(qbuf + GQA * kQStride + 64 + 4 * ks);
+                        }
+                    }
+                    const int cu = (ks ^ cen_swz) * 4;
+                    const float4 al = *reinterpret_cast<const float4*>(cA + cu), ah = *reinterpret_cast<const float4*>(cA + 64 + cu);
+                    const float4 bl = *reinterpret_cast<const float4*>(cB + cu), bh = *reinterpret_cast<const float4*>(cB + 64 + cu);
+                    float kAl[4] = {al.x, al.y, al.z, al.w}, kAh[4] = {ah.x, ah.y, ah.z, ah.w};
+                    float kBl[4] = {bl.x, bl.y, bl.z, bl.w}, kBh[4] = {bh.x, bh.y, bh.z, bh.w};
                     if constexpr (Field::kSlotwise) {
+                        // the four walks advance together, one coordinate each at a time
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            h0[e] = f0.bits1(4 * ks + e);
-                            h1[e] = f1.bits1(4 * ks + e);
-                            h2[e] = f2.bits1(4 * ks + e);
-                            h3[e] = f3.bits1(4 * ks + e);
+                            fAl.add1(4 * ks + e, kAl[e]);
+                            fAh.add1(4 * ks + e, kAh[e]);
+                            fBl.add1(4 * ks + e, kBl[e]);
+                            fBh.add1(4 * ks + e, kBh[e]);
                         }
                     } else {
-                        f0.bits4(ks, h0);
-                        f1.bits4(ks, h1);
-                        f2.bits4(ks, h2);
-                        f3.bits4(ks, h3);
+                        fAl.add4(ks, kAl, kscA);
+                        fAh.add4(ks, kAh, kscA);
+                        fBl.add4(ks, kBl, kscB);
+                        fBh.add4(ks, kBh, kscB);
                     }
-                    mma_16816(acc[2 * ks], h0[0] | (h1[0] << 16), h0[1] | (h1[1] << 16), h2[0] | (h3[0] << 16),
-                              h2[1] | (h3[1] << 16), pb0, pb1);
-                    mma_16816(acc[2 * ks + 1], h0[2] | (h1[2] << 16), h0[3] | (h1[3] << 16), h2[2] | (h3[2] << 16),
-                              h2[3] | (h3[3] << 16), pb0, pb1);
-                }
-            }
-            __syncwarp();  // rank-base table is rewritten next tile
-        }
-        if (it + 1 < ntiles) write_query(it + 1);
-        __syncthreads();  // ring slot free, next query tile visible
-        if (it + kStages < ntiles) issue(it + kStages);
-    }
-    if (lost && lane == 0) atomicOr(&timed_out, 1u);
-
-    // ---- combine warps, write the split partial ----------------------------------------------
+                    float rAl[4], rAh[4], rBl[4], rBh[4];
 #pragma unroll
-    for (int off = 4; off < 32; off <<= 1) {
-        l_part[0] += __shfl_xor_sync(0xffffffffu, l_part[0], off);
-        l_part[1] += __shfl_xor_sync(0xffffffffu, l_part[1], off);
-    }
-    if (g == 0) {
+                    for (int e2 = 0; e2 < 2; ++e2) {
+                        const float4 ta = trA_r[ks * 2 + e2];  // (cos, sin) of two neighbouring frequencies
+                        const float4 tb = trB_r[ks * 2 + e2];
+                        const int e = 2 * e2;
+                        rAl[e] = kAl[e] * ta.x - kAh[e] * ta.y;
+                        rAh[e] = kAh[e] * ta.x + kAl[e] * ta.y;
+                        rAl[e + 1] = kAl[e + 1] * ta.z - kAh[e + 1] * ta.w;
+                        rAh[e + 1] = kAh[e + 1] * ta.z + kAl[e + 1] * ta.w;
+                        rBl[e] = kBl[e] * tb.x - kBh[e] * tb.y;
+                        rBh[e] = kBh[e] * tb.x + kBl[e] * tb.y;
+                        rBl[e + 1] = kBl[e + 1] * tb.z - kBh[e + 1] * tb.w;
+                        rBh[e + 1] = kBh[e + 1] * tb.z + kBl[e + 1] * tb.w;
+                    }
+                    uint32_t a0, a1, a2, a3, l0, l1, l2, l3;
+                    split_h2(rAl[0], rAl[1], a0, l0);
+                    split_h2(rBl[0], rBl[1], a1, l1);
+                    split_h2(rAl[2], rAl[3], a2, l2);
+                    split_h2(rBl[2], rBl[3], a3, l3);
+                    mma_16816(sc, a0, a1, a2, a3, qh_l.x, qh_l.y);
+                    if constexpr (!kPackQ) mma_16816(sc2, a0, a1, a2, a3, ql_l.x, ql_l.y);
+                    mma_16816(sc3, l0, l1, l2, l3, qh_l.x, qh_l.y);
+                    split_h2(rAh[0], rAh[1], a0, l0);
+                    split_h2(rBh[0], rBh[1], a1, l1);
+                    split_h2(rAh[2], rAh[3], a2, l2);
+                    split_h2(rBh[2], rBh[3], a3, l3);
+                    mma_16816(sc, a0, a1, a2, a3, qh_h.x, qh_h.y);
+                    if constexpr (!kPackQ) mma_16816(sc2, a0, a1, a2, a3, ql_h.x, ql_h.y);
+                    mma_16816(sc3, l0, l1, l2, l3, qh_h.x, qh_h.y);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) sc[i] += sc2[i] + sc3[i];
+                if constexpr (kPackQ) {
+                    // columns h (query hi) and h + 4 (query lo) of a head sit in lanes q and q ^ 2; afterwards
+                    // lanes q = 2, 3 repeat heads 0..3 (their results are never stored)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) sc[i] += __shfl_xor_sync(0xffffffffu, sc[i], 2);
+                }
+                // value fields of tokens 2q, 2q+1, 2q+8, 2q+9, coordinates [16g, 16g+16): set up before the softmax so
+                // that their mask and rank-base loads are in flight during it
+                const unsigned char* pv_bytes = reinterpret_cast<const unsigned char*>(pre_v);
+                const int r0 = 2 * qd, r1 = 2 * qd + 1, r2 = 2 * qd + 8, r3 = 2 * qd + 9;
+                Field f0 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r0, g, r0 < nvalid);
+                Field f1 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r1, g, r1 < nvalid);
+                Field f2 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r2, g, r2 < nvalid);
+                Field f3 = ML::field(st.vp, st.vm, pv_bytes, warp * 16 + r3, g, r3 < nvalid);
+
+                // sc: c0,c1 = (token g, heads 2q, 2q+1), c2,c3 = (token g+8, ...), log2 domain
+                if (!okA) sc[0] = sc[1] = -INFINITY;
+                if (!okB) sc[2] = sc[3] = -INFINITY;
+
+                // ================= softmax (lazy running maximum) =================
+                float mt[2] = {fmaxf(sc[0], sc[2]), fmaxf(sc[1], sc[3])};
+#pragma unroll
+                for (int off = 4; off < 32; off <<= 1) {
+                    mt[0] = fmaxf(mt[0], __shfl_xor_sync(0xffffffffu, mt[0], off));
+                    mt[1] = fmaxf(mt[1], __shfl_xor_sync(0xffffffffu, mt[1], off));
+                }
+                const bool grow = mt[0] > m_used[0] + kRescaleThreshold || mt[1] > m_used[1] + kRescaleThreshold;
+                if (__any_sync(0xffffffffu, grow)) {
+                    float alpha[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const float m_new = fmaxf(m_used[u], mt[u]);
+                        alpha[u] = (m_used[u] == -INFINITY) ? 0.f : fast_exp2(m_used[u] - m_new);
+                        m_used[u] = m_new;
+                        l_part[u] *= alpha[u];
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        acc[i][0] *= alpha[0], acc[i][2] *= alpha[0];
+                        acc[i][1] *= alpha[1], acc[i][3] *= alpha[1];
+                    }
+#pragma unroll
+                    for (int mb = 0; mb < 4; ++mb) {
+                        bacc[mb][0] *= alpha[0], bacc[mb][2] *= alpha[0];
+                        bacc[mb][1] *= alpha[1], bacc[mb][3] *= alpha[1];
+                    }
+                }
+                float pr[4];
+                pr[0] = fast_exp2(sc[0] - m_used[0]), pr[1] = fast_exp2(sc[1] - m_used[1]);
+                pr[2] = fast_exp2(sc[2] - m_used[0]), pr[3] = fast_exp2(sc[3] - m_used[1]);
+                __half2 p01 = __floats2half2_rn(pr[0], pr[1]), p23 = __floats2half2_rn(pr[2], pr[3]);
+                const float2 p01f = __half22float2(p01), p23f = __half22float2(p23);
+                l_part[0] += p01f.x + p23f.x;
+                l_part[1] += p01f.y + p23f.y;
+                // P as B operand (tokens x heads): transpose the two 8x8 halves
+                uint32_t pb0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p01));
+                uint32_t pb1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p23));
+                {
+                    // cluster mass: one-hot rows A[c][t] = (value id of token t == c), built two tokens at a
+                    // time by a packed FP16 compare; tokens beyond the end have p = 0
+                    const int w0 = __shfl_sync(0xffffffffu, ids_cur, 16 + 2 * qd), w1 = __shfl_sync(0xffffffffu, ids_cur, 17 + 2 * qd);
+                    const int w2 = __shfl_sync(0xffffffffu, ids_cur, 24 + 2 * qd), w3 = __shfl_sync(0xffffffffu, ids_cur, 25 + 2 * qd);
+                    const __half2 gg = __half2half2(__int2half_rn(g));
+                    const __half2 d01 = __hsub2(__halves2half2(__int2half_rn(w0), __int2half_rn(w1)), gg);
+                    const __half2 d23 = __hsub2(__halves2half2(__int2half_rn(w2), __int2half_rn(w3)), gg);
+#pragma unroll
+                    for (int mb = 0; mb < 4; ++mb) {
+                        if (16 * mb < p.cv) {
+                            const __half2 lo = __float2half2_rn(16.f * mb), hi = __float2half2_rn(16.f * mb + 8.f);
+                            const __half2 a0 = __heq2(d01, lo), a1 = __heq2(d01, hi), a2 = __heq2(d23, lo), a3 = __heq2(d23, hi);
+                            mma_16816(bacc[mb], *reinterpret_cast<const uint32_t*>(&a0), *reinterpret_cast<const uint32_t*>(&a1),
+                                      *reinterpret_cast<const uint32_t*>(&a2), *reinterpret_cast<const uint32_t*>(&a3), pb0, pb1);
+                        }
+                    }
+                }
+                if constexpr (ML::kScaleP) {
+                    // quantised values enter the MMA as integer codes: their per-token scale rides on P
+                    const float vsA = h2f_bits(__shfl_sync(0xffffffffu, scl_cur, 16 + g));
+                    const float vsB = h2f_bits(__shfl_sync(0xffffffffu, scl_cur, 24 + g));
+                    p01 = __floats2half2_rn(p01f.x * vsA, p01f.y * vsA);
+                    p23 = __floats2half2_rn(p23f.x * vsB, p23f.y * vsB);
+                    pb0 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p01));
+                    pb1 = movmatrix_trans(*reinterpret_cast<const uint32_t*>(&p23));
+                }
+
+                // O^T += Vres^T . P.  Values: tokens 2q, 2q+1, 2q+8, 2q+9 of the block, coordinates [16g, 16g+16);
+                // m-block i holds coordinates 16g + 2i (rows g) and 16g + 2i + 1 (rows g + 8), so that the MMAs
+                // follow the field walks two coordinates at a time
+                {
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        uint32_t h0[4], h1[4], h2[4], h3[4];
+                        if constexpr (Field::kSlotwise) {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                h0[e] = f0.bits1(4 * ks + e);
+                                h1[e] = f1.bits1(4 * ks + e);
+                                h2[e] = f2.bits1(4 * ks + e);
+                                h3[e] = f3.bits1(4 * ks + e);
+                            }
+                        } else {
+                            f0.bits4(ks, h0);
+                            f1.bits4(ks, h1);
+                            f2.bits4(ks, h2);
+                            f3.bits4(ks, h3);
+                        }
+                        mma_16816(acc[2 * ks], h0[0] | (h1[0] << 16), h0[1] | (h1[1] << 16), h2[0] | (h3[0] << 16),
+                                  h2[1] | (h3[1] << 16), pb0, pb1);
+                        mma_16816(acc[2 * ks + 1], h0[2] | (h1[2] << 16), h0[3] | (h1[3] << 16), h2[2] | (h3[2] << 16),
+                                  h2[3] | (h3[3] << 16), pb0, pb1);
+                    }
+                }
+                __syncwarp();  // rank-base table is rewritten next tile
+            }
+            if (it + 1 < ntiles) write_query(it + 1);
+            __syncthreads();  // ring slot free, next query tile visible
+            if (it + kStages < ntiles) issue(it + kStages);
+        }
+        ring += static_cast<uint32_t>(ntiles);
+
+        // ---- combine warps, write the segment's partial -------------------------------------------
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            l_part[0] += __shfl_xor_sync(0xffffffffu, l_part[0], off);
+            l_part[1] += __shfl_xor_sync(0xffffffffu, l_part[1], off);
+        }
+        if (g == 0) {
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int h = 2 * qd + u;
+                if (h < GQA) red_m[h][warp] = m_used[u], red_l[h][warp] = l_part[u];
+            }
+        }
+        __syncthreads();
+        float* red_acc = reinterpret_cast<float*>(smem_raw);  // [warps][GQA][128], stage memory is free now
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
             const int h = 2 * qd + u;
-            if (h < GQA) red_m[h][warp] = m_used[u], red_l[h][warp] = l_part[u];
-        }
-    }
-    __syncthreads();
-    float* red_acc = reinterpret_cast<float*>(smem_raw);  // [warps][GQA][128], stage memory is free now
+            if (h < GQA) {
+                float fm = red_m[h][0];
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-        const int h = 2 * qd + u;
-        if (h < GQA) {
-            float fm = red_m[h][0];
+                for (int w = 1; w < kWarpsM; ++w) fm = fmaxf(fm, red_m[h][w]);
+                const float scale = (m_used[u] == -INFINITY) ? 0.f : fast_exp2(m_used[u] - fm);
+                float* dst = red_acc + (warp * GQA + h) * kHeadDim + 16 * g;
 #pragma unroll
-            for (int w = 1; w < kWarpsM; ++w) fm = fmaxf(fm, red_m[h][w]);
-            const float scale = (m_used[u] == -INFINITY) ? 0.f : fast_exp2(m_used[u] - fm);
-            float* dst = red_acc + (warp * GQA + h) * kHeadDim + 16 * g;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                dst[2 * i] = acc[i][u] * scale;
-                dst[2 * i + 1] = acc[i][2 + u] * scale;
-            }
-            if (qd * 2 + u < GQA) {
+                for (int i = 0; i < 8; ++i) {
+                    dst[2 * i] = acc[i][u] * scale;
+                    dst[2 * i + 1] = acc[i][2 + u] * scale;
+                }
                 float* bdst = beta_s + (warp * GQA + h) * kMaxClusters + g;
 #pragma unroll
                 for (int mb = 0; mb < 4; ++mb) bdst[16 * mb] = bacc[mb][u], bdst[16 * mb + 8] = bacc[mb][2 + u];
             }
         }
-    }
-    __syncthreads();
-    const size_t part = static_cast<size_t>(b) * p.nh + hkv * GQA;
-    for (int idx = tid; idx < GQA * kHeadDim; idx += kThreadsM) {
-        const int h = idx / kHeadDim, d = idx % kHeadDim;
-        float sum = 0.f;
+        __syncthreads();
+        const size_t part = static_cast<size_t>(b) * p.nh + hkv * GQA;
+        if (slot >= 0 && slot < p.splits) {
+            for (int idx = tid; idx < GQA * kHeadDim; idx += kThreadsM) {
+                const int h = idx / kHeadDim, d = idx % kHeadDim;
+                float sum = 0.f;
 #pragma unroll
-        for (int w = 0; w < kWarpsM; ++w) sum += red_acc[(w * GQA + h) * kHeadDim + d];
-        p.ws_delta[((part + h) * p.splits + split) * kHeadDim + d] = sum;
-    }
-    for (int idx = tid; idx < GQA * kMaxClusters; idx += kThreadsM) {
-        const int h = idx / kMaxClusters, c = idx % kMaxClusters;
-        float fm = red_m[h][0];
+                for (int w = 0; w < kWarpsM; ++w) sum += red_acc[(w * GQA + h) * kHeadDim + d];
+                p.ws_delta[((part + h) * p.splits + slot) * kHeadDim + d] = sum;
+            }
+            for (int idx = tid; idx < GQA * kMaxClusters; idx += kThreadsM) {
+                const int h = idx / kMaxClusters, c = idx % kMaxClusters;
+                float fm = red_m[h][0];
 #pragma unroll
-        for (int w = 1; w < kWarpsM; ++w) fm = fmaxf(fm, red_m[h][w]);
-        float sum = 0.f;
+                for (int w = 1; w < kWarpsM; ++w) fm = fmaxf(fm, red_m[h][w]);
+                float sum = 0.f;
 #pragma unroll
-        for (int w = 0; w < kWarpsM; ++w) {
-            const float scale = (red_m[h][w] == -INFINITY) ? 0.f : fast_exp2(red_m[h][w] - fm);
-            sum += beta_s[(w * GQA + h) * kMaxClusters + c] * scale;
+                for (int w = 0; w < kWarpsM; ++w) {
+                    const float scale = (red_m[h][w] == -INFINITY) ? 0.f : fast_exp2(red_m[h][w] - fm);
+                    sum += beta_s[(w * GQA + h) * kMaxClusters + c] * scale;
+                }
+                p.ws_beta[((part + h) * p.splits + slot) * kMaxClusters + c] = sum;
+            }
+            if (tid < GQA) {
+                const int h = tid;
+                float fm = red_m[h][0];
+                for (int w = 1; w < kWarpsM; ++w) fm = fmaxf(fm, red_m[h][w]);
+                float fl = 0.f;
+                for (int w = 0; w < kWarpsM; ++w)
+                    fl += (red_m[h][w] == -INFINITY) ? 0.f : red_l[h][w] * fast_exp2(red_m[h][w] - fm);
+                p.ws_m[(part + h) * p.splits + slot] = fm;
+                p.ws_l[(part + h) * p.splits + slot] = fl;
+            }
+            // the segment that ends its unit marks the unit's unused slots as empty
+            if (closes_unit) {
+                for (int idx = tid; idx < GQA * (p.splits - slot - 1); idx += kThreadsM) {
+                    const int h = idx % GQA, s = slot + 1 + idx / GQA;
+                    p.ws_m[(part + h) * p.splits + s] = -INFINITY;
+                    p.ws_l[(part + h) * p.splits + s] = 0.f;
+                }
+            }
+        } else if (tid == 0) {
+            atomicOr(p.status, RESKV_STATUS_STATE_RANGE);
         }
-        p.ws_beta[((part + h) * p.splits + split) * kMaxClusters + c] = sum;
     }
-    if (tid < GQA) {
-        const int h = tid;
-        float fm = red_m[h][0];
-        for (int w = 1; w < kWarpsM; ++w) fm = fmaxf(fm, red_m[h][w]);
-        float fl = 0.f;
-        for (int w = 0; w < kWarpsM; ++w)
-            fl += (red_m[h][w] == -INFINITY) ? 0.f : red_l[h][w] * fast_exp2(red_m[h][w] - fm);
-        p.ws_m[(part + h) * p.splits + split] = fm;
-        p.ws_l[(part + h) * p.splits + split] = fl;
-    }
+    if (lost && lane == 0) atomicOr(&timed_out, 1u);
+    __syncthreads();
     if (tid == 0 && timed_out) atomicOr(p.status, RESKV_STATUS_WAIT_TIMEOUT);
 }
 

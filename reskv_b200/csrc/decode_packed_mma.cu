@@ -8,14 +8,21 @@ namespace {
 #include "decode_mma.cuh"
 
 template <int GQA, class ML>
-int launch(const DecodeParams& p, int units, cudaStream_t stream) {
+int launch(const DecodeParams& p, int, cudaStream_t stream) {
     const size_t smem = mma::smem_bytes<GQA, ML>(p.ck);
     auto kern = mma::decode_mma_kernel<GQA, ML>;
-    if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 static_cast<int>(smem)),
-                            "cudaFuncSetAttribute(decode_mma packed)"))
-        return rc;
-    kern<<<dim3(p.splits, units), mma::kThreadsM, smem, stream>>>(p);
+    // allowed once per kernel instance and device (bit mask over device ordinals), for the largest centroid table
+    static unsigned long long done = 0;
+    int dev = 0;
+    if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+    if (dev < 0 || dev >= 64 || !(done >> dev & 1ull)) {
+        if (int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     static_cast<int>(mma::smem_bytes<GQA, ML>(kMaxClusters))),
+                                "cudaFuncSetAttribute(decode_mma packed)"))
+            return rc;
+        if (dev >= 0 && dev < 64) done |= 1ull << dev;
+    }
+    kern<<<p.grid, mma::kThreadsM, smem, stream>>>(p);
     return check_cuda(cudaGetLastError(), "decode_mma (packed layout) launch");
 }
 
