@@ -11,19 +11,32 @@ stand-in for model activations, queries and appended tokens ~ N(0,1).
 
 One *step* is one decode step of that layer for the whole batch: append the new
 token's K/V to the dense window (every 64th step the oldest 64 tokens are
-clustered incrementally and compressed) and run the fused split-K attention
-over compressed segment + window.  ``value`` counts tokens (= sequences x steps)
+clustered incrementally and compressed; the window is positioned so that the
+fourth timed step is such a step) and run the fused split-K attention over
+compressed segment + window.  ``value`` counts tokens (= sequences x steps)
 per second with all inputs resident in HBM; ``e2e`` is the same loop driven
 from pinned host buffers (query / key / value of the step copied to the device,
 the attention output copied back, every step, inside the timed region).
 
+Next to the headline line the default run adds, on one GPU: ``sweep`` (batch
+1/4/8/16/32: attention kernel and prefill clustering + compression timed
+separately) and ``model`` (random-weight Llama-3.1-8B-shaped model, 8192-token
+prompt, batch 1 and 32, greedy decode with the compressed and with a dense FP16
+cache: the tok/s half of the metric).
+
 With ``torchrun`` (N > 1) every rank runs its own batch of 32 sequences -- the
 (sequence, KV head) units are independent, so there is no collective on the
-data path -- and the job value is N x 32 x K / max-over-ranks time.
+data path -- and the job value is N x 32 x K / max-over-ranks time (weak
+scaling).  Two more keys are added there: ``strong`` -- attention only, context
+65536, a fixed total of 64 sequences x 8 KV heads = 512 units partitioned
+contiguously over the ranks (``reskv_b200.sharding``), no collective -- and
+``model_tp`` -- the model tensor-parallel over all ranks (NCCL all-reduce after
+the output and down projections), context 32768, batch 32, with the time spent
+in the all-reduces measured separately.
 
 ``--impl reference`` times the CPU restatement of the reference's own Python
 path (oracle/: reconstruct + RoPE + FP32 attention, reference.py:12-91) on the
-host cores, on a bounded sample of the same workload.
+host cores: K steps, each a bounded sample (one sequence) of the same workload.
 """
 
 from __future__ import annotations
@@ -46,10 +59,9 @@ CLUSTERS, MAX_CLUSTERS, ITERS, RECENT, GROUP = 32, 64, 10, 32, 64
 METRIC = "Llama-3.1-8B decode tok/s @8K ctx b1-32; fused attn HBM GB/s vs peak"
 UNIT = "tok/s (one decoder attention layer: cache update + fused compressed attention)"
 
-# DRAM bytes per launch of the dominant kernel from the committed ncu capture
-# (profiles/), keyed by workload name; None until a capture exists.
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernel, from an ncu
+# capture of this workload, keyed by workload name; None for workloads that were not captured.
 NCU_TRAFFIC_BYTES = {
-    # profiles/decode_bitmap_mma_b32_ctx8192_s075.md: dram__bytes_read.sum + dram__bytes_write.sum of one launch
     "llama31-8b-layer attn decode ctx8192 b32 s0.75 fp16 unstructured": 339.6e6 + 8.0e6,
 }
 
@@ -57,7 +69,7 @@ NCU_TRAFFIC_BYTES = {
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=512)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=32)
@@ -65,18 +77,24 @@ def parse():
     ap.add_argument("--sparsity", type=float, default=0.75)
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--model-batches", default="",
-                    help="comma list: also run the random-weight Llama-3.1-8B-shaped model end to end (prefill of "
-                         "--context tokens, greedy decode) with the compressed and with a dense FP16 cache "
-                         "(extra key 'model')")
-    ap.add_argument("--model-new-tokens", type=int, default=128)
-    ap.add_argument("--model-tp", action="store_true",
-                    help="under torchrun: run the --model-batches model tensor-parallel over all ranks (NCCL "
-                         "all-reduce after the output and down projections) instead of skipping it")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the batch sweep (extra key 'sweep')")
+    ap.add_argument("--no-model", action="store_true", help="skip the end-to-end model runs (extra key 'model')")
+    ap.add_argument("--no-multi", action="store_true",
+                    help="under torchrun: skip the strong-scaling attention run and the tensor-parallel model")
+    ap.add_argument("--model-batches", default="1,32",
+                    help="comma list of batch sizes of the random-weight Llama-3.1-8B-shaped model run (prefill of "
+                         "--context tokens, greedy decode, compressed and dense FP16 cache)")
+    ap.add_argument("--model-new-tokens", type=int, default=64)
+    ap.add_argument("--strong-context", type=int, default=65536)
+    ap.add_argument("--strong-batch", type=int, default=64)
+    ap.add_argument("--tp-context", type=int, default=32768)
+    ap.add_argument("--tp-batch", type=int, default=32)
+    ap.add_argument("--tp-new-tokens", type=int, default=128)
+    ap.add_argument("--only", default="", choices=["", "encode", "kmeans"],
+                    help="run just one stage a few times and print its CUDA-event times (small command lines for "
+                         "profiler captures): 'encode' = the residual packers, 'kmeans' = prefill clustering")
     ap.add_argument("--plans", action="store_true",
                     help="also time the attention kernel of every residual layout at --batch / --context (extra key 'plans')")
-    ap.add_argument("--sweep", action="store_true",
-                    help="also time attention and a prefill compression at batch 1/4/8/16/32 (extra key 'sweep')")
     return ap.parse_args()
 
 
@@ -92,57 +110,19 @@ def algorithmic_bytes(batch, t_comp, t_dense, nnz, ck, cv):
     return batch * H_KV * (t_comp * per_token + (ck + cv) * 256 + t_dense * 512) + batch * H_Q * DIM * 2 * 2
 
 
-# ---- CPU arm (oracle) ----------------------------------------------------------------
-def cpu_attention_sample(a, budget_s):
-    """Oracle attention (+ amortised group compression) for ONE sequence of the
-    workload on the host cores; returns (tokens per second, description)."""
-    import numpy as np
-
-    from oracle import attention as oatt
-    from oracle import encode as oenc
-    from oracle import kmeans as okm
-
-    rng = np.random.default_rng(0)
+def config_dict(a):
+    """The workload description both arms print."""
     t_c = (a.context - RECENT) // GROUP * GROUP
     nnz = int(128 * (1 - a.sparsity))
-
-    def mix(t):
-        cen = rng.standard_normal((1, H_KV, 32, 128), dtype=np.float32)
-        which = rng.integers(0, 32, (1, H_KV, t))
-        x = np.take_along_axis(cen, np.broadcast_to(which[..., None], (1, H_KV, t, 128)), axis=2)
-        x = (x + 0.3 * rng.standard_normal((1, H_KV, t, 128), dtype=np.float32))
-        return (x * np.exp(rng.standard_normal((1, H_KV, 1, 128), dtype=np.float32))).astype(np.float16)
-
-    k, v = mix(t_c), mix(t_c)
-    cen = (rng.standard_normal((1, H_KV, 32, 128)) * 0.5).astype(np.float16)
-    ids = rng.integers(0, 32, (1, H_KV, t_c)).astype(np.int32)
-    caches = []
-    for x in (k, v):
-        p, m = oenc.encode_unstructured_fp16(x, cen, ids, nnz)
-        caches.append(dict(layout="unstructured", bits=16, centroids=cen, ids=ids, payload=p, metadata=m, scale=None))
-    q = rng.standard_normal((1, H_Q, 1, 128)).astype(np.float16)
-    freq = oatt.theta_frequencies(THETA)
-    qr = oatt.rotate(q, np.array([a.context]), freq).astype(np.float16)
-    kr, vr = mix(RECENT + GROUP // 2), mix(RECENT + GROUP // 2)
-    # one decode-time group compression, amortised over GROUP steps
-    t0 = time.perf_counter()
-    grp = mix(GROUP)
-    c2, i2, _ = okm.incremental(grp, cen, MAX_CLUSTERS)
-    oenc.encode_unstructured_fp16(grp, c2, i2, nnz)
-    oenc.encode_unstructured_fp16(grp, c2, i2, nnz)
-    compress_s = (time.perf_counter() - t0) / GROUP
-    steps, elapsed = 0, 0.0
-    while elapsed < budget_s and steps < 64:
-        t0 = time.perf_counter()
-        oatt.attention_compressed(q, caches[0], caches[1], position=a.context, inv_freq=freq, recent=(qr, kr, vr))
-        elapsed += time.perf_counter() - t0
-        steps += 1
-    per_step = elapsed / steps + compress_s
-    sample = (f"1 of {a.batch} sequences, {steps} decode steps of the workload (numpy oracle: decode bitmap, "
-              f"RoPE, FP32 attention) + 1/{GROUP} of one group compression")
-    return 1.0 / per_step, sample
+    mb = algorithmic_bytes(a.batch, t_c, a.context - t_c, nnz, CLUSTERS, CLUSTERS) / 1e6
+    return {"workload": workload_name(a), "batch_per_gpu": a.batch, "context": a.context, "sparsity": a.sparsity,
+            "q_heads": H_Q, "kv_heads": H_KV, "head_dim": DIM, "clusters": CLUSTERS, "kmeans_iterations": ITERS,
+            "recent": RECENT, "group": GROUP,
+            "l2": "inputs larger than L2 (compressed cache %.0f MB per step)" % mb,
+            "sharding": "independent (sequence x KV-head) units per GPU, no collective"}
 
 
+# ---- CPU arm (oracle) ----------------------------------------------------------------
 def cpu_cores():
     try:
         return len(os.sched_getaffinity(0))
@@ -150,18 +130,114 @@ def cpu_cores():
         return os.cpu_count() or 1
 
 
+class CpuSequence:
+    """ONE sequence of the workload for the numpy oracle (reconstruct every layout, RoPE, FP32 attention).
+    The 8 KV heads are independent: they run on a thread pool (numpy releases the GIL in its kernels)."""
+
+    def __init__(self, a):
+        import numpy as np
+
+        from oracle import attention as oatt
+        from oracle import encode as oenc
+
+        self.a, self.np, self.oatt = a, np, oatt
+        rng = self.rng = np.random.default_rng(0)
+        t_c = (a.context - RECENT) // GROUP * GROUP
+        self.nnz = nnz = int(128 * (1 - a.sparsity))
+        k, v = self.mix(t_c), self.mix(t_c)
+        self.cen = cen = (rng.standard_normal((1, H_KV, 32, 128)) * 0.5).astype(np.float16)
+        ids = rng.integers(0, 32, (1, H_KV, t_c)).astype(np.int32)
+        self.heads = []
+        for h in range(H_KV):
+            sl = slice(h, h + 1)
+            pair = []
+            for x in (k, v):
+                p, m = oenc.encode_unstructured_fp16(x[:, sl], cen[:, sl], ids[:, sl], nnz)
+                pair.append(dict(layout="unstructured", bits=16, centroids=cen[:, sl], ids=ids[:, sl], payload=p,
+                                 metadata=m, scale=None))
+            self.heads.append(pair)
+        self.q = rng.standard_normal((1, H_Q, 1, 128)).astype(np.float16)
+        self.freq = oatt.theta_frequencies(THETA)
+        self.qr = oatt.rotate(self.q, np.array([a.context]), self.freq).astype(np.float16)
+        self.kr, self.vr = self.mix(RECENT + GROUP // 2), self.mix(RECENT + GROUP // 2)
+        self.threads = max(1, min(H_KV, cpu_cores()))
+        from concurrent.futures import ThreadPoolExecutor
+
+        self.pool = ThreadPoolExecutor(self.threads)
+
+    def mix(self, t):
+        np, rng = self.np, self.rng
+        cen = rng.standard_normal((1, H_KV, 32, 128), dtype=np.float32)
+        which = rng.integers(0, 32, (1, H_KV, t))
+        x = np.take_along_axis(cen, np.broadcast_to(which[..., None], (1, H_KV, t, 128)), axis=2)
+        x = (x + 0.3 * rng.standard_normal((1, H_KV, t, 128), dtype=np.float32))
+        return (x * np.exp(rng.standard_normal((1, H_KV, 1, 128), dtype=np.float32))).astype(np.float16)
+
+    def group_compression_seconds(self):
+        """One decode-time group compression (incremental clustering + two packers)."""
+        from oracle import encode as oenc
+        from oracle import kmeans as okm
+
+        t0 = time.perf_counter()
+        grp = self.mix(GROUP)
+        c2, i2, _ = okm.incremental(grp, self.cen, MAX_CLUSTERS)
+        oenc.encode_unstructured_fp16(grp, c2, i2, self.nnz)
+        oenc.encode_unstructured_fp16(grp, c2, i2, self.nnz)
+        return time.perf_counter() - t0
+
+    def attention_step(self):
+        g = H_Q // H_KV
+
+        def one(h):
+            kc, vc = self.heads[h]
+            hq = slice(h * g, (h + 1) * g)
+            return self.oatt.attention_compressed(self.q[:, hq], kc, vc, position=self.a.context, inv_freq=self.freq,
+                                                  recent=(self.qr[:, hq], self.kr[:, h:h + 1], self.vr[:, h:h + 1]))
+
+        t0 = time.perf_counter()
+        list(self.pool.map(one, range(H_KV)))
+        return time.perf_counter() - t0
+
+
+def cpu_attention_sample(a, budget_s):
+    """Bounded CPU baseline for the GPU arm's line: (tokens per second, cores used, description)."""
+    seq = CpuSequence(a)
+    compress_s = seq.group_compression_seconds() / GROUP
+    steps, elapsed = 0, 0.0
+    while elapsed < budget_s and steps < 64:
+        elapsed += seq.attention_step()
+        steps += 1
+    per_step = elapsed / steps + compress_s
+    sample = (f"1 of {a.batch} sequences, {steps} decode steps of the workload (numpy oracle: decode bitmap, "
+              f"RoPE, FP32 attention; {seq.threads} threads over the KV heads) + 1/{GROUP} of one group compression")
+    return 1.0 / per_step, seq.threads, sample
+
+
 def run_reference(a):
+    """K timed steps (after W warm-up steps); each step is a bounded sample of the workload: the decode step of
+    ONE of the batch's sequences (attention over its 8 KV heads + 1/64 of a group compression)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps_budget = max(4.0, min(60.0, 0.2 * a.steps))
-    value, sample = cpu_attention_sample(a, steps_budget)
+    seq = CpuSequence(a)
+    compress_s = seq.group_compression_seconds() / GROUP
+    for _ in range(a.warmup):
+        seq.attention_step()
+    t0 = time.perf_counter()
+    for _ in range(a.steps):
+        seq.attention_step()
+    per_step = (time.perf_counter() - t0) / a.steps + compress_s
+    value = 1.0 / per_step  # tokens per second: one sequence advances one token per sampled step
+    sample = (f"every step = 1 of the {a.batch} sequences of a batch step (numpy oracle: decode bitmap, RoPE, FP32 "
+              f"attention; {seq.threads} threads over the KV heads) + 1/{GROUP} of one group compression; "
+              f"ms_per_step is the measured time of that sampled step, a whole batch step takes {a.batch} x as long")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps,
-        "warmup": a.warmup, "ms_per_step": 1000.0 / value, "higher_is_better": True, "scaling": "weak",
+        "warmup": a.warmup, "ms_per_step": 1000.0 * per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(a), "note": "CPU restatement of the reference path (oracle/), not the GPU"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cpu_cores(), "kind": "port", "sample": sample},
+        "config": config_dict(a),
+        "note": "CPU restatement of the reference path (oracle/) on the host cores, not the GPU",
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": seq.threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -349,10 +425,12 @@ def run_plans(a, dev, inv_freq):
     return out
 
 
-def run_model(a, dev, group=None):
+def run_model(a, dev, group, context, batches, n_new):
     """Prefill + greedy decode of the Llama-3.1-8B-shaped model (random FP16 weights, uniform random
     prompt ids as in the reference's benchmarks/timing.py:60-66) with both cache kinds.  With a process
-    group the model is tensor-parallel over it and times are the maximum over ranks."""
+    group the model is tensor-parallel over it, times are the maximum over ranks, and the time of the
+    64 all-reduces of a decode step (after the output and down projections of 32 layers) is measured on
+    its own with the same message size."""
     import torch
     import torch.distributed as dist
 
@@ -372,9 +450,24 @@ def run_model(a, dev, group=None):
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
         return t.item()
 
-    n_new = a.model_new_tokens
-    for batch in [int(x) for x in a.model_batches.split(",")]:
-        ids = torch.randint(128, shape.vocab, (batch, a.context), generator=torch.Generator().manual_seed(42)).to(dev)
+    def allreduce_ms_per_token(batch):
+        if group is None:
+            return None
+        x = torch.zeros(batch, shape.hidden, dtype=torch.float16, device=dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(2 * shape.layers):
+            dist.all_reduce(x, group=group)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(8 * 2 * shape.layers):
+            dist.all_reduce(x, group=group)
+        e1.record()
+        torch.cuda.synchronize()
+        return slowest(e0.elapsed_time(e1) / 8)
+
+    for batch in batches:
+        ids = torch.randint(128, shape.vocab, (batch, context), generator=torch.Generator().manual_seed(42)).to(dev)
+        comm_ms = allreduce_ms_per_token(batch)
         for kind in ("reskv", "dense"):
             model.cache_kind = kind
             model.caches = None
@@ -401,13 +494,118 @@ def run_model(a, dev, group=None):
                 tok = step(tok).argmax(-1)
             torch.cuda.synchronize()
             decode_ms = slowest((time.perf_counter() - t0) * 1e3)
-            out.append({"batch": batch, "cache": kind, "decode_loop": mode, "context": a.context, "new_tokens": n_new,
-                        "tensor_parallel": model.tp,
-                        "prefill_ms": prefill_ms, "tpot_ms": decode_ms / n_new,
-                        "decode_tok_per_s": batch * n_new / (decode_ms * 1e-3),
-                        "cache_bytes": model.cache_bytes()})
+            run = {"batch": batch, "cache": kind, "decode_loop": mode, "context": context, "new_tokens": n_new,
+                   "tensor_parallel": model.tp, "prefill_ms": prefill_ms, "tpot_ms": decode_ms / n_new,
+                   "decode_tok_per_s": batch * n_new / (decode_ms * 1e-3), "cache_bytes": model.cache_bytes()}
+            if comm_ms is not None:
+                run["allreduce_ms_per_token_standalone"] = comm_ms
+            out.append(run)
         model.caches = None
+    del model
+    torch.cuda.empty_cache()
     return out
+
+
+def run_only(a):
+    """One stage on its own, at --batch / --context: a short, fixed sequence of launches for a profiler."""
+    import torch
+
+    from reskv_b200 import ResKVKernelConfig
+    from reskv_b200.compression import _encode, cluster
+    from reskv_b200.synthetic import gaussian, mixture
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    n = (a.context - RECENT) // GROUP * GROUP
+    x = mixture(a.batch, H_KV, n, seed=3, device=dev)
+    res = {"only": a.only, "batch": a.batch, "tokens": n}
+
+    def timed(fn, reps=3):
+        fn()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        ev[0].record()
+        for _ in range(reps):
+            fn()
+        ev[1].record()
+        torch.cuda.synchronize()
+        return ev[0].elapsed_time(ev[1]) / reps
+
+    if a.only == "encode":
+        cen = gaussian(a.batch, H_KV, CLUSTERS, DIM, seed=4, device=dev)
+        ids = torch.randint(CLUSTERS, (a.batch, H_KV, n), device=dev, dtype=torch.int32)
+        for name, kw in (("fp16_bitmap_nnz32", dict(sparsity=0.75, bits=16)), ("fp16_bitmap_nnz64", dict(sparsity=0.5, bits=16)),
+                         ("int4_nnz64", dict(sparsity=0.5, bits=4)), ("fp16_tiled", dict(sparsity=0.5, bits=16, layout="tiled"))):
+            plan = ResKVKernelConfig(layout=kw.pop("layout", "unstructured"), **kw).resolve(a.batch)
+            res[name + "_ms"] = timed(lambda: _encode(x, cen, ids, plan))
+        res["input_bytes"] = x.numel() * 2
+    else:
+        res["kmeans_k_ms"] = timed(lambda: cluster(x, CLUSTERS, ITERS), reps=2)
+        res["kmeans_v_ms"] = timed(lambda: cluster(x, CLUSTERS, ITERS, value=True), reps=2)
+    print(json.dumps(res))
+
+
+def run_strong(a, dev, rank, world, inv_freq):
+    """Attention only, fixed total work: ``--strong-batch`` sequences x 8 KV heads at ``--strong-context``,
+    the (sequence, KV head) units partitioned contiguously over the ranks, no collective on the data path.
+    Returns the slowest rank's time per attention call."""
+    import torch
+    import torch.distributed as dist
+
+    import reskv_b200._extension as ext
+    from reskv_b200 import ResKVKernelConfig
+    from reskv_b200.compression import _encode, cluster
+    from reskv_b200.sharding import unit_range
+    from reskv_b200.synthetic import gaussian, mixture
+
+    ctx, batch = a.strong_context, a.strong_batch
+    n = (ctx - RECENT) // GROUP * GROUP
+    lo, hi = unit_range(batch * H_KV, world, rank)
+    units = hi - lo
+    cfg = ResKVKernelConfig(sparsity=a.sparsity, bits=16, layout="unstructured", num_clusters=CLUSTERS,
+                            max_clusters=MAX_CLUSTERS, group_size=GROUP, recent_size=RECENT, kmeans_iterations=ITERS)
+    plan = cfg.resolve(batch)
+    nnz = plan.nnz
+    # this rank's units as a [units, 1, T, ...] cache (one KV head per "sequence": a unit is self-contained)
+    parts = {k: [] for k in ("kc", "ki", "kp", "km", "vc", "vi", "vp", "vm")}
+    for u0 in range(0, units, 32):  # 32 units at a time bound the FP16 staging memory
+        m = min(32, units - u0)
+        for side in ("k", "v"):
+            x = mixture(m, 1, n, seed=5000 + 2 * (lo + u0) + (side == "v"), device=dev)
+            cen, ids = cluster(x, CLUSTERS, 3, value=side == "v")  # 3 iterations: set-up, not what is timed
+            ct = _encode(x, cen, ids, plan)
+            for key, t in (("c", ct.centroids), ("i", ct.cluster_ids), ("p", ct.payload), ("m", ct.metadata)):
+                parts[side + key].append(t.reshape(m, *t.shape[2:]))
+            del x
+    kc, ki, kp, km, vc, vi, vp, vm = (torch.cat(parts[k]) for k in ("kc", "ki", "kp", "km", "vc", "vi", "vp", "vm"))
+    gqa = H_Q // H_KV
+    q = gaussian(units * gqa, DIM, seed=77 + rank, device=dev)
+    qr = rope(q, ctx, inv_freq)
+    kr = gaussian(units, 1, ctx - n, DIM, seed=78 + rank, device=dev)
+    vr = gaussian(units, 1, ctx - n, DIM, seed=79 + rank, device=dev)
+    ops = ext.load_extension("cluster_mass", plan, dev.index)
+    call = lambda: ops.decode_fp16(q, kc, ki, kp, km, vc, vi, vp, vm, 1, gqa, 0, ctx, THETA, DIM ** -0.5, False, 0,  # noqa: E731
+                                   inv_freq, (qr, kr, vr))
+    for _ in range(3):
+        call()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 8
+    dist.barrier()
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(reps):
+        call()
+    stop.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = torch.tensor([start.elapsed_time(stop) / reps], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item()
+    total_bytes = algorithmic_bytes(batch, n, ctx - n, nnz, CLUSTERS, CLUSTERS)
+    return {"workload": f"attention only, context {ctx}, {batch} sequences x {H_KV} KV heads = {batch * H_KV} units "
+                        f"partitioned contiguously over the ranks, sparsity {a.sparsity}, no collective",
+            "scaling": "strong", "units_total": batch * H_KV, "units_this_rank": units, "ms_per_call_max_over_ranks": ms,
+            "tok_per_s": batch / (ms * 1e-3), "GBps_all_gpus": total_bytes / ms / 1e6,
+            "algorithmic_bytes_all_gpus": total_bytes}
 
 
 def run_gpu(a):
@@ -452,19 +650,22 @@ def run_gpu(a):
     prefill_compress_ms = (time.perf_counter() - t0) * 1e3
     del k_raw, v_all, k_rot, tail
 
-    total = W + 2 * K
+    # Untimed tokens that position the window: a group compression happens when the window is full, i.e. every
+    # GROUP appends; `lead` appends make the fourth timed step of the device-resident loop such a step.
+    lead = ((-(W + 4)) % GROUP - (layer.live - RECENT)) % GROUP
+    total = lead + W + 2 * K
     q_all = gaussian(total, B, H_Q, 1, DIM, seed=seed + 2, device=dev)
     k_new = gaussian(total, B, H_KV, 1, DIM, seed=seed + 3, device=dev)
     v_new = gaussian(total, B, H_KV, 1, DIM, seed=seed + 4, device=dev)
-    host_q, host_k, host_v = (x[W + K:].cpu().pin_memory() for x in (q_all, k_new, v_new))
+    host_q, host_k, host_v = (x[lead + W + K:].cpu().pin_memory() for x in (q_all, k_new, v_new))
     host_out = torch.empty((B, H_Q, 1, DIM), dtype=torch.float16).pin_memory()
     # RoPE of the new token's q / k is the model's job (torch ops before the cache
     # update): for the device-resident loop it is applied ahead of the timed region
-    q_rot = torch.stack([rope(q_all[i], a.context + i, inv_freq) for i in range(W + K)])
-    k_rot = torch.stack([rope(k_new[i], a.context + i, inv_freq) for i in range(W + K)])
+    q_rot = torch.stack([rope(q_all[i], a.context + i, inv_freq) for i in range(lead + W + K)])
+    k_rot = torch.stack([rope(k_new[i], a.context + i, inv_freq) for i in range(lead + W + K)])
 
     state = {"pos": a.context, "bytes": 0.0, "calls": 0}
-    att_events, upd_events, kern_events = [], [], []
+    att_events, upd_events, kern_events, compressed_at = [], [], [], []
     lib = ext.library()
 
     def step(q, k, v, timed, q_r=None, k_r=None):
@@ -477,6 +678,7 @@ def run_gpu(a):
                 ev.record()  # creates the native event handle
             lib.reskv_decode_set_timing_events(e[3].cuda_event, e[4].cuda_event)
             e[0].record()
+        before = layer.compressed.seq_len
         keys, values = layer.update(k_r, v, {"raw_keys": k})
         if timed:
             e[1].record()
@@ -487,6 +689,7 @@ def run_gpu(a):
             upd_events.append((e[0], e[1]))
             att_events.append((e[1], e[2]))
             kern_events.append((e[3], e[4]))
+            compressed_at.append(layer.compressed.seq_len != before)
             ck, cv = layer.compressed.key.centroids.shape[2], layer.compressed.value.centroids.shape[2]
             state["bytes"] += algorithmic_bytes(B, layer.compressed.seq_len, keys.shape[2], nnz, ck, cv)
             state["calls"] += 1
@@ -498,7 +701,7 @@ def run_gpu(a):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(W):
+    for i in range(lead + W):
         step(q_all[i], k_new[i], v_new[i], False, q_rot[i], k_rot[i])
 
     # ---- timed region 1: inputs resident in HBM ---------------------------------------
@@ -507,16 +710,17 @@ def run_gpu(a):
     barrier()
     clocks.mark()
     start.record()
-    for i in range(W, W + K):
+    for i in range(lead + W, lead + W + K):
         step(q_all[i], k_new[i], v_new[i], True, q_rot[i], k_rot[i])
     stop.record()
     barrier()
-    clocks.mark()
     launches = ext.launch_count - launches0
     ms_total = start.elapsed_time(stop)
     att_ms = sum(s.elapsed_time(e) for s, e in att_events)
-    upd_ms = sum(s.elapsed_time(e) for s, e in upd_events)
+    upd = [s.elapsed_time(e) for s, e in upd_events]
     kern_ms = sum(s.elapsed_time(e) for s, e in kern_events)  # partial kernel only, no launch gaps
+    upd_compress = [t for t, c in zip(upd, compressed_at) if c]
+    upd_append = [t for t, c in zip(upd, compressed_at) if not c]
 
     # ---- timed region 2: host buffers in, host result out, every step -------------------
     barrier()
@@ -529,22 +733,25 @@ def run_gpu(a):
         host_out.copy_(out, non_blocking=True)
     stop.record()
     barrier()
+    clocks.mark()
     ms_e2e = start.elapsed_time(stop)
 
     times = torch.tensor([ms_total, ms_e2e, att_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms_total, ms_e2e, att_ms_max = times.tolist()
+    del layer, q_all, k_new, v_new, q_rot, k_rot
+    torch.cuda.empty_cache()
 
-    sweep = None
-    if a.sweep and world == 1:
-        sweep = run_sweep(a, dev, cfg, inv_freq, nnz)
+    sweep = run_sweep(a, dev, cfg, inv_freq, nnz) if world == 1 and not a.no_sweep else None
     plans = run_plans(a, dev, inv_freq) if a.plans and world == 1 else None
-    model_runs = None
-    if a.model_batches and (world == 1 or a.model_tp):
-        del layer, q_all, k_new, v_new, q_rot, k_rot
+    model_runs = strong = model_tp = None
+    if world == 1 and not a.no_model:
+        model_runs = run_model(a, dev, None, a.context, [int(x) for x in a.model_batches.split(",")], a.model_new_tokens)
+    if world > 1 and not a.no_multi:
+        strong = run_strong(a, dev, rank, world, inv_freq)
         torch.cuda.empty_cache()
-        model_runs = run_model(a, dev, dist.group.WORLD if world > 1 else None)
+        model_tp = run_model(a, dev, dist.group.WORLD, a.tp_context, [a.tp_batch], a.tp_new_tokens)
     clock_summary = clocks.summary()
     if rank == 0:
         peaks = {}
@@ -559,12 +766,7 @@ def run_gpu(a):
             "metric": METRIC, "value": world * B * K / (ms_total * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": name, "batch_per_gpu": B, "context": a.context, "sparsity": a.sparsity,
-                       "q_heads": H_Q, "kv_heads": H_KV, "head_dim": DIM, "clusters": CLUSTERS,
-                       "kmeans_iterations": ITERS, "recent": RECENT, "group": GROUP,
-                       "l2": "inputs larger than L2 (compressed cache %.0f MB per step)" % (
-                           state["bytes"] / state["calls"] / 1e6),
-                       "sharding": "independent (sequence x KV-head) units per GPU, no collective"},
+            "config": config_dict(a),
             "clocks": clock_summary,
             "e2e": {"value": world * B * K / (ms_e2e * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": int(host_q[0].nbytes + host_k[0].nbytes + host_v[0].nbytes),
@@ -578,8 +780,12 @@ def run_gpu(a):
                          "ms_per_launch": kern_ms / state["calls"],
                          "ms_per_attention_call_incl_merge_and_launch_gaps": att_ms / state["calls"],
                          "traffic": NCU_TRAFFIC_BYTES.get(name)},
-            "phases_ms_per_step": {"attention": att_ms / K, "cache_update_incl_group_compression": upd_ms / K,
-                                   "prefill_cluster_and_compress_ms": prefill_compress_ms},
+            "phases_ms_per_step": {
+                "attention": att_ms / K,
+                "cache_update_append": statistics.median(upd_append) if upd_append else None,
+                "group_compression_steps_in_timed_region": len(upd_compress),
+                "cache_update_with_group_compression": statistics.mean(upd_compress) if upd_compress else None,
+                "prefill_cluster_and_compress_ms": prefill_compress_ms},
         }
         if sweep is not None:
             line["sweep"] = sweep
@@ -587,10 +793,13 @@ def run_gpu(a):
             line["plans"] = plans
         if model_runs is not None:
             line["model"] = model_runs
+        if strong is not None:
+            line["strong"] = strong
+        if model_tp is not None:
+            line["model_tp"] = model_tp
         if world == 1 and not a.no_cpu_baseline:
-            value, sample = cpu_attention_sample(a, a.cpu_seconds)
-            line["cpu_baseline"] = {"value": value, "unit": UNIT, "cores": cpu_cores(), "kind": "port",
-                                    "sample": sample}
+            value, threads, sample = cpu_attention_sample(a, a.cpu_seconds)
+            line["cpu_baseline"] = {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -600,5 +809,7 @@ if __name__ == "__main__":
     args = parse()
     if args.impl == "reference":
         run_reference(args)
+    elif args.only:
+        run_only(args)
     else:
         run_gpu(args)

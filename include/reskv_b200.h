@@ -153,6 +153,12 @@ int reskv_window_append(void* window_k, void* window_raw, void* window_v, const 
                         const void* v, int batch, int kv_heads, int window_capacity, const int32_t* step_state,
                         void* stream);
 
+/* The same three-row copy for eager callers that track the window length on the host:
+ * slot (0 <= slot < window_capacity) is given by value.  Replaces the three slice copies
+ * of the reference's cache update (reskv/cache.py:55-60) by one launch. */
+int reskv_window_write(void* window_k, void* window_raw, void* window_v, const void* k_rot, const void* k_raw,
+                       const void* v, int batch, int kv_heads, int window_capacity, int slot, void* stream);
+
 int reskv_decode_step(int layout, int bits, int nnz, const void* q, const void* k_centroids, const void* k_ids,
                       const void* k_payload, const void* k_meta, const void* k_scale, const void* v_centroids,
                       const void* v_ids, const void* v_payload, const void* v_meta, const void* v_scale, int batch,
@@ -198,16 +204,21 @@ int reskv_silu_mul(const void* gate_up, void* out, int rows, int ffn, void* stre
  * critical loop where an allocation would serialise the device, or a C / C++ /
  * cgo host that links the library without torch's caching allocator.
  *
- *   - Limit: batch * q_heads * splits * 776 + 256 bytes must fit the array
- *     (8 MiB: e.g. 1024 query heads x 10 splits).  Larger problems are refused
- *     with RESKV_ERR_LIMIT and a message; pass a smaller `splits` or use the
- *     workspace variant.
+ *   - Limit: batch * q_heads * slots * 776 + 256 bytes must fit the array (8 MiB:
+ *     e.g. 1024 query heads x 10 slots), where slots = `splits` if given, else the
+ *     library's own partial count (at most ceil(2 * SMs / (batch * kv_heads)) + 1).
+ *     Larger problems are refused with RESKV_ERR_LIMIT and a message; pass a
+ *     smaller `splits` or use the workspace variant.
  *   - Every GPU on which the library is loaded holds the array until exit.
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress) and keeps it; make that first call outside any
- *     stream capture.
+ *     stream capture.  The kept address is written without a lock: two host
+ *     threads making their first call on one device at the same time both look
+ *     it up and store the same value.
  *   - All calls on a device share the array and it keeps the last call's contents;
- *     the call clears the 256-byte status header itself.  Two calls whose kernels
+ *     the call clears the 256-byte status header itself, after its arguments
+ *     passed validation (a refused call writes nothing); read the status word
+ *     with reskv_decode_noalloc_status.  Two calls whose kernels
  *     can overlap on the GPU (different streams, or graphs replayed concurrently)
  *     race on it: serialise them. */
 #define RESKV_NOALLOC_SCRATCH_BYTES (8 * 1024 * 1024)
@@ -221,19 +232,17 @@ int reskv_decode_bitmap_fp16_noalloc(const void* q, const void* k_centroids, con
                                      const void* recent_k, const void* recent_v, int recent_tokens, void* out,
                                      float* out_m, float* out_l, void* stream);
 
-/* Selects the partial kernel reskv_decode_bitmap_fp16 launches: 0 = tensor-core
- * tiles of 16 tokens (default), 1 = the simpler warp-per-token kernel (kept for
- * cross-checking).  Process-wide; no counterpart in the reference. */
-int reskv_decode_set_variant(int variant);
-
-/* Profiling aid: cudaEvent_t handles that every following reskv_decode_bitmap_fp16
- * call records on its stream immediately before and after the partial kernel, so
- * that the kernel's own duration can be read without launch gaps.  NULL, NULL
- * switches it off.  Process-wide; no counterpart in the reference. */
-int reskv_decode_set_timing_events(void* start, void* stop);
-
-/* The split count reskv_decode_bitmap_fp16 uses for splits == 0. */
+/* The split count the fixed-split schedule would use for splits == 0 (what the warp-per-token kernel
+ * runs with; the tensor-core kernel balances all tiles over two CTAs per SM instead, see
+ * reskv_decode_bitmap_fp16_workspace_bytes for its scratch need). */
 int reskv_decode_auto_splits(int batch, int kv_heads, int tokens);
+
+/* Reads the device status word (RESKV_STATUS_* bits) that the kernels of reskv_decode_bitmap_fp16_noalloc
+ * OR into the header of the built-in scratch: one 4-byte cudaMemcpyAsync to status_out (host memory;
+ * pinned memory keeps the copy asynchronous) on `stream`, i.e. ordered behind the decode calls already
+ * enqueued there.  Read status_out after synchronising the stream, and before the next noalloc call on
+ * the device: that call clears the word.  No counterpart in the reference. */
+int reskv_decode_noalloc_status(uint32_t* status_out, void* stream);
 
 /* ---- recent-window merge ------------------------------------------------------
  * Replaces cluster_mass.merge_recent (cluster_mass.cu:1461-1508): joint softmax
@@ -309,6 +318,20 @@ int reskv_kmeans(const void* x, int batch, int kv_heads, int tokens, int64_t x_t
 int reskv_kmeans_incremental(const void* x, int batch, int kv_heads, int tokens, int64_t x_tok_stride,
                              const void* old_centroids, int old_clusters, void* new_centroids, int new_clusters,
                              int32_t* ids, void* stream);
+
+/* ---- test and profiling hooks ---------------------------------------------------------
+ * NOT part of the surface a production host binds: both calls set process-wide state without any
+ * synchronisation (they change what every thread's next decode call does) and exist for the test suite
+ * (which runs every decode test on both partial kernels) and for bench.py (kernel time without launch
+ * gaps).  No counterpart in the reference. */
+
+/* Selects the partial kernel the decode entry points launch: 0 = tensor-core tiles of 16 tokens
+ * (default), 1 = the simpler warp-per-token kernel (kept for cross-checking). */
+int reskv_decode_set_variant(int variant);
+
+/* cudaEvent_t handles that every following decode call records on its stream immediately before and
+ * after the partial kernel.  NULL, NULL switches it off. */
+int reskv_decode_set_timing_events(void* start, void* stop);
 
 #ifdef __cplusplus
 }

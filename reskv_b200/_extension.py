@@ -55,6 +55,7 @@ SIGNATURES = {
         [_I, _I] + [_P] * 11 + [_I, _I, _I, _I, _L, _I, _I, _I, _I, _F, _P, _F, _I, _P, _P, _P, _I, _P, _Z, _P, _P, _P, _P],
     ),
     "reskv_window_append": (_I, [_P] * 6 + [_I, _I, _I, _P, _P]),
+    "reskv_window_write": (_I, [_P] * 6 + [_I, _I, _I, _I, _P]),
     "reskv_decode_step": (
         _I,
         [_I, _I, _I] + [_P] * 11 + [_I, _I, _I, _I, _L, _I, _I, _I, _F, _P, _F, _I, _P, _P, _P, _I, _P, _P, _Z, _P, _P],
@@ -64,6 +65,7 @@ SIGNATURES = {
     "reskv_rope_split": (_I, [_P, _I, _I, _I, _P, _P] + [_P] * 7 + [_I, _P]),
     "reskv_silu_mul": (_I, [_P, _P, _I, _I, _P]),
     "reskv_decode_auto_splits": (_I, [_I, _I, _I]),
+    "reskv_decode_noalloc_status": (_I, [_P, _P]),
     "reskv_decode_set_variant": (_I, [_I]),
     "reskv_decode_set_timing_events": (_I, [_P, _P]),
     "reskv_merge_recent_scores": (_I, [_P] * 5 + [_I, _I, _I, _I, _P, _P]),

@@ -41,73 +41,109 @@ class _LayerBase:
 
 
 class ResKVLayerCache(_HFLayer or _LayerBase):
-    """Cache of one attention layer (reference cache.py:10-103)."""
+    """Cache of one attention layer (reference cache.py:10-103).
+
+    Dense segment = ``sink_tokens`` attention sinks (the first tokens of the sequence, never compressed)
+    followed by the sliding window; both live in one buffer ``[B, H, sinks + recent + group, 128]`` so that
+    ``update`` can hand them to ``attention(..., recent=)`` as one tensor.  The compressed segment then
+    starts at position ``sink_tokens``: pass ``start_position=layer.start_position`` to ``attention``.
+    The reference's CUDA cache has no sinks (``sink_tokens=0``, the default, reproduces it); with sinks the
+    split follows its accuracy path (reskv/accuracy.py:160-168): ``floor((T - recent - sinks) / group) *
+    group`` prompt tokens are compressed, starting behind the sinks.
+    """
 
     is_sliding = False
 
-    def __init__(self, config: ResKVKernelConfig):
+    def __init__(self, config: ResKVKernelConfig, sink_tokens: int = 0):
         super().__init__()
+        if type(sink_tokens) is not int or sink_tokens < 0:
+            raise ValueError("sink_tokens must be a non-negative integer")
         self.config = config
+        self.sink_tokens = sink_tokens
         self.compressed = None
         self.raw_keys = None
         self.length = 0  # tokens seen
-        self.live = 0    # tokens in the dense window
+        self.live = 0    # tokens in the dense segment (sinks included)
         self.plan = None
+        self._lib = None
+
+    @property
+    def start_position(self) -> int:
+        """Position of the first compressed token (= number of sink tokens actually held)."""
+        return min(self.sink_tokens, self.length)
 
     def lazy_initialization(self, key_states, value_states=None):
+        from ._extension import bound_library
+
         b, h, _, d = key_states.shape
-        slots = self.config.recent_size + self.config.group_size
+        slots = self.sink_tokens + self.config.recent_size + self.config.group_size
         self.keys = torch.empty((b, h, slots, d), device=key_states.device, dtype=key_states.dtype)
         self.raw_keys = torch.empty_like(self.keys)
         self.values = torch.empty_like(self.keys)
         self.plan = self.config.resolve(b)
+        self._lib = bound_library(key_states.device)
         self.is_initialized = True
 
     def update(self, key_states, value_states, cache_kwargs=None, *args, **kwargs):
         """Append rotated keys / values (``cache_kwargs['raw_keys']`` = keys before
-        RoPE).  Returns the dense window ``(keys, values)``."""
+        RoPE).  Returns the dense segment ``(keys, values)``: sinks, then the window."""
         raw = (cache_kwargs or {}).get("raw_keys")
         if raw is None:
             raise ValueError("ResKV cache update requires pre-RoPE raw_keys")
         q_len = key_states.shape[2]
         if not self.is_initialized:
             self.lazy_initialization(key_states, value_states)
-        cfg = self.config
         if self.length == 0:
-            n = max(0, q_len - cfg.recent_size) // cfg.group_size * cfg.group_size
-            if n:
-                self.compressed = compress(raw[:, :, :n].contiguous(), value_states[:, :, :n].contiguous(), cfg,
-                                           plan=self.plan)
-            self.live = q_len - n
-            if self.live > self.keys.shape[2]:
-                raise ValueError("prefill leaves more dense tokens than the window holds")
-            self.keys[:, :, : self.live].copy_(key_states[:, :, n:])
-            self.raw_keys[:, :, : self.live].copy_(raw[:, :, n:])
-            self.values[:, :, : self.live].copy_(value_states[:, :, n:])
+            self._take_prompt(key_states, raw, value_states)
+        elif q_len != 1:
+            raise ValueError("ResKV continuation supports one token per step; chunked prefill is unsupported")
         else:
-            if q_len != 1:
-                raise ValueError("ResKV continuation supports one token per step; chunked prefill is unsupported")
-            at = self.live
-            self.keys[:, :, at : at + 1].copy_(key_states)
-            self.raw_keys[:, :, at : at + 1].copy_(raw)
-            self.values[:, :, at : at + 1].copy_(value_states)
-            self.live += 1
-            if self.live == self.keys.shape[2]:
-                self._compress_oldest_group()
+            self._take_token(key_states, raw, value_states)
         self.length += q_len
         return self.keys[:, :, : self.live], self.values[:, :, : self.live]
 
+    def _take_prompt(self, keys, raw, values):
+        """Split a prompt of T tokens into sinks [0, s), a compressed run [s, s + n) and the dense tail."""
+        cfg, t = self.config, keys.shape[2]
+        s = min(self.sink_tokens, t)
+        n = max(0, t - cfg.recent_size - s) // cfg.group_size * cfg.group_size
+        if n:
+            self.compressed = compress(raw[:, :, s : s + n].contiguous(), values[:, :, s : s + n].contiguous(), cfg,
+                                       plan=self.plan)
+        self.live = t - n
+        if self.live > self.keys.shape[2]:
+            raise ValueError("prefill leaves more dense tokens than the window holds")
+        for buf, src in ((self.keys, keys), (self.raw_keys, raw), (self.values, values)):
+            buf[:, :, :s].copy_(src[:, :, :s])
+            buf[:, :, s : self.live].copy_(src[:, :, s + n :])
+
+    def _take_token(self, key, raw, value):
+        """One launch writes the token's rotated key, raw key and value into slot ``live`` of the three
+        buffers; a full window then gives its oldest group to the compressed segment."""
+        from ._extension import _stream, check
+
+        b, h, cap, _ = self.keys.shape
+        if key.dtype == torch.float16 and key.is_cuda:
+            check(self._lib.reskv_window_write(self.keys.data_ptr(), self.raw_keys.data_ptr(), self.values.data_ptr(),
+                                               key.contiguous().data_ptr(), raw.contiguous().data_ptr(),
+                                               value.contiguous().data_ptr(), b, h, cap, self.live, _stream(key.device)))
+        else:  # other dtypes (a BF16 model before its cast): plain slice copies
+            at = self.live
+            for buf, src in ((self.keys, key), (self.raw_keys, raw), (self.values, value)):
+                buf[:, :, at : at + 1].copy_(src)
+        self.live += 1
+        if self.live == cap:
+            self._compress_oldest_group()
+
     def _compress_oldest_group(self):
-        n = self.config.group_size
-        self.compressed = compress(self.raw_keys[:, :, :n].contiguous(), self.values[:, :, :n].contiguous(),
+        s, n = self.sink_tokens, self.config.group_size
+        self.compressed = compress(self.raw_keys[:, :, s : s + n].contiguous(), self.values[:, :, s : s + n].contiguous(),
                                    self.config, previous=self.compressed, plan=self.plan)
-        remain = self.live - n
+        remain = self.live - s - n
         for buf in (self.keys, self.raw_keys, self.values):
-            if remain <= n:
-                buf[:, :, :remain].copy_(buf[:, :, n : self.live])  # source and target do not overlap
-            else:
-                buf[:, :, :remain].copy_(buf[:, :, n : self.live].clone())
-        self.live = remain
+            tail = buf[:, :, s + n : self.live]
+            buf[:, :, s : s + remain].copy_(tail if remain <= n else tail.clone())  # clone only when the ranges overlap
+        self.live = s + remain
 
     # -- Hugging Face cache-layer interface ---------------------------------------
     def get_seq_length(self):
@@ -150,8 +186,8 @@ class _CacheBase:
 class ResKVCache(_HFCache or _CacheBase):
     """One ``ResKVLayerCache`` per layer (reference cache.py:106-122)."""
 
-    def __init__(self, config: ResKVKernelConfig, num_layers: int):
-        super().__init__(layers=[ResKVLayerCache(config) for _ in range(num_layers)])
+    def __init__(self, config: ResKVKernelConfig, num_layers: int, sink_tokens: int = 0):
+        super().__init__(layers=[ResKVLayerCache(config, sink_tokens) for _ in range(num_layers)])
 
     def crop(self, max_length):
         raise NotImplementedError("ResKV does not support speculative cache rollback")

@@ -444,6 +444,7 @@ struct MergeParams {
     float scaling;
     const int32_t* dyn;  // device step state: dyn[1] = recent tokens (overrides tr), or null
     int recent_cap;      // tokens between units in rk / rv (== tr for contiguous windows)
+    uint32_t* status;    // device status word of the call's workspace, or null
 };
 
 constexpr int kMergeThreads = 128;
@@ -484,6 +485,9 @@ __global__ void __launch_bounds__(1024) decode_merge_kernel(const MergeParams p,
     float* part_s = reinterpret_cast<float*>(rv_s + kRecentChunk * kHeadDim);  // [gqa][4 warps][kPartStride]
     float* sc_s = part_s + gqa * (kMergeThreads / 32) * kPartStride + h * sc_stride;
     const int tr = p.dyn ? min(p.dyn[1], recent_max) : p.tr;
+    // a window count beyond the buffers is cut (the newest tokens are then missing from the result): tell the host
+    if (p.dyn && p.status && tid == 0 && unit == 0 && (p.dyn[1] > recent_max || p.dyn[1] < 0))
+        atomicOr(p.status, RESKV_STATUS_STATE_RANGE);
     const bool dot_scores = tr > 0 && !p.rscores;
     const __half* rk_g = p.rk ? p.rk + static_cast<size_t>(unit) * p.recent_cap * kHeadDim : nullptr;
     const __half* rv_g = p.rv ? p.rv + static_cast<size_t>(unit) * p.recent_cap * kHeadDim : nullptr;
@@ -847,6 +851,7 @@ struct DecodeArgs {
     void* stream;
     const int32_t* dyn = nullptr;  // device step state {pos_q, recent tokens}
     int recent_cap = 0;            // window capacity in tokens when dyn is given
+    bool clear_status = false;     // zero the workspace's status header once the arguments are accepted
 };
 
 // Which partial kernel dispatch_layout will pick for this call (its partial plan differs).
@@ -899,6 +904,11 @@ int decode_common(const DecodeArgs& a, LayoutId layout, bool has_meta, bool has_
     if (!a.workspace || a.workspace_bytes < need)
         return fail(RESKV_ERR_WORKSPACE, "%s: workspace of %zu bytes needed, %zu given", who, need, a.workspace_bytes);
 
+    if (a.clear_status) {
+        if (int rc = check_cuda(cudaMemsetAsync(a.workspace, 0, kWsHeader, static_cast<cudaStream_t>(a.stream)),
+                                "cudaMemsetAsync(decode scratch header)"))
+            return rc;
+    }
     const size_t rows = static_cast<size_t>(a.batch) * a.q_heads * splits;
     float* wsf = reinterpret_cast<float*>(static_cast<unsigned char*>(a.workspace) + kWsHeader);
     DecodeParams p{};
@@ -942,6 +952,7 @@ int decode_common(const DecodeArgs& a, LayoutId layout, bool has_meta, bool has_
     mp.kh = a.kv_heads, mp.nh = a.q_heads, mp.splits = splits, mp.cv = a.cv, mp.tr = a.recent_tokens;
     mp.scaling = a.scaling;
     mp.dyn = a.dyn, mp.recent_cap = a.dyn ? a.recent_cap : a.recent_tokens;
+    mp.status = p.status;
     return launch_merge(mp, units, a.dyn ? a.recent_cap : a.recent_tokens, s);
 }
 }  // namespace
@@ -1065,7 +1076,9 @@ namespace {
 // Device address of g_noalloc_scratch on the current device.  In host code the
 // array's name is only a handle for the runtime, not something a kernel can
 // dereference, so the address is looked up once per device (with that device
-// current) and remembered.
+// current) and remembered.  The remembered value is written without a lock: two
+// host threads that make their first call on a device together both look the
+// address up and store the same value.
 int noalloc_scratch_address(void** out) {
     static void* cached[64] = {nullptr};
     int dev = 0;
@@ -1107,16 +1120,24 @@ extern "C" int reskv_decode_bitmap_fp16_noalloc(const void* q, const void* k_cen
                     batch * q_heads, eff, need, RESKV_NOALLOC_SCRATCH_BYTES);
     void* scratch = nullptr;
     if (int rc = noalloc_scratch_address(&scratch)) return rc;
-    // the array still holds the previous call's data; only the status header has to start at zero
-    // (every partial slot that the merge reads is written by this call's partial kernel first)
-    if (int rc = check_cuda(cudaMemsetAsync(scratch, 0, kWsHeader, static_cast<cudaStream_t>(stream)),
-                            "cudaMemsetAsync(built-in decode scratch header)"))
-        return rc;
-    const DecodeArgs a{q, k_centroids, k_ids, k_payload, k_bitmap, nullptr, v_centroids, v_ids, v_payload, v_bitmap,
-                       nullptr, batch, kv_heads, q_heads, tokens, tok_stride, k_clusters, v_clusters, start_pos, pos_q,
-                       rope_theta, inv_freq, scaling, splits, recent_q, recent_k, recent_v, recent_tokens, scratch,
-                       static_cast<size_t>(RESKV_NOALLOC_SCRATCH_BYTES), out, out_m, out_l, stream};
+    // the array still holds the previous call's data; only the status header has to start at zero (every
+    // partial slot that the merge reads is written or marked empty by this call's partial kernel first):
+    // decode_common clears it once the arguments have been accepted
+    DecodeArgs a{q, k_centroids, k_ids, k_payload, k_bitmap, nullptr, v_centroids, v_ids, v_payload, v_bitmap,
+                 nullptr, batch, kv_heads, q_heads, tokens, tok_stride, k_clusters, v_clusters, start_pos, pos_q,
+                 rope_theta, inv_freq, scaling, splits, recent_q, recent_k, recent_v, recent_tokens, scratch,
+                 static_cast<size_t>(RESKV_NOALLOC_SCRATCH_BYTES), out, out_m, out_l, stream};
+    a.clear_status = true;
     return decode_common(a, nnz == 32 ? kBitmap32 : kBitmap64, true, false, "decode_bitmap_fp16_noalloc");
+}
+
+extern "C" int reskv_decode_noalloc_status(uint32_t* status_out, void* stream) {
+    if (!status_out) return fail(RESKV_ERR_INVALID, "decode_noalloc_status: null destination");
+    void* scratch = nullptr;
+    if (int rc = noalloc_scratch_address(&scratch)) return rc;
+    return check_cuda(cudaMemcpyAsync(status_out, scratch, sizeof(uint32_t), cudaMemcpyDeviceToHost,
+                                      static_cast<cudaStream_t>(stream)),
+                      "cudaMemcpyAsync(built-in decode scratch status)");
 }
 
 static int merge_recent_common(const void* comp_out, const float* comp_m, const float* comp_l, const float* scores,

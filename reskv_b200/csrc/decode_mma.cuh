@@ -477,6 +477,8 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
     const long long work_total = static_cast<long long>(p.units) * n_pad;
     long long work = static_cast<long long>(blockIdx.x) * chunk;
     const long long work_end = min(work_total, work + chunk);
+    // a device-side token count beyond the buffers is cut to the token stride: tell the host
+    if (p.dyn && blockIdx.x == 0 && tid == 0 && p.dyn[2] > p.tok_stride) atomicOr(p.status, RESKV_STATUS_STATE_RANGE);
     if (work >= work_end) return;
 
     if (tid == 0) {

@@ -48,7 +48,7 @@ class ResKVAttention(LlamaAttention):
             else:
                 model_rope = layer.config.rope_mode == "model"
                 out = attention(q, layer.compressed, position=layer.length - 1,
-                                rope_theta=_rope_theta(self.config),
+                                start_position=layer.start_position, rope_theta=_rope_theta(self.config),
                                 inv_freq=self.rope_frequencies if model_rope else None,
                                 scaling=self.scaling, recent=(q_rot, window_k, window_v))
         else:
@@ -126,7 +126,8 @@ class ResKVForCausalLM(LlamaForCausalLM):
         if past_key_values is not None and not isinstance(past_key_values, ResKVCache):
             raise ValueError("past_key_values must be a ResKVCache")
         if use_cache and past_key_values is None:
-            past_key_values = ResKVCache(self.kernel_config, len(self.model.layers))
+            # `sink_tokens` (default 0, like the reference's CUDA cache) may be set on the model instance
+            past_key_values = ResKVCache(self.kernel_config, len(self.model.layers), getattr(self, "sink_tokens", 0))
         if attention_mask is not None and not bool(attention_mask.eq(1).all()):
             raise ValueError("ResKV requires equal-length unpadded batches")
         given = input_ids if input_ids is not None else inputs_embeds

@@ -87,13 +87,15 @@ class ResKVLlama:
     """
 
     def __init__(self, shape: LlamaShape = LlamaShape(), kernel_config: ResKVKernelConfig | None = None, *,
-                 cache: str = "reskv", device="cuda", seed: int = 0, group=None, prefill_chunk: int = 65536):
+                 cache: str = "reskv", device="cuda", seed: int = 0, group=None, prefill_chunk: int = 65536,
+                 sink_tokens: int = 0):
         if cache not in ("reskv", "dense"):
             raise ValueError("cache must be 'reskv' or 'dense'")
         self.shape, self.cache_kind, self.device = shape, cache, torch.device(device)
         self.kernel_config = kernel_config or ResKVKernelConfig()
         if not isinstance(self.kernel_config, ResKVKernelConfig):
             raise TypeError(f"expected ResKVKernelConfig, got {type(self.kernel_config).__name__}")
+        self.sink_tokens = int(sink_tokens)  # leading tokens kept dense (attention sinks); compression starts behind them
         self.group = group
         self.tp = 1 if group is None else torch.distributed.get_world_size(group)
         if shape.kv_heads % self.tp or shape.heads % self.tp or shape.ffn % self.tp:
@@ -189,7 +191,7 @@ class ResKVLlama:
                 k_raw[i:i + rows], k_rot[i:i + rows], v_all[i:i + rows] = k, kr, v
                 del q, k, v, qr, kr, out
             if self.cache_kind == "reskv":
-                cache = ResKVLayerCache(self.kernel_config)
+                cache = ResKVLayerCache(self.kernel_config, self.sink_tokens)
                 cache.update(k_rot, v_all, {"raw_keys": k_raw})
                 if reserve and cache.compressed is not None:
                     total = cache.compressed.seq_len + reserve
@@ -224,8 +226,8 @@ class ResKVLlama:
             if self.cache_kind == "reskv":
                 keys, values = cache.update(kr, v, {"raw_keys": k.contiguous()})
                 if cache.compressed is not None:
-                    att = attention(q.contiguous(), cache.compressed, position=pos, inv_freq=self.inv_freq,
-                                    scaling=self.scaling, recent=(qr, keys, values))
+                    att = attention(q.contiguous(), cache.compressed, position=pos, start_position=cache.start_position,
+                                    inv_freq=self.inv_freq, scaling=self.scaling, recent=(qr, keys, values))
                 else:
                     att = F.scaled_dot_product_attention(qr, keys, values, enable_gqa=True, scale=self.scaling)
             else:
@@ -305,7 +307,7 @@ class ResKVLlama:
                 check(lib.reskv_decode_step(layout, plan.bits, plan.nnz, q_raw.data_ptr(), kc.data_ptr(), ki.data_ptr(),
                                             kp.data_ptr(), ptr(km), ptr(ks), vc.data_ptr(), vi.data_ptr(), vp.data_ptr(),
                                             ptr(vm), ptr(vs), b, self.h_kv, self.h_q, key.seq_len, key.token_stride,
-                                            kc.shape[1], vc.shape[1], 0, float(self.shape.rope_theta),
+                                            kc.shape[1], vc.shape[1], cache.start_position, float(self.shape.rope_theta),
                                             self.inv_freq.data_ptr(), float(self.scaling), 0, q_rot.data_ptr(),
                                             cache.keys.data_ptr(), cache.values.data_ptr(), cap, state,
                                             self._workspace.data_ptr(), self._workspace.numel(), att.data_ptr(), stream),
@@ -345,7 +347,8 @@ class ResKVLlama:
             self._centroids = [tuple(torch.zeros((batch * self.h_kv, rows, 128), dtype=torch.float16, device=self.device)
                                      for _ in range(2)) for _ in self.caches]
             self._sync_graph_inputs()
-            need = library().reskv_decode_bitmap_fp16_workspace_bytes(batch, self.h_kv, self.h_q, 1 << 20, 64)
+            # scratch for any compressed length up to 2^20 tokens with the library's own schedule
+            need = library().reskv_decode_bitmap_fp16_workspace_bytes(batch, self.h_kv, self.h_q, 1 << 20, 0)
             self._workspace = torch.zeros(need, dtype=torch.uint8, device=self.device)
         else:
             if _flash_kvcache is None:

@@ -24,3 +24,12 @@ def pytest_configure(config):
 def golden():
     """Vectors recorded from the reference's own CPU code (tests/golden/make_golden.py)."""
     return dict(np.load(ROOT / "tests" / "golden" / "reference_vectors.npz"))
+
+
+@pytest.fixture(scope="session")
+def gpu_golden():
+    """Vectors recorded from the reference's CUDA code on a B200 (tests/golden/make_golden_gpu.py)."""
+    path = ROOT / "tests" / "golden" / "reference_gpu_vectors.npz"
+    if not path.exists():
+        pytest.skip("tests/golden/reference_gpu_vectors.npz has not been recorded")
+    return dict(np.load(path))

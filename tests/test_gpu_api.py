@@ -178,6 +178,45 @@ def test_incremental_cache_matches_one_shot_attention():
     assert torch.equal(values.cpu(), v[:, :, n:])
 
 
+def test_cache_with_sink_tokens_at_the_reference_cpu_configuration():
+    """One Llama-3.1-8B-shaped layer, batch 1, 8 KV heads, context 8192, 4 sink tokens, window 32, group 64,
+    sparsity 0.5: the prompt splits into 4 sinks + 8128 compressed tokens + 60 dense ones; 70 more tokens cross
+    one group compression.  Attention over (sinks + compressed + window) equals dense attention over the
+    reconstructed cache at the original positions."""
+    from reskv_b200 import ResKVKernelConfig, attention
+    from reskv_b200.cache import ResKVLayerCache
+    from reskv_b200.synthetic import gaussian, mixture
+
+    cfg = ResKVKernelConfig(sparsity=0.5, layout="unstructured", kmeans_iterations=10, num_clusters=32)
+    b, h, t0, extra, sinks = 1, 8, 8192, 70, 4
+    k, v = mixture(b, h, t0 + extra, seed=21), mixture(b, h, t0 + extra, seed=22)
+    freq = oatt.theta_frequencies(500000.0)
+
+    def rot(x, start):
+        return torch.from_numpy(oatt.rotate(np16(x), np.arange(start, start + x.shape[2]), freq)).half()
+
+    layer = ResKVLayerCache(cfg, sink_tokens=sinks)
+    keys, values = layer.update(cuda(rot(k[:, :, :t0], 0)), cuda(v[:, :, :t0]), {"raw_keys": cuda(k[:, :, :t0])})
+    assert layer.start_position == sinks and layer.compressed.seq_len == 8128 and layer.live == sinks + 60
+    assert torch.equal(values[:, :, :sinks].cpu(), v[:, :, :sinks]) and torch.equal(values[:, :, sinks:].cpu(), v[:, :, sinks + 8128:t0])
+    for i in range(t0, t0 + extra):
+        keys, values = layer.update(cuda(rot(k[:, :, i:i + 1], i)), cuda(v[:, :, i:i + 1]),
+                                    {"raw_keys": cuda(k[:, :, i:i + 1])})
+    n = layer.compressed.seq_len
+    assert n == 8128 + 64 and layer.live == sinks + (t0 + extra - sinks - n)
+    assert torch.equal(values.cpu(), torch.cat((v[:, :, :sinks], v[:, :, sinks + n:]), 2))
+    assert torch.equal(keys[:, :, :sinks].cpu(), rot(k[:, :, :sinks], 0))
+    pos = t0 + extra - 1
+    q = gaussian(b, h * 4, 1, 128, seed=23)
+    qr = torch.from_numpy(oatt.rotate(np16(q), np.array([pos]), freq)).half()
+    out = attention(cuda(q), layer.compressed, position=pos, start_position=layer.start_position,
+                    recent=(cuda(qr), keys, values))
+    want = reference(q, layer.compressed, position=pos, start_position=sinks, recent=(qr, keys.cpu(), values.cpu()))
+    assert_attention_close(out, want)
+    with pytest.raises(ValueError, match="sink_tokens"):
+        ResKVLayerCache(cfg, sink_tokens=-1)
+
+
 def test_layouts_have_different_selection_semantics():
     from reskv_b200 import ResKVKernelConfig, compress
 

@@ -28,7 +28,7 @@ def _rope(x, pos, inv_freq):
     return torch.cat((a * cos - b * sin, b * cos + a * sin), dim=-1).to(x.dtype)
 
 
-def _step(cache, q, qr, win_k, win_v, state, tokens_arg, splits, rows=None):
+def _step(cache, q, qr, win_k, win_v, state, tokens_arg, splits, rows=None, expect_status=0):
     """One reskv_decode_step call; centroid tables optionally padded to `rows` zero rows."""
     from reskv_b200 import _extension as ext
 
@@ -65,7 +65,7 @@ def _step(cache, q, qr, win_k, win_v, state, tokens_arg, splits, rows=None):
                                ext._stream(torch.device(DEV)))
     ext.check(rc, launches=2)
     torch.cuda.synchronize()
-    assert int(ws[:4].view(torch.int32).item()) == 0, "kernel status word set"
+    assert int(ws[:4].view(torch.int32).item()) == expect_status, "unexpected kernel status word"
     return out.reshape(b, hq, 1, 128)
 
 
@@ -105,6 +105,14 @@ def test_counts_from_the_step_state_match_the_by_value_call(sparsity, bits, layo
     torch.testing.assert_close(got.float(), want.float(), atol=2e-3, rtol=1e-2)
     got = _step(cache, q, qr, win_k, win_v, state(t), 9 * 64, 4, rows=64)  # 10 tiles over 4 splits: 3,3,3,1
     torch.testing.assert_close(got.float(), want.float(), atol=2e-3, rtol=1e-2)
+    if sparsity == 0.75 and bits == 16 and layout == "unstructured":
+        # counts beyond the buffers are cut (window tokens to the capacity, compressed tokens to the token
+        # stride) and reported: bit RESKV_STATUS_STATE_RANGE (2) of the status word, no fault
+        over = torch.tensor([pos, cap + 1, t, 0], dtype=torch.int32, device=DEV)
+        _step(cache, q, qr, win_k, win_v, over, t, 0, expect_status=2)
+        if kernel_variant == "tensor-core":
+            over = torch.tensor([pos + 4096, live, cache.key.token_stride + 1, 0], dtype=torch.int32, device=DEV)
+            _step(cache, q, qr, win_k, win_v, over, t, 0, expect_status=2)
     got = _step(cache, q, qr, win_k, win_v, state(t - 64), t, 4)  # 9 tiles over 4 splits: the last split is empty
     short = compress(k[:, :, :t].contiguous(), v[:, :, :t].contiguous(), cfg)
     # the first t - 64 tokens of the same cache, by value

@@ -86,7 +86,11 @@ def test_matches_the_workspace_entry_point_on_consecutive_calls(nnz):
     for splits, rec, want in ((0, None, ref), (5, recent, ref_recent), (0, None, ref)):
         rc, out, m, l = _call_noalloc(lib, qd, key, value, kh, kh * gqa, t + 2, splits, rec)
         assert rc == 0, lib.reskv_last_error().decode()
+        # no bounded wait ran out and no slot index was out of range: the status word of the built-in scratch is 0
+        status = torch.full((1,), 0xFFFF, dtype=torch.int32).pin_memory()
+        assert lib.reskv_decode_noalloc_status(status.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
         torch.cuda.synchronize()
+        assert int(status.item()) == 0
         assert _close(out, want)
         if rec is None:
             assert torch.allclose(m, ref_m, atol=2e-3) and torch.allclose(l, ref_l, rtol=5e-3)
