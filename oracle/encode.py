@@ -96,12 +96,27 @@ def encode_tiled_fp16(x, centroids, ids, nnz: int, structured: bool):
     return values, words.astype(np.uint32).view(np.int32)
 
 
-def encode_structured_int4(x, centroids, ids):
+def near_half_integer(quotient: np.ndarray, ulps: int = 4) -> np.ndarray:
+    """Quotients within ``ulps`` float32 units in the last place of ``n + 1/2``.
+
+    The reference is built with ``--use_fast_math``, so its divisions are the GPU's approximate
+    ``div.approx.ftz.f32`` (a reciprocal of up to 1 ulp error times the numerator) where this restatement
+    divides exactly.  The two can round to different integers only when the quotient sits this close to a
+    rounding boundary; the CUDA kernels of this repository issue the same approximate division as the
+    reference, the comparisons against *this* restatement set those codes aside and count them."""
+    q = np.abs(quotient.astype(np.float64))
+    dist = np.abs(q - (np.floor(q) + 0.5))
+    return dist <= ulps * np.spacing(np.maximum(q, 1.0).astype(np.float32)).astype(np.float64)
+
+
+def encode_structured_int4(x, centroids, ids, return_ambiguous: bool = False):
     """-> ``(packed i32 [B,H,T,4], meta i32 [B,H,T,2], scale f16 [B,H,T])``.
 
     One coordinate of every four (compression.cu:189-204), scale
     ``s = amax * fp32(1/7)`` kept in FP32 for the division and stored as FP16
-    (:224-227), ``q = clamp(rint(r / s), -7, 7)`` (:233-235).
+    (:224-227), ``q = clamp(rint(r / s), -7, 7)`` (:233-235).  With
+    ``return_ambiguous`` a fourth result marks the groups ``[B,H,T,32]`` whose
+    quotient lies on a rounding boundary (see ``near_half_integer``).
     """
     r32 = residual_fp32(x, centroids, ids)
     groups = _keys(r32).reshape(*r32.shape[:-1], 32, 4)
@@ -109,34 +124,53 @@ def encode_structured_int4(x, centroids, ids):
     compact = np.take_along_axis(r32.reshape(*r32.shape[:-1], 32, 4), best[..., None], axis=-1)[..., 0]
     amax = np.abs(compact).max(-1)
     s = np.where(amax > 0, amax * (np.float32(1.0) / np.float32(7.0)), np.float32(1.0)).astype(np.float32)
-    q = np.clip(np.rint(compact / s[..., None]), -7, 7).astype(np.int64) & 15
+    quotient = compact / s[..., None]
+    q = np.clip(np.rint(quotient), -7, 7).astype(np.int64) & 15
     packed = (q.reshape(*q.shape[:-1], 4, 8) << (np.arange(8) * 4)).sum(-1)
     meta = (best.astype(np.int64).reshape(*best.shape[:-1], 2, 16) << (np.arange(16) * 2)).sum(-1)
-    return (
-        packed.astype(np.uint32).view(np.int32),
-        meta.astype(np.uint32).view(np.int32),
-        s.astype(np.float16),
-    )
+    out = (packed.astype(np.uint32).view(np.int32), meta.astype(np.uint32).view(np.int32), s.astype(np.float16))
+    return (*out, near_half_integer(quotient)) if return_ambiguous else out
 
 
-def encode_quantized(x, centroids, ids, nnz: int, bits: int):
-    """-> ``(words i32 [B,H,T,4*bits], scale f16 [B,H,T])`` (compression.cu:244-383).
+def quantized_codes(r32: np.ndarray, mask: np.ndarray, bits: int):
+    """Scale and signed codes of the unstructured quantiser -> ``(h f16 [...], q int64 [...,128],
+    quotient f32 [...,128])`` (compression.cu:354-368).
 
-    Global top-``nnz`` of 128; ``h = fp16(max|r_sel| / QMAX)`` with
-    ``QMAX = 2**(bits-1) - 1`` (``h = 1`` for an all-zero selection, :354-355);
-    ``q = clamp(rint(r / fp32(h)), -QMAX, QMAX)`` (:367-368); every coordinate
-    is stored, discarded ones as 0; value ``i`` of a word at bit ``i * bits``.
+    ``h = fp16(amax * fp32(1 / QMAX))``: the reference divides by the constant ``QMAX`` under
+    ``--use_fast_math``, which the compiler turns into a multiplication by the rounded reciprocal (pinned by a
+    recorded token whose two forms round to different FP16 values).  ``q = clamp(lrintf(r / fp32(h)))`` for
+    kept coordinates, 0 for discarded ones.  When ``h`` underflows to 0 (all kept residuals below
+    ``QMAX * 2**-25``) the quotient is +-inf or NaN and the reference's ``(int)lrintf(.)`` keeps the low 32 bits
+    of the saturated 64-bit conversion: -1 for positive residuals, 0 for negative ones and for zeros.
     """
     qmax = (1 << (bits - 1)) - 1
+    amax = np.where(mask, np.abs(r32), np.float32(0)).max(-1).astype(np.float32)
+    recip = np.float32(1.0) / np.float32(qmax)
+    h = np.where(amax > 0, amax * recip, np.float32(1.0)).astype(np.float32).astype(np.float16)
+    hf = h.astype(np.float32)[..., None]
+    with np.errstate(divide="ignore", invalid="ignore"):
+        quotient = (r32 / hf).astype(np.float32)
+        q = np.clip(np.rint(quotient), -qmax, qmax)
+    q = np.where(hf == 0, np.where(r32 > 0, -1.0, 0.0), np.nan_to_num(q))
+    return h, np.where(mask, q, 0).astype(np.int64), np.where(mask & (hf != 0), quotient, np.float32(0))
+
+
+def encode_quantized(x, centroids, ids, nnz: int, bits: int, return_ambiguous: bool = False):
+    """-> ``(words i32 [B,H,T,4*bits], scale f16 [B,H,T])`` (compression.cu:244-383).
+
+    Global top-``nnz`` of 128; scale and codes as in ``quantized_codes``; every coordinate
+    is stored, discarded ones as 0; value ``i`` of a word at bit ``i * bits``.  With
+    ``return_ambiguous`` a third result marks the coordinates ``[B,H,T,128]`` whose
+    quotient lies on a rounding boundary (see ``near_half_integer``).
+    """
     r32 = residual_fp32(x, centroids, ids)
     mask = topk_mask(_keys(r32), nnz)
-    amax = np.where(mask, np.abs(r32), np.float32(0)).max(-1).astype(np.float32)
-    h = np.where(amax > 0, amax / np.float32(qmax), np.float32(1.0)).astype(np.float32).astype(np.float16)
-    q = np.rint(r32 / h.astype(np.float32)[..., None])
-    q = np.where(mask, np.clip(q, -qmax, qmax), 0).astype(np.int64) & ((1 << bits) - 1)
+    h, q, quotient = quantized_codes(r32, mask, bits)
+    q = q & ((1 << bits) - 1)
     per = 32 // bits
     words = (q.reshape(*q.shape[:-1], HEAD_DIM // per, per) << (np.arange(per) * bits)).sum(-1)
-    return words.astype(np.uint32).view(np.int32), h
+    out = (words.astype(np.uint32).view(np.int32), h)
+    return (*out, near_half_integer(quotient) & mask) if return_ambiguous else out
 
 
 def encode_compact(x, centroids, ids, nnz: int, bits: int):
@@ -146,12 +180,10 @@ def encode_compact(x, centroids, ids, nnz: int, bits: int):
     coordinates are stored (ascending coordinate order) next to the MSB-first
     bitmap of the unstructured FP16 layout.  No counterpart in the reference.
     """
-    qmax = (1 << (bits - 1)) - 1
     r32 = residual_fp32(x, centroids, ids)
     mask = topk_mask(_keys(r32), nnz)
-    amax = np.where(mask, np.abs(r32), np.float32(0)).max(-1).astype(np.float32)
-    h = np.where(amax > 0, amax / np.float32(qmax), np.float32(1.0)).astype(np.float32).astype(np.float16)
-    q = np.clip(np.rint(r32 / h.astype(np.float32)[..., None]), -qmax, qmax).astype(np.int64) & ((1 << bits) - 1)
+    h, q, _ = quantized_codes(r32, mask, bits)
+    q = q & ((1 << bits) - 1)
     order = np.argsort(~mask, axis=-1, kind="stable")[..., :nnz]  # kept coordinates, ascending
     codes = np.take_along_axis(q, order, axis=-1)
     per = 32 // bits

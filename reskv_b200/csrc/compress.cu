@@ -6,7 +6,8 @@
 // every metadata word of every layout one or two instructions, and ranks are
 // popcounts of votes.  Rounding points (they decide bit-exactness against the
 // reference): r = fp32(x) - fp32(c); the selection key is |fp16(r)|; FP16
-// layouts store fp16(r); quantisers divide the FP32 r with IEEE division.
+// layouts store fp16(r); quantisers divide the FP32 r with the GPU's approximate
+// division, as the reference's fast-math build does (see div_fast).
 // Ties keep the lower coordinate.
 //
 // The global top-k of the unstructured layouts is a bisection on the 15-bit key
@@ -30,6 +31,35 @@ struct EncodeParams {
     int64_t x_stride, out_stride;
     int units, tokens, clusters, nnz;
 };
+
+// The reference is built with --use_fast_math: `a / b` is the GPU's approximate division (one reciprocal
+// approximation times the numerator, div.approx.ftz.f32) and a division by a constant becomes a multiplication
+// by its rounded reciprocal.  Quantised codes whose exact quotient sits on a rounding boundary depend on that,
+// so the same instruction is issued here (vectors recorded from the reference's kernels on a B200 are matched
+// to the bit, including the tokens whose scale underflows to 0).
+__device__ __forceinline__ float div_fast(float a, float b) {
+    float q;
+    asm("div.approx.ftz.f32 %0, %1, %2;" : "=f"(q) : "f"(a), "f"(b));
+    return q;
+}
+
+// (int)lrintf(x): round to nearest even into 64 bits (saturating; NaN -> INT64_MIN), keep the low 32 bits.
+// Finite quotients are unaffected; +inf becomes -1 and -inf / NaN become 0, which is what the reference's
+// `(int)lrintf(r / 0)` yields for a token whose FP16 scale underflowed (compression.cu:366-367).
+__device__ __forceinline__ int lrint_low32(float x) { return static_cast<int>(__float2ll_rn(x)); }
+
+// Scale of the unstructured quantiser: fp16(amax / QMAX) with the division by the constant done as a
+// multiplication by fp32(1 / QMAX) (compression.cu:354-355 under --use_fast_math); 1 for an all-zero selection.
+template <int QMAX>
+__device__ __forceinline__ __half quant_scale(float amax) {
+    constexpr float kRecip = 1.0f / static_cast<float>(QMAX);
+    return amax > 0.f ? __float2half_rn(amax * kRecip) : __float2half_rn(1.f);
+}
+
+template <int QMAX>
+__device__ __forceinline__ int quant_code(float r, float s) {
+    return max(-QMAX, min(QMAX, lrint_low32(div_fast(r, s))));
+}
 
 struct Residual {
     float r[4];       // fp32 residual of coordinates lane + 32 i
@@ -137,17 +167,14 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) encode_quantized_kernel(con
         for (int i = 0; i < 4; ++i) amax = fmaxf(amax, keep[i] ? fabsf(res.r[i]) : 0.f);
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, off));
-        const __half hs = amax > 0.f ? __float2half_rn(__fdiv_rn(amax, static_cast<float>(kQmax))) : __float2half_rn(1.f);
+        const __half hs = quant_scale<kQmax>(amax);
         const float s = __half2float(hs);
         const size_t orow = static_cast<size_t>(unit) * p.out_stride + t;
         int32_t* words = static_cast<int32_t*>(p.payload) + orow * (4 * BITS);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             int q = 0;
-            if (keep[i]) {
-                const float f = rintf(__fdiv_rn(res.r[i], s));
-                q = static_cast<int>(fminf(fmaxf(f, -static_cast<float>(kQmax)), static_cast<float>(kQmax)));
-            }
+            if (keep[i]) q = quant_code<kQmax>(res.r[i], s);
             // coordinate d = lane + 32 i sits at bit (d % kPer) * BITS of word d / kPer
             uint32_t w = (static_cast<uint32_t>(q) & ((1u << BITS) - 1u)) << ((lane % kPer) * BITS);
 #pragma unroll
@@ -181,7 +208,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) encode_compact_kernel(const
         for (int i = 0; i < 4; ++i) amax = fmaxf(amax, keep[i] ? fabsf(res.r[i]) : 0.f);
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, off));
-        const __half hs = amax > 0.f ? __float2half_rn(__fdiv_rn(amax, static_cast<float>(kQmax))) : __float2half_rn(1.f);
+        const __half hs = quant_scale<kQmax>(amax);
         const float s = __half2float(hs);
         if (lane < 8) scratch[warp][lane] = 0u;
         __syncwarp();
@@ -190,8 +217,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) encode_compact_kernel(const
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             if (keep[i]) {
-                const float f = rintf(__fdiv_rn(res.r[i], s));
-                const int q = static_cast<int>(fminf(fmaxf(f, -static_cast<float>(kQmax)), static_cast<float>(kQmax)));
+                const int q = quant_code<kQmax>(res.r[i], s);
                 const int r = base + __popc(vote[i] & below);
                 atomicOr(&scratch[warp][r / kPer], (static_cast<uint32_t>(q) & ((1u << BITS) - 1u)) << ((r % kPer) * BITS));
             }
@@ -292,8 +318,8 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) encode_structured_int4_kern
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             // group g = 8 i + lane / 4; nibble g % 8 of word g / 8 = i; index bits 2 (g % 16) of meta word g / 16
-            const float f = rintf(__fdiv_rn(comp[i], s));
-            const int q = static_cast<int>(fminf(fmaxf(f, -7.f), 7.f));
+            // q = clamp(__float2int_rn(r / s)) with the approximate division (compression.cu:233-234)
+            const int q = max(-7, min(7, __float2int_rn(div_fast(comp[i], s))));
             const bool leader = in_group == 0;
             uint32_t w = leader ? ((static_cast<uint32_t>(q) & 15u) << (4 * (lane >> 2))) : 0u;
             w = __reduce_or_sync(kFull, w);

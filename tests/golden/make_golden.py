@@ -51,9 +51,11 @@ def mixture(rng, b, h, t, clusters=8, sigma=0.3, outliers=True):
 
 
 def main(ref_root: str):
-    sys.path.insert(0, ref_root)
-    sys.path.insert(0, str(ROOT))
+    sys.path.insert(0, str(ROOT))   # the oracle package
+    sys.path.insert(0, ref_root)    # first: `reskv` must be the reference, not this repository's alias package
     import reskv.compression as rc
+    if Path(rc.__file__).resolve().is_relative_to(ROOT / "reskv"):
+        sys.exit("`reskv` resolved to this repository's alias package; pass the path of the reference checkout")
     import reskv.reference as rr
     from reskv.config import KernelPlan, ResKVKernelConfig
     from reskv.tensors import CompressedKV, CompressedTensor

@@ -21,21 +21,55 @@ def g(gpu_golden):
     return gpu_golden
 
 
+def _codes(words, bits):
+    per = 32 // bits
+    q = ((words.astype(np.int64) & 0xFFFFFFFF)[..., None] >> (np.arange(per) * bits)) & ((1 << bits) - 1)
+    q = q.reshape(*words.shape[:-1], -1)
+    sign = 1 << (bits - 1)
+    return (q ^ sign) - sign
+
+
+def _compare_packed(layout, bits, nnz, x, cen, ids, ref_payload, ref_meta, ref_scale, keep=None):
+    """Oracle against recorded tensors.  Everything must be equal to the bit, except quantised codes whose
+    exact quotient sits on a rounding boundary (the reference divides approximately, ``--use_fast_math``):
+    those may differ by one step and are returned as ``(token index..., coordinate, oracle code, reference
+    code)`` rows so that the caller can state how many there are."""
+    keep = np.ones(ids.shape, bool) if keep is None else keep
+    ambiguous = None
+    if bits == 16:
+        p, m, s = oenc.encode(layout, bits, nnz, x, cen, ids)
+    elif layout == "structured":
+        p, m, s, ambiguous = oenc.encode_structured_int4(x, cen, ids, return_ambiguous=True)
+    else:
+        (p, s, ambiguous), m = oenc.encode_quantized(x, cen, ids, nnz, bits, return_ambiguous=True), None
+    if m is not None:
+        assert np.array_equal(m[keep], ref_meta[keep]), "metadata differs"
+    if s is not None:
+        assert np.array_equal(s.view(np.uint16), ref_scale.view(np.uint16)), "scale bits differ"
+    if bits == 16:
+        assert np.array_equal(p[keep].view(np.uint16), ref_payload[keep].view(np.uint16)), "payload bits differ"
+        return []
+    mine, theirs = _codes(p, bits), _codes(ref_payload, bits)
+    differ = mine != theirs
+    assert not (differ & ~ambiguous).any(), "codes differ away from rounding boundaries"
+    assert (np.abs(mine - theirs)[differ] == 1).all()
+    return [(*idx, int(mine[tuple(idx)]), int(theirs[tuple(idx)])) for idx in np.argwhere(differ)]
+
+
 @pytest.mark.parametrize("layout,bits,nnz", PACKER_PLANS)
 def test_packers_bit_exact(g, layout, bits, nnz):
-    """Words, metadata and scale bits of every token -- ties, zeros, extremes and subnormal rows included."""
+    """Words, metadata and scale bits of every token -- ties, zeros, extremes and subnormal rows included.
+    The only codes that differ from the reference kernels' output in these 384 tokens: the exact tie
+    -64 / (128 / 7) = -3.5 of the 1-of-4 INT4 packer, once per head (approximate division: -4, exact: -3)."""
     key = f"pk_{layout}_{bits}_{nnz}"
-    p, m, s = oenc.encode(layout, bits, nnz, g["pk_x"], g["pk_cen"], g["pk_ids"])
-    if p.dtype == np.float16:
-        assert np.array_equal(p.view(np.uint16), g[key + "_payload"].view(np.uint16))
-    else:
-        assert np.array_equal(p, g[key + "_payload"])
-    if m is not None:
-        assert np.array_equal(m, g[key + "_meta"])
-    if s is not None:
-        assert np.array_equal(s.view(np.uint16), g[key + "_scale"].view(np.uint16))
-    dense = olay.reconstruct(layout, bits, g["pk_cen"], g["pk_ids"], p, m, s)
-    assert np.array_equal(dense, g[key + "_dense"])
+    boundary = _compare_packed(layout, bits, nnz, g["pk_x"], g["pk_cen"], g["pk_ids"], g[key + "_payload"],
+                               g.get(key + "_meta"), g.get(key + "_scale"))
+    expected = {("structured", 4, 32): 2}.get((layout, bits, nnz), 0)
+    assert len(boundary) == expected, boundary
+    if not boundary:
+        p, m, s = oenc.encode(layout, bits, nnz, g["pk_x"], g["pk_cen"], g["pk_ids"])
+        dense = olay.reconstruct(layout, bits, g["pk_cen"], g["pk_ids"], p, m, s)
+        assert np.array_equal(dense, g[key + "_dense"])
 
 
 @pytest.mark.parametrize("nnz", [32, 64])
@@ -105,20 +139,17 @@ def test_packed_caches_and_attention_of_the_eleven_plans(g, bits, sparsity, layo
     reference's own test tolerance of the oracle."""
     tag = "at_" + case_tag(bits, sparsity, layout, fusion)
     nnz = int(128 * (1 - sparsity))
+    boundary = []
     for side, x in (("k", g["at_k"]), ("v", g["at_v"])):
         c = _cache(g, tag, side)
+        keep = None
         if bits == 16 and layout == "unstructured":   # torch encoder: tie order is library-defined
             keys = np.abs(oenc.residual_fp32(x, c["centroids"], c["ids"]).astype(np.float16)).astype(np.float32)
             keep = ~oenc.tie_tokens(keys, nnz)
-        else:
-            keep = np.ones(c["ids"].shape, bool)
-        p, m, s = oenc.encode(layout, bits, nnz, x, c["centroids"], c["ids"])
-        assert np.array_equal(p[keep].view(np.uint16 if p.dtype == np.float16 else p.dtype),
-                              c["payload"][keep].view(np.uint16 if p.dtype == np.float16 else p.dtype))
-        if m is not None:
-            assert np.array_equal(m[keep], c["metadata"][keep])
-        if s is not None:
-            assert np.array_equal(s.view(np.uint16), c["scale"].view(np.uint16))
+        boundary += _compare_packed(layout, bits, nnz, x, c["centroids"], c["ids"], c["payload"], c["metadata"],
+                                    c["scale"], keep)
+    # one value residual of the INT4 sparsity-0.5 cache divides to exactly 2.5 (approximate division: 3, exact: 2)
+    assert len(boundary) == (1 if (bits, sparsity, layout) == (4, 0.5, "unstructured") else 0), boundary
     kc, vc = _cache(g, tag, "k"), _cache(g, tag, "v")
     for suffix, recent in (("", None), ("_recent", (g["at_qr"], g["at_kr"], g["at_vr"]))):
         want = oatt.attention_compressed(g["at_q"], kc, vc, position=288, inv_freq=g["at_freq"], recent=recent)
