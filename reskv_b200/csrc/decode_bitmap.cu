@@ -783,7 +783,7 @@ PartialPlan plan_partials(int units, int tokens, int splits_req, bool tensor_cor
     }
     const long long max_tiles = dyn ? (tok_stride + kTile - 1) / kTile : tiles;
     const long long all = static_cast<long long>(units) * (dyn ? max_tiles : tiles);
-    long long grid = 2ll * sm_count();
+    long long grid = static_cast<long long>(RESKV_MMA_CTAS_PER_SM) * sm_count();
     if (grid > all) grid = all;
     const long long chunk = (static_cast<long long>(units) * tiles + grid - 1) / grid;
     if (dyn) {

@@ -52,7 +52,6 @@ constexpr int kWarpsM = 4;        // one 16-token block per warp and tile
 constexpr int kThreadsM = kWarpsM * 32;
 constexpr int kCenStride = 132;   // floats per centroid row in shared memory (row r starts 4r banks on)
 constexpr int kTrigStride = 64;   // float2 per row of the sin/cos table (swizzled, see trig_index)
-constexpr int kTrigRowsCompact = 16;  // compact table: angles 8 m f_i (rows m = 0..7) and g f_i (rows 8 + g)
 constexpr int kQStride = 132;     // halfs per query row
 constexpr int kQSets = 2;         // query stored as FP16 hi and lo
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
@@ -72,17 +71,11 @@ constexpr int stages_for() {
     return sizeof(StageM<ML>) <= 12800 ? 3 : 2;
 }
 
-// The sin/cos values a lane keeps in registers are read once from a shared table.  The full table
-// (64 tile offsets x 64 frequencies, 32 KB) is the cheapest to read; layouts whose ring of stages
-// is large use a 16-row table instead (a tile offset j = 8 m + g is the sum of two table angles,
-// the lane combines its rows by angle addition), so that two CTAs still fit one SM.
-template <class ML>
-constexpr bool compact_trig() {
-    return sizeof(StageM<ML>) * stages_for<ML>() > 40000;
-}
+// The sin/cos values a lane keeps in registers are read once from a shared table (64 tile offsets x 64
+// frequencies, 32 KB) that aliases the ring of stages.
 template <class ML>
 constexpr int trig_rows() {
-    return compact_trig<ML>() ? kTrigRowsCompact : kTileM;
+    return kTileM;
 }
 
 // Shared-memory layouts chosen so that the 16-byte loads of a quarter warp
@@ -126,9 +119,18 @@ __device__ __forceinline__ void split_h2(float x0, float x1, uint32_t& hi, uint3
     lo = *reinterpret_cast<const uint32_t*>(&l);
 }
 
+// The sin/cos table is only read once per CTA (into registers, before the first tile is requested), so it
+// shares its memory with the ring of stages.
+template <class ML>
+constexpr size_t stage_region_bytes() {
+    constexpr size_t ring = sizeof(StageM<ML>) * stages_for<ML>();
+    constexpr size_t table = trig_rows<ML>() * kTrigStride * sizeof(float2);
+    return ring > table ? ring : table;
+}
+
 template <int GQA, class ML>
 constexpr size_t smem_bytes(int ck) {
-    return sizeof(StageM<ML>) * stages_for<ML>() + trig_rows<ML>() * kTrigStride * sizeof(float2) +
+    return stage_region_bytes<ML>() +
            static_cast<size_t>(ck) * kCenStride * sizeof(float) + 2 * kQSets * GQA * kQStride * sizeof(__half) +
            kWarpsM * 2 * 16 * sizeof(uint2) + kWarpsM * GQA * kMaxClusters * sizeof(float);
 }
@@ -434,8 +436,12 @@ struct LayoutMmaStructInt4 {
     }
 };
 
+#ifndef RESKV_MMA_CTAS_PER_SM
+#define RESKV_MMA_CTAS_PER_SM 2  // resident CTAs the register allocation aims at (4 warps each)
+#endif
+
 template <int GQA, class ML>
-__global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kThreadsM, RESKV_MMA_CTAS_PER_SM) decode_mma_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int kStages = stages_for<ML>();
     constexpr int kItems = (GQA * 32 + kThreadsM - 1) / kThreadsM;  // query items per thread
@@ -446,8 +452,8 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
     using StageT = StageM<ML>;
     using Field = typename ML::Field;
     StageT* stages = reinterpret_cast<StageT*>(smem_raw);
-    float2* trig = reinterpret_cast<float2*>(smem_raw + sizeof(StageT) * kStages);
-    float* kc_s = reinterpret_cast<float*>(trig + trig_rows<ML>() * kTrigStride);
+    float2* trig = reinterpret_cast<float2*>(smem_raw);  // aliases the stages: dead before the first copy is issued
+    float* kc_s = reinterpret_cast<float*>(smem_raw + stage_region_bytes<ML>());
     __half* qf = reinterpret_cast<__half*>(kc_s + static_cast<size_t>(p.ck) * kCenStride);  // [2 bufs][hi, lo][GQA][kQStride]
     uint2* pre = reinterpret_cast<uint2*>(qf + 2 * kQSets * GQA * kQStride);  // [warps][K, V][16]
     float* beta_s = reinterpret_cast<float*>(pre + kWarpsM * 2 * 16);  // [warps][GQA][64]
@@ -491,16 +497,7 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
     {
         const int i = tid & 63, half = tid >> 6;
         const float f = rope_freq(p.inv_freq, p.theta, i);
-        if constexpr (compact_trig<ML>()) {
-            // half 0 fills rows 0..7 (angle step 8 f), half 1 rows 8..15 (step f)
-            float s1, c1, s = 0.f, c = 1.f;
-            sincosf((half ? 1.f : 8.f) * f, &s1, &c1);
-            for (int r = 0; r < 8; ++r) {
-                trig[(half * 8 + r) * kTrigStride + i] = make_float2(c, s);
-                const float ns = s * c1 + c * s1, nc = c * c1 - s * s1;
-                s = ns, c = nc;
-            }
-        } else {
+        {
             const int j0 = half * 32;
             float s, c, s1, c1;
             sincosf(static_cast<float>(j0) * f, &s, &c);
@@ -529,18 +526,7 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
     // sin/cos of this lane's two rows (tile offsets 16 warp + g and + 8) and 16 frequencies: the
     // same in every tile, so they live in registers for the whole kernel
     float4 trA_r[8], trB_r[8];
-    if constexpr (compact_trig<ML>()) {
-        // row A = tile offset 16 warp + g = 8 (2 warp) + g, row B = 8 (2 warp + 1) + g
-        const float4* fine = reinterpret_cast<const float4*>(trig + (8 + g) * kTrigStride + 16 * qd);
-        const float4* baseA = reinterpret_cast<const float4*>(trig + (2 * warp) * kTrigStride + 16 * qd);
-        const float4* baseB = reinterpret_cast<const float4*>(trig + (2 * warp + 1) * kTrigStride + 16 * qd);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {  // frequencies 16 qd + 2u, + 1 as (cos, sin, cos, sin)
-            const float4 f = fine[u], a = baseA[u], b = baseB[u];
-            trA_r[u] = make_float4(a.x * f.x - a.y * f.y, a.y * f.x + a.x * f.y, a.z * f.z - a.w * f.w, a.w * f.z + a.z * f.w);
-            trB_r[u] = make_float4(b.x * f.x - b.y * f.y, b.y * f.x + b.x * f.y, b.z * f.z - b.w * f.w, b.w * f.z + b.z * f.w);
-        }
-    } else {
+    {
         const int tokA = warp * 16 + g, tokB = tokA + 8;
         const float4* trA = reinterpret_cast<const float4*>(trig + tokA * kTrigStride);
         const float4* trB = reinterpret_cast<const float4*>(trig + tokB * kTrigStride);
@@ -552,6 +538,7 @@ __global__ void __launch_bounds__(kThreadsM, 2) decode_mma_kernel(const DecodePa
         }
     }
 
+    __syncthreads();  // every lane has its sin/cos values: the table's memory becomes the ring of stages
     const float q_mul = p.scaling * kLog2e;
     uint2* pre_k = pre + warp * 32;
     uint2* pre_v = pre_k + 16;
