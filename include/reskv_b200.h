@@ -298,8 +298,12 @@ int reskv_encode_structured_int4(const void* x, const void* centroids, const int
 /* ---- clustering ------------------------------------------------------------------
  * Lloyd iterations per (sequence, KV head); replaces the torch loop of cluster()
  * (reskv/compression.py:19-53: cdist + argmin + one_hot + bmm per iteration).
- * value == 0: FP32 centres, empty clusters keep their centre (K); value != 0:
- * centres rounded to FP16 each iteration, empty clusters become 0 (V).
+ * Bit 0 of `value`: 0 = FP32 centres, empty clusters keep their centre (K); 1 =
+ * centres rounded to FP16 each iteration, empty clusters become 0 (V).  Bit 1 of
+ * `value`: accumulate the cluster sums as 2^24-scaled integers (every mean the
+ * correctly rounded one) instead of the default for up to 32 centres, FP32 partial
+ * sums formed on the tensor cores in a fixed order (same assignments, means within
+ * one FP16 unit in the last place, 2-3x faster; both forms are reproducible).
  * Initial centres are the tokens at linspace(0, tokens-1, clusters).  Writes
  * centroids f16 [B*KH,clusters,128] (after the last update) and ids i32
  * [B*KH,tokens] (from the last assignment, i.e. relative to the centres before

@@ -240,8 +240,9 @@ class CompressionOps(_Ops):
                                                     _stream(x.device)))
         return packed, meta, scale
 
-    def kmeans(self, x, count, iterations, value):
-        """Lloyd clustering -> (centroids f16 [B,H,C,128], ids i32 [B,H,T])."""
+    def kmeans(self, x, count, iterations, value, exact=False):
+        """Lloyd clustering -> (centroids f16 [B,H,C,128], ids i32 [B,H,T]).  ``exact``: accumulate the cluster
+        sums as integers (correctly rounded means) instead of FP32 partial sums on the tensor cores."""
         if x.dtype != torch.float16 or x.ndim != 4 or x.shape[3] != 128 or not x.is_contiguous():
             raise ValueError("kmeans expects contiguous FP16 x[B,H,T,128]")
         _same_device(self.device.index, x)
@@ -252,7 +253,7 @@ class CompressionOps(_Ops):
         ws = torch.empty(need, dtype=torch.uint8, device=x.device)
         centroids = torch.empty((b, h, count, 128), dtype=torch.float16, device=x.device)
         ids = torch.empty((b, h, t), dtype=torch.int32, device=x.device)
-        check(self.lib.reskv_kmeans(x.data_ptr(), b, h, t, t, count, iterations, int(bool(value)), ws.data_ptr(), need,
+        check(self.lib.reskv_kmeans(x.data_ptr(), b, h, t, t, count, iterations, int(bool(value)) | (2 if exact else 0), ws.data_ptr(), need,
                                     centroids.data_ptr(), ids.data_ptr(), _stream(x.device)), launches=1 + 2 * iterations)
         return centroids, ids
 

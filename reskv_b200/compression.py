@@ -31,7 +31,7 @@ def _ops(x: torch.Tensor):
 
 
 @torch.no_grad()
-def cluster(x: torch.Tensor, count: int = 32, iterations: int = 10, *, value: bool = False):
+def cluster(x: torch.Tensor, count: int = 32, iterations: int = 10, *, value: bool = False, exact: bool = False):
     """Lloyd clustering per (sequence, KV head) -> ``(centres f16 [B,H,C,128],
     ids i32 [B,H,T])`` (reference compression.py:19-53).
 
@@ -46,12 +46,16 @@ def cluster(x: torch.Tensor, count: int = 32, iterations: int = 10, *, value: bo
     whatever ``torch.cdist``'s matrix form rounds to, in FP16 for V), and for
     ``T < count`` on the K path the surplus centres repeat tokens instead of
     adding jitter from the global RNG.
+
+    ``exact`` (not in the reference): accumulate the cluster sums as integers, which makes every mean the
+    correctly rounded one.  The default (up to 32 centres) sums FP32 partials on the tensor cores in a fixed
+    order -- equally reproducible, 2-3x faster, means within one FP16 unit in the last place of the exact ones.
     """
     _require_kv(x, "cluster input")
     t = x.shape[2]
     if value:
         count = min(count, t)
-    return _ops(x).kmeans(x.contiguous(), int(count), int(iterations), value)
+    return _ops(x).kmeans(x.contiguous(), int(count), int(iterations), value, exact)
 
 
 @torch.no_grad()

@@ -1,4 +1,6 @@
 // Residual packers: x - centroid[id] -> top-magnitude selection -> compact layout.
+// (The unstructured FP16 bitmap and the unstructured INT4 / INT2 packers run one thread per token and live in
+// compress_topk.cu; this file holds the entry points of all layouts and the kernels of the others.)
 //
 // One warp encodes one token; lane l owns coordinates {l, l+32, l+64, l+96}.
 // With that ownership a warp vote of "lane keeps coordinate l+32i" *is* the
@@ -13,53 +15,10 @@
 // The global top-k of the unstructured layouts is a bisection on the 15-bit key
 // pattern: a vote per owned coordinate counts the keys >= candidate, so no data
 // moves between lanes.
-#include "common.cuh"
+#include "compress_common.cuh"
 
 namespace reskv {
 namespace {
-
-constexpr int kWarpsPerCta = 8;
-constexpr uint32_t kFull = 0xffffffffu;
-
-struct EncodeParams {
-    const __half* x;        // [units, x_stride, 128]
-    const __half* cen;      // [units, clusters, 128]
-    const int32_t* ids;     // [units, tokens]
-    void* payload;          // layout dependent
-    void* meta;             // layout dependent or null
-    __half* scale;          // [units, out_stride] or null
-    int64_t x_stride, out_stride;
-    int units, tokens, clusters, nnz;
-};
-
-// The reference is built with --use_fast_math: `a / b` is the GPU's approximate division (one reciprocal
-// approximation times the numerator, div.approx.ftz.f32) and a division by a constant becomes a multiplication
-// by its rounded reciprocal.  Quantised codes whose exact quotient sits on a rounding boundary depend on that,
-// so the same instruction is issued here (vectors recorded from the reference's kernels on a B200 are matched
-// to the bit, including the tokens whose scale underflows to 0).
-__device__ __forceinline__ float div_fast(float a, float b) {
-    float q;
-    asm("div.approx.ftz.f32 %0, %1, %2;" : "=f"(q) : "f"(a), "f"(b));
-    return q;
-}
-
-// (int)lrintf(x): round to nearest even into 64 bits (saturating; NaN -> INT64_MIN), keep the low 32 bits.
-// Finite quotients are unaffected; +inf becomes -1 and -inf / NaN become 0, which is what the reference's
-// `(int)lrintf(r / 0)` yields for a token whose FP16 scale underflowed (compression.cu:366-367).
-__device__ __forceinline__ int lrint_low32(float x) { return static_cast<int>(__float2ll_rn(x)); }
-
-// Scale of the unstructured quantiser: fp16(amax / QMAX) with the division by the constant done as a
-// multiplication by fp32(1 / QMAX) (compression.cu:354-355 under --use_fast_math); 1 for an all-zero selection.
-template <int QMAX>
-__device__ __forceinline__ __half quant_scale(float amax) {
-    constexpr float kRecip = 1.0f / static_cast<float>(QMAX);
-    return amax > 0.f ? __float2half_rn(amax * kRecip) : __float2half_rn(1.f);
-}
-
-template <int QMAX>
-__device__ __forceinline__ int quant_code(float r, float s) {
-    return max(-QMAX, min(QMAX, lrint_low32(div_fast(r, s))));
-}
 
 struct Residual {
     float r[4];       // fp32 residual of coordinates lane + 32 i
@@ -114,75 +73,6 @@ __device__ __forceinline__ void select_topk(const uint32_t (&key)[4], int k, int
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) vote[i] = __ballot_sync(kFull, keep[i]);
-}
-
-// ---- unstructured FP16: bitmap (MSB first) + packed values ----------------------
-__global__ void __launch_bounds__(kWarpsPerCta * 32) encode_bitmap_fp16_kernel(const EncodeParams p) {
-    const int lane = threadIdx.x & 31;
-    const long long rows = static_cast<long long>(p.units) * p.tokens;
-    for (long long row = static_cast<long long>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5); row < rows;
-         row += static_cast<long long>(gridDim.x) * kWarpsPerCta) {
-        const int unit = static_cast<int>(row / p.tokens), t = static_cast<int>(row % p.tokens);
-        const Residual res = load_residual(p, unit, t, lane);
-        bool keep[4];
-        uint32_t vote[4];
-        select_topk(res.key, p.nnz, lane, keep, vote);
-        const size_t orow = static_cast<size_t>(unit) * p.out_stride + t;
-        __half* pay = static_cast<__half*>(p.payload) + orow * p.nnz;
-        const uint32_t below = (1u << lane) - 1u;
-        int base = 0;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            if (keep[i]) pay[base + __popc(vote[i] & below)] = res.h[i];
-            base += __popc(vote[i]);
-        }
-        if (lane == 0) {
-            // word w of the bitmap: coordinate d at bit 63 - d % 64
-            uint4 bm;
-            bm.y = __brev(vote[0]);
-            bm.x = __brev(vote[1]);
-            bm.w = __brev(vote[2]);
-            bm.z = __brev(vote[3]);
-            static_cast<uint4*>(p.meta)[orow] = bm;
-        }
-    }
-}
-
-// ---- unstructured INT4 / INT2: every coordinate stored, discarded ones as 0 ----------
-template <int BITS>
-__global__ void __launch_bounds__(kWarpsPerCta * 32) encode_quantized_kernel(const EncodeParams p) {
-    constexpr int kQmax = (1 << (BITS - 1)) - 1;
-    constexpr int kPer = 32 / BITS;   // values per word, a power of two <= 16
-    const int lane = threadIdx.x & 31;
-    const long long rows = static_cast<long long>(p.units) * p.tokens;
-    for (long long row = static_cast<long long>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5); row < rows;
-         row += static_cast<long long>(gridDim.x) * kWarpsPerCta) {
-        const int unit = static_cast<int>(row / p.tokens), t = static_cast<int>(row % p.tokens);
-        const Residual res = load_residual(p, unit, t, lane);
-        bool keep[4];
-        uint32_t vote[4];
-        select_topk(res.key, p.nnz, lane, keep, vote);
-        float amax = 0.f;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) amax = fmaxf(amax, keep[i] ? fabsf(res.r[i]) : 0.f);
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, off));
-        const __half hs = quant_scale<kQmax>(amax);
-        const float s = __half2float(hs);
-        const size_t orow = static_cast<size_t>(unit) * p.out_stride + t;
-        int32_t* words = static_cast<int32_t*>(p.payload) + orow * (4 * BITS);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            int q = 0;
-            if (keep[i]) q = quant_code<kQmax>(res.r[i], s);
-            // coordinate d = lane + 32 i sits at bit (d % kPer) * BITS of word d / kPer
-            uint32_t w = (static_cast<uint32_t>(q) & ((1u << BITS) - 1u)) << ((lane % kPer) * BITS);
-#pragma unroll
-            for (int off = 1; off < kPer; off <<= 1) w |= __shfl_xor_sync(kFull, w, off);
-            if (lane % kPer == 0) words[(lane + 32 * i) / kPer] = static_cast<int32_t>(w);
-        }
-        if (lane == 0) p.scale[orow] = hs;
-    }
 }
 
 // ---- compact quantised: bitmap + codes of the retained coordinates only ---------------
@@ -368,9 +258,9 @@ extern "C" int reskv_encode_bitmap_fp16(const void* x, const void* centroids, co
     if (nnz < 1 || nnz > 127) return fail(RESKV_ERR_INVALID, "encode_bitmap_fp16: nnz must be in [1,127], got %d", nnz);
     EncodeParams p{static_cast<const __half*>(x), static_cast<const __half*>(centroids), ids, payload, bitmap, nullptr,
                    x_tok_stride, out_tok_stride, batch * kv_heads, tokens, clusters, nnz};
-    const long long rows = static_cast<long long>(p.units) * tokens;
-    encode_bitmap_fp16_kernel<<<grid_for(rows), kWarpsPerCta * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    return check_cuda(cudaGetLastError(), "encode_bitmap_fp16 launch");
+    if (!aligned16(x) || !aligned16(centroids) || !aligned16(payload))
+        return fail(RESKV_ERR_INVALID, "encode_bitmap_fp16: x, centroids and payload must be 16-byte aligned");
+    return launch_topk_bitmap_fp16(p, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int reskv_encode_quantized(const void* x, const void* centroids, const int32_t* ids, int batch, int kv_heads,
@@ -384,13 +274,9 @@ extern "C" int reskv_encode_quantized(const void* x, const void* centroids, cons
     if (bits != 2 && bits != 4) return fail(RESKV_ERR_INVALID, "encode_quantized: bits must be 2 or 4, got %d", bits);
     EncodeParams p{static_cast<const __half*>(x), static_cast<const __half*>(centroids), ids, words, nullptr,
                    static_cast<__half*>(scale), x_tok_stride, out_tok_stride, batch * kv_heads, tokens, clusters, nnz};
-    const long long rows = static_cast<long long>(p.units) * tokens;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (bits == 4)
-        encode_quantized_kernel<4><<<grid_for(rows), kWarpsPerCta * 32, 0, s>>>(p);
-    else
-        encode_quantized_kernel<2><<<grid_for(rows), kWarpsPerCta * 32, 0, s>>>(p);
-    return check_cuda(cudaGetLastError(), "encode_quantized launch");
+    if (!aligned16(x) || !aligned16(centroids) || !aligned16(words))
+        return fail(RESKV_ERR_INVALID, "encode_quantized: x, centroids and words must be 16-byte aligned");
+    return launch_topk_quantized(p, bits, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int reskv_encode_compact(const void* x, const void* centroids, const int32_t* ids, int batch, int kv_heads,

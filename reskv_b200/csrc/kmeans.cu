@@ -14,6 +14,14 @@
 // the new centres independent of scheduling and equal to the correctly rounded
 // mean -- results are reproducible run to run.
 //
+// That exact accumulation costs ~100 warp instructions per token (128 coordinates x two shared-memory atomics).
+// The default for up to 32 centres is therefore a second form that keeps the exact *assignment* but forms the
+// cluster sums on the tensor cores as onehot(ids)^T . X (the token rows are already in registers as MMA
+// operands; movmatrix turns them into the other operand), FP32 accumulators per warp, warps added in index
+// order, and the CTA's FP32 partial sums flushed as 2^24-scaled integers.  Every step has a fixed order or is
+// an integer addition, so results are still reproducible run to run; the means can differ from the correctly
+// rounded ones by FP32 rounding of the partial sums (checked: within one FP16 unit in the last place).
+//
 // K flavour: FP32 centres, an empty cluster keeps its centre.
 // V flavour: centres rounded to FP16 after every update, an empty cluster becomes 0.
 #include "common.cuh"
@@ -24,7 +32,9 @@ namespace {
 constexpr uint32_t kFull = 0xffffffffu;
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
-constexpr int kChunk = 512;  // tokens per CTA: keeps the split 32-bit counters from overflowing
+constexpr int kChunk = 512;  // tokens per CTA, exact accumulation: keeps the split 32-bit counters from overflowing
+constexpr int kChunkFast = 1024;  // tokens per CTA, tensor-core accumulation (fewer table set-ups)
+constexpr int kRedStride = 132;   // floats per cluster row of the cross-warp reduction buffer
 constexpr float kFix = 16777216.0f;  // 2^24
 
 struct KmeansParams {
@@ -114,19 +124,28 @@ __device__ __forceinline__ int kstep_offset(int ks, int q) { return (ks < 4 ? 0 
 
 // grid (chunks, units).  Tensor-core assignment of the chunk's tokens (see the file header), then
 // exact accumulation of sums and counts.  HILO = centres are FP32 (key flavour): use hi + lo FP16.
-template <bool HILO>
-__global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const KmeansParams p, int padded) {
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
+// FAST: cluster sums on the tensor cores (needs padded <= 32), else exact integer accumulation.
+template <bool HILO, bool FAST>
+__global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const KmeansParams p, int padded, int chunk) {
     extern __shared__ __align__(16) unsigned char smem[];
     float* cen_s = reinterpret_cast<float*>(smem);                              // [C][128] FP32 centres (exact path)
     int* lo_s = reinterpret_cast<int*>(cen_s + p.clusters * kHeadDim);          // [C][128] low 20 bits
     int* hi_s = lo_s + p.clusters * kHeadDim;                                   // [C][128] the rest
-    int* cnt_s = hi_s + p.clusters * kHeadDim;                                  // [C]
+    // FAST reuses the two counter arrays as its FP32 reduction buffer [32][kRedStride] (the host sizes for the larger)
+    const int counter_ints = FAST ? max(2 * p.clusters * kHeadDim, 32 * kRedStride) : 2 * p.clusters * kHeadDim;
+    int* cnt_s = lo_s + counter_ints;                                           // [C]
     float* cn_s = reinterpret_cast<float*>(cnt_s + kMaxClusters);               // [padded] |c|^2, +inf for padding
     __half* ch_s = reinterpret_cast<__half*>(cn_s + kMaxClusters);              // [padded][132] FP16 hi
     __half* cl_s = ch_s + padded * kCenHalfStride;                              // [padded][132] FP16 lo (HILO)
     __shared__ float cmax_s;
     const int unit = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, q = lane & 3;
-    const int t_begin = blockIdx.x * kChunk, t_end = min(p.tokens, t_begin + kChunk);
+    const int t_begin = blockIdx.x * chunk, t_end = min(p.tokens, t_begin + chunk);
     const float* cen_g = p.centres + static_cast<size_t>(unit) * p.clusters * kHeadDim;
     for (int i = tid; i < p.clusters * kHeadDim; i += kThreads) {
         cen_s[i] = cen_g[i];
@@ -166,6 +185,15 @@ __global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const Kmean
     __syncthreads();
     const float cmax = cmax_s;
     const __half* xu = p.x + static_cast<size_t>(unit) * p.x_stride * kHeadDim;
+    // FAST: sums[cluster 16 mb + g (+8)][coordinate kstep_offset(ks, q) + 2 h + (0, 1)] of this warp's tokens,
+    // n-block nb = 2 ks + h
+    float acc_s[FAST ? 2 : 1][FAST ? 16 : 1][4];
+    if constexpr (FAST) {
+#pragma unroll
+        for (int mb = 0; mb < 2; ++mb)
+#pragma unroll
+            for (int nb = 0; nb < 16; ++nb) acc_s[mb][nb][0] = acc_s[mb][nb][1] = acc_s[mb][nb][2] = acc_s[mb][nb][3] = 0.f;
+    }
 
     for (int t0 = t_begin + warp * 16; t0 < t_end; t0 += kWarps * 16) {
         // A fragments: rows t0 + g and t0 + g + 8, the lane's 32 coordinates of each
@@ -266,6 +294,41 @@ __global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const Kmean
             if (r0 < t_end) p.ids[static_cast<size_t>(unit) * p.tokens + r0] = c1[0];
             if (r1 < t_end) p.ids[static_cast<size_t>(unit) * p.tokens + r1] = c1[1];
         }
+        if constexpr (FAST) {
+            // onehot(ids)^T . X: A = one-hot rows (cluster x token) from a packed FP16 compare of the ids, B = the
+            // token rows transposed (movmatrix of the A fragments of the distance step); rows beyond the end are 0
+            const int v0 = r0 < t_end ? c1[0] : -1, v1 = r1 < t_end ? c1[1] : -1;
+            const int w0 = __shfl_sync(kFull, v0, 8 * q), w1 = __shfl_sync(kFull, v0, 8 * q + 4);
+            const int w2 = __shfl_sync(kFull, v1, 8 * q), w3 = __shfl_sync(kFull, v1, 8 * q + 4);
+            const __half2 gg = __half2half2(__int2half_rn(g));
+            const __half2 d01 = __hsub2(__halves2half2(__int2half_rn(w0), __int2half_rn(w1)), gg);
+            const __half2 d23 = __hsub2(__halves2half2(__int2half_rn(w2), __int2half_rn(w3)), gg);
+            uint32_t oh[2][4];
+#pragma unroll
+            for (int mb = 0; mb < 2; ++mb) {
+                const __half2 lo = __float2half2_rn(16.f * mb), hi = __float2half2_rn(16.f * mb + 8.f);
+                const __half2 e0 = __heq2(d01, lo), e1 = __heq2(d01, hi), e2 = __heq2(d23, lo), e3 = __heq2(d23, hi);
+                oh[mb][0] = *reinterpret_cast<const uint32_t*>(&e0), oh[mb][1] = *reinterpret_cast<const uint32_t*>(&e1);
+                oh[mb][2] = *reinterpret_cast<const uint32_t*>(&e2), oh[mb][3] = *reinterpret_cast<const uint32_t*>(&e3);
+            }
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                const uint32_t b00 = movmatrix_trans(a[ks][0]), b01 = movmatrix_trans(a[ks][1]);
+                const uint32_t b10 = movmatrix_trans(a[ks][2]), b11 = movmatrix_trans(a[ks][3]);
+#pragma unroll
+                for (int mb = 0; mb < 2; ++mb) {
+                    if (16 * mb < padded) {
+                        mma_f16(acc_s[mb][2 * ks], oh[mb][0], oh[mb][1], oh[mb][2], oh[mb][3], b00, b01);
+                        mma_f16(acc_s[mb][2 * ks + 1], oh[mb][0], oh[mb][1], oh[mb][2], oh[mb][3], b10, b11);
+                    }
+                }
+            }
+            if (q == 0) {
+                if (r0 < t_end) atomicAdd(&cnt_s[c1[0]], 1);
+                if (r1 < t_end) atomicAdd(&cnt_s[c1[1]], 1);
+            }
+            continue;
+        }
         // exact accumulation, one token at a time with the warp across its coordinates
         const int rows = min(16, t_end - t0);
         for (int r = 0; r < rows; ++r) {
@@ -286,6 +349,36 @@ __global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const Kmean
     }
     __syncthreads();
     long long* sums_g = p.sums + static_cast<size_t>(unit) * p.clusters * kHeadDim;
+    if constexpr (FAST) {
+        // warps add their partial sums in index order into one buffer (the integer counters' memory, unused
+        // in this form), then the CTA's sums go out as 2^24-scaled integers
+        float* red = reinterpret_cast<float*>(lo_s);  // [32][kRedStride] <= 2 * [C][128] ints
+        for (int w = 0; w < kWarps; ++w) {
+            if (warp == w) {
+#pragma unroll
+                for (int mb = 0; mb < 2; ++mb)
+#pragma unroll
+                    for (int nb = 0; nb < 16; ++nb)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int cl = 16 * mb + g + 8 * (e >> 1);
+                            const int d = kstep_offset(nb >> 1, q) + 2 * (nb & 1) + (e & 1);
+                            float* slot = red + cl * kRedStride + d;
+                            *slot = (w == 0) ? acc_s[mb][nb][e] : *slot + acc_s[mb][nb][e];
+                        }
+            }
+            __syncthreads();
+        }
+        for (int i = tid; i < p.clusters * kHeadDim; i += kThreads) {
+            const int cl = i / kHeadDim, d = i % kHeadDim;
+            if (cnt_s[cl] > 0)
+                atomicAdd(reinterpret_cast<unsigned long long*>(sums_g + i),
+                          static_cast<unsigned long long>(__float2ll_rn(red[cl * kRedStride + d] * kFix)));
+        }
+        for (int c = tid; c < p.clusters; c += kThreads)
+            if (cnt_s[c] > 0) atomicAdd(&p.counts[unit * p.clusters + c], cnt_s[c]);
+        return;
+    }
     for (int i = tid; i < p.clusters * kHeadDim; i += kThreads) {
         if (cnt_s[i / kHeadDim] > 0) {
             const long long v = static_cast<long long>(hi_s[i]) * 1048576LL + lo_s[i];
@@ -414,21 +507,31 @@ extern "C" int reskv_kmeans(const void* x, int batch, int kv_heads, int tokens, 
         // fewer tokens than centres: every token once, then tokens repeated in order
         for (int c = 0; c < clusters; ++c) init.idx[c] = c % tokens;
     }
+    // `value`: bit 0 = V flavour, bit 1 = exact (integer) accumulation of the cluster sums
+    const bool exact = (value & 2) != 0;
+    value &= 1;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     kmeans_init_kernel<<<units, 256, 0, s>>>(p, init, value);
     const int padded = (clusters + 7) / 8 * 8;
-    const size_t smem = static_cast<size_t>(clusters) * kHeadDim * (sizeof(float) + 2 * sizeof(int)) +
+    // the integer-counter arrays double as the FP32 reduction buffer [32][kRedStride] of the tensor-core form
+    size_t counters = static_cast<size_t>(clusters) * kHeadDim * 2 * sizeof(int);
+    const bool fast = !exact && padded <= 32;
+    if (fast && counters < 32 * kRedStride * sizeof(float)) counters = 32 * kRedStride * sizeof(float);
+    const size_t smem = static_cast<size_t>(clusters) * kHeadDim * sizeof(float) + counters +
                         kMaxClusters * (sizeof(int) + sizeof(float)) +
                         static_cast<size_t>(padded) * kCenHalfStride * sizeof(__half) * (value ? 1 : 2);
-    auto kernel = value ? kmeans_assign_mma_kernel<false> : kmeans_assign_mma_kernel<true>;
+    void (*kernel)(const KmeansParams, int, int) =
+        fast ? (value ? kmeans_assign_mma_kernel<false, true> : kmeans_assign_mma_kernel<true, true>)
+             : (value ? kmeans_assign_mma_kernel<false, false> : kmeans_assign_mma_kernel<true, false>);
     if (smem > 48 * 1024) {
         if (int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
                                 "cudaFuncSetAttribute(kmeans_assign)"))
             return rc;
     }
-    const dim3 grid((tokens + kChunk - 1) / kChunk, units);
+    const int chunk = fast ? kChunkFast : kChunk;
+    const dim3 grid((tokens + chunk - 1) / chunk, units);
     for (int it = 0; it < iterations; ++it) {
-        kernel<<<grid, kThreads, smem, s>>>(p, padded);
+        kernel<<<grid, kThreads, smem, s>>>(p, padded, chunk);
         kmeans_update_kernel<<<units, 256, 0, s>>>(p, value, it + 1 == iterations ? static_cast<__half*>(centroids) : nullptr);
     }
     return check_cuda(cudaGetLastError(), "kmeans launch");

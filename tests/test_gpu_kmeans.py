@@ -12,10 +12,10 @@ DEV = "cuda"
 NEAR_TIE = 1e-5  # relative gap of the two smallest squared distances below which FP32 may pick either
 
 
-def _cluster(x, count, iters, value=False):
+def _cluster(x, count, iters, value=False, exact=False):
     from reskv_b200.compression import cluster
 
-    cen, ids = cluster(x.to(DEV), count, iters, value=value)
+    cen, ids = cluster(x.to(DEV), count, iters, value=value, exact=exact)
     torch.cuda.synchronize()
     return np16(cen), np16(ids)
 
@@ -29,12 +29,31 @@ def test_single_iteration_is_exact(value, count):
     from reskv_b200.synthetic import mixture
 
     x = mixture(2, 2, 700, seed=count, clusters=7)
-    cen, ids = _cluster(x, count, 1, value)
+    cen, ids = _cluster(x, count, 1, value, exact=True)
     want_c, want_i, margin = okm.cluster(np16(x), count, 1, value=value)
     diff = ids != want_i
     assert (margin[diff] < NEAR_TIE).all(), f"{diff.sum()} assignments differ beyond near-ties"
     if not diff.any():
         assert np.array_equal(cen.view(np.uint16), want_c.view(np.uint16))
+
+
+@pytest.mark.parametrize("value", [False, True])
+@pytest.mark.parametrize("count,tokens", [(1, 700), (8, 700), (32, 700), (32, 3000), (20, 1025)])
+def test_tensor_core_sums_stay_within_one_fp16_ulp_of_the_exact_means(value, count, tokens):
+    """The default accumulation (one-hot x tokens on the tensor cores, FP32 partial sums in a fixed order): same
+    assignments as the exact form after one iteration, every centre coordinate within one FP16 unit in the last
+    place of the correctly rounded mean, and reproducible run to run."""
+    from reskv_b200.synthetic import mixture
+
+    x = mixture(2, 2, tokens, seed=count + tokens, clusters=7)
+    exact_c, exact_i = _cluster(x, count, 1, value, exact=True)
+    fast_c, fast_i = _cluster(x, count, 1, value)
+    assert np.array_equal(fast_i, exact_i)
+    a, b = fast_c.astype(np.float32), exact_c.astype(np.float32)
+    assert (np.abs(a - b) <= np.spacing(np.abs(exact_c)).astype(np.float32)).all()
+    assert (fast_c.view(np.uint16) != exact_c.view(np.uint16)).mean() < 0.02
+    again_c, again_i = _cluster(x, count, 1, value)
+    assert np.array_equal(again_c.view(np.uint16), fast_c.view(np.uint16)) and np.array_equal(again_i, fast_i)
 
 
 @pytest.mark.parametrize("value", [False, True])
