@@ -11,9 +11,9 @@
 //   * the thread forms r = fp32(x) - fp32(c) and keeps the 128 selection keys |fp16(r)| as 64 packed pairs;
 //     the pairing is (coordinate a + 16 in the low half, coordinate a in the high half), which makes the
 //     masks of the packed comparisons fall straight onto the MSB-first bitmap words;
-//   * the k-th largest key is found by bisection on its 15 bits: a round is 64 packed comparisons whose
-//     all-ones / all-zeros half masks are subtracted from one 32-bit accumulator (the two 16-bit counters
-//     are recovered from it afterwards), i.e. about 1.5 instructions per key pair and round;
+//   * the k-th largest key is found by bisection on its 15 bits: a round is 64 packed comparisons (1.0 / 0.0
+//     per half, integer pipe) summed by packed FP16 additions (floating-point pipe), two instructions per key
+//     pair and round on two different pipes;
 //   * ties at the threshold keep the lower coordinates; the kept FP16 residuals are compacted in place in
 //     the thread's own row and the warp writes the 32 rows out with 16-byte stores.
 //
@@ -67,11 +67,15 @@ __device__ __forceinline__ void select_topk_thread(const uint32_t (&key)[64], in
     for (int bit = 14; bit >= 0; --bit) {
         const uint32_t cand = v | (1u << bit);
         const __half2 c2 = as_half2(cand | (cand << 16));
-        // acc = -(sum of masks): low half counts the true low halves, high half = (true high) - (true low)
-        uint32_t acc = 0;
+        // the comparisons (1.0 / 0.0 per half) issue on the integer pipe, their sums on the FP16 pipe; counts up
+        // to 128 are exact in FP16; four accumulators keep the addition chains short
+        __half2 acc[4];
 #pragma unroll
-        for (int j = 0; j < 64; j += 2) acc = acc - __hge2_mask(as_half2(key[j]), c2) - __hge2_mask(as_half2(key[j + 1]), c2);
-        const int cnt = static_cast<int>((2u * (acc & 0xffffu) + (acc >> 16)) & 0xffffu);
+        for (int u = 0; u < 4; ++u) acc[u] = __hge2(as_half2(key[u]), c2);
+#pragma unroll
+        for (int j = 4; j < 64; ++j) acc[j & 3] = __hadd2(acc[j & 3], __hge2(as_half2(key[j]), c2));
+        const __half2 total = __hadd2(__hadd2(acc[0], acc[1]), __hadd2(acc[2], acc[3]));
+        const int cnt = __half2int_rn(__hadd(__low2half(total), __high2half(total)));
         if (cnt >= k) v = cand, n_ge = cnt;
     }
     const __half2 v2 = as_half2(v | (v << 16));

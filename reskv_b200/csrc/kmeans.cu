@@ -33,7 +33,7 @@ constexpr uint32_t kFull = 0xffffffffu;
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 constexpr int kChunk = 512;  // tokens per CTA, exact accumulation: keeps the split 32-bit counters from overflowing
-constexpr int kChunkFast = 1024;  // tokens per CTA, tensor-core accumulation (fewer table set-ups)
+constexpr int kChunkFastMax = 4096;  // most tokens per CTA with tensor-core accumulation
 constexpr int kRedStride = 132;   // floats per cluster row of the cross-warp reduction buffer
 constexpr float kFix = 16777216.0f;  // 2^24
 
@@ -137,8 +137,8 @@ __global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const Kmean
     float* cen_s = reinterpret_cast<float*>(smem);                              // [C][128] FP32 centres (exact path)
     int* lo_s = reinterpret_cast<int*>(cen_s + p.clusters * kHeadDim);          // [C][128] low 20 bits
     int* hi_s = lo_s + p.clusters * kHeadDim;                                   // [C][128] the rest
-    // FAST reuses the two counter arrays as its FP32 reduction buffer [32][kRedStride] (the host sizes for the larger)
-    const int counter_ints = FAST ? max(2 * p.clusters * kHeadDim, 32 * kRedStride) : 2 * p.clusters * kHeadDim;
+    // FAST uses the counter arrays' place for its FP32 reduction slabs [warps][32][kRedStride] (sized by the host)
+    const int counter_ints = FAST ? kWarps * 32 * kRedStride : 2 * p.clusters * kHeadDim;
     int* cnt_s = lo_s + counter_ints;                                           // [C]
     float* cn_s = reinterpret_cast<float*>(cnt_s + kMaxClusters);               // [padded] |c|^2, +inf for padding
     __half* ch_s = reinterpret_cast<__half*>(cn_s + kMaxClusters);              // [padded][132] FP16 hi
@@ -231,29 +231,43 @@ __global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const Kmean
         }
         float d1[2] = {INFINITY, INFINITY}, d2[2] = {INFINITY, INFINITY};
         int c1[2] = {0, 0};
-        for (int nb = 0; nb < padded / 8; ++nb) {
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            const __half* hrow = ch_s + (nb * 8 + g) * kCenHalfStride;
-            const __half* lrow = cl_s + (nb * 8 + g) * kCenHalfStride;
+        // two centre blocks at a time: their accumulation chains are independent, which keeps the tensor pipe fed
+        // with few resident warps
+        for (int nb0 = 0; nb0 < padded / 8; nb0 += 2) {
+            float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            const bool two = nb0 + 1 < padded / 8;
+            const int nb1 = two ? nb0 + 1 : nb0;
+            const __half* hrow0 = ch_s + (nb0 * 8 + g) * kCenHalfStride;
+            const __half* lrow0 = cl_s + (nb0 * 8 + g) * kCenHalfStride;
+            const __half* hrow1 = ch_s + (nb1 * 8 + g) * kCenHalfStride;
+            const __half* lrow1 = cl_s + (nb1 * 8 + g) * kCenHalfStride;
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
-                const uint2 bh = *reinterpret_cast<const uint2*>(hrow + kstep_offset(ks, q));
-                mma_f16(acc, a[ks][0], a[ks][1], a[ks][2], a[ks][3], bh.x, bh.y);
+                const uint2 bh0 = *reinterpret_cast<const uint2*>(hrow0 + kstep_offset(ks, q));
+                const uint2 bh1 = *reinterpret_cast<const uint2*>(hrow1 + kstep_offset(ks, q));
+                mma_f16(acc[0], a[ks][0], a[ks][1], a[ks][2], a[ks][3], bh0.x, bh0.y);
+                mma_f16(acc[1], a[ks][0], a[ks][1], a[ks][2], a[ks][3], bh1.x, bh1.y);
                 if (HILO) {
-                    const uint2 bl = *reinterpret_cast<const uint2*>(lrow + kstep_offset(ks, q));
-                    mma_f16(acc, a[ks][0], a[ks][1], a[ks][2], a[ks][3], bl.x, bl.y);
+                    const uint2 bl0 = *reinterpret_cast<const uint2*>(lrow0 + kstep_offset(ks, q));
+                    const uint2 bl1 = *reinterpret_cast<const uint2*>(lrow1 + kstep_offset(ks, q));
+                    mma_f16(acc[0], a[ks][0], a[ks][1], a[ks][2], a[ks][3], bl0.x, bl0.y);
+                    mma_f16(acc[1], a[ks][0], a[ks][1], a[ks][2], a[ks][3], bl1.x, bl1.y);
                 }
             }
-            const int col = nb * 8 + 2 * q;
-            const float n0 = cn_s[col], n1 = cn_s[col + 1];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int r = e >> 1, c = col + (e & 1);
-                const float d = fmaf(-2.f, acc[e], (e & 1) ? n1 : n0);
-                if (d < d1[r]) {
-                    d2[r] = d1[r], d1[r] = d, c1[r] = c;
-                } else if (d < d2[r]) {
-                    d2[r] = d;
+            for (int h = 0; h < 2; ++h) {
+                if (h == 1 && !two) break;
+                const int col = (nb0 + h) * 8 + 2 * q;
+                const float n0 = cn_s[col], n1 = cn_s[col + 1];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int r = e >> 1, c = col + (e & 1);
+                    const float d = fmaf(-2.f, acc[h][e], (e & 1) ? n1 : n0);
+                    if (d < d1[r]) {
+                        d2[r] = d1[r], d1[r] = d, c1[r] = c;
+                    } else if (d < d2[r]) {
+                        d2[r] = d;
+                    }
                 }
             }
         }
@@ -350,30 +364,33 @@ __global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const Kmean
     __syncthreads();
     long long* sums_g = p.sums + static_cast<size_t>(unit) * p.clusters * kHeadDim;
     if constexpr (FAST) {
-        // warps add their partial sums in index order into one buffer (the integer counters' memory, unused
-        // in this form), then the CTA's sums go out as 2^24-scaled integers
-        float* red = reinterpret_cast<float*>(lo_s);  // [32][kRedStride] <= 2 * [C][128] ints
-        for (int w = 0; w < kWarps; ++w) {
-            if (warp == w) {
+        // every warp stores its partial sums in a slab of its own (the integer counters' memory, unused in this
+        // form, enlarged by the host); the slabs are added in warp order and the CTA's sums go out as 2^24-scaled
+        // integers
+        float* red = reinterpret_cast<float*>(lo_s);  // [warps][32][kRedStride]
+        {
+            float* mine = red + warp * 32 * kRedStride;
 #pragma unroll
-                for (int mb = 0; mb < 2; ++mb)
+            for (int mb = 0; mb < 2; ++mb)
 #pragma unroll
-                    for (int nb = 0; nb < 16; ++nb)
+                for (int nb = 0; nb < 16; ++nb)
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int cl = 16 * mb + g + 8 * (e >> 1);
-                            const int d = kstep_offset(nb >> 1, q) + 2 * (nb & 1) + (e & 1);
-                            float* slot = red + cl * kRedStride + d;
-                            *slot = (w == 0) ? acc_s[mb][nb][e] : *slot + acc_s[mb][nb][e];
-                        }
-            }
-            __syncthreads();
+                    for (int e = 0; e < 4; e += 2) {
+                        const int cl = 16 * mb + g + 8 * (e >> 1);
+                        const int d = kstep_offset(nb >> 1, q) + 2 * (nb & 1);
+                        *reinterpret_cast<float2*>(mine + cl * kRedStride + d) = make_float2(acc_s[mb][nb][e], acc_s[mb][nb][e + 1]);
+                    }
         }
+        __syncthreads();
         for (int i = tid; i < p.clusters * kHeadDim; i += kThreads) {
             const int cl = i / kHeadDim, d = i % kHeadDim;
-            if (cnt_s[cl] > 0)
+            if (cnt_s[cl] > 0) {
+                float sum = 0.f;
+#pragma unroll
+                for (int w = 0; w < kWarps; ++w) sum += red[(w * 32 + cl) * kRedStride + d];  // fixed order
                 atomicAdd(reinterpret_cast<unsigned long long*>(sums_g + i),
-                          static_cast<unsigned long long>(__float2ll_rn(red[cl * kRedStride + d] * kFix)));
+                          static_cast<unsigned long long>(__float2ll_rn(sum * kFix)));
+            }
         }
         for (int c = tid; c < p.clusters; c += kThreads)
             if (cnt_s[c] > 0) atomicAdd(&p.counts[unit * p.clusters + c], cnt_s[c]);
@@ -516,7 +533,7 @@ extern "C" int reskv_kmeans(const void* x, int batch, int kv_heads, int tokens, 
     // the integer-counter arrays double as the FP32 reduction buffer [32][kRedStride] of the tensor-core form
     size_t counters = static_cast<size_t>(clusters) * kHeadDim * 2 * sizeof(int);
     const bool fast = !exact && padded <= 32;
-    if (fast && counters < 32 * kRedStride * sizeof(float)) counters = 32 * kRedStride * sizeof(float);
+    if (fast) counters = static_cast<size_t>(kWarps) * 32 * kRedStride * sizeof(float);
     const size_t smem = static_cast<size_t>(clusters) * kHeadDim * sizeof(float) + counters +
                         kMaxClusters * (sizeof(int) + sizeof(float)) +
                         static_cast<size_t>(padded) * kCenHalfStride * sizeof(__half) * (value ? 1 : 2);
@@ -528,7 +545,13 @@ extern "C" int reskv_kmeans(const void* x, int batch, int kv_heads, int tokens, 
                                 "cudaFuncSetAttribute(kmeans_assign)"))
             return rc;
     }
-    const int chunk = fast ? kChunkFast : kChunk;
+    // tensor-core form: as many tokens per CTA as still leave about two CTAs per SM (set-up and the final
+    // reduction are per CTA), between kChunk and kChunkFastMax
+    int chunk = kChunk;
+    if (fast) {
+        const long long want = static_cast<long long>(units) * tokens / (2ll * sm_count());
+        chunk = static_cast<int>(want < kChunk ? kChunk : want > kChunkFastMax ? kChunkFastMax : (want + 127) / 128 * 128);
+    }
     const dim3 grid((tokens + chunk - 1) / chunk, units);
     for (int it = 0; it < iterations; ++it) {
         kernel<<<grid, kThreads, smem, s>>>(p, padded, chunk);

@@ -14,13 +14,27 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 from transformers import LlamaForCausalLM
-from transformers.models.llama.modeling_llama import LlamaAttention, apply_rotary_pos_emb
+from transformers.models.llama.modeling_llama import LlamaAttention, LlamaMLP, apply_rotary_pos_emb
 
 from .._attention import attention
 from ..cache import ResKVCache
 from ..config import ResKVKernelConfig, _model_settings
 
 _SUPPORTED_ROPE = ("default", "llama3", "linear")
+
+
+class ResKVMLP(LlamaMLP):
+    """Feed-forward block for inference: the up projection is multiplied into the activated gate in place, so
+    one ``[..., intermediate]`` temporary lives at a time instead of two (same role as the reference's class
+    of this name, reskv/models/llama.py:14-22).  Whenever autograd is recording, or in training mode, it is the
+    stock ``LlamaMLP`` -- the in-place product would destroy a tensor the backward pass needs."""
+
+    def forward(self, x):
+        if self.training or torch.is_grad_enabled():
+            return super().forward(x)
+        hidden = self.act_fn(self.gate_proj(x))
+        hidden *= self.up_proj(x)
+        return self.down_proj(hidden)
 
 
 class ResKVAttention(LlamaAttention):
@@ -94,6 +108,7 @@ class ResKVForCausalLM(LlamaForCausalLM):
         self.kernel_config = settings
         for index, block in enumerate(self.model.layers):
             block.self_attn = ResKVAttention(config, index)
+            block.mlp = ResKVMLP(config)
         self.post_init()
 
     @classmethod

@@ -51,6 +51,14 @@ def test_reference_config_tests(tmp_path):
 
 
 @needs_checkout
+def test_reference_mlp_tests(tmp_path):
+    """``tests/test_mlp.py`` of the reference (equality with the stock MLP, gradients untouched); its one
+    CUDA case is skipped on a machine without a GPU."""
+    counts, failed, tail = _run("test_mlp.py", tmp_path)
+    assert not failed and counts.get("error", 0) == 0 and counts.get("passed", 0) >= 3, tail
+
+
+@needs_checkout
 @pytest.mark.gpu
 def test_reference_cuda_tests(tmp_path):
     counts, failed, tail = _run("test_cuda.py", tmp_path)
