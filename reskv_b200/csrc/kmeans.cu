@@ -35,6 +35,7 @@ constexpr int kThreads = kWarps * 32;
 constexpr int kChunk = 512;  // tokens per CTA, exact accumulation: keeps the split 32-bit counters from overflowing
 constexpr int kChunkFastMax = 4096;  // most tokens per CTA with tensor-core accumulation
 constexpr int kRedStride = 132;   // floats per cluster row of the cross-warp reduction buffer
+constexpr int kXsRow = 2 * kHeadDim + 16;  // bytes per staged token row (16-byte loads of eight lanes in distinct banks)
 constexpr float kFix = 16777216.0f;  // 2^24
 
 struct KmeansParams {
@@ -195,19 +196,43 @@ __global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const Kmean
             for (int nb = 0; nb < 16; ++nb) acc_s[mb][nb][0] = acc_s[mb][nb][1] = acc_s[mb][nb][2] = acc_s[mb][nb][3] = 0.f;
     }
 
+    // FAST: the warp's next 16 token rows travel to shared memory (16-byte asynchronous copies, rows 16 bytes
+    // apart from dense) while the current block is being processed; the block is read into registers at the
+    // top of the loop, which frees the buffer for the copy of the one after
+    unsigned char* xs_w = reinterpret_cast<unsigned char*>(cl_s + (HILO ? padded * kCenHalfStride : 0)) + warp * 16 * kXsRow;
+    auto stage_rows = [&](int t0) {
+        const int n = min(16, t_end - t0);
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(xu + static_cast<size_t>(t0) * kHeadDim);
+        for (int i = lane; i < n * 16; i += 32) cp_async16(xs_w + (i >> 4) * kXsRow + (i & 15) * 16, src + i * 16);
+    };
+    if constexpr (FAST) {
+        if (t_begin + warp * 16 < t_end) stage_rows(t_begin + warp * 16);
+    }
+
     for (int t0 = t_begin + warp * 16; t0 < t_end; t0 += kWarps * 16) {
         // A fragments: rows t0 + g and t0 + g + 8, the lane's 32 coordinates of each
         const int r0 = t0 + g, r1 = t0 + g + 8;
         uint32_t a[8][4];
         {
             uint4 v[2][4];
+            if constexpr (FAST) {
+                asm volatile("cp.async.wait_all;" ::: "memory");
+                __syncwarp();
+            }
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 const int row = r ? r1 : r0;
-                const uint4* src = reinterpret_cast<const uint4*>(xu + static_cast<size_t>(row) * kHeadDim);
+                const uint4* src = FAST ? reinterpret_cast<const uint4*>(xs_w + (g + 8 * r) * kXsRow)
+                                        : reinterpret_cast<const uint4*>(xu + static_cast<size_t>(row) * kHeadDim);
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    v[r][k] = row < t_end ? __ldg(src + (k < 2 ? 0 : 8) + 2 * q + (k & 1)) : make_uint4(0, 0, 0, 0);
+                for (int k = 0; k < 4; ++k) {
+                    const uint4* at = src + (k < 2 ? 0 : 8) + 2 * q + (k & 1);
+                    v[r][k] = row < t_end ? (FAST ? *at : __ldg(at)) : make_uint4(0, 0, 0, 0);
+                }
+            }
+            if constexpr (FAST) {
+                __syncwarp();  // every lane has its rows in registers
+                if (t0 + kWarps * 16 < t_end) stage_rows(t0 + kWarps * 16);
             }
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
@@ -231,32 +256,38 @@ __global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const Kmean
         }
         float d1[2] = {INFINITY, INFINITY}, d2[2] = {INFINITY, INFINITY};
         int c1[2] = {0, 0};
-        // two centre blocks at a time: their accumulation chains are independent, which keeps the tensor pipe fed
-        // with few resident warps
-        for (int nb0 = 0; nb0 < padded / 8; nb0 += 2) {
-            float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-            const bool two = nb0 + 1 < padded / 8;
-            const int nb1 = two ? nb0 + 1 : nb0;
-            const __half* hrow0 = ch_s + (nb0 * 8 + g) * kCenHalfStride;
-            const __half* lrow0 = cl_s + (nb0 * 8 + g) * kCenHalfStride;
-            const __half* hrow1 = ch_s + (nb1 * 8 + g) * kCenHalfStride;
-            const __half* lrow1 = cl_s + (nb1 * 8 + g) * kCenHalfStride;
+        // four centre blocks at a time: their accumulation chains are independent, which keeps the tensor pipe fed
+        // with few resident warps (blocks beyond the padded count repeat the last one and are ignored)
+        constexpr int kChains = 4;
+        for (int nb0 = 0; nb0 < padded / 8; nb0 += kChains) {
+            float acc[kChains][4];
+            const __half* hrow[kChains];
+            const __half* lrow[kChains];
+#pragma unroll
+            for (int h = 0; h < kChains; ++h) {
+                acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.f;
+                const int nb = min(nb0 + h, padded / 8 - 1);
+                hrow[h] = ch_s + (nb * 8 + g) * kCenHalfStride;
+                lrow[h] = cl_s + (nb * 8 + g) * kCenHalfStride;
+            }
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
-                const uint2 bh0 = *reinterpret_cast<const uint2*>(hrow0 + kstep_offset(ks, q));
-                const uint2 bh1 = *reinterpret_cast<const uint2*>(hrow1 + kstep_offset(ks, q));
-                mma_f16(acc[0], a[ks][0], a[ks][1], a[ks][2], a[ks][3], bh0.x, bh0.y);
-                mma_f16(acc[1], a[ks][0], a[ks][1], a[ks][2], a[ks][3], bh1.x, bh1.y);
+#pragma unroll
+                for (int h = 0; h < kChains; ++h) {
+                    const uint2 bh = *reinterpret_cast<const uint2*>(hrow[h] + kstep_offset(ks, q));
+                    mma_f16(acc[h], a[ks][0], a[ks][1], a[ks][2], a[ks][3], bh.x, bh.y);
+                }
                 if (HILO) {
-                    const uint2 bl0 = *reinterpret_cast<const uint2*>(lrow0 + kstep_offset(ks, q));
-                    const uint2 bl1 = *reinterpret_cast<const uint2*>(lrow1 + kstep_offset(ks, q));
-                    mma_f16(acc[0], a[ks][0], a[ks][1], a[ks][2], a[ks][3], bl0.x, bl0.y);
-                    mma_f16(acc[1], a[ks][0], a[ks][1], a[ks][2], a[ks][3], bl1.x, bl1.y);
+#pragma unroll
+                    for (int h = 0; h < kChains; ++h) {
+                        const uint2 bl = *reinterpret_cast<const uint2*>(lrow[h] + kstep_offset(ks, q));
+                        mma_f16(acc[h], a[ks][0], a[ks][1], a[ks][2], a[ks][3], bl.x, bl.y);
+                    }
                 }
             }
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                if (h == 1 && !two) break;
+            for (int h = 0; h < kChains; ++h) {
+                if (nb0 + h >= padded / 8) break;
                 const int col = (nb0 + h) * 8 + 2 * q;
                 const float n0 = cn_s[col], n1 = cn_s[col + 1];
 #pragma unroll
@@ -532,11 +563,12 @@ extern "C" int reskv_kmeans(const void* x, int batch, int kv_heads, int tokens, 
     const int padded = (clusters + 7) / 8 * 8;
     // the integer-counter arrays double as the FP32 reduction buffer [32][kRedStride] of the tensor-core form
     size_t counters = static_cast<size_t>(clusters) * kHeadDim * 2 * sizeof(int);
-    const bool fast = !exact && padded <= 32;
+    const bool fast = !exact && padded <= 32 && aligned16(x);  // the row staging copies 16-byte pieces
     if (fast) counters = static_cast<size_t>(kWarps) * 32 * kRedStride * sizeof(float);
     const size_t smem = static_cast<size_t>(clusters) * kHeadDim * sizeof(float) + counters +
                         kMaxClusters * (sizeof(int) + sizeof(float)) +
-                        static_cast<size_t>(padded) * kCenHalfStride * sizeof(__half) * (value ? 1 : 2);
+                        static_cast<size_t>(padded) * kCenHalfStride * sizeof(__half) * (value ? 1 : 2) +
+                        (fast ? static_cast<size_t>(kWarps) * 16 * kXsRow : 0);
     void (*kernel)(const KmeansParams, int, int) =
         fast ? (value ? kmeans_assign_mma_kernel<false, true> : kmeans_assign_mma_kernel<true, true>)
              : (value ? kmeans_assign_mma_kernel<false, false> : kmeans_assign_mma_kernel<true, false>);
