@@ -93,6 +93,12 @@ def parse():
     ap.add_argument("--only", default="", choices=["", "encode", "kmeans"],
                     help="run just one stage a few times and print its CUDA-event times (small command lines for "
                          "profiler captures): 'encode' = the residual packers, 'kmeans' = prefill clustering")
+    ap.add_argument("--compare-reference-gpu", default="", metavar="CHECKOUT",
+                    help="time the reference's own CUDA extension (imported from this checkout, JIT-built by torch on "
+                         "first use: minutes per kernel family) and this library on the same inputs with the "
+                         "reference's kernel micro-benchmark protocol; prints one JSON line per case and nothing else")
+    ap.add_argument("--compare-worker", default="", choices=["", "reference", "b200"], help=argparse.SUPPRESS)
+    ap.add_argument("--compare-batches", default="1,32")
     ap.add_argument("--plans", action="store_true",
                     help="also time the attention kernel of every residual layout at --batch / --context (extra key 'plans')")
     return ap.parse_args()
@@ -515,6 +521,70 @@ def run_model(a, dev, group, context, batches, n_new):
     return out
 
 
+def run_compare_worker(a):
+    """One side of --compare-reference-gpu (a process of its own: both packages answer to `import reskv`).
+    Protocol of the reference's benchmarks/kernels.py:18-31,51-90: K, V randn * 0.5, random centroids * 0.1, random
+    ids, clustering injected, decode = median of 5 x 30 attention() calls, compression = compress() with the
+    given clustering, CUDA events."""
+    import torch
+
+    if a.compare_worker == "reference":
+        sys.path.insert(0, a.compare_reference_gpu)
+        from reskv import ResKVKernelConfig, attention, compress
+        from reskv.reference import reference_attention
+    else:
+        from reskv_b200 import ResKVKernelConfig, attention, compress
+        from reskv_b200.reference import reference_attention
+
+    def event_ms(fn, warmup, repeats):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        vals = []
+        for _ in range(5):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(repeats):
+                fn()
+            e.record()
+            e.synchronize()
+            vals.append(s.elapsed_time(e) / repeats)
+        return sorted(vals)[2]
+
+    t = a.context
+    for b in [int(x) for x in a.compare_batches.split(",")]:
+        for sparsity, layout in ((0.75, "unstructured"), (0.75, "auto"), (0.5, "unstructured")):
+            torch.manual_seed(42)
+            k = torch.randn(b, H_KV, t, DIM, device="cuda", dtype=torch.float16) * 0.5
+            v = torch.randn_like(k) * 0.5
+            kc = torch.randn(b, H_KV, 32, DIM, device="cuda", dtype=torch.float16) * 0.1
+            vc = torch.randn_like(kc) * 0.1
+            ki = torch.randint(32, (b, H_KV, t), device="cuda", dtype=torch.int32)
+            vi = torch.randint(32, (b, H_KV, t), device="cuda", dtype=torch.int32)
+            q = torch.randn(b, H_Q, 1, DIM, device="cuda", dtype=torch.float16) * 0.5
+            cfg = ResKVKernelConfig(sparsity=sparsity, layout=layout)
+            t0 = time.time()
+            make = lambda: compress(k, v, cfg, clustering=((kc, ki), (vc, vi)))  # noqa: E731
+            cache = make()
+            fn = lambda: attention(q, cache, position=t)  # noqa: E731
+            out = fn()
+            torch.cuda.synchronize()
+            first = time.time() - t0
+            err = (out.float() - reference_attention(q, cache, position=t)).abs().max().item()
+            print(json.dumps({"impl": a.compare_worker, "batch": b, "sparsity": sparsity, "layout": layout,
+                              "plan": {"layout": cache.key.plan.layout, "bits": cache.key.plan.bits}, "decode_ms": event_ms(fn, 5, 30),
+                              "compression_ms": event_ms(make, 2, 5), "first_call_s": first,
+                              "max_abs_error_vs_fp32_attention": err}), flush=True)
+            del k, v, cache
+
+
+def run_compare(a):
+    for side in ("reference", "b200"):
+        subprocess.run([sys.executable, str(ROOT / "bench.py"), "--compare-worker", side, "--compare-reference-gpu",
+                        a.compare_reference_gpu, "--compare-batches", a.compare_batches, "--context", str(a.context)],
+                       check=True)
+
+
 def run_only(a):
     """One stage on its own, at --batch / --context: a short, fixed sequence of launches for a profiler."""
     import torch
@@ -818,6 +888,10 @@ if __name__ == "__main__":
     args = parse()
     if args.impl == "reference":
         run_reference(args)
+    elif args.compare_worker:
+        run_compare_worker(args)
+    elif args.compare_reference_gpu:
+        run_compare(args)
     elif args.only:
         run_only(args)
     else:
