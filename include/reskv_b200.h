@@ -303,7 +303,10 @@ int reskv_encode_structured_int4(const void* x, const void* centroids, const int
  * `value`: accumulate the cluster sums as 2^24-scaled integers (every mean the
  * correctly rounded one) instead of the default for up to 32 centres, FP32 partial
  * sums formed on the tensor cores in a fixed order (same assignments, means within
- * one FP16 unit in the last place, 2-3x faster; both forms are reproducible).
+ * one FP16 unit in the last place, several times faster; both forms are
+ * reproducible).  That default runs on tcgen05.mma with TMA-fed token tiles (x must
+ * be 16-byte aligned, otherwise the integer form is used); bit 2 of `value`
+ * selects its earlier mma.sync form (kept as a cross-check for the tests).
  * Initial centres are the tokens at linspace(0, tokens-1, clusters).  Writes
  * centroids f16 [B*KH,clusters,128] (after the last update) and ids i32
  * [B*KH,tokens] (from the last assignment, i.e. relative to the centres before
@@ -313,6 +316,10 @@ size_t reskv_kmeans_workspace_bytes(int batch, int kv_heads, int clusters);
 int reskv_kmeans(const void* x, int batch, int kv_heads, int tokens, int64_t x_tok_stride, int clusters,
                  int iterations, int value, void* workspace, size_t workspace_bytes, void* centroids, int32_t* ids,
                  void* stream);
+
+/* Status word of the kernels of the last reskv_kmeans call on this workspace (RESKV_STATUS_* bits: a bounded
+ * wait inside a kernel ran out; 0 = clean).  Copies 4 bytes to the host and synchronises `stream`. */
+int reskv_kmeans_status(const void* workspace, int batch, int kv_heads, int clusters, uint32_t* status, void* stream);
 
 /* Decode-time step; replaces _incremental_cluster (reskv/compression.py:56-69).
  * Copies old_centroids f16 [B*KH,old_clusters,128] into new_centroids

@@ -76,6 +76,7 @@ SIGNATURES = {
     "reskv_encode_structured_int4": (_I, [_P, _P, _P, _I, _I, _I, _L, _I, _P, _P, _P, _L, _P]),
     "reskv_kmeans_workspace_bytes": (_Z, [_I, _I, _I]),
     "reskv_kmeans": (_I, [_P, _I, _I, _I, _L, _I, _I, _I, _P, _Z, _P, _P, _P]),
+    "reskv_kmeans_status": (_I, [_P, _I, _I, _I, _P, _P]),
     "reskv_kmeans_incremental": (_I, [_P, _I, _I, _I, _L, _P, _I, _P, _I, _P, _P]),
 }
 
@@ -240,9 +241,11 @@ class CompressionOps(_Ops):
                                                     _stream(x.device)))
         return packed, meta, scale
 
-    def kmeans(self, x, count, iterations, value, exact=False):
+    def kmeans(self, x, count, iterations, value, exact=False, warp_mma=False, return_status=False):
         """Lloyd clustering -> (centroids f16 [B,H,C,128], ids i32 [B,H,T]).  ``exact``: accumulate the cluster
-        sums as integers (correctly rounded means) instead of FP32 partial sums on the tensor cores."""
+        sums as integers (correctly rounded means) instead of FP32 partial sums on the tensor cores; ``warp_mma``:
+        the mma.sync form of the tensor-core sums instead of the tcgen05 one; ``return_status``: also return the
+        kernels' status word (synchronises the stream)."""
         if x.dtype != torch.float16 or x.ndim != 4 or x.shape[3] != 128 or not x.is_contiguous():
             raise ValueError("kmeans expects contiguous FP16 x[B,H,T,128]")
         _same_device(self.device.index, x)
@@ -253,8 +256,13 @@ class CompressionOps(_Ops):
         ws = torch.empty(need, dtype=torch.uint8, device=x.device)
         centroids = torch.empty((b, h, count, 128), dtype=torch.float16, device=x.device)
         ids = torch.empty((b, h, t), dtype=torch.int32, device=x.device)
-        check(self.lib.reskv_kmeans(x.data_ptr(), b, h, t, t, count, iterations, int(bool(value)) | (2 if exact else 0), ws.data_ptr(), need,
+        flags = int(bool(value)) | (2 if exact else 0) | (4 if warp_mma else 0)
+        check(self.lib.reskv_kmeans(x.data_ptr(), b, h, t, t, count, iterations, flags, ws.data_ptr(), need,
                                     centroids.data_ptr(), ids.data_ptr(), _stream(x.device)), launches=1 + 2 * iterations)
+        if return_status:
+            word = ctypes.c_uint32(0xFFFFFFFF)
+            check(self.lib.reskv_kmeans_status(ws.data_ptr(), b, h, count, ctypes.addressof(word), _stream(x.device)))
+            return centroids, ids, word.value
         return centroids, ids
 
     def kmeans_incremental(self, x, centroids, append):

@@ -31,7 +31,8 @@ def _ops(x: torch.Tensor):
 
 
 @torch.no_grad()
-def cluster(x: torch.Tensor, count: int = 32, iterations: int = 10, *, value: bool = False, exact: bool = False):
+def cluster(x: torch.Tensor, count: int = 32, iterations: int = 10, *, value: bool = False, exact: bool = False,
+            warp_mma: bool = False, return_status: bool = False):
     """Lloyd clustering per (sequence, KV head) -> ``(centres f16 [B,H,C,128],
     ids i32 [B,H,T])`` (reference compression.py:19-53).
 
@@ -49,13 +50,15 @@ def cluster(x: torch.Tensor, count: int = 32, iterations: int = 10, *, value: bo
 
     ``exact`` (not in the reference): accumulate the cluster sums as integers, which makes every mean the
     correctly rounded one.  The default (up to 32 centres) sums FP32 partials on the tensor cores in a fixed
-    order -- equally reproducible, 2-3x faster, means within one FP16 unit in the last place of the exact ones.
+    order -- equally reproducible, several times faster, means within one FP16 unit in the last place of the exact
+    ones.  That default runs on ``tcgen05.mma`` with the token tiles brought in by TMA; ``warp_mma`` selects the
+    earlier ``mma.sync`` form of the same computation, ``return_status`` appends the kernels' status word.
     """
     _require_kv(x, "cluster input")
     t = x.shape[2]
     if value:
         count = min(count, t)
-    return _ops(x).kmeans(x.contiguous(), int(count), int(iterations), value, exact)
+    return _ops(x).kmeans(x.contiguous(), int(count), int(iterations), value, exact, warp_mma, return_status)
 
 
 @torch.no_grad()

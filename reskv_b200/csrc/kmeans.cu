@@ -24,6 +24,8 @@
 //
 // K flavour: FP32 centres, an empty cluster keeps its centre.
 // V flavour: centres rounded to FP16 after every update, an empty cluster becomes 0.
+#include <cuda.h>  // CUtensorMap and its enums; the encoder itself is looked up at run time
+
 #include "common.cuh"
 
 namespace reskv {
@@ -44,6 +46,7 @@ struct KmeansParams {
     long long* sums;       // [units, C, 128] 2^24-scaled integer sums, zero on entry
     int* counts;           // [units, C], zero on entry
     int32_t* ids;          // [units, tokens]
+    uint32_t* status;      // RESKV_STATUS_* bits (a bounded wait that ran out); cleared by the init kernel
     int64_t x_stride;
     int units, tokens, clusters;
 };
@@ -61,6 +64,7 @@ __global__ void kmeans_init_kernel(KmeansParams p, InitIndex init, int value) {
         p.sums[(static_cast<size_t>(unit) * p.clusters + c) * kHeadDim + d] = 0;
     }
     for (int c = threadIdx.x; c < p.clusters; c += blockDim.x) p.counts[unit * p.clusters + c] = 0;
+    if (unit == 0 && threadIdx.x == 0) *p.status = 0u;
     (void)value;
 }
 
@@ -437,6 +441,308 @@ __global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const Kmean
         if (cnt_s[c] > 0) atomicAdd(&p.counts[unit * p.clusters + c], cnt_s[c]);
 }
 
+// ---- tcgen05 form of the assignment kernel (up to 32 centres) ---------------------------------------------------
+// One CTA streams `chunk` tokens of one unit in tiles of 128 tokens.  A tile arrives by two tensor-map copies
+// (TMA, 128-byte swizzle: coordinates 0..63 and 64..127 of 128 rows) and is used three times without ever
+// passing through registers:
+//   * distances: D[128 tokens x 64] = X . [c_hi | c_lo]^T, X as the K-major A operand of tcgen05.mma, the centre
+//     halves as a K-major B operand written once per CTA; accumulator in TMEM, double buffered;
+//   * thread t (= TMEM lane t = token row t) reads its row of D, ranks the centres, re-ranks near-ties exactly
+//     (same bound and same exact path as the mma.sync form) and sets one element of a one-hot operand
+//     onehot[32 clusters x 128 tokens];
+//   * sums: S^T[128 coordinates x 32 clusters] += X^T . onehot^T, the same tile now read as the MN-major A operand,
+//     accumulated in TMEM over the CTA's whole token range and flushed once as 2^24-scaled integers.
+// The MMAs and the copies are issued by thread 0; completion travels through mbarriers, every wait is bounded.
+constexpr int kUThreads = 128;
+constexpr int kUTile = 128;
+constexpr int kUStages = 3;
+constexpr int kUBoxBytes = kUTile * 128;       // 128 rows x 64 coordinates
+constexpr int kUTileBytes = 2 * kUBoxBytes;
+constexpr int kUOneHotBytes = 2 * 32 * 128;    // [2 token halves][32 clusters][64 tokens] FP16
+constexpr uint32_t kUTmemCols = 256;           // distances 2 x 64 columns, sums 32 columns; a power of two
+constexpr uint32_t kUColD = 0, kUColS = 128;
+
+// Shared-memory matrix descriptor, 128-byte swizzle, address bits [4, 18), leading / stride byte offsets.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(lbo_bytes >> 4) << 16) |
+           (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// FP16 x FP16 -> FP32, M = 128, N = n; a_mn: A is MN-major (the token tile read transposed).
+__host__ __device__ constexpr uint32_t umma_idesc(int n, bool a_mn) {
+    return (1u << 4) | (a_mn ? (1u << 15) : 0u) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// One arrival on `bar` once every MMA issued so far by the calling thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// 32 consecutive TMEM columns of the calling thread's lane (lane = 32 * (warp % 4) + lane id).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// One box of a rank-3 tensor map (coordinate, token, unit) -> shared memory, completion counted on `bar`.
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+            smem_u32(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+// Byte offset of 16-byte piece `piece` (0..7) of row `row` in a [rows][128 B] block with the 128-byte swizzle.
+__device__ __forceinline__ uint32_t sw128(int row, int piece) { return row * 128 + ((piece ^ (row & 7)) << 4); }
+
+template <bool HILO>
+__global__ void __launch_bounds__(kUThreads) kmeans_assign_umma_kernel(const KmeansParams p,
+                                                                        const __grid_constant__ CUtensorMap xmap, int chunk) {
+    extern __shared__ unsigned char smem_u[];
+    constexpr int kN = HILO ? 64 : 32;  // rows of the centre operand: hi halves, then lo halves
+    unsigned char* base = smem_u + ((1024u - (smem_u32(smem_u) & 1023u)) & 1023u);  // swizzled blocks: 1024-byte aligned
+    unsigned char* xs = base;                                   // [stages][2 halves][128 tokens][128 B]
+    unsigned char* cop = xs + kUStages * kUTileBytes;           // [2 halves][kN rows][128 B]
+    unsigned char* oh = cop + 2 * kN * 128;                     // [2 buffers][2 token halves][32 clusters][128 B]
+    float* cen_s = reinterpret_cast<float*>(oh + 2 * kUOneHotBytes);  // [32][128] FP32 centres (exact re-ranking)
+    float* cn_s = cen_s + 32 * kHeadDim;                        // [32] |c|^2, +inf for padding
+    int* cnt_s = reinterpret_cast<int*>(cn_s + 32);             // [32]
+    __shared__ uint64_t bar_x[kUStages], bar_d[2], bar_s[2];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ float cmax_s;
+
+    const int unit = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t_begin = blockIdx.x * chunk, t_end = min(p.tokens, t_begin + chunk);
+    const int n_tiles = (t_end - t_begin + kUTile - 1) / kUTile;
+    const float* cen_g = p.centres + static_cast<size_t>(unit) * p.clusters * kHeadDim;
+    bool lost = false;
+
+    if (tid == 0) {
+        for (int s = 0; s < kUStages; ++s) mbar_init(&bar_x[s], 1);
+        mbar_init(&bar_d[0], 1), mbar_init(&bar_d[1], 1), mbar_init(&bar_s[0], 1), mbar_init(&bar_s[1], 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(kUTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    auto load_tile = [&](int j) {  // thread 0
+        unsigned char* dst = xs + (j % kUStages) * kUTileBytes;
+        uint64_t* bar = &bar_x[j % kUStages];
+        mbar_arrive_expect_tx(bar, kUTileBytes);
+        tma_load_3d(dst, &xmap, 0, t_begin + j * kUTile, unit, bar);
+        tma_load_3d(dst + kUBoxBytes, &xmap, 64, t_begin + j * kUTile, unit, bar);
+    };
+    __syncthreads();  // barriers initialised
+    if (tid == 0)
+        for (int j = 0; j < kUStages - 1 && j < n_tiles; ++j) load_tile(j);
+
+    // ---- per CTA: centre operand (FP16 hi | lo rows, swizzled), FP32 centres, |c|^2, empty one-hot buffers ----
+    for (int i = tid; i < 32 * kHeadDim; i += kUThreads) {
+        const int c = i / kHeadDim, d = i % kHeadDim;
+        const float v = c < p.clusters ? cen_g[i] : 0.f;
+        cen_s[i] = v;
+        const __half h = __float2half_rn(v);
+        unsigned char* at = cop + (d >> 6) * (kN * 128) + ((d & 7) << 1);
+        *reinterpret_cast<__half*>(at + sw128(c, (d & 63) >> 3)) = h;
+        if (HILO) *reinterpret_cast<__half*>(at + sw128(32 + c, (d & 63) >> 3)) = __float2half_rn(v - __half2float(h));
+    }
+    for (int i = tid; i < 2 * kUOneHotBytes / 16; i += kUThreads) reinterpret_cast<uint4*>(oh)[i] = make_uint4(0, 0, 0, 0);
+    if (tid < 32) cnt_s[tid] = 0;
+    __syncthreads();
+    for (int c = warp; c < 32; c += kUThreads / 32) {
+        float acc = INFINITY;
+        if (c < p.clusters) {
+            acc = 0.f;
+            for (int d = lane; d < kHeadDim; d += 32) {
+                float v = cen_s[c * kHeadDim + d];
+                const __half h = __float2half_rn(v);
+                v = __half2float(h);
+                if (HILO) v += __half2float(__float2half_rn(cen_s[c * kHeadDim + d] - v));  // what the MMA sees
+                acc = fmaf(v, v, acc);
+            }
+            for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(kFull, acc, off);
+        }
+        if (lane == 0) cn_s[c] = acc;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float m = 0.f;
+        for (int c = 0; c < p.clusters; ++c) m = fmaxf(m, cn_s[c]);
+        cmax_s = m;
+    }
+    proxy_fence();  // the operands written above are read by the tensor core (async proxy)
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const float cmax = cmax_s;
+    const uint32_t tmem = tmem_base_s;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const __half* xu = p.x + static_cast<size_t>(unit) * p.x_stride * kHeadDim;
+
+    auto issue_distances = [&](int j) {  // thread 0; tile j has landed
+        const uint32_t xa = smem_u32(xs + (j % kUStages) * kUTileBytes), ca = smem_u32(cop);
+        const uint32_t d = tmem + kUColD + (j & 1) * 64;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {  // 16 coordinates per step: 32 bytes inside the swizzled 128-byte row
+            const uint64_t a = umma_desc(xa + (ks >> 2) * kUBoxBytes + (ks & 3) * 32, 16, 1024);
+            const uint64_t b = umma_desc(ca + (ks >> 2) * (kN * 128) + (ks & 3) * 32, 16, 1024);
+            umma_f16(d, a, b, umma_idesc(kN, false), ks > 0);
+        }
+        umma_commit(&bar_d[j & 1]);
+    };
+    auto issue_sums = [&](int j) {  // thread 0; one-hot buffer j & 1 complete and visible
+        const uint32_t xa = smem_u32(xs + (j % kUStages) * kUTileBytes), oa = smem_u32(oh + (j & 1) * kUOneHotBytes);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {  // 16 tokens per step: two 8-row groups of the tile = 2048 bytes
+            const uint64_t a = umma_desc(xa + ks * 2048, kUBoxBytes, 1024);  // MN-major: other half of the coordinates at LBO
+            const uint64_t b = umma_desc(oa + (ks >> 2) * (32 * 128) + (ks & 3) * 32, 16, 1024);
+            umma_f16(tmem + kUColS, a, b, umma_idesc(32, true), (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(&bar_s[j & 1]);
+    };
+
+    if (tid == 0) {
+        lost |= !mbar_wait(&bar_x[0], 0);
+        issue_distances(0);
+    }
+    int prev_even = -1, prev_odd = -1;  // byte offset of the element this thread set in each one-hot buffer
+    for (int i = 0; i < n_tiles; ++i) {
+        const int b = i & 1, st = i % kUStages;
+        if (tid == 0 && i + 1 < n_tiles) {  // distances of the next tile run while this one is ranked
+            lost |= !mbar_wait(&bar_x[(i + 1) % kUStages], ((i + 1) / kUStages) & 1);
+            issue_distances(i + 1);
+        }
+        lost |= !mbar_wait(&bar_x[st], (i / kUStages) & 1);  // this thread reads the tile too (|x|^2)
+        lost |= !mbar_wait(&bar_d[b], (i >> 1) & 1);
+        tc_fence_after();
+        const int row = t_begin + i * kUTile + tid;
+        const bool live = row < t_end;
+        float d1 = INFINITY, d2 = INFINITY;
+        int c1 = 0;
+        {
+            uint32_t hi[32];
+            tmem_ld32(tmem + lane_base + kUColD + b * 64, hi);
+            if constexpr (HILO) {
+                uint32_t lo[32];
+                tmem_ld32(tmem + lane_base + kUColD + b * 64 + 32, lo);
+                tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < 32; ++c) hi[c] = __float_as_uint(__uint_as_float(hi[c]) + __uint_as_float(lo[c]));
+            } else {
+                tmem_ld_wait();
+            }
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                const float d = fmaf(-2.f, __uint_as_float(hi[c]), cn_s[c]);
+                if (d < d1) {
+                    d2 = d1, d1 = d, c1 = c;
+                } else if (d < d2) {
+                    d2 = d;
+                }
+            }
+        }
+        // |x|^2 for the near-tie bound: packed FP16 products, eight at a time (an overflow gives +inf: re-rank)
+        float xn = 0.f;
+        {
+            const unsigned char* xt = xs + st * kUTileBytes;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const uint4 v = *reinterpret_cast<const uint4*>(xt + (j >> 3) * kUBoxBytes + sw128(tid, j & 7));
+                const __half2* h = reinterpret_cast<const __half2*>(&v);
+                __half2 s = __hmul2(h[0], h[0]);
+                s = __hfma2(h[1], h[1], s), s = __hfma2(h[2], h[2], s), s = __hfma2(h[3], h[3], s);
+                const float2 f = __half22float2(s);
+                xn += f.x + f.y;
+            }
+        }
+        // near-ties: re-rank with the exact FP32 sum, the warp working on one token at a time
+        const bool tie = live && !((d2 - d1) > kTieBound * (1.01f * xn + cmax));
+        uint32_t redo = __ballot_sync(kFull, tie);
+        while (redo) {
+            const int src = __ffs(redo) - 1;
+            redo &= redo - 1;
+            const __half* xr = xu + static_cast<size_t>(t_begin + i * kUTile + warp * 32 + src) * kHeadDim;
+            float xv[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) xv[k] = __half2float(xr[lane + 32 * k]);
+            float best;
+            int c;
+            nearest(cen_s, p.clusters, xv, lane, best, c);
+            if (lane == src) c1 = c;
+        }
+        if (live) {
+            p.ids[static_cast<size_t>(unit) * p.tokens + row] = c1;
+            atomicAdd(&cnt_s[c1], 1);
+        }
+        // one-hot buffer b was last read by the sums of tile i - 2
+        if (i >= 2) lost |= !mbar_wait(&bar_s[b], ((i - 2) >> 1) & 1);
+        {
+            unsigned char* ob = oh + b * kUOneHotBytes;
+            const int prev = b ? prev_odd : prev_even;
+            if (prev >= 0) *reinterpret_cast<unsigned short*>(ob + prev) = 0;
+            int at = -1;
+            if (live) {
+                at = (tid >> 6) * (32 * 128) + sw128(c1, (tid & 63) >> 3) + ((tid & 7) << 1);
+                *reinterpret_cast<unsigned short*>(ob + at) = 0x3C00;  // 1.0
+            }
+            if (b) prev_odd = at; else prev_even = at;
+        }
+        proxy_fence();
+        tc_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+            issue_sums(i);
+            if (i + kUStages - 1 < n_tiles) {  // the stage of tile i - 1 is free once its sums have run
+                if (i >= 1) lost |= !mbar_wait(&bar_s[(i - 1) & 1], ((i - 1) >> 1) & 1);
+                load_tile(i + kUStages - 1);
+            }
+        }
+    }
+    // the commit of the last sums covers every MMA of this CTA
+    lost |= !mbar_wait(&bar_s[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
+    tc_fence_after();
+    {
+        uint32_t sum[32];
+        tmem_ld32(tmem + lane_base + kUColS, sum);
+        tmem_ld_wait();
+        long long* sums_g = p.sums + static_cast<size_t>(unit) * p.clusters * kHeadDim;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+            if (c < p.clusters && cnt_s[c] > 0)
+                atomicAdd(reinterpret_cast<unsigned long long*>(sums_g + c * kHeadDim + tid),
+                          static_cast<unsigned long long>(__float2ll_rn(__uint_as_float(sum[c]) * kFix)));
+        }
+    }
+    if (tid < p.clusters && cnt_s[tid] > 0) atomicAdd(&p.counts[unit * p.clusters + tid], cnt_s[tid]);
+    if (lost) atomicOr(p.status, RESKV_STATUS_WAIT_TIMEOUT);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kUTmemCols) : "memory");
+}
+
 // New centres from the exact sums; clears sums and counts for the next round.
 // `final_out` (FP16 [units, C, 128]) is written when non-null.
 __global__ void kmeans_update_kernel(KmeansParams p, int value, __half* final_out) {
@@ -510,9 +816,65 @@ void linspace_indices(int t, int count, int* out) {
     }
 }
 
+// sums, centres, counts, then 256 bytes whose first word is the status word
 size_t kmeans_ws_bytes(int units, int clusters) {
     const size_t per = static_cast<size_t>(units) * clusters;
     return per * kHeadDim * (sizeof(float) + sizeof(long long)) + per * sizeof(int) + 256;
+}
+
+using TensorMapEncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                       const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                       CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, looked up once through the runtime (no link against libcuda).
+TensorMapEncodeFn tensor_map_encoder() {
+    static const TensorMapEncodeFn fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &found) != cudaSuccess ||
+            found != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return reinterpret_cast<TensorMapEncodeFn>(f);
+    }();
+    return fn;
+}
+
+template <bool HILO>
+int launch_umma(const KmeansParams& p, int value, int iterations, void* centroids, cudaStream_t s) {
+    TensorMapEncodeFn encode = tensor_map_encoder();
+    if (!encode) return fail(RESKV_ERR_CUDA, "kmeans: the driver offers no cuTensorMapEncodeTiled");
+    // x as (coordinate, token, unit): boxes of 64 coordinates x 128 tokens, 128-byte swizzle, zeros beyond the
+    // last token of a unit
+    CUtensorMap xmap;
+    const cuuint64_t dims[3] = {kHeadDim, static_cast<cuuint64_t>(p.tokens), static_cast<cuuint64_t>(p.units)};
+    const cuuint64_t strides[2] = {kHeadDim * sizeof(__half), static_cast<cuuint64_t>(p.x_stride) * kHeadDim * sizeof(__half)};
+    const cuuint32_t box[3] = {64, kUTile, 1}, elem[3] = {1, 1, 1};
+    const CUresult made = encode(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<__half*>(p.x), dims, strides, box, elem,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (made != CUDA_SUCCESS) return fail(RESKV_ERR_CUDA, "kmeans: cuTensorMapEncodeTiled failed with code %d", static_cast<int>(made));
+    constexpr int kN = HILO ? 64 : 32;
+    const size_t smem = 1024 + static_cast<size_t>(kUStages) * kUTileBytes + 2 * kN * 128 + 2 * kUOneHotBytes +
+                        32 * kHeadDim * sizeof(float) + 32 * (sizeof(float) + sizeof(int));
+    static unsigned long long prepared = 0;  // per-device bit: the shared-memory attribute is set
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!((prepared >> (dev & 63)) & 1ull)) {
+        if (int rc = check_cuda(cudaFuncSetAttribute(kmeans_assign_umma_kernel<HILO>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     static_cast<int>(smem)),
+                                "cudaFuncSetAttribute(kmeans_assign_umma)"))
+            return rc;
+        prepared |= 1ull << (dev & 63);
+    }
+    // tokens per CTA: a multiple of the tile, about two CTAs' worth of work per SM, at most kChunkFastMax (FP32 partial sums)
+    const long long want = static_cast<long long>(p.units) * p.tokens / (2ll * sm_count());
+    const int chunk = static_cast<int>(want < kChunk ? kChunk : want > kChunkFastMax ? kChunkFastMax : (want + 127) / 128 * 128);
+    const dim3 grid((p.tokens + chunk - 1) / chunk, p.units);
+    for (int it = 0; it < iterations; ++it) {
+        kmeans_assign_umma_kernel<HILO><<<grid, kUThreads, smem, s>>>(p, xmap, chunk);
+        kmeans_update_kernel<<<p.units, 256, 0, s>>>(p, value, it + 1 == iterations ? static_cast<__half*>(centroids) : nullptr);
+    }
+    return check_cuda(cudaGetLastError(), "kmeans launch");
 }
 
 }  // namespace
@@ -545,6 +907,7 @@ extern "C" int reskv_kmeans(const void* x, int batch, int kv_heads, int tokens, 
     p.sums = static_cast<long long*>(workspace);  // 8-byte aligned first
     p.centres = reinterpret_cast<float*>(p.sums + per);
     p.counts = reinterpret_cast<int*>(p.centres + per);
+    p.status = reinterpret_cast<uint32_t*>(p.counts + static_cast<size_t>(units) * clusters);
     p.ids = ids;
     p.x_stride = x_tok_stride;
     p.units = units, p.tokens = tokens, p.clusters = clusters;
@@ -555,8 +918,9 @@ extern "C" int reskv_kmeans(const void* x, int batch, int kv_heads, int tokens, 
         // fewer tokens than centres: every token once, then tokens repeated in order
         for (int c = 0; c < clusters; ++c) init.idx[c] = c % tokens;
     }
-    // `value`: bit 0 = V flavour, bit 1 = exact (integer) accumulation of the cluster sums
-    const bool exact = (value & 2) != 0;
+    // `value`: bit 0 = V flavour, bit 1 = exact (integer) accumulation of the cluster sums, bit 2 = the mma.sync
+    // form of the tensor-core sums instead of the tcgen05 one
+    const bool exact = (value & 2) != 0, warp_mma = (value & 4) != 0;
     value &= 1;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     kmeans_init_kernel<<<units, 256, 0, s>>>(p, init, value);
@@ -564,6 +928,7 @@ extern "C" int reskv_kmeans(const void* x, int batch, int kv_heads, int tokens, 
     // the integer-counter arrays double as the FP32 reduction buffer [32][kRedStride] of the tensor-core form
     size_t counters = static_cast<size_t>(clusters) * kHeadDim * 2 * sizeof(int);
     const bool fast = !exact && padded <= 32 && aligned16(x);  // the row staging copies 16-byte pieces
+    if (fast && warp_mma) return value ? launch_umma<false>(p, value, iterations, centroids, s) : launch_umma<true>(p, value, iterations, centroids, s);
     if (fast) counters = static_cast<size_t>(kWarps) * 32 * kRedStride * sizeof(float);
     const size_t smem = static_cast<size_t>(clusters) * kHeadDim * sizeof(float) + counters +
                         kMaxClusters * (sizeof(int) + sizeof(float)) +
@@ -590,6 +955,19 @@ extern "C" int reskv_kmeans(const void* x, int batch, int kv_heads, int tokens, 
         kmeans_update_kernel<<<units, 256, 0, s>>>(p, value, it + 1 == iterations ? static_cast<__half*>(centroids) : nullptr);
     }
     return check_cuda(cudaGetLastError(), "kmeans launch");
+}
+
+extern "C" int reskv_kmeans_status(const void* workspace, int batch, int kv_heads, int clusters, uint32_t* status, void* stream) {
+    if (!workspace || !status) return fail(RESKV_ERR_INVALID, "kmeans_status: null pointer");
+    if (batch < 1 || kv_heads < 1 || clusters < 1 || clusters > kMaxClusters) return fail(RESKV_ERR_INVALID, "kmeans_status: bad sizes");
+    const size_t per = static_cast<size_t>(batch) * kv_heads * clusters;
+    const size_t at = per * kHeadDim * (sizeof(float) + sizeof(long long)) + per * sizeof(int);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (int rc = check_cuda(cudaMemcpyAsync(status, static_cast<const unsigned char*>(workspace) + at, sizeof(uint32_t),
+                                            cudaMemcpyDeviceToHost, s),
+                            "kmeans_status copy"))
+        return rc;
+    return check_cuda(cudaStreamSynchronize(s), "kmeans_status synchronize");
 }
 
 extern "C" int reskv_kmeans_incremental(const void* x, int batch, int kv_heads, int tokens, int64_t x_tok_stride,
