@@ -446,21 +446,32 @@ __global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const Kmean
 // (TMA, 128-byte swizzle: coordinates 0..63 and 64..127 of 128 rows) and is used three times without ever
 // passing through registers:
 //   * distances: D[128 tokens x 64] = X . [c_hi | c_lo]^T, X as the K-major A operand of tcgen05.mma, the centre
-//     halves as a K-major B operand written once per CTA; accumulator in TMEM, double buffered;
-//   * thread t (= TMEM lane t = token row t) reads its row of D, ranks the centres, re-ranks near-ties exactly
-//     (same bound and same exact path as the mma.sync form) and sets one element of a one-hot operand
+//     halves as a K-major B operand written once per CTA; accumulator in TMEM, double buffered, issued two tiles
+//     ahead of its use;
+//   * ranking: sixteen warps, four threads per token (TMEM lane = token row; warp w reads lanes 32 (w % 4).. and
+//     the eight centres 8 (w / 4)..), their partial results go to shared memory;
+//   * merging: four more warps, one thread per token, merge the four parts, re-rank near-ties exactly (same bound
+//     and same exact path as the mma.sync form), write the id and set one element of a one-hot operand
 //     onehot[32 clusters x 128 tokens];
 //   * sums: S^T[128 coordinates x 32 clusters] += X^T . onehot^T, the same tile now read as the MN-major A operand,
-//     accumulated in TMEM over the CTA's whole token range and flushed once as 2^24-scaled integers.
-// The MMAs and the copies are issued by thread 0; completion travels through mbarriers, every wait is bounded.
-constexpr int kUThreads = 128;
+//     accumulated in TMEM (four accumulators in turn) over the CTA's whole token range and flushed once as
+//     2^24-scaled integers.
+// Two more warps issue the asynchronous work, one the distance MMAs, one the copies and the sum MMAs; they stay
+// converged (descriptor arithmetic on the uniform datapath) and elect one lane per instruction.  The roles run
+// concurrently on different tiles and hand over through mbarriers only (double-buffered distances, parts and
+// one-hot operand); every wait is bounded.
+constexpr int kURankWarps = 16;                // four per TMEM lane quarter: eight centres each
+constexpr int kUMergeWarps = 4;                // one per TMEM lane quarter
+constexpr int kUThreads = (kURankWarps + kUMergeWarps + 2) * 32;  // + one warp issuing the distance MMAs, one the copies and the sum MMAs
 constexpr int kUTile = 128;
-constexpr int kUStages = 3;
+constexpr int kUStages = 5;
 constexpr int kUBoxBytes = kUTile * 128;       // 128 rows x 64 coordinates
 constexpr int kUTileBytes = 2 * kUBoxBytes;
 constexpr int kUOneHotBytes = 2 * 32 * 128;    // [2 token halves][32 clusters][64 tokens] FP16
-constexpr uint32_t kUTmemCols = 256;           // distances 2 x 64 columns, sums 32 columns; a power of two
+constexpr uint32_t kUTmemCols = 256;           // distances 2 x 64 columns, sums 4 x 32 columns
 constexpr uint32_t kUColD = 0, kUColS = 128;
+constexpr int kUSumBuffers = 4;                // tile i adds to accumulator i % 4: shorter FP32 chains, no MMA-to-MMA dependency
+constexpr int kUChunkMax = 8192;               // most tokens per CTA (2048 per accumulator)
 
 // Shared-memory matrix descriptor, 128-byte swizzle, address bits [4, 18), leading / stride byte offsets.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
@@ -490,16 +501,14 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// 32 consecutive TMEM columns of the calling thread's lane (lane = 32 * (warp % 4) + lane id).
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
+// Eight consecutive TMEM columns of the calling thread's lane (lane = 32 * (warp % 4) + lane id).
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&r)[8]) {
+    uint32_t u[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7])
+                 : "r"(taddr));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r[i] = __uint_as_float(u[i]);
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -515,19 +524,34 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
 // Byte offset of 16-byte piece `piece` (0..7) of row `row` in a [rows][128 B] block with the 128-byte swizzle.
 __device__ __forceinline__ uint32_t sw128(int row, int piece) { return row * 128 + ((piece ^ (row & 7)) << 4); }
 
+// True in exactly one lane of a converged warp (the same lane every time).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t chosen;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(chosen));
+    return chosen != 0;
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 template <bool HILO>
-__global__ void __launch_bounds__(kUThreads) kmeans_assign_umma_kernel(const KmeansParams p,
-                                                                        const __grid_constant__ CUtensorMap xmap, int chunk) {
+__global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const KmeansParams p,
+                                                                           const __grid_constant__ CUtensorMap xmap, int chunk) {
     extern __shared__ unsigned char smem_u[];
     constexpr int kN = HILO ? 64 : 32;  // rows of the centre operand: hi halves, then lo halves
     unsigned char* base = smem_u + ((1024u - (smem_u32(smem_u) & 1023u)) & 1023u);  // swizzled blocks: 1024-byte aligned
     unsigned char* xs = base;                                   // [stages][2 halves][128 tokens][128 B]
     unsigned char* cop = xs + kUStages * kUTileBytes;           // [2 halves][kN rows][128 B]
     unsigned char* oh = cop + 2 * kN * 128;                     // [2 buffers][2 token halves][32 clusters][128 B]
-    float* cen_s = reinterpret_cast<float*>(oh + 2 * kUOneHotBytes);  // [32][128] FP32 centres (exact re-ranking)
+    float4* part_s = reinterpret_cast<float4*>(oh + 2 * kUOneHotBytes);  // [2 buffers][4 centre groups][128 rows]: d1, d2, c1, |x|^2 part
+    float* cen_s = reinterpret_cast<float*>(part_s + 2 * 4 * kUTile);    // [32][128] FP32 centres (exact re-ranking)
     float* cn_s = cen_s + 32 * kHeadDim;                        // [32] |c|^2, +inf for padding
     int* cnt_s = reinterpret_cast<int*>(cn_s + 32);             // [32]
-    __shared__ uint64_t bar_x[kUStages], bar_d[2], bar_s[2];
+    // full: tile landed (TMA bytes).  dist / sums: MMAs complete (tcgen05.commit).  parts: 512 ranking threads have
+    // read the distance buffer and written their part.  parts_free: 128 merging threads have read the parts.
+    // onehot: 128 merging threads have written the one-hot operand.
+    __shared__ uint64_t bar_full[kUStages], bar_dist[2], bar_sums[2], bar_parts[2], bar_parts_free[2], bar_onehot[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ float cmax_s;
 
@@ -538,8 +562,12 @@ __global__ void __launch_bounds__(kUThreads) kmeans_assign_umma_kernel(const Kme
     bool lost = false;
 
     if (tid == 0) {
-        for (int s = 0; s < kUStages; ++s) mbar_init(&bar_x[s], 1);
-        mbar_init(&bar_d[0], 1), mbar_init(&bar_d[1], 1), mbar_init(&bar_s[0], 1), mbar_init(&bar_s[1], 1);
+        for (int s = 0; s < kUStages; ++s) mbar_init(&bar_full[s], 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&bar_dist[b], 1), mbar_init(&bar_sums[b], 1);
+            mbar_init(&bar_parts[b], kURankWarps * 32), mbar_init(&bar_parts_free[b], kUMergeWarps * 32);
+            mbar_init(&bar_onehot[b], kUMergeWarps * 32);
+        }
         mbar_fence_init();
     }
     if (warp == 0) {
@@ -547,15 +575,17 @@ __global__ void __launch_bounds__(kUThreads) kmeans_assign_umma_kernel(const Kme
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    auto load_tile = [&](int j) {  // thread 0
-        unsigned char* dst = xs + (j % kUStages) * kUTileBytes;
-        uint64_t* bar = &bar_x[j % kUStages];
-        mbar_arrive_expect_tx(bar, kUTileBytes);
-        tma_load_3d(dst, &xmap, 0, t_begin + j * kUTile, unit, bar);
-        tma_load_3d(dst + kUBoxBytes, &xmap, 64, t_begin + j * kUTile, unit, bar);
-    };
     __syncthreads();  // barriers initialised
-    if (tid == 0)
+    auto load_tile = [&](int j) {  // converged warp
+        unsigned char* dst = xs + (j % kUStages) * kUTileBytes;
+        uint64_t* bar = &bar_full[j % kUStages];
+        if (elect_one()) {
+            mbar_arrive_expect_tx(bar, kUTileBytes);
+            tma_load_3d(dst, &xmap, 0, t_begin + j * kUTile, unit, bar);
+            tma_load_3d(dst + kUBoxBytes, &xmap, 64, t_begin + j * kUTile, unit, bar);
+        }
+    };
+    if (warp == kURankWarps + kUMergeWarps + 1)
         for (int j = 0; j < kUStages - 1 && j < n_tiles; ++j) load_tile(j);
 
     // ---- per CTA: centre operand (FP16 hi | lo rows, swizzled), FP32 centres, |c|^2, empty one-hot buffers ----
@@ -596,144 +626,191 @@ __global__ void __launch_bounds__(kUThreads) kmeans_assign_umma_kernel(const Kme
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const float cmax = cmax_s;
     const uint32_t tmem = tmem_base_s;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
     const __half* xu = p.x + static_cast<size_t>(unit) * p.x_stride * kHeadDim;
 
-    auto issue_distances = [&](int j) {  // thread 0; tile j has landed
-        const uint32_t xa = smem_u32(xs + (j % kUStages) * kUTileBytes), ca = smem_u32(cop);
-        const uint32_t d = tmem + kUColD + (j & 1) * 64;
+    if (warp < kURankWarps) {
+        // ---- ranking: four threads per token, eight centres and a quarter of |x|^2 each ----------------------
+        const int quarter = warp & 3, cpart = warp >> 2, row_in_tile = quarter * 32 + lane;
+        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+        float cn_r[8];
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {  // 16 coordinates per step: 32 bytes inside the swizzled 128-byte row
-            const uint64_t a = umma_desc(xa + (ks >> 2) * kUBoxBytes + (ks & 3) * 32, 16, 1024);
-            const uint64_t b = umma_desc(ca + (ks >> 2) * (kN * 128) + (ks & 3) * 32, 16, 1024);
-            umma_f16(d, a, b, umma_idesc(kN, false), ks > 0);
-        }
-        umma_commit(&bar_d[j & 1]);
-    };
-    auto issue_sums = [&](int j) {  // thread 0; one-hot buffer j & 1 complete and visible
-        const uint32_t xa = smem_u32(xs + (j % kUStages) * kUTileBytes), oa = smem_u32(oh + (j & 1) * kUOneHotBytes);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {  // 16 tokens per step: two 8-row groups of the tile = 2048 bytes
-            const uint64_t a = umma_desc(xa + ks * 2048, kUBoxBytes, 1024);  // MN-major: other half of the coordinates at LBO
-            const uint64_t b = umma_desc(oa + (ks >> 2) * (32 * 128) + (ks & 3) * 32, 16, 1024);
-            umma_f16(tmem + kUColS, a, b, umma_idesc(32, true), (j > 0 || ks > 0) ? 1u : 0u);
-        }
-        umma_commit(&bar_s[j & 1]);
-    };
-
-    if (tid == 0) {
-        lost |= !mbar_wait(&bar_x[0], 0);
-        issue_distances(0);
-    }
-    int prev_even = -1, prev_odd = -1;  // byte offset of the element this thread set in each one-hot buffer
-    for (int i = 0; i < n_tiles; ++i) {
-        const int b = i & 1, st = i % kUStages;
-        if (tid == 0 && i + 1 < n_tiles) {  // distances of the next tile run while this one is ranked
-            lost |= !mbar_wait(&bar_x[(i + 1) % kUStages], ((i + 1) / kUStages) & 1);
-            issue_distances(i + 1);
-        }
-        lost |= !mbar_wait(&bar_x[st], (i / kUStages) & 1);  // this thread reads the tile too (|x|^2)
-        lost |= !mbar_wait(&bar_d[b], (i >> 1) & 1);
-        tc_fence_after();
-        const int row = t_begin + i * kUTile + tid;
-        const bool live = row < t_end;
-        float d1 = INFINITY, d2 = INFINITY;
-        int c1 = 0;
-        {
-            uint32_t hi[32];
-            tmem_ld32(tmem + lane_base + kUColD + b * 64, hi);
+        for (int c = 0; c < 8; ++c) cn_r[c] = cn_s[8 * cpart + c];
+        for (int i = 0; i < n_tiles; ++i) {
+            const int b = i & 1, st = i % kUStages;
+            lost |= !mbar_wait(&bar_full[st], (i / kUStages) & 1);  // this thread reads the tile too (|x|^2)
+            lost |= !mbar_wait(&bar_dist[b], (i >> 1) & 1);
+            tc_fence_after();
+            float acc[8];
+            tmem_ld8(tmem + lane_base + kUColD + b * 64 + 8 * cpart, acc);
             if constexpr (HILO) {
-                uint32_t lo[32];
-                tmem_ld32(tmem + lane_base + kUColD + b * 64 + 32, lo);
+                float lo[8];
+                tmem_ld8(tmem + lane_base + kUColD + b * 64 + 32 + 8 * cpart, lo);
                 tmem_ld_wait();
 #pragma unroll
-                for (int c = 0; c < 32; ++c) hi[c] = __float_as_uint(__uint_as_float(hi[c]) + __uint_as_float(lo[c]));
+                for (int c = 0; c < 8; ++c) acc[c] += lo[c];
             } else {
                 tmem_ld_wait();
             }
+            float d1 = INFINITY, d2 = INFINITY;
+            int c1 = 0;
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                const float d = fmaf(-2.f, __uint_as_float(hi[c]), cn_s[c]);
+            for (int c = 0; c < 8; ++c) {
+                const float d = fmaf(-2.f, acc[c], cn_r[c]);
                 if (d < d1) {
-                    d2 = d1, d1 = d, c1 = c;
+                    d2 = d1, d1 = d, c1 = 8 * cpart + c;
                 } else if (d < d2) {
                     d2 = d;
                 }
             }
-        }
-        // |x|^2 for the near-tie bound: packed FP16 products, eight at a time (an overflow gives +inf: re-rank)
-        float xn = 0.f;
-        {
-            const unsigned char* xt = xs + st * kUTileBytes;
+            // |x|^2 for the near-tie bound: packed FP16 products, eight at a time (an overflow gives +inf: re-rank)
+            float xn = 0.f;
+            const unsigned char* xt = xs + st * kUTileBytes + (cpart >> 1) * kUBoxBytes;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const uint4 v = *reinterpret_cast<const uint4*>(xt + (j >> 3) * kUBoxBytes + sw128(tid, j & 7));
+            for (int j = 0; j < 4; ++j) {
+                const uint4 v = *reinterpret_cast<const uint4*>(xt + sw128(row_in_tile, 4 * (cpart & 1) + j));
                 const __half2* h = reinterpret_cast<const __half2*>(&v);
                 __half2 s = __hmul2(h[0], h[0]);
                 s = __hfma2(h[1], h[1], s), s = __hfma2(h[2], h[2], s), s = __hfma2(h[3], h[3], s);
                 const float2 f = __half22float2(s);
                 xn += f.x + f.y;
             }
+            if (i >= 2) lost |= !mbar_wait(&bar_parts_free[b], ((i - 2) >> 1) & 1);  // parts of tile i - 2 were merged
+            part_s[(b * 4 + cpart) * kUTile + row_in_tile] = make_float4(d1, d2, __int_as_float(c1), xn);
+            tc_fence_before();
+            mbar_arrive(&bar_parts[b]);
         }
-        // near-ties: re-rank with the exact FP32 sum, the warp working on one token at a time
-        const bool tie = live && !((d2 - d1) > kTieBound * (1.01f * xn + cmax));
-        uint32_t redo = __ballot_sync(kFull, tie);
-        while (redo) {
-            const int src = __ffs(redo) - 1;
-            redo &= redo - 1;
-            const __half* xr = xu + static_cast<size_t>(t_begin + i * kUTile + warp * 32 + src) * kHeadDim;
-            float xv[4];
+    } else if (warp < kURankWarps + kUMergeWarps) {
+        // ---- merging: one thread per token -------------------------------------------------------------------
+        const int quarter = warp - kURankWarps, row_in_tile = quarter * 32 + lane;
+        const float cmax = cmax_s;
+        int prev_even = -1, prev_odd = -1;  // byte offset of the element this thread set in each one-hot buffer
+        for (int i = 0; i < n_tiles; ++i) {
+            const int b = i & 1;
+            const int row = t_begin + i * kUTile + row_in_tile;
+            const bool live = row < t_end;
+            lost |= !mbar_wait(&bar_parts[b], (i >> 1) & 1);
+            float4 m = part_s[(b * 4) * kUTile + row_in_tile];
+            float d1 = m.x, d2 = m.y, xn = m.w;
+            int c1 = __float_as_int(m.z);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) xv[k] = __half2float(xr[lane + 32 * k]);
-            float best;
-            int c;
-            nearest(cen_s, p.clusters, xv, lane, best, c);
-            if (lane == src) c1 = c;
-        }
-        if (live) {
-            p.ids[static_cast<size_t>(unit) * p.tokens + row] = c1;
-            atomicAdd(&cnt_s[c1], 1);
-        }
-        // one-hot buffer b was last read by the sums of tile i - 2
-        if (i >= 2) lost |= !mbar_wait(&bar_s[b], ((i - 2) >> 1) & 1);
-        {
+            for (int k = 1; k < 4; ++k) {  // ascending centre groups: a strict comparison keeps the lower index on ties
+                m = part_s[(b * 4 + k) * kUTile + row_in_tile];
+                if (m.x < d1) {
+                    d2 = fminf(d1, m.y), d1 = m.x, c1 = __float_as_int(m.z);
+                } else {
+                    d2 = fminf(d2, m.x);
+                }
+                xn += m.w;
+            }
+            mbar_arrive(&bar_parts_free[b]);
+            // near-ties: re-rank with the exact FP32 sum, the warp working on one token at a time
+            const bool tie = live && !((d2 - d1) > kTieBound * (1.01f * xn + cmax));
+            uint32_t redo = __ballot_sync(kFull, tie);
+            while (redo) {
+                const int src = __ffs(redo) - 1;
+                redo &= redo - 1;
+                const __half* xr = xu + static_cast<size_t>(t_begin + i * kUTile + quarter * 32 + src) * kHeadDim;
+                float xv[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) xv[k] = __half2float(xr[lane + 32 * k]);
+                float best;
+                int c;
+                nearest(cen_s, p.clusters, xv, lane, best, c);
+                if (lane == src) c1 = c;
+            }
+            if (live) {
+                p.ids[static_cast<size_t>(unit) * p.tokens + row] = c1;
+                atomicAdd(&cnt_s[c1], 1);
+            }
+            // one-hot buffer b was last read by the sums of tile i - 2
+            if (i >= 2) lost |= !mbar_wait(&bar_sums[b], ((i - 2) >> 1) & 1);
             unsigned char* ob = oh + b * kUOneHotBytes;
             const int prev = b ? prev_odd : prev_even;
             if (prev >= 0) *reinterpret_cast<unsigned short*>(ob + prev) = 0;
             int at = -1;
             if (live) {
-                at = (tid >> 6) * (32 * 128) + sw128(c1, (tid & 63) >> 3) + ((tid & 7) << 1);
+                at = (row_in_tile >> 6) * (32 * 128) + sw128(c1, (row_in_tile & 63) >> 3) + ((row_in_tile & 7) << 1);
                 *reinterpret_cast<unsigned short*>(ob + at) = 0x3C00;  // 1.0
             }
             if (b) prev_odd = at; else prev_even = at;
+            proxy_fence();  // the tensor core (async proxy) reads what this thread wrote
+            mbar_arrive(&bar_onehot[b]);
         }
-        proxy_fence();
-        tc_fence_before();
-        __syncthreads();
-        if (tid == 0) {
+    } else if (warp == kURankWarps + kUMergeWarps) {
+        // ---- distance MMAs, two tiles ahead of their use (whole warp, one elected lane per instruction) -------
+        const uint64_t a0 = umma_desc(smem_u32(xs), 16, 1024), b0 = umma_desc(smem_u32(cop), 16, 1024);
+        auto issue_distances = [&](int j) {  // tile j has landed, distance buffer j & 1 has been read
+            const uint64_t a = a0 + static_cast<uint64_t>(((j % kUStages) * kUTileBytes) >> 4);
+            const uint32_t d = tmem + kUColD + (j & 1) * 64;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {  // 16 coordinates per step: 32 bytes inside the swizzled 128-byte row
+                const uint64_t ak = a + static_cast<uint64_t>(((ks >> 2) * kUBoxBytes + (ks & 3) * 32) >> 4);
+                const uint64_t bk = b0 + static_cast<uint64_t>(((ks >> 2) * (kN * 128) + (ks & 3) * 32) >> 4);
+                if (elect_one()) umma_f16(d, ak, bk, umma_idesc(kN, false), ks > 0);
+            }
+            if (elect_one()) umma_commit(&bar_dist[j & 1]);
+        };
+        for (int j = 0; j < 2 && j < n_tiles; ++j) {
+            lost |= !mbar_wait(&bar_full[j], 0);
+            issue_distances(j);
+        }
+        for (int i = 0; i + 2 < n_tiles; ++i) {
+            lost |= !mbar_wait(&bar_parts[i & 1], (i >> 1) & 1);  // distance buffer i & 1 has been read by all ranking threads
+            lost |= !mbar_wait(&bar_full[(i + 2) % kUStages], ((i + 2) / kUStages) & 1);
             tc_fence_after();
-            issue_sums(i);
+            issue_distances(i + 2);
+        }
+    } else {
+        // ---- sum MMAs and the copies that refill the stages they free -----------------------------------------
+        const uint64_t a0 = umma_desc(smem_u32(xs), kUBoxBytes, 1024);  // MN-major: other half of the coordinates at LBO
+        const uint64_t b0 = umma_desc(smem_u32(oh), 16, 1024);
+        for (int i = 0; i < n_tiles; ++i) {
+            const int b = i & 1;
+            const uint64_t a = a0 + static_cast<uint64_t>(((i % kUStages) * kUTileBytes) >> 4);
+            const uint64_t o = b0 + static_cast<uint64_t>((b * kUOneHotBytes) >> 4);
+            const uint32_t d = tmem + kUColS + (i % kUSumBuffers) * 32;
+            lost |= !mbar_wait(&bar_onehot[b], (i >> 1) & 1);
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {  // 16 tokens per step: two 8-row groups of the tile = 2048 bytes
+                const uint64_t ak = a + static_cast<uint64_t>((ks * 2048) >> 4);
+                const uint64_t bk = o + static_cast<uint64_t>(((ks >> 2) * (32 * 128) + (ks & 3) * 32) >> 4);
+                if (elect_one()) umma_f16(d, ak, bk, umma_idesc(32, true), (i >= kUSumBuffers || ks > 0) ? 1u : 0u);
+            }
+            if (elect_one()) umma_commit(&bar_sums[b]);
             if (i + kUStages - 1 < n_tiles) {  // the stage of tile i - 1 is free once its sums have run
-                if (i >= 1) lost |= !mbar_wait(&bar_s[(i - 1) & 1], ((i - 1) >> 1) & 1);
+                if (i >= 1) lost |= !mbar_wait(&bar_sums[(i - 1) & 1], ((i - 1) >> 1) & 1);
                 load_tile(i + kUStages - 1);
             }
         }
     }
     // the commit of the last sums covers every MMA of this CTA
-    lost |= !mbar_wait(&bar_s[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
-    tc_fence_after();
-    {
-        uint32_t sum[32];
-        tmem_ld32(tmem + lane_base + kUColS, sum);
+    if (warp < kURankWarps) {
+        lost |= !mbar_wait(&bar_sums[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
+        tc_fence_after();
+    }
+    __syncthreads();
+    if (warp < kURankWarps) {
+        const int quarter = warp & 3, cpart = warp >> 2, row_in_tile = quarter * 32 + lane;
+        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+        float sum[8];  // coordinate row_in_tile, clusters 8 cpart ..: the accumulators added in index order
+        tmem_ld8(tmem + lane_base + kUColS + 8 * cpart, sum);
         tmem_ld_wait();
+        for (int a = 1; a < kUSumBuffers && a < n_tiles; ++a) {
+            float more[8];
+            tmem_ld8(tmem + lane_base + kUColS + a * 32 + 8 * cpart, more);
+            tmem_ld_wait();
+#pragma unroll
+            for (int k = 0; k < 8; ++k) sum[k] += more[k];
+        }
         long long* sums_g = p.sums + static_cast<size_t>(unit) * p.clusters * kHeadDim;
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
+        for (int k = 0; k < 8; ++k) {
+            const int c = 8 * cpart + k;
             if (c < p.clusters && cnt_s[c] > 0)
-                atomicAdd(reinterpret_cast<unsigned long long*>(sums_g + c * kHeadDim + tid),
-                          static_cast<unsigned long long>(__float2ll_rn(__uint_as_float(sum[c]) * kFix)));
+                atomicAdd(reinterpret_cast<unsigned long long*>(sums_g + c * kHeadDim + row_in_tile),
+                          static_cast<unsigned long long>(__float2ll_rn(sum[k] * kFix)));
         }
     }
     if (tid < p.clusters && cnt_s[tid] > 0) atomicAdd(&p.counts[unit * p.clusters + tid], cnt_s[tid]);
@@ -855,7 +932,7 @@ int launch_umma(const KmeansParams& p, int value, int iterations, void* centroid
     if (made != CUDA_SUCCESS) return fail(RESKV_ERR_CUDA, "kmeans: cuTensorMapEncodeTiled failed with code %d", static_cast<int>(made));
     constexpr int kN = HILO ? 64 : 32;
     const size_t smem = 1024 + static_cast<size_t>(kUStages) * kUTileBytes + 2 * kN * 128 + 2 * kUOneHotBytes +
-                        32 * kHeadDim * sizeof(float) + 32 * (sizeof(float) + sizeof(int));
+                        2 * 4 * kUTile * sizeof(float4) + 32 * kHeadDim * sizeof(float) + 32 * (sizeof(float) + sizeof(int));
     static unsigned long long prepared = 0;  // per-device bit: the shared-memory attribute is set
     int dev = 0;
     cudaGetDevice(&dev);
@@ -866,9 +943,18 @@ int launch_umma(const KmeansParams& p, int value, int iterations, void* centroid
             return rc;
         prepared |= 1ull << (dev & 63);
     }
-    // tokens per CTA: a multiple of the tile, about two CTAs' worth of work per SM, at most kChunkFastMax (FP32 partial sums)
-    const long long want = static_cast<long long>(p.units) * p.tokens / (2ll * sm_count());
-    const int chunk = static_cast<int>(want < kChunk ? kChunk : want > kChunkFastMax ? kChunkFastMax : (want + 127) / 128 * 128);
+    // tokens per CTA: one CTA per SM at a time, a CTA costs its tiles plus about six tile times of set-up, pipeline
+    // fill and flush; take the number of chunks per unit with the shortest estimated makespan
+    const int tiles = (p.tokens + kUTile - 1) / kUTile, sms = sm_count();
+    int chunk = kUTile;
+    long long best = -1;
+    for (int k = 1; k <= tiles; ++k) {
+        const int per = (tiles + k - 1) / k;
+        if (per * kUTile > kUChunkMax) continue;
+        const long long ctas = static_cast<long long>(p.units) * ((tiles + per - 1) / per);
+        const long long cost = ((ctas + sms - 1) / sms) * (per + 6);
+        if (best < 0 || cost < best) best = cost, chunk = per * kUTile;
+    }
     const dim3 grid((p.tokens + chunk - 1) / chunk, p.units);
     for (int it = 0; it < iterations; ++it) {
         kmeans_assign_umma_kernel<HILO><<<grid, kUThreads, smem, s>>>(p, xmap, chunk);
@@ -928,7 +1014,7 @@ extern "C" int reskv_kmeans(const void* x, int batch, int kv_heads, int tokens, 
     // the integer-counter arrays double as the FP32 reduction buffer [32][kRedStride] of the tensor-core form
     size_t counters = static_cast<size_t>(clusters) * kHeadDim * 2 * sizeof(int);
     const bool fast = !exact && padded <= 32 && aligned16(x);  // the row staging copies 16-byte pieces
-    if (fast && warp_mma) return value ? launch_umma<false>(p, value, iterations, centroids, s) : launch_umma<true>(p, value, iterations, centroids, s);
+    if (fast && !warp_mma) return value ? launch_umma<false>(p, value, iterations, centroids, s) : launch_umma<true>(p, value, iterations, centroids, s);
     if (fast) counters = static_cast<size_t>(kWarps) * 32 * kRedStride * sizeof(float);
     const size_t smem = static_cast<size_t>(clusters) * kHeadDim * sizeof(float) + counters +
                         kMaxClusters * (sizeof(int) + sizeof(float)) +
