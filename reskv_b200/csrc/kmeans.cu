@@ -537,7 +537,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 
 template <bool HILO>
 __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const KmeansParams p,
-                                                                           const __grid_constant__ CUtensorMap xmap, int chunk) {
+                                                                           const __grid_constant__ CUtensorMap xmap, int chunk,
+                                                                           int first, int last) {
     extern __shared__ unsigned char smem_u[];
     constexpr int kN = HILO ? 64 : 32;  // rows of the centre operand: hi halves, then lo halves
     unsigned char* base = smem_u + ((1024u - (smem_u32(smem_u) & 1023u)) & 1023u);  // swizzled blocks: 1024-byte aligned
@@ -638,7 +639,7 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
         for (int c = 0; c < 8; ++c) cn_r[c] = cn_s[8 * cpart + c];
         for (int i = 0; i < n_tiles; ++i) {
             const int b = i & 1, st = i % kUStages;
-            lost |= !mbar_wait(&bar_full[st], (i / kUStages) & 1);  // this thread reads the tile too (|x|^2)
+            if (first) lost |= !mbar_wait(&bar_full[st], (i / kUStages) & 1);  // this thread reads the tile too (|x|^2)
             lost |= !mbar_wait(&bar_dist[b], (i >> 1) & 1);
             tc_fence_after();
             float acc[8];
@@ -663,17 +664,20 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
                     d2 = d;
                 }
             }
-            // |x|^2 for the near-tie bound: packed FP16 products, eight at a time (an overflow gives +inf: re-rank)
+            // |x|^2 for the near-tie bound: packed FP16 products, eight at a time (an overflow gives +inf: re-rank).
+            // Only the first Lloyd iteration forms it; the merging threads park it in the id buffer for the others.
             float xn = 0.f;
-            const unsigned char* xt = xs + st * kUTileBytes + (cpart >> 1) * kUBoxBytes;
+            if (first) {
+                const unsigned char* xt = xs + st * kUTileBytes + (cpart >> 1) * kUBoxBytes;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint4 v = *reinterpret_cast<const uint4*>(xt + sw128(row_in_tile, 4 * (cpart & 1) + j));
-                const __half2* h = reinterpret_cast<const __half2*>(&v);
-                __half2 s = __hmul2(h[0], h[0]);
-                s = __hfma2(h[1], h[1], s), s = __hfma2(h[2], h[2], s), s = __hfma2(h[3], h[3], s);
-                const float2 f = __half22float2(s);
-                xn += f.x + f.y;
+                for (int j = 0; j < 4; ++j) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(xt + sw128(row_in_tile, 4 * (cpart & 1) + j));
+                    const __half2* h = reinterpret_cast<const __half2*>(&v);
+                    __half2 s = __hmul2(h[0], h[0]);
+                    s = __hfma2(h[1], h[1], s), s = __hfma2(h[2], h[2], s), s = __hfma2(h[3], h[3], s);
+                    const float2 f = __half22float2(s);
+                    xn += f.x + f.y;
+                }
             }
             if (i >= 2) lost |= !mbar_wait(&bar_parts_free[b], ((i - 2) >> 1) & 1);  // parts of tile i - 2 were merged
             part_s[(b * 4 + cpart) * kUTile + row_in_tile] = make_float4(d1, d2, __int_as_float(c1), xn);
@@ -685,42 +689,86 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
         const int quarter = warp - kURankWarps, row_in_tile = quarter * 32 + lane;
         const float cmax = cmax_s;
         int prev_even = -1, prev_odd = -1;  // byte offset of the element this thread set in each one-hot buffer
+        // |x|^2 of a token is the same in every Lloyd iteration: the first one stores it (as FP32 bits) where the
+        // token's id goes, the following ones read it from there one tile ahead, the last one writes the id
+        int32_t* ids_u = p.ids + static_cast<size_t>(unit) * p.tokens;
+        float xn_next = 0.f;
+        if (!first && t_begin + row_in_tile < t_end) xn_next = __int_as_float(ids_u[t_begin + row_in_tile]);
         for (int i = 0; i < n_tiles; ++i) {
             const int b = i & 1;
             const int row = t_begin + i * kUTile + row_in_tile;
             const bool live = row < t_end;
+            float xn = xn_next;
+            if (!first && row + kUTile < t_end) xn_next = __int_as_float(ids_u[row + kUTile]);
             lost |= !mbar_wait(&bar_parts[b], (i >> 1) & 1);
-            float4 m = part_s[(b * 4) * kUTile + row_in_tile];
-            float d1 = m.x, d2 = m.y, xn = m.w;
-            int c1 = __float_as_int(m.z);
+            float4 pm[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) pm[k] = part_s[(b * 4 + k) * kUTile + row_in_tile];
+            mbar_arrive(&bar_parts_free[b]);
+            float d1 = pm[0].x, d2 = pm[0].y;
+            int c1 = __float_as_int(pm[0].z);
+            if (first) xn = pm[0].w;
 #pragma unroll
             for (int k = 1; k < 4; ++k) {  // ascending centre groups: a strict comparison keeps the lower index on ties
-                m = part_s[(b * 4 + k) * kUTile + row_in_tile];
-                if (m.x < d1) {
-                    d2 = fminf(d1, m.y), d1 = m.x, c1 = __float_as_int(m.z);
+                if (pm[k].x < d1) {
+                    d2 = fminf(d1, pm[k].y), d1 = pm[k].x, c1 = __float_as_int(pm[k].z);
                 } else {
-                    d2 = fminf(d2, m.x);
+                    d2 = fminf(d2, pm[k].x);
                 }
-                xn += m.w;
+                if (first) xn += pm[k].w;
             }
-            mbar_arrive(&bar_parts_free[b]);
-            // near-ties: re-rank with the exact FP32 sum, the warp working on one token at a time
-            const bool tie = live && !((d2 - d1) > kTieBound * (1.01f * xn + cmax));
+            // near-ties: re-rank with the exact FP32 sum, the warp working on one token at a time.  Only centres
+            // whose distance lies inside the bound can win; when every centre group has at most one of those the
+            // exact sums of these few are enough (same arithmetic, same order as `nearest`), otherwise all are ranked.
+            const float bound = kTieBound * (1.01f * xn + cmax);
+            const bool tie = live && !((d2 - d1) > bound);
             uint32_t redo = __ballot_sync(kFull, tie);
             while (redo) {
                 const int src = __ffs(redo) - 1;
                 redo &= redo - 1;
+                const float s_d1 = __shfl_sync(kFull, d1, src), s_bound = __shfl_sync(kFull, bound, src);
+                bool all = false;
+                int cand[4], n_cand = 0;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float k_d1 = __shfl_sync(kFull, pm[k].x, src), k_d2 = __shfl_sync(kFull, pm[k].y, src);
+                    const int k_c = __shfl_sync(kFull, __float_as_int(pm[k].z), src);
+                    if (!((k_d2 - s_d1) > s_bound)) all = true;
+                    cand[k] = k_c;
+                    if (!((k_d1 - s_d1) > s_bound)) n_cand |= 1 << k;
+                }
                 const __half* xr = xu + static_cast<size_t>(t_begin + i * kUTile + quarter * 32 + src) * kHeadDim;
                 float xv[4];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) xv[k] = __half2float(xr[lane + 32 * k]);
-                float best;
-                int c;
-                nearest(cen_s, p.clusters, xv, lane, best, c);
+                float best = INFINITY;
+                int c = 0;
+                if (all) {
+                    nearest(cen_s, p.clusters, xv, lane, best, c);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        if (!((n_cand >> k) & 1)) continue;
+                        const float* crow = cen_s + cand[k] * kHeadDim;
+                        float acc = 0.f;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float df = xv[e] - crow[lane + 32 * e];
+                            acc = fmaf(df, df, acc);
+                        }
+#pragma unroll
+                        for (int off = 16; off > 0; off >>= 1) acc = acc + __shfl_xor_sync(kFull, acc, off);
+                        if (acc < best) best = acc, c = cand[k];  // ascending centre index: the lower one wins ties
+                    }
+                }
                 if (lane == src) c1 = c;
             }
             if (live) {
-                p.ids[static_cast<size_t>(unit) * p.tokens + row] = c1;
+                if (last) {
+                    ids_u[row] = c1;
+                } else if (first) {
+                    ids_u[row] = __float_as_int(xn);
+                }
                 atomicAdd(&cnt_s[c1], 1);
             }
             // one-hot buffer b was last read by the sums of tile i - 2
@@ -957,7 +1005,7 @@ int launch_umma(const KmeansParams& p, int value, int iterations, void* centroid
     }
     const dim3 grid((p.tokens + chunk - 1) / chunk, p.units);
     for (int it = 0; it < iterations; ++it) {
-        kmeans_assign_umma_kernel<HILO><<<grid, kUThreads, smem, s>>>(p, xmap, chunk);
+        kmeans_assign_umma_kernel<HILO><<<grid, kUThreads, smem, s>>>(p, xmap, chunk, it == 0, it + 1 == iterations);
         kmeans_update_kernel<<<p.units, 256, 0, s>>>(p, value, it + 1 == iterations ? static_cast<__half*>(centroids) : nullptr);
     }
     return check_cuda(cudaGetLastError(), "kmeans launch");
