@@ -456,13 +456,13 @@ __global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const Kmean
 //   * sums: S^T[128 coordinates x 32 clusters] += X^T . onehot^T, the same tile now read as the MN-major A operand,
 //     accumulated in TMEM (four accumulators in turn) over the CTA's whole token range and flushed once as
 //     2^24-scaled integers.
-// Two more warps issue the asynchronous work, one the distance MMAs, one the copies and the sum MMAs; they stay
+// Three more warps issue the asynchronous work (distance MMAs, sum MMAs, copies); they stay
 // converged (descriptor arithmetic on the uniform datapath) and elect one lane per instruction.  The roles run
 // concurrently on different tiles and hand over through mbarriers only (double-buffered distances, parts and
 // one-hot operand); every wait is bounded.
 constexpr int kURankWarps = 16;                // four per TMEM lane quarter: eight centres each
 constexpr int kUMergeWarps = 4;                // one per TMEM lane quarter
-constexpr int kUThreads = (kURankWarps + kUMergeWarps + 2) * 32;  // + one warp issuing the distance MMAs, one the copies and the sum MMAs
+constexpr int kUThreads = (kURankWarps + kUMergeWarps + 3) * 32;  // + three issuing warps: distance MMAs, sum MMAs, copies
 constexpr int kUTile = 128;
 constexpr int kUStages = 5;
 constexpr int kUBoxBytes = kUTile * 128;       // 128 rows x 64 coordinates
@@ -554,7 +554,6 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
     // onehot: 128 merging threads have written the one-hot operand.
     __shared__ uint64_t bar_full[kUStages], bar_dist[2], bar_sums[2], bar_parts[2], bar_parts_free[2], bar_onehot[2];
     __shared__ uint32_t tmem_base_s;
-    __shared__ float cmax_s;
 
     const int unit = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int t_begin = blockIdx.x * chunk, t_end = min(p.tokens, t_begin + chunk);
@@ -586,47 +585,55 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
             tma_load_3d(dst + kUBoxBytes, &xmap, 64, t_begin + j * kUTile, unit, bar);
         }
     };
-    if (warp == kURankWarps + kUMergeWarps + 1)
-        for (int j = 0; j < kUStages - 1 && j < n_tiles; ++j) load_tile(j);
+    if (warp == kURankWarps + kUMergeWarps + 2)
+        for (int j = 0; j < kUStages && j < n_tiles; ++j) load_tile(j);
 
     // ---- per CTA: centre operand (FP16 hi | lo rows, swizzled), FP32 centres, |c|^2, empty one-hot buffers ----
-    for (int i = tid; i < 32 * kHeadDim; i += kUThreads) {
-        const int c = i / kHeadDim, d = i % kHeadDim;
-        const float v = c < p.clusters ? cen_g[i] : 0.f;
-        cen_s[i] = v;
-        const __half h = __float2half_rn(v);
-        unsigned char* at = cop + (d >> 6) * (kN * 128) + ((d & 7) << 1);
-        *reinterpret_cast<__half*>(at + sw128(c, (d & 63) >> 3)) = h;
-        if (HILO) *reinterpret_cast<__half*>(at + sw128(32 + c, (d & 63) >> 3)) = __float2half_rn(v - __half2float(h));
+    {
+        // four coordinates per thread and step, all loads of a thread in flight together
+        constexpr int kSteps = (32 * kHeadDim / 4 + kUThreads - 1) / kUThreads;
+        float4 v[kSteps];
+#pragma unroll
+        for (int k = 0; k < kSteps; ++k) {
+            const int i4 = tid + k * kUThreads;
+            v[k] = (i4 < 32 * kHeadDim / 4 && i4 / (kHeadDim / 4) < p.clusters) ? __ldg(reinterpret_cast<const float4*>(cen_g) + i4)
+                                                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int k = 0; k < kSteps; ++k) {
+            const int i4 = tid + k * kUThreads;
+            if (i4 >= 32 * kHeadDim / 4) break;
+            const int c = i4 / (kHeadDim / 4), d = (i4 % (kHeadDim / 4)) * 4;
+            reinterpret_cast<float4*>(cen_s)[i4] = v[k];
+            const __half2 h01 = __floats2half2_rn(v[k].x, v[k].y), h23 = __floats2half2_rn(v[k].z, v[k].w);
+            unsigned char* at = cop + (d >> 6) * (kN * 128) + ((d & 7) << 1);
+            *reinterpret_cast<uint2*>(at + sw128(c, (d & 63) >> 3)) =
+                make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+            float2 f01 = __half22float2(h01), f23 = __half22float2(h23);  // what the MMA sees: hi (+ lo)
+            if (HILO) {
+                const __half2 l01 = __floats2half2_rn(v[k].x - f01.x, v[k].y - f01.y);
+                const __half2 l23 = __floats2half2_rn(v[k].z - f23.x, v[k].w - f23.y);
+                *reinterpret_cast<uint2*>(at + sw128(32 + c, (d & 63) >> 3)) =
+                    make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
+                const float2 g01 = __half22float2(l01), g23 = __half22float2(l23);
+                f01.x += g01.x, f01.y += g01.y, f23.x += g23.x, f23.y += g23.y;
+            }
+            // |c|^2: the 32 threads of a warp hold one centre (kUThreads is a multiple of 32)
+            float sq = fmaf(f01.x, f01.x, fmaf(f01.y, f01.y, fmaf(f23.x, f23.x, f23.y * f23.y)));
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(kFull, sq, off);
+            if (lane == 0) cn_s[c] = c < p.clusters ? sq : INFINITY;
+        }
     }
     for (int i = tid; i < 2 * kUOneHotBytes / 16; i += kUThreads) reinterpret_cast<uint4*>(oh)[i] = make_uint4(0, 0, 0, 0);
     if (tid < 32) cnt_s[tid] = 0;
-    __syncthreads();
-    for (int c = warp; c < 32; c += kUThreads / 32) {
-        float acc = INFINITY;
-        if (c < p.clusters) {
-            acc = 0.f;
-            for (int d = lane; d < kHeadDim; d += 32) {
-                float v = cen_s[c * kHeadDim + d];
-                const __half h = __float2half_rn(v);
-                v = __half2float(h);
-                if (HILO) v += __half2float(__float2half_rn(cen_s[c * kHeadDim + d] - v));  // what the MMA sees
-                acc = fmaf(v, v, acc);
-            }
-            for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(kFull, acc, off);
-        }
-        if (lane == 0) cn_s[c] = acc;
-    }
-    __syncthreads();
-    if (tid == 0) {
-        float m = 0.f;
-        for (int c = 0; c < p.clusters; ++c) m = fmaxf(m, cn_s[c]);
-        cmax_s = m;
-    }
     proxy_fence();  // the operands written above are read by the tensor core (async proxy)
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    float cmax = lane < p.clusters ? cn_s[lane] : 0.f;  // largest |c|^2, in every thread
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) cmax = fmaxf(cmax, __shfl_xor_sync(kFull, cmax, off));
     const uint32_t tmem = tmem_base_s;
     const __half* xu = p.x + static_cast<size_t>(unit) * p.x_stride * kHeadDim;
 
@@ -687,7 +694,6 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
     } else if (warp < kURankWarps + kUMergeWarps) {
         // ---- merging: one thread per token -------------------------------------------------------------------
         const int quarter = warp - kURankWarps, row_in_tile = quarter * 32 + lane;
-        const float cmax = cmax_s;
         int prev_even = -1, prev_odd = -1;  // byte offset of the element this thread set in each one-hot buffer
         // |x|^2 of a token is the same in every Lloyd iteration: the first one stores it (as FP32 bits) where the
         // token's id goes, the following ones read it from there one tile ahead, the last one writes the id
@@ -809,8 +815,14 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
             tc_fence_after();
             issue_distances(i + 2);
         }
+    } else if (warp == kURankWarps + kUMergeWarps + 2) {
+        // ---- copies: a stage is refilled as soon as the sums of the tile it held have run ---------------------
+        for (int i = 0; i + kUStages < n_tiles; ++i) {
+            lost |= !mbar_wait(&bar_sums[i & 1], (i >> 1) & 1);
+            load_tile(i + kUStages);
+        }
     } else {
-        // ---- sum MMAs and the copies that refill the stages they free -----------------------------------------
+        // ---- sum MMAs ---------------------------------------------------------------------------------------
         const uint64_t a0 = umma_desc(smem_u32(xs), kUBoxBytes, 1024);  // MN-major: other half of the coordinates at LBO
         const uint64_t b0 = umma_desc(smem_u32(oh), 16, 1024);
         for (int i = 0; i < n_tiles; ++i) {
@@ -827,10 +839,6 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
                 if (elect_one()) umma_f16(d, ak, bk, umma_idesc(32, true), (i >= kUSumBuffers || ks > 0) ? 1u : 0u);
             }
             if (elect_one()) umma_commit(&bar_sums[b]);
-            if (i + kUStages - 1 < n_tiles) {  // the stage of tile i - 1 is free once its sums have run
-                if (i >= 1) lost |= !mbar_wait(&bar_sums[(i - 1) & 1], ((i - 1) >> 1) & 1);
-                load_tile(i + kUStages - 1);
-            }
         }
     }
     // the commit of the last sums covers every MMA of this CTA
@@ -1062,7 +1070,7 @@ extern "C" int reskv_kmeans(const void* x, int batch, int kv_heads, int tokens, 
     // the integer-counter arrays double as the FP32 reduction buffer [32][kRedStride] of the tensor-core form
     size_t counters = static_cast<size_t>(clusters) * kHeadDim * 2 * sizeof(int);
     const bool fast = !exact && padded <= 32 && aligned16(x);  // the row staging copies 16-byte pieces
-    if (fast && !warp_mma) return value ? launch_umma<false>(p, value, iterations, centroids, s) : launch_umma<true>(p, value, iterations, centroids, s);
+    if (fast && !warp_mma && aligned16(workspace)) return value ? launch_umma<false>(p, value, iterations, centroids, s) : launch_umma<true>(p, value, iterations, centroids, s);
     if (fast) counters = static_cast<size_t>(kWarps) * 32 * kRedStride * sizeof(float);
     const size_t smem = static_cast<size_t>(clusters) * kHeadDim * sizeof(float) + counters +
                         kMaxClusters * (sizeof(int) + sizeof(float)) +
