@@ -282,13 +282,15 @@ int reskv_encode_quantized(const void* x, const void* centroids, const int32_t* 
                            void* scale, int64_t out_tok_stride, void* stream);
 
 /* Tiled (structured == 0, 16-bit masks) or 4:16 structured (4-bit indices) FP16:
- * values f16 [.., nnz] in (tile, rank) order, meta i32 [.., 4].  Replaces
- * compression.compress_fp16 (reskv/csrc/compression.cu:57-147,423-473). */
+ * values f16 [.., nnz] in (tile, rank) order, meta i32 [.., 4].  x, centroids, values
+ * and meta 16-byte aligned.  Replaces compression.compress_fp16
+ * (reskv/csrc/compression.cu:57-147,423-473). */
 int reskv_encode_tiled_fp16(const void* x, const void* centroids, const int32_t* ids, int batch, int kv_heads,
                             int tokens, int64_t x_tok_stride, int clusters, int nnz, int structured, void* values,
                             void* meta, int64_t out_tok_stride, void* stream);
 
 /* 1-of-4 structured INT4: packed i32 [.., 4], meta i32 [.., 2], scale f16 [..].
+ * x, centroids and packed 16-byte, meta 8-byte aligned.
  * Replaces compression.compress_structured_int4
  * (reskv/csrc/compression.cu:153-239,475-504). */
 int reskv_encode_structured_int4(const void* x, const void* centroids, const int32_t* ids, int batch, int kv_heads,

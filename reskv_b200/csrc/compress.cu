@@ -1,18 +1,17 @@
-// Residual packers: x - centroid[id] -> top-magnitude selection -> compact layout.
-// (The unstructured FP16 bitmap and the unstructured INT4 / INT2 packers run one thread per token and live in
-// compress_topk.cu; this file holds the entry points of all layouts and the kernels of the others.)
+// Residual packers: x - centroid[id] -> top-magnitude selection -> packed layout.
+// This file holds the C entry points of all layouts and the kernel of the compact quantised layout; the
+// layouts of the reference run one thread per token and live in compress_topk.cu.
 //
-// One warp encodes one token; lane l owns coordinates {l, l+32, l+64, l+96}.
+// Compact layout: one warp encodes one token; lane l owns coordinates {l, l+32, l+64, l+96}.
 // With that ownership a warp vote of "lane keeps coordinate l+32i" *is* the
-// keep-mask of coordinates 32i..32i+31 (LSB = lowest coordinate), which makes
-// every metadata word of every layout one or two instructions, and ranks are
+// keep-mask of coordinates 32i..32i+31 (LSB = lowest coordinate), and ranks are
 // popcounts of votes.  Rounding points (they decide bit-exactness against the
-// reference): r = fp32(x) - fp32(c); the selection key is |fp16(r)|; FP16
-// layouts store fp16(r); quantisers divide the FP32 r with the GPU's approximate
+// reference): r = fp32(x) - fp32(c); the selection key is |fp16(r)|;
+// quantisers divide the FP32 r with the GPU's approximate
 // division, as the reference's fast-math build does (see div_fast).
 // Ties keep the lower coordinate.
 //
-// The global top-k of the unstructured layouts is a bisection on the 15-bit key
+// The global top-k is a bisection on the 15-bit key
 // pattern: a vote per owned coordinate counts the keys >= candidate, so no data
 // moves between lanes.
 #include "compress_common.cuh"
@@ -129,104 +128,6 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) encode_compact_kernel(const
     }
 }
 
-// ---- tiled (mask) / structured 4:16 (indices) FP16 -----------------------------------
-// Tile j = coordinates 16j..16j+15 = half-warp (j % 2) of owned coordinate i = j / 2.
-template <bool STRUCT>
-__global__ void __launch_bounds__(kWarpsPerCta * 32) encode_tiled_fp16_kernel(const EncodeParams p) {
-    const int lane = threadIdx.x & 31, sub = lane & 15;
-    const int per_tile = p.nnz / 8;
-    const long long rows = static_cast<long long>(p.units) * p.tokens;
-    for (long long row = static_cast<long long>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5); row < rows;
-         row += static_cast<long long>(gridDim.x) * kWarpsPerCta) {
-        const int unit = static_cast<int>(row / p.tokens), t = static_cast<int>(row % p.tokens);
-        const Residual res = load_residual(p, unit, t, lane);
-        const size_t orow = static_cast<size_t>(unit) * p.out_stride + t;
-        __half* val = static_cast<__half*>(p.payload) + orow * p.nnz;
-        int32_t* meta = static_cast<int32_t*>(p.meta) + orow * 4;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            // position of this coordinate in its tile's (key desc, index asc) order
-            int beat = 0;
-#pragma unroll
-            for (int off = 1; off < 16; ++off) {
-                const int src = (lane & 16) | ((sub + off) & 15);
-                const uint32_t other = __shfl_sync(kFull, res.key[i], src);
-                const int osub = (sub + off) & 15;
-                beat += (other > res.key[i]) || (other == res.key[i] && osub < sub);
-            }
-            const bool keep = beat < per_tile;
-            const uint32_t vote = __ballot_sync(kFull, keep);
-            const uint32_t tile_mask = (vote >> (lane & 16)) & 0xffffu;
-            const int rank = __popc(tile_mask & ((1u << sub) - 1u));
-            const int tile = 2 * i + (lane >> 4);
-            if (keep) val[tile * per_tile + rank] = res.h[i];
-            if constexpr (STRUCT) {
-                // four 4-bit in-tile indices, rank r at bit 4r; tile 2i low half, 2i+1 high half
-                uint32_t code = keep ? (static_cast<uint32_t>(sub) << (4 * rank + (lane & 16))) : 0u;
-                code = __reduce_or_sync(kFull, code);
-                if (lane == 0) meta[i] = static_cast<int32_t>(code);
-            } else {
-                if (lane == 0) meta[i] = static_cast<int32_t>(vote);
-            }
-        }
-    }
-}
-
-// ---- structured INT4: one coordinate of every four ------------------------------------
-__global__ void __launch_bounds__(kWarpsPerCta * 32) encode_structured_int4_kernel(const EncodeParams p) {
-    const int lane = threadIdx.x & 31, in_group = lane & 3;
-    const long long rows = static_cast<long long>(p.units) * p.tokens;
-    for (long long row = static_cast<long long>(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5); row < rows;
-         row += static_cast<long long>(gridDim.x) * kWarpsPerCta) {
-        const int unit = static_cast<int>(row / p.tokens), t = static_cast<int>(row % p.tokens);
-        const Residual res = load_residual(p, unit, t, lane);
-        float comp[4];   // the group's chosen residual (valid in every lane of the group)
-        int which[4];
-        float amax = 0.f;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint32_t bk = res.key[i];
-            int bi = in_group;
-            float br = res.r[i];
-#pragma unroll
-            for (int off = 1; off < 4; off <<= 1) {
-                const uint32_t ok = __shfl_xor_sync(kFull, bk, off);
-                const int oi = __shfl_xor_sync(kFull, bi, off);
-                const float orr = __shfl_xor_sync(kFull, br, off);
-                if (ok > bk || (ok == bk && oi < bi)) bk = ok, bi = oi, br = orr;
-            }
-            comp[i] = br, which[i] = bi;
-            amax = fmaxf(amax, fabsf(br));
-        }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, off));
-        const float s = amax > 0.f ? amax * (1.0f / 7.0f) : 1.0f;
-        const size_t orow = static_cast<size_t>(unit) * p.out_stride + t;
-        int32_t* packed = static_cast<int32_t*>(p.payload) + orow * 4;
-        int32_t* meta = static_cast<int32_t*>(p.meta) + orow * 2;
-        uint32_t mword[2] = {0u, 0u};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            // group g = 8 i + lane / 4; nibble g % 8 of word g / 8 = i; index bits 2 (g % 16) of meta word g / 16
-            // q = clamp(__float2int_rn(r / s)) with the approximate division (compression.cu:233-234)
-            const int q = max(-7, min(7, __float2int_rn(div_fast(comp[i], s))));
-            const bool leader = in_group == 0;
-            uint32_t w = leader ? ((static_cast<uint32_t>(q) & 15u) << (4 * (lane >> 2))) : 0u;
-            w = __reduce_or_sync(kFull, w);
-            if (lane == 0) packed[i] = static_cast<int32_t>(w);
-            const int g = 8 * i + (lane >> 2);
-            if (leader) mword[i >> 1] |= static_cast<uint32_t>(which[i]) << (2 * (g & 15));
-        }
-        mword[0] = __reduce_or_sync(kFull, mword[0]);
-        mword[1] = __reduce_or_sync(kFull, mword[1]);
-        if (lane == 0) {
-            meta[0] = static_cast<int32_t>(mword[0]);
-            meta[1] = static_cast<int32_t>(mword[1]);
-            p.scale[orow] = __float2half_rn(s);
-        }
-    }
-}
-
 int check_common(const char* who, const void* x, const void* cen, const void* ids, const void* payload, int batch,
                  int kv_heads, int tokens, int64_t x_stride, int clusters, int64_t out_stride) {
     if (!x || !cen || !ids || !payload) return fail(RESKV_ERR_INVALID, "%s: null tensor pointer", who);
@@ -311,13 +212,9 @@ extern "C" int reskv_encode_tiled_fp16(const void* x, const void* centroids, con
     if (structured && nnz != 32) return fail(RESKV_ERR_INVALID, "encode_tiled_fp16: the 4:16 index form needs nnz == 32");
     EncodeParams p{static_cast<const __half*>(x), static_cast<const __half*>(centroids), ids, values, meta, nullptr,
                    x_tok_stride, out_tok_stride, batch * kv_heads, tokens, clusters, nnz};
-    const long long rows = static_cast<long long>(p.units) * tokens;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (structured)
-        encode_tiled_fp16_kernel<true><<<grid_for(rows), kWarpsPerCta * 32, 0, s>>>(p);
-    else
-        encode_tiled_fp16_kernel<false><<<grid_for(rows), kWarpsPerCta * 32, 0, s>>>(p);
-    return check_cuda(cudaGetLastError(), "encode_tiled_fp16 launch");
+    if (!aligned16(x) || !aligned16(centroids) || !aligned16(values) || !aligned16(meta))
+        return fail(RESKV_ERR_INVALID, "encode_tiled_fp16: x, centroids, values and meta must be 16-byte aligned");
+    return launch_topk_tiled_fp16(p, structured != 0, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int reskv_encode_structured_int4(const void* x, const void* centroids, const int32_t* ids, int batch,
@@ -329,7 +226,7 @@ extern "C" int reskv_encode_structured_int4(const void* x, const void* centroids
     if (!meta || !scale) return fail(RESKV_ERR_INVALID, "encode_structured_int4: null metadata or scale pointer");
     EncodeParams p{static_cast<const __half*>(x), static_cast<const __half*>(centroids), ids, packed, meta,
                    static_cast<__half*>(scale), x_tok_stride, out_tok_stride, batch * kv_heads, tokens, clusters, 32};
-    const long long rows = static_cast<long long>(p.units) * tokens;
-    encode_structured_int4_kernel<<<grid_for(rows), kWarpsPerCta * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    return check_cuda(cudaGetLastError(), "encode_structured_int4 launch");
+    if (!aligned16(x) || !aligned16(centroids) || !aligned16(packed) || (reinterpret_cast<uintptr_t>(meta) & 7u) != 0)
+        return fail(RESKV_ERR_INVALID, "encode_structured_int4: x, centroids and packed must be 16-byte, meta 8-byte aligned");
+    return launch_topk_structured_int4(p, static_cast<cudaStream_t>(stream));
 }

@@ -1,5 +1,6 @@
-// Definitions shared by the residual packers (compress.cu: one warp per token; compress_topk.cu: one thread
-// per token for the two layouts that select the globally largest residuals).
+// Definitions shared by the residual packers (compress_topk.cu: one thread per token, the form every layout of
+// the reference uses when its pointers are 16-byte aligned; compress.cu: one warp per token, the compact layout
+// and the route for unaligned pointers).
 #pragma once
 
 #include "common.cuh"
@@ -20,6 +21,8 @@ struct EncodeParams {
 // Launchers of the thread-per-token kernels (compress_topk.cu).
 int launch_topk_bitmap_fp16(const EncodeParams& p, cudaStream_t stream);
 int launch_topk_quantized(const EncodeParams& p, int bits, cudaStream_t stream);
+int launch_topk_tiled_fp16(const EncodeParams& p, bool indexed, cudaStream_t stream);  // tile masks / 4:16 indices
+int launch_topk_structured_int4(const EncodeParams& p, cudaStream_t stream);
 
 namespace {
 

@@ -1,5 +1,6 @@
-// Residual packers of the two layouts that keep the globally largest residuals of a token
-// (unstructured FP16 bitmap; unstructured INT4 / INT2): one THREAD per token.
+// Residual packers, one THREAD per token: the layouts that keep the globally largest residuals of a token
+// (unstructured FP16 bitmap; unstructured INT4 / INT2), the layouts that keep the largest of every 16-coordinate
+// tile (tiled masks, 4:16 indices) and the 1-of-4 INT4 layout.
 //
 // The warp-per-token form spends most of its instructions on cross-lane traffic: every round of the
 // threshold bisection ends in a warp reduction, ranks and masks are votes and popcounts.  With a whole
@@ -17,6 +18,10 @@
 //   * ties at the threshold keep the lower coordinates; the kept FP16 residuals are compacted in place in
 //     the thread's own row and the warp writes the 32 rows out with 16-byte stores.
 //
+// The tiled layouts run the same bisection per tile, two tiles at a time in the two halves of the packed
+// operations (the accept decision is a packed comparison as well, so nothing is ever unpacked); the 1-of-4 layout
+// compares four keys per group.
+//
 // Rounding points are those of compress.cu (they decide bit-exactness): selection key |fp16(r)|, FP16 layouts
 // store fp16(r), the quantisers divide the FP32 r with the approximate division of the reference's build.
 #include <cuda_fp16.h>
@@ -31,7 +36,7 @@ constexpr int kTopkThreads = kTopkWarps * 32;
 constexpr int kRowBytes = 2 * kHeadDim + 16;  // shared-memory row of one token / one centroid
 constexpr int kChunkTokens = kTopkThreads;    // tokens a CTA takes per pass (32 per warp)
 
-enum class TopkMode { kBitmapFp16, kQuant4, kQuant2 };
+enum class TopkMode { kBitmapFp16, kQuant4, kQuant2, kTiledFp16, kStructFp16, kStructInt4 };
 
 __device__ __forceinline__ float half_lo(uint32_t v) {
     return __half2float(__ushort_as_half(static_cast<unsigned short>(v & 0xffffu)));
@@ -107,6 +112,54 @@ __device__ __forceinline__ void select_topk_thread(const uint32_t (&key)[64], in
     }
 }
 
+// Keep-mask of the `m` largest keys of every 16-coordinate tile, lower coordinate first among equal keys.
+// key[16 p + j] holds coordinate 32 p + j (tile 2 p) in its LOW and 32 p + 16 + j (tile 2 p + 1) in its HIGH half;
+// keep[p] has coordinate 32 p + q at bit q (the tiled metadata word of the reference, compression.cu:126-139).
+__device__ __forceinline__ void select_tiles_thread(const uint32_t (&key)[64], int m, uint32_t (&keep)[4]) {
+    const __half2 m2 = __float2half2_rn(static_cast<float>(m));
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        // per half: largest v with count(key >= v) >= m; counts up to 16 are exact in FP16
+        uint32_t v2 = 0;
+        for (int bit = 14; bit >= 0; --bit) {
+            const uint32_t both = (1u << bit) | (1u << (bit + 16));
+            const __half2 c2 = as_half2(v2 | both);
+            __half2 a0 = __hge2(as_half2(key[16 * p]), c2), a1 = __hge2(as_half2(key[16 * p + 1]), c2);
+#pragma unroll
+            for (int j = 2; j < 16; j += 2) {
+                a0 = __hadd2(a0, __hge2(as_half2(key[16 * p + j]), c2));
+                a1 = __hadd2(a1, __hge2(as_half2(key[16 * p + j + 1]), c2));
+            }
+            v2 |= both & __hge2_mask(__hadd2(a0, a1), m2);  // each half accepts the bit on its own count
+        }
+        const __half2 t2 = as_half2(v2);
+        uint32_t ge = 0u, gt = 0u;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const uint32_t place = (1u << j) | (0x10000u << j);
+            ge |= __hge2_mask(as_half2(key[16 * p + j]), t2) & place;
+            gt |= __hgt2_mask(as_half2(key[16 * p + j]), t2) & place;
+        }
+        uint32_t kept = 0u;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t g = (ge >> (16 * h)) & 0xffffu, t = (gt >> (16 * h)) & 0xffffu;
+            uint32_t k = g;
+            if (__popc(g) != m) {  // more keys equal to the threshold than places left: the lowest coordinates stay
+                int need = m - __popc(t);
+                uint32_t eq = g ^ t;
+                k = t;
+                while (eq != 0u && need > 0) {
+                    const uint32_t first = eq & (0u - eq);
+                    eq ^= first, k |= first, --need;
+                }
+            }
+            kept |= k << (16 * h);
+        }
+        keep[p] = kept;
+    }
+}
+
 template <TopkMode MODE>
 __global__ void __launch_bounds__(kTopkThreads, 4) encode_topk_kernel(const EncodeParams p) {
     extern __shared__ __align__(16) unsigned char topk_smem[];
@@ -137,6 +190,61 @@ __global__ void __launch_bounds__(kTopkThreads, 4) encode_topk_kernel(const Enco
 
         uint32_t keep[4] = {0u, 0u, 0u, 0u};
         const size_t orow = static_cast<size_t>(unit) * p.out_stride + t0 + lane;
+        constexpr bool kTiles = MODE == TopkMode::kTiledFp16 || MODE == TopkMode::kStructFp16;
+        constexpr bool kFp16Rows = MODE == TopkMode::kBitmapFp16 || kTiles;  // the row becomes the FP16 payload
+        if constexpr (MODE == TopkMode::kStructInt4) {
+            // one residual of every four consecutive coordinates: the largest |fp16(r)|, lowest index on ties;
+            // FP32 scale amax / 7, codes with the approximate division (compression.cu:153-239)
+            if (lane < ntok) {
+                int id = p.ids[static_cast<size_t>(unit) * p.tokens + t0 + lane];
+                id = min(max(id, 0), p.clusters - 1);
+                const unsigned char* crow = cen_s + id * kRowBytes;
+                uint32_t which[2] = {0u, 0u};  // 2-bit in-group index of group g at bit 2 (g % 16) of word g / 16
+                float amax = 0.f;
+#pragma unroll 1
+                for (int pc = 0; pc < 4; ++pc) {
+                    float r[32];
+                    residual_piece(xrow, crow, pc, r);
+                    uint32_t w = 0u;
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        uint32_t bk = __half_as_ushort(__float2half_rn(r[4 * g])) & 0x7fffu, bi = 0u;
+                        float br = r[4 * g];
+#pragma unroll
+                        for (int e = 1; e < 4; ++e) {
+                            const uint32_t k = __half_as_ushort(__float2half_rn(r[4 * g + e])) & 0x7fffu;
+                            if (k > bk) bk = k, bi = e, br = r[4 * g + e];
+                        }
+                        amax = fmaxf(amax, fabsf(br));
+                        w |= bi << (2 * g);
+                    }
+                    if (pc < 2) which[0] |= w << (16 * pc); else which[1] |= w << (16 * (pc - 2));
+                }
+                const float s = amax > 0.f ? amax * (1.0f / 7.0f) : 1.0f;
+                uint32_t out[4];
+#pragma unroll 1
+                for (int pc = 0; pc < 4; ++pc) {
+                    float r[32];
+                    residual_piece(xrow, crow, pc, r);
+                    const uint32_t w = (pc < 2 ? which[0] >> (16 * pc) : which[1] >> (16 * (pc - 2))) & 0xffffu;
+                    uint32_t word = 0u;
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        const uint32_t bi = (w >> (2 * g)) & 3u;
+                        const float br = bi == 0u ? r[4 * g] : bi == 1u ? r[4 * g + 1] : bi == 2u ? r[4 * g + 2] : r[4 * g + 3];
+                        const int q = max(-7, min(7, __float2int_rn(div_fast(br, s))));
+                        word |= (static_cast<uint32_t>(q) & 15u) << (4 * g);
+                    }
+                    if (pc == 0) out[0] = word; else if (pc == 1) out[1] = word; else if (pc == 2) out[2] = word; else out[3] = word;
+                }
+                const size_t orow = static_cast<size_t>(unit) * p.out_stride + t0 + lane;
+                static_cast<uint4*>(p.payload)[orow] = make_uint4(out[0], out[1], out[2], out[3]);
+                static_cast<uint2*>(p.meta)[orow] = make_uint2(which[0], which[1]);
+                p.scale[orow] = __float2half_rn(s);
+            }
+            __syncthreads();  // rows are rewritten by the next pass
+            continue;
+        }
         if (lane < ntok) {
             int id = p.ids[static_cast<size_t>(unit) * p.tokens + t0 + lane];
             id = min(max(id, 0), p.clusters - 1);
@@ -148,8 +256,8 @@ __global__ void __launch_bounds__(kTopkThreads, 4) encode_topk_kernel(const Enco
                 residual_piece(xrow, crow, pc, r);
 #pragma unroll
                 for (int j = 0; j < 16; ++j)
-                    key[16 * pc + j] = as_u32(__floats2half2_rn(r[16 + j], r[j])) & 0x7fff7fffu;
-                if constexpr (MODE == TopkMode::kBitmapFp16) {
+                    key[16 * pc + j] = as_u32(kTiles ? __floats2half2_rn(r[j], r[16 + j]) : __floats2half2_rn(r[16 + j], r[j])) & 0x7fff7fffu;
+                if constexpr (kFp16Rows) {
                     // fp16(r) in coordinate order replaces the (fully consumed) x values of this piece
 #pragma unroll
                     for (int m = 0; m < 4; ++m) {
@@ -162,9 +270,37 @@ __global__ void __launch_bounds__(kTopkThreads, 4) encode_topk_kernel(const Enco
                     }
                 }
             }
-            select_topk_thread(key, p.nnz, keep);
+            if constexpr (kTiles) {
+                select_tiles_thread(key, p.nnz / 8, keep);
+                // compact the kept values to the front of the row, ascending coordinates (= tile, then rank)
+                unsigned short* vals = reinterpret_cast<unsigned short*>(xrow);
+                int n = 0;
+                uint32_t code[4] = {0u, 0u, 0u, 0u};  // 4:16 form: four 4-bit in-tile indices per tile, rank r at bit 4 r
+#pragma unroll
+                for (int pc = 0; pc < 4; ++pc) {
+                    uint32_t w = keep[pc];
+                    int rank = 0;
+                    while (w != 0u) {
+                        const int q = __ffs(w) - 1;
+                        w &= w - 1u;
+                        vals[n++] = vals[32 * pc + q];
+                        if constexpr (MODE == TopkMode::kStructFp16) {
+                            // ranks restart at the second tile of the word (bit 16): four values per tile
+                            code[pc] |= static_cast<uint32_t>(q & 15) << (4 * (rank & 3) + (q & 16));
+                            ++rank;
+                        }
+                    }
+                }
+                if constexpr (MODE == TopkMode::kStructFp16)
+                    static_cast<uint4*>(p.meta)[orow] = make_uint4(code[0], code[1], code[2], code[3]);
+                else
+                    static_cast<uint4*>(p.meta)[orow] = make_uint4(keep[0], keep[1], keep[2], keep[3]);
+            } else {
+                select_topk_thread(key, p.nnz, keep);
+            }
 
-            if constexpr (MODE == TopkMode::kBitmapFp16) {
+            if constexpr (kTiles) {
+            } else if constexpr (MODE == TopkMode::kBitmapFp16) {
                 // compact the kept values to the front of the row (write index <= read index throughout)
                 unsigned short* vals = reinterpret_cast<unsigned short*>(xrow);
                 int n = 0;
@@ -225,7 +361,7 @@ __global__ void __launch_bounds__(kTopkThreads, 4) encode_topk_kernel(const Enco
                 p.scale[orow] = hs;
             }
         }
-        if constexpr (MODE == TopkMode::kBitmapFp16) {
+        if constexpr (kFp16Rows) {
             __syncwarp();
             // the warp's rows are consecutive in the output: 16-byte pieces when the row length allows it
             unsigned char* dst = reinterpret_cast<unsigned char*>(static_cast<__half*>(p.payload) +
@@ -277,6 +413,15 @@ int launch_topk(const EncodeParams& p, cudaStream_t stream, const char* what) {
 
 int launch_topk_bitmap_fp16(const EncodeParams& p, cudaStream_t stream) {
     return launch_topk<TopkMode::kBitmapFp16>(p, stream, "encode_bitmap_fp16 launch");
+}
+
+int launch_topk_tiled_fp16(const EncodeParams& p, bool indexed, cudaStream_t stream) {
+    return indexed ? launch_topk<TopkMode::kStructFp16>(p, stream, "encode_tiled_fp16 launch")
+                   : launch_topk<TopkMode::kTiledFp16>(p, stream, "encode_tiled_fp16 launch");
+}
+
+int launch_topk_structured_int4(const EncodeParams& p, cudaStream_t stream) {
+    return launch_topk<TopkMode::kStructInt4>(p, stream, "encode_structured_int4 launch");
 }
 
 int launch_topk_quantized(const EncodeParams& p, int bits, cudaStream_t stream) {
