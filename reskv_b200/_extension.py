@@ -186,57 +186,58 @@ class CompressionOps(_Ops):
             raise ValueError("compression ops expect FP16 x/centroids and int32 ids")
         if x.ndim != 4 or centroids.ndim != 4 or ids.ndim != 3 or x.shape[3] != 128 or centroids.shape[3] != 128:
             raise ValueError("compression ops expect x[B,H,T,128], centroids[B,H,C,128], ids[B,H,T]")
-        if not (x.is_contiguous() and centroids.is_contiguous() and ids.is_contiguous()):
-            raise ValueError("compression ops expect contiguous tensors")
+        stride = token_stride_of(x)
+        if stride is None or not (centroids.is_contiguous() and ids.is_contiguous()):
+            raise ValueError("compression ops expect contiguous tensors (x may be a token slice of a dense buffer)")
         _same_device(self.device.index, x, centroids, ids)
         b, h, t, _ = x.shape
-        return b, h, t, centroids.shape[2]
+        return b, h, t, centroids.shape[2], stride
 
     def compress_bitmap_fp16(self, x, centroids, ids, nnz):
         """Unstructured FP16 -> (payload f16 [B,H,T,nnz], bitmap i64 [B,H,T,2]).
         The reference has no native op for this layout (torch ops,
         compression.py:75-89); it is one kernel here."""
-        b, h, t, c = self._dims(x, centroids, ids)
+        b, h, t, c, xs = self._dims(x, centroids, ids)
         payload = torch.empty((b, h, t, nnz), dtype=torch.float16, device=x.device)
         bitmap = torch.empty((b, h, t, 2), dtype=torch.int64, device=x.device)
-        check(self.lib.reskv_encode_bitmap_fp16(x.data_ptr(), centroids.data_ptr(), ids.data_ptr(), b, h, t, t, c,
+        check(self.lib.reskv_encode_bitmap_fp16(x.data_ptr(), centroids.data_ptr(), ids.data_ptr(), b, h, t, xs, c,
                                                 nnz, payload.data_ptr(), bitmap.data_ptr(), t, _stream(x.device)))
         return payload, bitmap
 
     def compress_fp16(self, x, centroids, ids, nnz, structured):
-        b, h, t, c = self._dims(x, centroids, ids)
+        b, h, t, c, xs = self._dims(x, centroids, ids)
         values = torch.empty((b, h, t, nnz), dtype=torch.float16, device=x.device)
         meta = torch.empty((b, h, t, 4), dtype=torch.int32, device=x.device)
-        check(self.lib.reskv_encode_tiled_fp16(x.data_ptr(), centroids.data_ptr(), ids.data_ptr(), b, h, t, t, c, nnz,
+        check(self.lib.reskv_encode_tiled_fp16(x.data_ptr(), centroids.data_ptr(), ids.data_ptr(), b, h, t, xs, c, nnz,
                                                int(bool(structured)), values.data_ptr(), meta.data_ptr(), t,
                                                _stream(x.device)))
         return values, meta
 
     def compress_quantized(self, x, centroids, ids, nnz, bits):
-        b, h, t, c = self._dims(x, centroids, ids)
+        b, h, t, c, xs = self._dims(x, centroids, ids)
         words = torch.empty((b, h, t, 4 * bits), dtype=torch.int32, device=x.device)
         scale = torch.empty((b, h, t), dtype=torch.float16, device=x.device)
-        check(self.lib.reskv_encode_quantized(x.data_ptr(), centroids.data_ptr(), ids.data_ptr(), b, h, t, t, c, nnz,
+        check(self.lib.reskv_encode_quantized(x.data_ptr(), centroids.data_ptr(), ids.data_ptr(), b, h, t, xs, c, nnz,
                                               bits, words.data_ptr(), scale.data_ptr(), t, _stream(x.device)))
         return words, scale
 
     def compress_compact(self, x, centroids, ids, nnz, bits):
         """Compact quantised layout (not in the reference): ``(words i32 [B,H,T,nnz*bits/32],
         bitmap i64 [B,H,T,2], scale f16 [B,H,T])``."""
-        b, h, t, c = self._dims(x, centroids, ids)
+        b, h, t, c, xs = self._dims(x, centroids, ids)
         words = torch.empty((b, h, t, nnz * bits // 32), dtype=torch.int32, device=x.device)
         bitmap = torch.empty((b, h, t, 2), dtype=torch.int64, device=x.device)
         scale = torch.empty((b, h, t), dtype=torch.float16, device=x.device)
-        check(self.lib.reskv_encode_compact(x.data_ptr(), centroids.data_ptr(), ids.data_ptr(), b, h, t, t, c, nnz, bits,
+        check(self.lib.reskv_encode_compact(x.data_ptr(), centroids.data_ptr(), ids.data_ptr(), b, h, t, xs, c, nnz, bits,
                                             words.data_ptr(), bitmap.data_ptr(), scale.data_ptr(), t, _stream(x.device)))
         return words, bitmap, scale
 
     def compress_structured_int4(self, x, centroids, ids):
-        b, h, t, c = self._dims(x, centroids, ids)
+        b, h, t, c, xs = self._dims(x, centroids, ids)
         packed = torch.empty((b, h, t, 4), dtype=torch.int32, device=x.device)
         meta = torch.empty((b, h, t, 2), dtype=torch.int32, device=x.device)
         scale = torch.empty((b, h, t), dtype=torch.float16, device=x.device)
-        check(self.lib.reskv_encode_structured_int4(x.data_ptr(), centroids.data_ptr(), ids.data_ptr(), b, h, t, t, c,
+        check(self.lib.reskv_encode_structured_int4(x.data_ptr(), centroids.data_ptr(), ids.data_ptr(), b, h, t, xs, c,
                                                     packed.data_ptr(), meta.data_ptr(), scale.data_ptr(), t,
                                                     _stream(x.device)))
         return packed, meta, scale
@@ -246,10 +247,11 @@ class CompressionOps(_Ops):
         sums as integers (correctly rounded means) instead of FP32 partial sums on the tensor cores; ``warp_mma``:
         the mma.sync form of the tensor-core sums instead of the tcgen05 one; ``return_status``: also return the
         kernels' status word (synchronises the stream)."""
-        if x.dtype != torch.float16 or x.ndim != 4 or x.shape[3] != 128 or not x.is_contiguous():
-            raise ValueError("kmeans expects contiguous FP16 x[B,H,T,128]")
+        if x.dtype != torch.float16 or x.ndim != 4 or x.shape[3] != 128 or token_stride_of(x) is None:
+            raise ValueError("kmeans expects FP16 x[B,H,T,128], dense or a token slice of a dense buffer")
         _same_device(self.device.index, x)
         b, h, t, _ = x.shape
+        xs = token_stride_of(x)
         need = self.lib.reskv_kmeans_workspace_bytes(b, h, count)
         if need == 0:
             raise ValueError("kmeans: cluster count must be in [1,64]")
@@ -257,7 +259,7 @@ class CompressionOps(_Ops):
         centroids = torch.empty((b, h, count, 128), dtype=torch.float16, device=x.device)
         ids = torch.empty((b, h, t), dtype=torch.int32, device=x.device)
         flags = int(bool(value)) | (2 if exact else 0) | (4 if warp_mma else 0)
-        check(self.lib.reskv_kmeans(x.data_ptr(), b, h, t, t, count, iterations, flags, ws.data_ptr(), need,
+        check(self.lib.reskv_kmeans(x.data_ptr(), b, h, t, xs, count, iterations, flags, ws.data_ptr(), need,
                                     centroids.data_ptr(), ids.data_ptr(), _stream(x.device)), launches=1 + 2 * iterations)
         if return_status:
             word = ctypes.c_uint32(0xFFFFFFFF)
@@ -269,14 +271,35 @@ class CompressionOps(_Ops):
         """Decode-time step -> (centroids f16 [B,H,C or C+1,128], ids i32 [B,H,T])."""
         _same_device(self.device.index, x, centroids)
         b, h, t, _ = x.shape
+        xs = token_stride_of(x)
+        if x.dtype != torch.float16 or xs is None:
+            raise ValueError("kmeans_incremental expects FP16 x[B,H,T,128], dense or a token slice of a dense buffer")
         old = centroids.shape[2]
         new = old + int(bool(append))
         centroids = centroids.contiguous()
         out = torch.empty((b, h, new, 128), dtype=torch.float16, device=x.device)
         ids = torch.empty((b, h, t), dtype=torch.int32, device=x.device)
-        check(self.lib.reskv_kmeans_incremental(x.data_ptr(), b, h, t, t, centroids.data_ptr(), old, out.data_ptr(),
+        check(self.lib.reskv_kmeans_incremental(x.data_ptr(), b, h, t, xs, centroids.data_ptr(), old, out.data_ptr(),
                                                 new, ids.data_ptr(), _stream(x.device)))
         return out, ids
+
+
+def token_stride_of(x: torch.Tensor):
+    """Tokens between consecutive (sequence, head) units of ``x[B,H,T,128]`` when ``x`` is dense or a token slice of
+    a dense ``[B,H,capacity,128]`` buffer (rows of 128 contiguous, units evenly spaced), else ``None``.  The kernels
+    take that stride next to the token count, so such a slice needs no copy."""
+    b, h, t, d = x.shape
+    if d != 128 or x.stride(3) != 1 or (t > 1 and x.stride(2) != 128):
+        return None
+    if h > 1:
+        step = x.stride(1)
+    elif b > 1:
+        step = x.stride(0)
+    else:
+        return t
+    if step % 128 or step // 128 < t or (h > 1 and b > 1 and x.stride(0) != h * step):
+        return None
+    return step // 128
 
 
 def _token_stride(rows: torch.Tensor, width: int) -> int:

@@ -108,8 +108,8 @@ class ResKVLayerCache(_HFLayer or _LayerBase):
         s = min(self.sink_tokens, t)
         n = max(0, t - cfg.recent_size - s) // cfg.group_size * cfg.group_size
         if n:
-            self.compressed = compress(raw[:, :, s : s + n].contiguous(), values[:, :, s : s + n].contiguous(), cfg,
-                                       plan=self.plan)
+            # token slices of dense tensors go to the kernels as they are (token stride), no copy
+            self.compressed = compress(raw[:, :, s : s + n], values[:, :, s : s + n], cfg, plan=self.plan)
         self.live = t - n
         if self.live > self.keys.shape[2]:
             raise ValueError("prefill leaves more dense tokens than the window holds")
@@ -137,8 +137,8 @@ class ResKVLayerCache(_HFLayer or _LayerBase):
 
     def _compress_oldest_group(self):
         s, n = self.sink_tokens, self.config.group_size
-        self.compressed = compress(self.raw_keys[:, :, s : s + n].contiguous(), self.values[:, :, s : s + n].contiguous(),
-                                   self.config, previous=self.compressed, plan=self.plan)
+        self.compressed = compress(self.raw_keys[:, :, s : s + n], self.values[:, :, s : s + n], self.config,
+                                   previous=self.compressed, plan=self.plan)
         remain = self.live - s - n
         for buf in (self.keys, self.raw_keys, self.values):
             tail = buf[:, :, s + n : self.live]

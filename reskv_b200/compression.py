@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from ._extension import load_extension
+from ._extension import load_extension, token_stride_of
 from .config import KernelPlan, ResKVKernelConfig
 from .tensors import CompressedKV, CompressedTensor
 
@@ -24,6 +24,12 @@ def _require_kv(x, role: str) -> None:
         raise ValueError(f"{role}: expected FP16 CUDA tensor [batch, kv_heads, tokens, 128]")
     if 0 in x.shape[:3]:
         raise ValueError(f"{role}: batch, head and token dimensions must be nonempty")
+
+
+def _dense_or_slice(x: torch.Tensor) -> torch.Tensor:
+    """``x`` itself when the kernels can address it (dense, or a token slice of a dense ``[B,H,capacity,128]``
+    buffer: they take a token stride), else a dense copy."""
+    return x if token_stride_of(x) is not None else x.contiguous()
 
 
 def _ops(x: torch.Tensor):
@@ -58,7 +64,7 @@ def cluster(x: torch.Tensor, count: int = 32, iterations: int = 10, *, value: bo
     t = x.shape[2]
     if value:
         count = min(count, t)
-    return _ops(x).kmeans(x.contiguous(), int(count), int(iterations), value, exact, warp_mma, return_status)
+    return _ops(x).kmeans(_dense_or_slice(x), int(count), int(iterations), value, exact, warp_mma, return_status)
 
 
 @torch.no_grad()
@@ -66,7 +72,7 @@ def _incremental_cluster(x, centers, config, *, value=False):
     """Append the group mean as a new centre until the limit is reached, then
     assign the group's tokens (reference compression.py:56-69)."""
     append = centers.shape[2] < config.max_clusters
-    return _ops(x).kmeans_incremental(x.contiguous(), centers.half(), append)
+    return _ops(x).kmeans_incremental(_dense_or_slice(x), centers.half(), append)
 
 
 @torch.no_grad()
@@ -76,7 +82,7 @@ def _encode(x, centers, ids, plan: KernelPlan, *, value=False):
     compatibility: K and V use the same selection rule here."""
     ids = ids.int().contiguous()
     centers = centers.half().contiguous()
-    x = x.contiguous()
+    x = _dense_or_slice(x)
     ops = _ops(x)
     metadata = scale = None
     if plan.layout == "compact":

@@ -75,6 +75,29 @@ def test_bit_exact_on_cluster_mixture(layout, bits, nnz, shape):
     _assert_like_oracle(ct, layout, bits, nnz, x, cen, ids)
 
 
+@pytest.mark.parametrize("layout,bits,nnz", PLANS)
+def test_token_slice_of_a_larger_buffer_needs_no_copy(layout, bits, nnz):
+    """x given as a token slice of a dense buffer whose other rows hold NaN: same packed bytes as the dense copy."""
+    from reskv_b200._extension import token_stride_of
+    from reskv_b200.compression import _encode
+    from reskv_b200.synthetic import gaussian, mixture
+
+    b, h, t, c = 2, 3, 200, 16
+    x = mixture(b, h, t, seed=31).to(DEV)
+    cen = gaussian(b, h, c, 128, seed=32).to(DEV)
+    ids = torch.randint(c, (b, h, t), generator=torch.Generator().manual_seed(33), dtype=torch.int32).to(DEV)
+    big = torch.full((b, h, t + 24, 128), float("nan"), dtype=torch.float16, device=DEV)
+    big[:, :, 5 : 5 + t] = x
+    view = big[:, :, 5 : 5 + t]
+    assert not view.is_contiguous() and token_stride_of(view) == t + 24
+    want = _encode(x, cen, ids, _plan(layout, bits, nnz))
+    got = _encode(view, cen, ids, _plan(layout, bits, nnz))
+    for a, w in ((got.payload, want.payload), (got.metadata, want.metadata), (got.scale, want.scale)):
+        assert (a is None) == (w is None)
+        if a is not None:
+            assert torch.equal(a.view(torch.uint8), w.view(torch.uint8))
+
+
 @pytest.mark.parametrize("layout,bits,nnz", REFERENCE_PLANS)
 def test_golden_inputs_and_reference_decoder(golden, layout, bits, nnz):
     """Same inputs as the fixtures: packed output equals what the reference's

@@ -145,3 +145,24 @@ def test_short_inputs():
     assert cen.shape[2] == 5 and sorted(ids.ravel().tolist()) == [0, 1, 2, 3, 4]
     cen, ids = _cluster(x, 8, 3)
     assert cen.shape[2] == 8 and ids.max() < 8
+
+
+@pytest.mark.parametrize("warp_mma", [False, True], ids=["tcgen05", "mma.sync"])
+@pytest.mark.parametrize("value", [False, True])
+def test_token_slice_of_a_larger_buffer_needs_no_copy(value, warp_mma):
+    """x given as a token slice [:, :, 3:3+T] of a dense buffer whose other rows hold NaN: the kernels take the
+    token stride, read nothing outside the slice and give the result of the dense copy."""
+    from reskv_b200._extension import token_stride_of
+    from reskv_b200.compression import cluster
+    from reskv_b200.synthetic import mixture
+
+    t = 1500
+    dense = mixture(2, 3, t, seed=5, clusters=9).to(DEV)
+    big = torch.full((2, 3, t + 40, 128), float("nan"), dtype=torch.float16, device=DEV)
+    big[:, :, 3 : 3 + t] = dense
+    view = big[:, :, 3 : 3 + t]
+    assert not view.is_contiguous() and token_stride_of(view) == t + 40
+    want_c, want_i, status = cluster(dense, 32, 3, value=value, warp_mma=warp_mma, return_status=True)
+    got_c, got_i, status2 = cluster(view, 32, 3, value=value, warp_mma=warp_mma, return_status=True)
+    assert status == 0 and status2 == 0
+    assert torch.equal(got_i, want_i) and torch.equal(got_c.view(torch.int16), want_c.view(torch.int16))
