@@ -450,7 +450,7 @@ __global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const Kmean
 //     ahead of its use;
 //   * ranking: sixteen warps, four threads per token (TMEM lane = token row; warp w reads lanes 32 (w % 4).. and
 //     the eight centres 8 (w / 4)..), their partial results go to shared memory;
-//   * merging: four more warps, one thread per token, merge the four parts, re-rank near-ties exactly (same bound
+//   * merging: eight more warps in two groups (even tiles, odd tiles), one thread per token, merge the four parts, re-rank near-ties exactly (same bound
 //     and same exact path as the mma.sync form), write the id and set one element of a one-hot operand
 //     onehot[32 clusters x 128 tokens];
 //   * sums: S^T[128 coordinates x 32 clusters] += X^T . onehot^T, the same tile now read as the MN-major A operand,
@@ -461,7 +461,8 @@ __global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const Kmean
 // concurrently on different tiles and hand over through mbarriers only (double-buffered distances, parts and
 // one-hot operand); every wait is bounded.
 constexpr int kURankWarps = 16;                // four per TMEM lane quarter: eight centres each
-constexpr int kUMergeWarps = 4;                // one per TMEM lane quarter
+constexpr int kUMergeGroupWarps = 4;           // a merging group: one warp per 32 token rows
+constexpr int kUMergeWarps = 2 * kUMergeGroupWarps;  // two groups, one for the even and one for the odd tiles
 constexpr int kUThreads = (kURankWarps + kUMergeWarps + 3) * 32;  // + three issuing warps: distance MMAs, sum MMAs, copies
 constexpr int kUTile = 128;
 constexpr int kUStages = 5;
@@ -565,8 +566,8 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
         for (int s = 0; s < kUStages; ++s) mbar_init(&bar_full[s], 1);
         for (int b = 0; b < 2; ++b) {
             mbar_init(&bar_dist[b], 1), mbar_init(&bar_sums[b], 1);
-            mbar_init(&bar_parts[b], kURankWarps * 32), mbar_init(&bar_parts_free[b], kUMergeWarps * 32);
-            mbar_init(&bar_onehot[b], kUMergeWarps * 32);
+            mbar_init(&bar_parts[b], kURankWarps * 32), mbar_init(&bar_parts_free[b], kUMergeGroupWarps * 32);
+            mbar_init(&bar_onehot[b], kUMergeGroupWarps * 32);
         }
         mbar_fence_init();
     }
@@ -692,20 +693,22 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
             mbar_arrive(&bar_parts[b]);
         }
     } else if (warp < kURankWarps + kUMergeWarps) {
-        // ---- merging: one thread per token -------------------------------------------------------------------
-        const int quarter = warp - kURankWarps, row_in_tile = quarter * 32 + lane;
-        int prev_even = -1, prev_odd = -1;  // byte offset of the element this thread set in each one-hot buffer
+        // ---- merging: one thread per token; the two groups take the even and the odd tiles, so each has two tile
+        // periods for its chain of dependent steps and owns one part buffer and one one-hot buffer ----------------
+        const int group = (warp - kURankWarps) / kUMergeGroupWarps, quarter = (warp - kURankWarps) % kUMergeGroupWarps;
+        const int row_in_tile = quarter * 32 + lane, b = group;
+        int prev = -1;  // byte offset of the element this thread set in its one-hot buffer
         // |x|^2 of a token is the same in every Lloyd iteration: the first one stores it (as FP32 bits) where the
         // token's id goes, the following ones read it from there one tile ahead, the last one writes the id
         int32_t* ids_u = p.ids + static_cast<size_t>(unit) * p.tokens;
         float xn_next = 0.f;
-        if (!first && t_begin + row_in_tile < t_end) xn_next = __int_as_float(ids_u[t_begin + row_in_tile]);
-        for (int i = 0; i < n_tiles; ++i) {
-            const int b = i & 1;
+        if (!first && t_begin + group * kUTile + row_in_tile < t_end)
+            xn_next = __int_as_float(ids_u[t_begin + group * kUTile + row_in_tile]);
+        for (int i = group; i < n_tiles; i += 2) {
             const int row = t_begin + i * kUTile + row_in_tile;
             const bool live = row < t_end;
             float xn = xn_next;
-            if (!first && row + kUTile < t_end) xn_next = __int_as_float(ids_u[row + kUTile]);
+            if (!first && row + 2 * kUTile < t_end) xn_next = __int_as_float(ids_u[row + 2 * kUTile]);
             lost |= !mbar_wait(&bar_parts[b], (i >> 1) & 1);
             float4 pm[4];
 #pragma unroll
@@ -780,14 +783,12 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
             // one-hot buffer b was last read by the sums of tile i - 2
             if (i >= 2) lost |= !mbar_wait(&bar_sums[b], ((i - 2) >> 1) & 1);
             unsigned char* ob = oh + b * kUOneHotBytes;
-            const int prev = b ? prev_odd : prev_even;
             if (prev >= 0) *reinterpret_cast<unsigned short*>(ob + prev) = 0;
-            int at = -1;
+            prev = -1;
             if (live) {
-                at = (row_in_tile >> 6) * (32 * 128) + sw128(c1, (row_in_tile & 63) >> 3) + ((row_in_tile & 7) << 1);
-                *reinterpret_cast<unsigned short*>(ob + at) = 0x3C00;  // 1.0
+                prev = (row_in_tile >> 6) * (32 * 128) + sw128(c1, (row_in_tile & 63) >> 3) + ((row_in_tile & 7) << 1);
+                *reinterpret_cast<unsigned short*>(ob + prev) = 0x3C00;  // 1.0
             }
-            if (b) prev_odd = at; else prev_even = at;
             proxy_fence();  // the tensor core (async proxy) reads what this thread wrote
             mbar_arrive(&bar_onehot[b]);
         }
