@@ -448,29 +448,28 @@ __global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const Kmean
 //   * distances: D[128 tokens x 64] = X . [c_hi | c_lo]^T, X as the K-major A operand of tcgen05.mma, the centre
 //     halves as a K-major B operand written once per CTA; accumulator in TMEM, double buffered, issued two tiles
 //     ahead of its use;
-//   * ranking: sixteen warps, four threads per token (TMEM lane = token row; warp w reads lanes 32 (w % 4).. and
-//     the eight centres 8 (w / 4)..), their partial results go to shared memory;
-//   * merging: eight more warps in two groups (even tiles, odd tiles), one thread per token, merge the four parts, re-rank near-ties exactly (same bound
-//     and same exact path as the mma.sync form), write the id and set one element of a one-hot operand
-//     onehot[32 clusters x 128 tokens];
+//   * ranking: one thread per token (TMEM lane = token row) reads its row of D with tcgen05.ld, ranks the centres,
+//     re-ranks near-ties exactly - only the centres inside the bound, with the arithmetic and order of the exact
+//     path of the mma.sync form -, writes the id and sets one element of a one-hot operand
+//     onehot[32 clusters x 128 tokens]; three groups of four warps take the tiles in turn, so each has three tile
+//     periods for its chain of dependent steps;
 //   * sums: S^T[128 coordinates x 32 clusters] += X^T . onehot^T, the same tile now read as the MN-major A operand,
 //     accumulated in TMEM (four accumulators in turn) over the CTA's whole token range and flushed once as
 //     2^24-scaled integers.
-// Three more warps issue the asynchronous work (distance MMAs, sum MMAs, copies); they stay
-// converged (descriptor arithmetic on the uniform datapath) and elect one lane per instruction.  The roles run
-// concurrently on different tiles and hand over through mbarriers only (double-buffered distances, parts and
-// one-hot operand); every wait is bounded.
-constexpr int kURankWarps = 16;                // four per TMEM lane quarter: eight centres each
-constexpr int kUMergeGroupWarps = 4;           // a merging group: one warp per 32 token rows
-constexpr int kUMergeWarps = 2 * kUMergeGroupWarps;  // two groups, one for the even and one for the odd tiles
-constexpr int kUThreads = (kURankWarps + kUMergeWarps + 3) * 32;  // + three issuing warps: distance MMAs, sum MMAs, copies
+// Three more warps issue the asynchronous work (distance MMAs, sum MMAs, copies); they stay converged (descriptor
+// arithmetic on the uniform datapath) and elect one lane per instruction.  The roles run concurrently on
+// different tiles and hand over through mbarriers only (triple-buffered distances and one-hot operands); every
+// wait is bounded.
+constexpr int kUGroups = 3;                    // token-owning groups; group g takes the tiles i = g (mod 3)
+constexpr int kUGroupWarps = 4;                // a group: one warp per 32 token rows (TMEM lane quarter)
+constexpr int kUThreads = (kUGroups * kUGroupWarps + 3) * 32;  // + three issuing warps: distance MMAs, sum MMAs, copies
 constexpr int kUTile = 128;
 constexpr int kUStages = 5;
 constexpr int kUBoxBytes = kUTile * 128;       // 128 rows x 64 coordinates
 constexpr int kUTileBytes = 2 * kUBoxBytes;
 constexpr int kUOneHotBytes = 2 * 32 * 128;    // [2 token halves][32 clusters][64 tokens] FP16
-constexpr uint32_t kUTmemCols = 256;           // distances 2 x 64 columns, sums 4 x 32 columns
-constexpr uint32_t kUColD = 0, kUColS = 128;
+constexpr uint32_t kUTmemCols = 512;           // distances 3 x 64 columns, sums 4 x 32 columns; a power of two
+constexpr uint32_t kUColD = 0, kUColS = 192;
 constexpr int kUSumBuffers = 4;                // tile i adds to accumulator i % 4: shorter FP32 chains, no MMA-to-MMA dependency
 constexpr int kUChunkMax = 8192;               // most tokens per CTA (2048 per accumulator)
 
@@ -511,6 +510,19 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&r)[8]) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) r[i] = __uint_as_float(u[i]);
 }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&r)[32]) {
+    uint32_t u[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
+          "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]), "=r"(u[16]),
+          "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]), "=r"(u[24]),
+          "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
+        : "r"(taddr));
+#pragma unroll
+    for (int i = 0; i < 32; ++i) r[i] = __uint_as_float(u[i]);
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // One box of a rank-3 tensor map (coordinate, token, unit) -> shared memory, completion counted on `bar`.
@@ -545,15 +557,13 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
     unsigned char* base = smem_u + ((1024u - (smem_u32(smem_u) & 1023u)) & 1023u);  // swizzled blocks: 1024-byte aligned
     unsigned char* xs = base;                                   // [stages][2 halves][128 tokens][128 B]
     unsigned char* cop = xs + kUStages * kUTileBytes;           // [2 halves][kN rows][128 B]
-    unsigned char* oh = cop + 2 * kN * 128;                     // [2 buffers][2 token halves][32 clusters][128 B]
-    float4* part_s = reinterpret_cast<float4*>(oh + 2 * kUOneHotBytes);  // [2 buffers][4 centre groups][128 rows]: d1, d2, c1, |x|^2 part
-    float* cen_s = reinterpret_cast<float*>(part_s + 2 * 4 * kUTile);    // [32][128] FP32 centres (exact re-ranking)
+    unsigned char* oh = cop + 2 * kN * 128;                     // [groups][2 token halves][32 clusters][128 B]
+    float* cen_s = reinterpret_cast<float*>(oh + kUGroups * kUOneHotBytes);  // [32][128] FP32 centres (exact re-ranking)
     float* cn_s = cen_s + 32 * kHeadDim;                        // [32] |c|^2, +inf for padding
     int* cnt_s = reinterpret_cast<int*>(cn_s + 32);             // [32]
-    // full: tile landed (TMA bytes).  dist / sums: MMAs complete (tcgen05.commit).  parts: 512 ranking threads have
-    // read the distance buffer and written their part.  parts_free: 128 merging threads have read the parts.
-    // onehot: 128 merging threads have written the one-hot operand.
-    __shared__ uint64_t bar_full[kUStages], bar_dist[2], bar_sums[2], bar_parts[2], bar_parts_free[2], bar_onehot[2];
+    // full: tile landed (TMA bytes).  dist / sums: MMAs complete (tcgen05.commit).  dist_free: the 128 threads of a
+    // group have read their distance buffer.  onehot: they have written their one-hot operand.
+    __shared__ uint64_t bar_full[kUStages], bar_dist[kUGroups], bar_dist_free[kUGroups], bar_onehot[kUGroups], bar_sums[kUGroups];
     __shared__ uint32_t tmem_base_s;
 
     const int unit = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -564,10 +574,9 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
 
     if (tid == 0) {
         for (int s = 0; s < kUStages; ++s) mbar_init(&bar_full[s], 1);
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < kUGroups; ++b) {
             mbar_init(&bar_dist[b], 1), mbar_init(&bar_sums[b], 1);
-            mbar_init(&bar_parts[b], kURankWarps * 32), mbar_init(&bar_parts_free[b], kUMergeGroupWarps * 32);
-            mbar_init(&bar_onehot[b], kUMergeGroupWarps * 32);
+            mbar_init(&bar_dist_free[b], kUGroupWarps * 32), mbar_init(&bar_onehot[b], kUGroupWarps * 32);
         }
         mbar_fence_init();
     }
@@ -586,7 +595,8 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
             tma_load_3d(dst + kUBoxBytes, &xmap, 64, t_begin + j * kUTile, unit, bar);
         }
     };
-    if (warp == kURankWarps + kUMergeWarps + 2)
+    constexpr int kWarpDist = kUGroups * kUGroupWarps, kWarpSums = kWarpDist + 1, kWarpCopy = kWarpDist + 2;
+    if (warp == kWarpCopy)
         for (int j = 0; j < kUStages && j < n_tiles; ++j) load_tile(j);
 
     // ---- per CTA: centre operand (FP16 hi | lo rows, swizzled), FP32 centres, |c|^2, empty one-hot buffers ----
@@ -626,7 +636,7 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
             if (lane == 0) cn_s[c] = c < p.clusters ? sq : INFINITY;
         }
     }
-    for (int i = tid; i < 2 * kUOneHotBytes / 16; i += kUThreads) reinterpret_cast<uint4*>(oh)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < kUGroups * kUOneHotBytes / 16; i += kUThreads) reinterpret_cast<uint4*>(oh)[i] = make_uint4(0, 0, 0, 0);
     if (tid < 32) cnt_s[tid] = 0;
     proxy_fence();  // the operands written above are read by the tensor core (async proxy)
     tc_fence_before();
@@ -638,48 +648,57 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
     const uint32_t tmem = tmem_base_s;
     const __half* xu = p.x + static_cast<size_t>(unit) * p.x_stride * kHeadDim;
 
-    if (warp < kURankWarps) {
-        // ---- ranking: four threads per token, eight centres and a quarter of |x|^2 each ----------------------
-        const int quarter = warp & 3, cpart = warp >> 2, row_in_tile = quarter * 32 + lane;
+    if (warp < kWarpDist) {
+        // ---- ranking: one thread per token; group g takes the tiles g, g + 3, ... with distance buffer g and
+        // one-hot buffer g ----------------------------------------------------------------------------------------
+        const int g = warp / kUGroupWarps, quarter = warp % kUGroupWarps, row_in_tile = quarter * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        float cn_r[8];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) cn_r[c] = cn_s[8 * cpart + c];
-        for (int i = 0; i < n_tiles; ++i) {
-            const int b = i & 1, st = i % kUStages;
-            if (first) lost |= !mbar_wait(&bar_full[st], (i / kUStages) & 1);  // this thread reads the tile too (|x|^2)
-            lost |= !mbar_wait(&bar_dist[b], (i >> 1) & 1);
+        int prev = -1;  // byte offset of the element this thread set in its one-hot buffer
+        // |x|^2 of a token is the same in every Lloyd iteration: the first one forms it and stores it (as FP32 bits)
+        // where the token's id goes, the following ones read it from there one tile ahead, the last one writes the id
+        int32_t* ids_u = p.ids + static_cast<size_t>(unit) * p.tokens;
+        float xn_next = 0.f;
+        if (!first && t_begin + g * kUTile + row_in_tile < t_end) xn_next = __int_as_float(ids_u[t_begin + g * kUTile + row_in_tile]);
+        for (int i = g; i < n_tiles; i += kUGroups) {
+            const int use = i / kUGroups, st = i % kUStages;
+            const int row = t_begin + i * kUTile + row_in_tile;
+            const bool live = row < t_end;
+            float xn = xn_next;
+            if (!first && row + kUGroups * kUTile < t_end) xn_next = __int_as_float(ids_u[row + kUGroups * kUTile]);
+            lost |= !mbar_wait(&bar_dist[g], use & 1);
             tc_fence_after();
-            float acc[8];
-            tmem_ld8(tmem + lane_base + kUColD + b * 64 + 8 * cpart, acc);
+            float d[32];
+            tmem_ld32(tmem + lane_base + kUColD + g * 64, d);
             if constexpr (HILO) {
-                float lo[8];
-                tmem_ld8(tmem + lane_base + kUColD + b * 64 + 32 + 8 * cpart, lo);
+                float lo[32];
+                tmem_ld32(tmem + lane_base + kUColD + g * 64 + 32, lo);
                 tmem_ld_wait();
 #pragma unroll
-                for (int c = 0; c < 8; ++c) acc[c] += lo[c];
+                for (int c = 0; c < 32; ++c) d[c] += lo[c];
             } else {
                 tmem_ld_wait();
             }
+            tc_fence_before();
+            mbar_arrive(&bar_dist_free[g]);  // the next distances of this group may be issued
             float d1 = INFINITY, d2 = INFINITY;
             int c1 = 0;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const float d = fmaf(-2.f, acc[c], cn_r[c]);
-                if (d < d1) {
-                    d2 = d1, d1 = d, c1 = 8 * cpart + c;
-                } else if (d < d2) {
-                    d2 = d;
+            for (int c = 0; c < 32; ++c) {
+                d[c] = fmaf(-2.f, d[c], cn_s[c]);
+                if (d[c] < d1) {
+                    d2 = d1, d1 = d[c], c1 = c;  // a strict comparison keeps the lower index on ties
+                } else if (d[c] < d2) {
+                    d2 = d[c];
                 }
             }
-            // |x|^2 for the near-tie bound: packed FP16 products, eight at a time (an overflow gives +inf: re-rank).
-            // Only the first Lloyd iteration forms it; the merging threads park it in the id buffer for the others.
-            float xn = 0.f;
             if (first) {
-                const unsigned char* xt = xs + st * kUTileBytes + (cpart >> 1) * kUBoxBytes;
+                // |x|^2 for the near-tie bound: packed FP16 products, eight at a time (an overflow gives +inf: re-rank)
+                lost |= !mbar_wait(&bar_full[st], (i / kUStages) & 1);
+                const unsigned char* xt = xs + st * kUTileBytes;
+                xn = 0.f;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(xt + sw128(row_in_tile, 4 * (cpart & 1) + j));
+                for (int j = 0; j < 16; ++j) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(xt + (j >> 3) * kUBoxBytes + sw128(row_in_tile, j & 7));
                     const __half2* h = reinterpret_cast<const __half2*>(&v);
                     __half2 s = __hmul2(h[0], h[0]);
                     s = __hfma2(h[1], h[1], s), s = __hfma2(h[2], h[2], s), s = __hfma2(h[3], h[3], s);
@@ -687,90 +706,40 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
                     xn += f.x + f.y;
                 }
             }
-            if (i >= 2) lost |= !mbar_wait(&bar_parts_free[b], ((i - 2) >> 1) & 1);  // parts of tile i - 2 were merged
-            part_s[(b * 4 + cpart) * kUTile + row_in_tile] = make_float4(d1, d2, __int_as_float(c1), xn);
-            tc_fence_before();
-            mbar_arrive(&bar_parts[b]);
-        }
-    } else if (warp < kURankWarps + kUMergeWarps) {
-        // ---- merging: one thread per token; the two groups take the even and the odd tiles, so each has two tile
-        // periods for its chain of dependent steps and owns one part buffer and one one-hot buffer ----------------
-        const int group = (warp - kURankWarps) / kUMergeGroupWarps, quarter = (warp - kURankWarps) % kUMergeGroupWarps;
-        const int row_in_tile = quarter * 32 + lane, b = group;
-        int prev = -1;  // byte offset of the element this thread set in its one-hot buffer
-        // |x|^2 of a token is the same in every Lloyd iteration: the first one stores it (as FP32 bits) where the
-        // token's id goes, the following ones read it from there one tile ahead, the last one writes the id
-        int32_t* ids_u = p.ids + static_cast<size_t>(unit) * p.tokens;
-        float xn_next = 0.f;
-        if (!first && t_begin + group * kUTile + row_in_tile < t_end)
-            xn_next = __int_as_float(ids_u[t_begin + group * kUTile + row_in_tile]);
-        for (int i = group; i < n_tiles; i += 2) {
-            const int row = t_begin + i * kUTile + row_in_tile;
-            const bool live = row < t_end;
-            float xn = xn_next;
-            if (!first && row + 2 * kUTile < t_end) xn_next = __int_as_float(ids_u[row + 2 * kUTile]);
-            lost |= !mbar_wait(&bar_parts[b], (i >> 1) & 1);
-            float4 pm[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) pm[k] = part_s[(b * 4 + k) * kUTile + row_in_tile];
-            mbar_arrive(&bar_parts_free[b]);
-            float d1 = pm[0].x, d2 = pm[0].y;
-            int c1 = __float_as_int(pm[0].z);
-            if (first) xn = pm[0].w;
-#pragma unroll
-            for (int k = 1; k < 4; ++k) {  // ascending centre groups: a strict comparison keeps the lower index on ties
-                if (pm[k].x < d1) {
-                    d2 = fminf(d1, pm[k].y), d1 = pm[k].x, c1 = __float_as_int(pm[k].z);
-                } else {
-                    d2 = fminf(d2, pm[k].x);
-                }
-                if (first) xn += pm[k].w;
-            }
-            // near-ties: re-rank with the exact FP32 sum, the warp working on one token at a time.  Only centres
-            // whose distance lies inside the bound can win; when every centre group has at most one of those the
-            // exact sums of these few are enough (same arithmetic, same order as `nearest`), otherwise all are ranked.
+            // near-ties: only a centre whose distance lies inside the bound can win; the warp forms the exact FP32
+            // sums of those few (same arithmetic, same order as `nearest`), one tied token at a time
             const float bound = kTieBound * (1.01f * xn + cmax);
-            const bool tie = live && !((d2 - d1) > bound);
-            uint32_t redo = __ballot_sync(kFull, tie);
+            uint32_t inside = 0u;
+            if (live && !((d2 - d1) > bound)) {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) inside |= !((d[c] - d1) > bound) ? 1u << c : 0u;
+            }
+            uint32_t redo = __ballot_sync(kFull, inside != 0u);
             while (redo) {
                 const int src = __ffs(redo) - 1;
                 redo &= redo - 1;
-                const float s_d1 = __shfl_sync(kFull, d1, src), s_bound = __shfl_sync(kFull, bound, src);
-                bool all = false;
-                int cand[4], n_cand = 0;
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float k_d1 = __shfl_sync(kFull, pm[k].x, src), k_d2 = __shfl_sync(kFull, pm[k].y, src);
-                    const int k_c = __shfl_sync(kFull, __float_as_int(pm[k].z), src);
-                    if (!((k_d2 - s_d1) > s_bound)) all = true;
-                    cand[k] = k_c;
-                    if (!((k_d1 - s_d1) > s_bound)) n_cand |= 1 << k;
-                }
+                uint32_t cands = __shfl_sync(kFull, inside, src) & (p.clusters >= 32 ? 0xffffffffu : (1u << p.clusters) - 1u);
                 const __half* xr = xu + static_cast<size_t>(t_begin + i * kUTile + quarter * 32 + src) * kHeadDim;
                 float xv[4];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) xv[k] = __half2float(xr[lane + 32 * k]);
                 float best = INFINITY;
-                int c = 0;
-                if (all) {
-                    nearest(cen_s, p.clusters, xv, lane, best, c);
-                } else {
+                int bc = 0;
+                while (cands) {  // ascending centre index: the lower one wins ties
+                    const int c = __ffs(cands) - 1;
+                    cands &= cands - 1;
+                    const float* crow = cen_s + c * kHeadDim;
+                    float acc = 0.f;
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        if (!((n_cand >> k) & 1)) continue;
-                        const float* crow = cen_s + cand[k] * kHeadDim;
-                        float acc = 0.f;
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float df = xv[e] - crow[lane + 32 * e];
-                            acc = fmaf(df, df, acc);
-                        }
-#pragma unroll
-                        for (int off = 16; off > 0; off >>= 1) acc = acc + __shfl_xor_sync(kFull, acc, off);
-                        if (acc < best) best = acc, c = cand[k];  // ascending centre index: the lower one wins ties
+                    for (int e = 0; e < 4; ++e) {
+                        const float df = xv[e] - crow[lane + 32 * e];
+                        acc = fmaf(df, df, acc);
                     }
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) acc = acc + __shfl_xor_sync(kFull, acc, off);
+                    if (acc < best) best = acc, bc = c;
                 }
-                if (lane == src) c1 = c;
+                if (lane == src) c1 = bc;
             }
             if (live) {
                 if (last) {
@@ -780,9 +749,9 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
                 }
                 atomicAdd(&cnt_s[c1], 1);
             }
-            // one-hot buffer b was last read by the sums of tile i - 2
-            if (i >= 2) lost |= !mbar_wait(&bar_sums[b], ((i - 2) >> 1) & 1);
-            unsigned char* ob = oh + b * kUOneHotBytes;
+            // one-hot buffer g was last read by the sums of tile i - 3
+            if (i >= kUGroups) lost |= !mbar_wait(&bar_sums[g], (use - 1) & 1);
+            unsigned char* ob = oh + g * kUOneHotBytes;
             if (prev >= 0) *reinterpret_cast<unsigned short*>(ob + prev) = 0;
             prev = -1;
             if (live) {
@@ -790,36 +759,31 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
                 *reinterpret_cast<unsigned short*>(ob + prev) = 0x3C00;  // 1.0
             }
             proxy_fence();  // the tensor core (async proxy) reads what this thread wrote
-            mbar_arrive(&bar_onehot[b]);
+            mbar_arrive(&bar_onehot[g]);
         }
-    } else if (warp == kURankWarps + kUMergeWarps) {
-        // ---- distance MMAs, two tiles ahead of their use (whole warp, one elected lane per instruction) -------
+    } else if (warp == kWarpDist) {
+        // ---- distance MMAs (whole warp, one elected lane per instruction): tile j goes to buffer j % 3 as soon as
+        // the group has read tile j - 3 out of it -------------------------------------------------------------------
         const uint64_t a0 = umma_desc(smem_u32(xs), 16, 1024), b0 = umma_desc(smem_u32(cop), 16, 1024);
-        auto issue_distances = [&](int j) {  // tile j has landed, distance buffer j & 1 has been read
+        for (int j = 0; j < n_tiles; ++j) {
+            const int buf = j % kUGroups;
+            if (j >= kUGroups) lost |= !mbar_wait(&bar_dist_free[buf], (j / kUGroups - 1) & 1);
+            lost |= !mbar_wait(&bar_full[j % kUStages], (j / kUStages) & 1);
+            tc_fence_after();
             const uint64_t a = a0 + static_cast<uint64_t>(((j % kUStages) * kUTileBytes) >> 4);
-            const uint32_t d = tmem + kUColD + (j & 1) * 64;
+            const uint32_t d = tmem + kUColD + buf * 64;
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {  // 16 coordinates per step: 32 bytes inside the swizzled 128-byte row
                 const uint64_t ak = a + static_cast<uint64_t>(((ks >> 2) * kUBoxBytes + (ks & 3) * 32) >> 4);
                 const uint64_t bk = b0 + static_cast<uint64_t>(((ks >> 2) * (kN * 128) + (ks & 3) * 32) >> 4);
                 if (elect_one()) umma_f16(d, ak, bk, umma_idesc(kN, false), ks > 0);
             }
-            if (elect_one()) umma_commit(&bar_dist[j & 1]);
-        };
-        for (int j = 0; j < 2 && j < n_tiles; ++j) {
-            lost |= !mbar_wait(&bar_full[j], 0);
-            issue_distances(j);
+            if (elect_one()) umma_commit(&bar_dist[buf]);
         }
-        for (int i = 0; i + 2 < n_tiles; ++i) {
-            lost |= !mbar_wait(&bar_parts[i & 1], (i >> 1) & 1);  // distance buffer i & 1 has been read by all ranking threads
-            lost |= !mbar_wait(&bar_full[(i + 2) % kUStages], ((i + 2) / kUStages) & 1);
-            tc_fence_after();
-            issue_distances(i + 2);
-        }
-    } else if (warp == kURankWarps + kUMergeWarps + 2) {
+    } else if (warp == kWarpCopy) {
         // ---- copies: a stage is refilled as soon as the sums of the tile it held have run ---------------------
         for (int i = 0; i + kUStages < n_tiles; ++i) {
-            lost |= !mbar_wait(&bar_sums[i & 1], (i >> 1) & 1);
+            lost |= !mbar_wait(&bar_sums[i % kUGroups], (i / kUGroups) & 1);
             load_tile(i + kUStages);
         }
     } else {
@@ -827,11 +791,11 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
         const uint64_t a0 = umma_desc(smem_u32(xs), kUBoxBytes, 1024);  // MN-major: other half of the coordinates at LBO
         const uint64_t b0 = umma_desc(smem_u32(oh), 16, 1024);
         for (int i = 0; i < n_tiles; ++i) {
-            const int b = i & 1;
+            const int buf = i % kUGroups;
             const uint64_t a = a0 + static_cast<uint64_t>(((i % kUStages) * kUTileBytes) >> 4);
-            const uint64_t o = b0 + static_cast<uint64_t>((b * kUOneHotBytes) >> 4);
+            const uint64_t o = b0 + static_cast<uint64_t>((buf * kUOneHotBytes) >> 4);
             const uint32_t d = tmem + kUColS + (i % kUSumBuffers) * 32;
-            lost |= !mbar_wait(&bar_onehot[b], (i >> 1) & 1);
+            lost |= !mbar_wait(&bar_onehot[buf], (i / kUGroups) & 1);
             tc_fence_after();
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {  // 16 tokens per step: two 8-row groups of the tile = 2048 bytes
@@ -839,35 +803,39 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
                 const uint64_t bk = o + static_cast<uint64_t>(((ks >> 2) * (32 * 128) + (ks & 3) * 32) >> 4);
                 if (elect_one()) umma_f16(d, ak, bk, umma_idesc(32, true), (i >= kUSumBuffers || ks > 0) ? 1u : 0u);
             }
-            if (elect_one()) umma_commit(&bar_sums[b]);
+            if (elect_one()) umma_commit(&bar_sums[buf]);
         }
     }
     // the commit of the last sums covers every MMA of this CTA
-    if (warp < kURankWarps) {
-        lost |= !mbar_wait(&bar_sums[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
+    const bool flusher = warp < 2 * kUGroupWarps;  // groups 0 and 1: coordinate row_in_tile, sixteen clusters each
+    if (flusher) {
+        lost |= !mbar_wait(&bar_sums[(n_tiles - 1) % kUGroups], ((n_tiles - 1) / kUGroups) & 1);
         tc_fence_after();
     }
     __syncthreads();
-    if (warp < kURankWarps) {
-        const int quarter = warp & 3, cpart = warp >> 2, row_in_tile = quarter * 32 + lane;
+    if (flusher) {
+        const int half = warp / kUGroupWarps, quarter = warp % kUGroupWarps, row_in_tile = quarter * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        float sum[8];  // coordinate row_in_tile, clusters 8 cpart ..: the accumulators added in index order
-        tmem_ld8(tmem + lane_base + kUColS + 8 * cpart, sum);
-        tmem_ld_wait();
-        for (int a = 1; a < kUSumBuffers && a < n_tiles; ++a) {
-            float more[8];
-            tmem_ld8(tmem + lane_base + kUColS + a * 32 + 8 * cpart, more);
-            tmem_ld_wait();
-#pragma unroll
-            for (int k = 0; k < 8; ++k) sum[k] += more[k];
-        }
         long long* sums_g = p.sums + static_cast<size_t>(unit) * p.clusters * kHeadDim;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const int c = 8 * cpart + k;
-            if (c < p.clusters && cnt_s[c] > 0)
-                atomicAdd(reinterpret_cast<unsigned long long*>(sums_g + c * kHeadDim + row_in_tile),
-                          static_cast<unsigned long long>(__float2ll_rn(sum[k] * kFix)));
+        for (int part = 0; part < 2; ++part) {
+            float sum[8];  // the accumulators added in index order
+            tmem_ld8(tmem + lane_base + kUColS + 16 * half + 8 * part, sum);
+            tmem_ld_wait();
+            for (int a = 1; a < kUSumBuffers && a < n_tiles; ++a) {
+                float more[8];
+                tmem_ld8(tmem + lane_base + kUColS + a * 32 + 16 * half + 8 * part, more);
+                tmem_ld_wait();
+#pragma unroll
+                for (int k = 0; k < 8; ++k) sum[k] += more[k];
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int c = 16 * half + 8 * part + k;
+                if (c < p.clusters && cnt_s[c] > 0)
+                    atomicAdd(reinterpret_cast<unsigned long long*>(sums_g + c * kHeadDim + row_in_tile),
+                              static_cast<unsigned long long>(__float2ll_rn(sum[k] * kFix)));
+            }
         }
     }
     if (tid < p.clusters && cnt_s[tid] > 0) atomicAdd(&p.counts[unit * p.clusters + tid], cnt_s[tid]);
@@ -988,8 +956,8 @@ int launch_umma(const KmeansParams& p, int value, int iterations, void* centroid
                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (made != CUDA_SUCCESS) return fail(RESKV_ERR_CUDA, "kmeans: cuTensorMapEncodeTiled failed with code %d", static_cast<int>(made));
     constexpr int kN = HILO ? 64 : 32;
-    const size_t smem = 1024 + static_cast<size_t>(kUStages) * kUTileBytes + 2 * kN * 128 + 2 * kUOneHotBytes +
-                        2 * 4 * kUTile * sizeof(float4) + 32 * kHeadDim * sizeof(float) + 32 * (sizeof(float) + sizeof(int));
+    const size_t smem = 1024 + static_cast<size_t>(kUStages) * kUTileBytes + 2 * kN * 128 + kUGroups * kUOneHotBytes +
+                        32 * kHeadDim * sizeof(float) + 32 * (sizeof(float) + sizeof(int));
     static unsigned long long prepared = 0;  // per-device bit: the shared-memory attribute is set
     int dev = 0;
     cudaGetDevice(&dev);
