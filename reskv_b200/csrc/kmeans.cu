@@ -683,13 +683,11 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
             float d1 = INFINITY, d2 = INFINITY;
             int c1 = 0;
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
+            for (int c = 0; c < 32; ++c) {  // branch-free: best, second best, index of the best
                 d[c] = fmaf(-2.f, d[c], cn_s[c]);
-                if (d[c] < d1) {
-                    d2 = d1, d1 = d[c], c1 = c;  // a strict comparison keeps the lower index on ties
-                } else if (d[c] < d2) {
-                    d2 = d[c];
-                }
+                d2 = fminf(d2, fmaxf(d[c], d1));
+                c1 = d[c] < d1 ? c : c1;  // a strict comparison keeps the lower index on ties
+                d1 = fminf(d1, d[c]);
             }
             if (first) {
                 // |x|^2 for the near-tie bound: packed FP16 products, eight at a time (an overflow gives +inf: re-rank)
