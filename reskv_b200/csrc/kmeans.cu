@@ -770,13 +770,16 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
             tc_fence_after();
             const uint64_t a = a0 + static_cast<uint64_t>(((j % kUStages) * kUTileBytes) >> 4);
             const uint32_t d = tmem + kUColD + buf * 64;
+            if (elect_one()) {  // the eight MMAs and their commit in one elected stretch
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {  // 16 coordinates per step: 32 bytes inside the swizzled 128-byte row
-                const uint64_t ak = a + static_cast<uint64_t>(((ks >> 2) * kUBoxBytes + (ks & 3) * 32) >> 4);
-                const uint64_t bk = b0 + static_cast<uint64_t>(((ks >> 2) * (kN * 128) + (ks & 3) * 32) >> 4);
-                if (elect_one()) umma_f16(d, ak, bk, umma_idesc(kN, false), ks > 0);
+                for (int ks = 0; ks < 8; ++ks) {  // 16 coordinates per step: 32 bytes inside the swizzled 128-byte row
+                    const uint64_t ak = a + static_cast<uint64_t>(((ks >> 2) * kUBoxBytes + (ks & 3) * 32) >> 4);
+                    const uint64_t bk = b0 + static_cast<uint64_t>(((ks >> 2) * (kN * 128) + (ks & 3) * 32) >> 4);
+                    umma_f16(d, ak, bk, umma_idesc(kN, false), ks > 0);
+                }
+                umma_commit(&bar_dist[buf]);
             }
-            if (elect_one()) umma_commit(&bar_dist[buf]);
+            __syncwarp();
         }
     } else if (warp == kWarpCopy) {
         // ---- copies: a stage is refilled as soon as the sums of the tile it held have run ---------------------
@@ -795,13 +798,16 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
             const uint32_t d = tmem + kUColS + (i % kUSumBuffers) * 32;
             lost |= !mbar_wait(&bar_onehot[buf], (i / kUGroups) & 1);
             tc_fence_after();
+            if (elect_one()) {
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {  // 16 tokens per step: two 8-row groups of the tile = 2048 bytes
-                const uint64_t ak = a + static_cast<uint64_t>((ks * 2048) >> 4);
-                const uint64_t bk = o + static_cast<uint64_t>(((ks >> 2) * (32 * 128) + (ks & 3) * 32) >> 4);
-                if (elect_one()) umma_f16(d, ak, bk, umma_idesc(32, true), (i >= kUSumBuffers || ks > 0) ? 1u : 0u);
+                for (int ks = 0; ks < 8; ++ks) {  // 16 tokens per step: two 8-row groups of the tile = 2048 bytes
+                    const uint64_t ak = a + static_cast<uint64_t>((ks * 2048) >> 4);
+                    const uint64_t bk = o + static_cast<uint64_t>(((ks >> 2) * (32 * 128) + (ks & 3) * 32) >> 4);
+                    umma_f16(d, ak, bk, umma_idesc(32, true), (i >= kUSumBuffers || ks > 0) ? 1u : 0u);
+                }
+                umma_commit(&bar_sums[buf]);
             }
-            if (elect_one()) umma_commit(&bar_sums[buf]);
+            __syncwarp();
         }
     }
     // the commit of the last sums covers every MMA of this CTA
