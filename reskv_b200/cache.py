@@ -77,9 +77,9 @@ class ResKVLayerCache(_HFLayer or _LayerBase):
 
         b, h, _, d = key_states.shape
         slots = self.sink_tokens + self.config.recent_size + self.config.group_size
-        self.keys = torch.empty((b, h, slots, d), device=key_states.device, dtype=key_states.dtype)
-        self.raw_keys = torch.empty_like(self.keys)
-        self.values = torch.empty_like(self.keys)
+        # one allocation for the three window buffers
+        window = torch.empty((3, b, h, slots, d), device=key_states.device, dtype=key_states.dtype)
+        self.keys, self.raw_keys, self.values = window[0], window[1], window[2]
         self.plan = self.config.resolve(b)
         self._lib = bound_library(key_states.device)
         self.is_initialized = True

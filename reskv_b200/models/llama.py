@@ -194,9 +194,7 @@ class ResKVLlama:
                 cache = ResKVLayerCache(self.kernel_config, self.sink_tokens)
                 cache.update(k_rot, v_all, {"raw_keys": k_raw})
                 if reserve and cache.compressed is not None:
-                    total = cache.compressed.seq_len + reserve
-                    cache.compressed.key = cache.compressed.key.reserve(total)
-                    cache.compressed.value = cache.compressed.value.reserve(total)
+                    cache.compressed = cache.compressed.reserve(cache.compressed.seq_len + reserve)
             else:
                 cache = _DenseLayerCache(b, self.h_kv, t + reserve, self.device)
                 cache.append(k_rot, v_all)

@@ -186,17 +186,7 @@ class CompressedTensor:
         n = self.seq_len
         if self.token_stride >= capacity and not copy:
             return self
-        capacity = max(capacity, n)
-        b, h = self.cluster_ids.shape[:2]
-        grown = []
-        for view in (self.cluster_ids, self.payload, self.metadata, self.scale):
-            if view is None:
-                grown.append(None)
-                continue
-            buf = view.new_empty((b, h, capacity) + tuple(view.shape[3:]))
-            buf[:, :, :n].copy_(view)
-            grown.append(buf)
-        return CompressedTensor._window(self.centroids, grown, n, self.plan)
+        return _regrow([self], max(capacity, n))[0]
 
     def append(self, other: "CompressedTensor") -> "CompressedTensor":
         """Tokens of ``self`` followed by those of ``other``.
@@ -259,6 +249,39 @@ class CompressedKV:
     @property
     def nbytes(self) -> int:
         return _storage_bytes((*self.key.tensors, *self.value.tensors))
+
+    def reserve(self, capacity: int) -> "CompressedKV":
+        """Both sides over buffers of at least ``capacity`` tokens, grown together in one allocation."""
+        if min(self.key.token_stride, self.value.token_stride) >= capacity:
+            return self
+        return CompressedKV(*_regrow([self.key, self.value], max(capacity, self.seq_len)))
+
+
+def _regrow(tensors, capacity: int):
+    """The given compressed tensors over fresh buffers of ``capacity`` tokens, all carved from ONE allocation (every
+    buffer starts on a 256-byte boundary): a layer's cache then costs one trip to the device allocator."""
+    plans = []
+    for ct in tensors:
+        b, h = ct.cluster_ids.shape[:2]
+        for view in (ct.cluster_ids, ct.payload, ct.metadata, ct.scale):
+            used = 0 if view is None else b * h * capacity * view[0, 0, 0].numel() * view.element_size()
+            plans.append((view, used, -(-used // 256) * 256))
+    arena = torch.empty(sum(size for _, _, size in plans), dtype=torch.uint8, device=tensors[0].cluster_ids.device)
+    out, at, it = [], 0, iter(plans)
+    for ct in tensors:
+        b, h = ct.cluster_ids.shape[:2]
+        n, grown = ct.seq_len, []
+        for _ in range(4):
+            view, used, size = next(it)
+            if view is None:
+                grown.append(None)
+                continue
+            buf = arena[at : at + used].view(view.dtype).view((b, h, capacity) + tuple(view.shape[3:]))
+            buf[:, :, :n].copy_(view)
+            grown.append(buf)
+            at += size
+        out.append(CompressedTensor._window(ct.centroids, grown, n, ct.plan))
+    return out
 
 
 def _storage_bytes(tensors) -> int:

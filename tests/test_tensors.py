@@ -51,3 +51,28 @@ def test_capacity_and_live_bytes():
     assert grown.live_nbytes == 2 * 4 * 128 * 2 + 2 * 164 * per_token
     assert grown.nbytes >= grown.live_nbytes and grown.token_stride >= 2 * 164
     assert parent.live_nbytes == 2 * 4 * 128 * 2 + 2 * 100 * per_token
+
+
+def test_joint_reserve_keeps_both_sides_and_shares_one_allocation():
+    """CompressedKV.reserve grows K and V together: same tokens, capacity as asked, one backing storage."""
+    from reskv_b200.config import KernelPlan
+    from reskv_b200.tensors import CompressedKV, CompressedTensor
+
+    plan = KernelPlan("unstructured", "deferred", 16, 32, 4, 0)
+    g = torch.Generator().manual_seed(5)
+
+    def side():
+        return CompressedTensor(torch.randn(2, 3, 4, 128, generator=g).half(),
+                                torch.randint(4, (2, 3, 10), generator=g, dtype=torch.int32),
+                                torch.randn(2, 3, 10, 32, generator=g).half(),
+                                torch.randint(1 << 40, (2, 3, 10, 2), generator=g, dtype=torch.int64), None, plan)
+
+    kv = CompressedKV(side(), side())
+    grown = kv.reserve(64)
+    assert grown.seq_len == 10 and grown.key.token_stride >= 64 and grown.value.token_stride >= 64
+    for a, b in ((kv.key, grown.key), (kv.value, grown.value)):
+        for x, y in zip(a.tensors, b.tensors):
+            assert (x is None and y is None) or torch.equal(x, y)
+    storages = {t.untyped_storage().data_ptr() for t in (*grown.key._buffers, *grown.value._buffers) if t is not None}
+    assert len(storages) == 1
+    assert grown.reserve(32) is grown
