@@ -76,3 +76,17 @@ def test_joint_reserve_keeps_both_sides_and_shares_one_allocation():
     storages = {t.untyped_storage().data_ptr() for t in (*grown.key._buffers, *grown.value._buffers) if t is not None}
     assert len(storages) == 1
     assert grown.reserve(32) is grown
+
+
+def test_token_stride_of_recognises_token_slices_only():
+    """Dense tensors and token slices of dense buffers carry a token stride; anything else does not."""
+    from reskv_b200._extension import token_stride_of
+
+    big = torch.zeros(2, 3, 50, 128, dtype=torch.float16)
+    assert token_stride_of(big) == 50
+    assert token_stride_of(big[:, :, 5:25]) == 50
+    assert token_stride_of(big[:, :1, 5:25]) == 150          # one head per sequence: units are whole sequences apart
+    assert token_stride_of(big[:1, :1, 5:25]) == 20          # a single unit: any stride will do
+    assert token_stride_of(big[:, :, ::2]) is None           # every other token
+    assert token_stride_of(big[:, ::2]) is None              # units no longer evenly spaced
+    assert token_stride_of(big.transpose(1, 2)) is None
