@@ -442,20 +442,20 @@ __global__ void __launch_bounds__(kThreads) kmeans_assign_mma_kernel(const Kmean
 }
 
 // ---- tcgen05 form of the assignment kernel (up to 32 centres) ---------------------------------------------------
-// One CTA streams `chunk` tokens of one unit in tiles of 128 tokens.  A tile arrives by two tensor-map copies
+// One CTA per SM; the 128-token tiles of all units are laid end to end and every CTA streams an equal share of them,
+// segment by segment (a segment = consecutive tiles of one unit).  A tile arrives by two tensor-map copies
 // (TMA, 128-byte swizzle: coordinates 0..63 and 64..127 of 128 rows) and is used three times without ever
 // passing through registers:
 //   * distances: D[128 tokens x 64] = X . [c_hi | c_lo]^T, X as the K-major A operand of tcgen05.mma, the centre
-//     halves as a K-major B operand written once per CTA; accumulator in TMEM, double buffered, issued two tiles
-//     ahead of its use;
+//     halves as a K-major B operand written once per segment; accumulator in TMEM, triple buffered;
 //   * ranking: one thread per token (TMEM lane = token row) reads its row of D with tcgen05.ld, ranks the centres,
 //     re-ranks near-ties exactly - only the centres inside the bound, with the arithmetic and order of the exact
 //     path of the mma.sync form -, writes the id and sets one element of a one-hot operand
 //     onehot[32 clusters x 128 tokens]; three groups of four warps take the tiles in turn, so each has three tile
 //     periods for its chain of dependent steps;
 //   * sums: S^T[128 coordinates x 32 clusters] += X^T . onehot^T, the same tile now read as the MN-major A operand,
-//     accumulated in TMEM (four accumulators in turn) over the CTA's whole token range and flushed once as
-//     2^24-scaled integers.
+//     accumulated in TMEM (four accumulators in turn) over the segment and flushed at its end as 2^24-scaled
+//     integers.
 // Three more warps issue the asynchronous work (distance MMAs, sum MMAs, copies); they stay converged (descriptor
 // arithmetic on the uniform datapath) and elect one lane per instruction.  The roles run concurrently on
 // different tiles and hand over through mbarriers only (triple-buffered distances and one-hot operands); every
@@ -548,9 +548,13 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+constexpr int kUWorkers = kUThreads - 32;  // everyone but the copying warp: these meet at the segment boundaries
+
+__device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kUWorkers) : "memory"); }
+
 template <bool HILO>
 __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const KmeansParams p,
-                                                                           const __grid_constant__ CUtensorMap xmap, int chunk,
+                                                                           const __grid_constant__ CUtensorMap xmap, int share,
                                                                            int first, int last) {
     extern __shared__ unsigned char smem_u[];
     constexpr int kN = HILO ? 64 : 32;  // rows of the centre operand: hi halves, then lo halves
@@ -561,19 +565,39 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
     float* cen_s = reinterpret_cast<float*>(oh + kUGroups * kUOneHotBytes);  // [32][128] FP32 centres (exact re-ranking)
     float* cn_s = cen_s + 32 * kHeadDim;                        // [32] |c|^2, +inf for padding
     int* cnt_s = reinterpret_cast<int*>(cn_s + 32);             // [32]
-    // full: tile landed (TMA bytes).  dist / sums: MMAs complete (tcgen05.commit).  dist_free: the 128 threads of a
-    // group have read their distance buffer.  onehot: they have written their one-hot operand.
-    __shared__ uint64_t bar_full[kUStages], bar_dist[kUGroups], bar_dist_free[kUGroups], bar_onehot[kUGroups], bar_sums[kUGroups];
+    // full: tile landed (TMA bytes).  dist / sums: MMAs complete (tcgen05.commit); empty: the same event as sums,
+    // counted per stage for the copying warp (a barrier of its own: no later completion can overtake its wait).
+    // dist_free: the 128 threads of a group have read their distance buffer.  onehot: they have written their one-hot
+    // operand.
+    __shared__ uint64_t bar_full[kUStages], bar_empty[kUStages], bar_dist[kUGroups], bar_dist_free[kUGroups], bar_onehot[kUGroups],
+        bar_sums[kUGroups];
     __shared__ uint32_t tmem_base_s;
 
-    const int unit = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int t_begin = blockIdx.x * chunk, t_end = min(p.tokens, t_begin + chunk);
-    const int n_tiles = (t_end - t_begin + kUTile - 1) / kUTile;
-    const float* cen_g = p.centres + static_cast<size_t>(unit) * p.clusters * kHeadDim;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // Work of the launch = the tiles of all units laid end to end; CTA c takes [c * share, (c + 1) * share) and walks
+    // it segment by segment (consecutive tiles of one unit, at most kUChunkMax tokens: one set of FP32 partial sums).
+    // Tiles are numbered q = 0, 1, ... through the CTA's whole range: stage q % 5, group / distance buffer / one-hot
+    // buffer q % 3, sum accumulator q % 4, and every barrier's phase follows from q, so the ring keeps turning across
+    // segment boundaries (the copies of the next segment are in flight while this one drains and flushes).
+    const int tiles_per_unit = (p.tokens + kUTile - 1) / kUTile;
+    const long long work_total = static_cast<long long>(p.units) * tiles_per_unit;
+    const long long work_begin = static_cast<long long>(blockIdx.x) * share;
+    const long long work_end = work_begin + share < work_total ? work_begin + share : work_total;
+    struct Segment {
+        int unit, tile0, tiles;
+    };
+    auto segment_at = [&](long long w) {
+        Segment sg;
+        sg.unit = static_cast<int>(w / tiles_per_unit);
+        sg.tile0 = static_cast<int>(w - static_cast<long long>(sg.unit) * tiles_per_unit);
+        const long long left = work_end - w;
+        sg.tiles = min(min(tiles_per_unit - sg.tile0, kUChunkMax / kUTile), static_cast<int>(left < 1 << 20 ? left : 1 << 20));
+        return sg;
+    };
     bool lost = false;
 
     if (tid == 0) {
-        for (int s = 0; s < kUStages; ++s) mbar_init(&bar_full[s], 1);
+        for (int s = 0; s < kUStages; ++s) mbar_init(&bar_full[s], 1), mbar_init(&bar_empty[s], 1);
         for (int b = 0; b < kUGroups; ++b) {
             mbar_init(&bar_dist[b], 1), mbar_init(&bar_sums[b], 1);
             mbar_init(&bar_dist_free[b], kUGroupWarps * 32), mbar_init(&bar_onehot[b], kUGroupWarps * 32);
@@ -585,264 +609,286 @@ __global__ void __launch_bounds__(kUThreads, 1) kmeans_assign_umma_kernel(const 
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    __syncthreads();  // barriers initialised
-    auto load_tile = [&](int j) {  // converged warp
-        unsigned char* dst = xs + (j % kUStages) * kUTileBytes;
-        uint64_t* bar = &bar_full[j % kUStages];
-        if (elect_one()) {
-            mbar_arrive_expect_tx(bar, kUTileBytes);
-            tma_load_3d(dst, &xmap, 0, t_begin + j * kUTile, unit, bar);
-            tma_load_3d(dst + kUBoxBytes, &xmap, 64, t_begin + j * kUTile, unit, bar);
-        }
-    };
-    constexpr int kWarpDist = kUGroups * kUGroupWarps, kWarpSums = kWarpDist + 1, kWarpCopy = kWarpDist + 2;
-    if (warp == kWarpCopy)
-        for (int j = 0; j < kUStages && j < n_tiles; ++j) load_tile(j);
-
-    // ---- per CTA: centre operand (FP16 hi | lo rows, swizzled), FP32 centres, |c|^2, empty one-hot buffers ----
-    {
-        // four coordinates per thread and step, all loads of a thread in flight together
-        constexpr int kSteps = (32 * kHeadDim / 4 + kUThreads - 1) / kUThreads;
-        float4 v[kSteps];
-#pragma unroll
-        for (int k = 0; k < kSteps; ++k) {
-            const int i4 = tid + k * kUThreads;
-            v[k] = (i4 < 32 * kHeadDim / 4 && i4 / (kHeadDim / 4) < p.clusters) ? __ldg(reinterpret_cast<const float4*>(cen_g) + i4)
-                                                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int k = 0; k < kSteps; ++k) {
-            const int i4 = tid + k * kUThreads;
-            if (i4 >= 32 * kHeadDim / 4) break;
-            const int c = i4 / (kHeadDim / 4), d = (i4 % (kHeadDim / 4)) * 4;
-            reinterpret_cast<float4*>(cen_s)[i4] = v[k];
-            const __half2 h01 = __floats2half2_rn(v[k].x, v[k].y), h23 = __floats2half2_rn(v[k].z, v[k].w);
-            unsigned char* at = cop + (d >> 6) * (kN * 128) + ((d & 7) << 1);
-            *reinterpret_cast<uint2*>(at + sw128(c, (d & 63) >> 3)) =
-                make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
-            float2 f01 = __half22float2(h01), f23 = __half22float2(h23);  // what the MMA sees: hi (+ lo)
-            if (HILO) {
-                const __half2 l01 = __floats2half2_rn(v[k].x - f01.x, v[k].y - f01.y);
-                const __half2 l23 = __floats2half2_rn(v[k].z - f23.x, v[k].w - f23.y);
-                *reinterpret_cast<uint2*>(at + sw128(32 + c, (d & 63) >> 3)) =
-                    make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
-                const float2 g01 = __half22float2(l01), g23 = __half22float2(l23);
-                f01.x += g01.x, f01.y += g01.y, f23.x += g23.x, f23.y += g23.y;
-            }
-            // |c|^2: the 32 threads of a warp hold one centre (kUThreads is a multiple of 32)
-            float sq = fmaf(f01.x, f01.x, fmaf(f01.y, f01.y, fmaf(f23.x, f23.x, f23.y * f23.y)));
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(kFull, sq, off);
-            if (lane == 0) cn_s[c] = c < p.clusters ? sq : INFINITY;
-        }
-    }
     for (int i = tid; i < kUGroups * kUOneHotBytes / 16; i += kUThreads) reinterpret_cast<uint4*>(oh)[i] = make_uint4(0, 0, 0, 0);
-    if (tid < 32) cnt_s[tid] = 0;
-    proxy_fence();  // the operands written above are read by the tensor core (async proxy)
     tc_fence_before();
-    __syncthreads();
+    __syncthreads();  // barriers initialised, TMEM allocated, one-hot buffers empty
     tc_fence_after();
-    float cmax = lane < p.clusters ? cn_s[lane] : 0.f;  // largest |c|^2, in every thread
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) cmax = fmaxf(cmax, __shfl_xor_sync(kFull, cmax, off));
     const uint32_t tmem = tmem_base_s;
-    const __half* xu = p.x + static_cast<size_t>(unit) * p.x_stride * kHeadDim;
+    constexpr int kWarpDist = kUGroups * kUGroupWarps, kWarpCopy = kWarpDist + 2;  // kWarpDist + 1 issues the sum MMAs
 
-    if (warp < kWarpDist) {
-        // ---- ranking: one thread per token; group g takes the tiles g, g + 3, ... with distance buffer g and
-        // one-hot buffer g ----------------------------------------------------------------------------------------
-        const int g = warp / kUGroupWarps, quarter = warp % kUGroupWarps, row_in_tile = quarter * 32 + lane;
-        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        int prev = -1;  // byte offset of the element this thread set in its one-hot buffer
-        // |x|^2 of a token is the same in every Lloyd iteration: the first one forms it and stores it (as FP32 bits)
-        // where the token's id goes, the following ones read it from there one tile ahead, the last one writes the id
-        int32_t* ids_u = p.ids + static_cast<size_t>(unit) * p.tokens;
-        float xn_next = 0.f;
-        if (!first && t_begin + g * kUTile + row_in_tile < t_end) xn_next = __int_as_float(ids_u[t_begin + g * kUTile + row_in_tile]);
-        for (int i = g; i < n_tiles; i += kUGroups) {
-            const int use = i / kUGroups, st = i % kUStages;
-            const int row = t_begin + i * kUTile + row_in_tile;
-            const bool live = row < t_end;
-            float xn = xn_next;
-            if (!first && row + kUGroups * kUTile < t_end) xn_next = __int_as_float(ids_u[row + kUGroups * kUTile]);
-            lost |= !mbar_wait(&bar_dist[g], use & 1);
-            tc_fence_after();
-            float d[32];
-            tmem_ld32(tmem + lane_base + kUColD + g * 64, d);
-            if constexpr (HILO) {
-                float lo[32];
-                tmem_ld32(tmem + lane_base + kUColD + g * 64 + 32, lo);
-                tmem_ld_wait();
-#pragma unroll
-                for (int c = 0; c < 32; ++c) d[c] += lo[c];
-            } else {
-                tmem_ld_wait();
-            }
-            tc_fence_before();
-            mbar_arrive(&bar_dist_free[g]);  // the next distances of this group may be issued
-            float d1 = INFINITY, d2 = INFINITY;
-            int c1 = 0;
-#pragma unroll
-            for (int c = 0; c < 32; ++c) {  // branch-free: best, second best, index of the best
-                d[c] = fmaf(-2.f, d[c], cn_s[c]);
-                d2 = fminf(d2, fmaxf(d[c], d1));
-                c1 = d[c] < d1 ? c : c1;  // a strict comparison keeps the lower index on ties
-                d1 = fminf(d1, d[c]);
-            }
-            if (first) {
-                // |x|^2 for the near-tie bound: packed FP16 products, eight at a time (an overflow gives +inf: re-rank)
-                lost |= !mbar_wait(&bar_full[st], (i / kUStages) & 1);
-                const unsigned char* xt = xs + st * kUTileBytes;
-                xn = 0.f;
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(xt + (j >> 3) * kUBoxBytes + sw128(row_in_tile, j & 7));
-                    const __half2* h = reinterpret_cast<const __half2*>(&v);
-                    __half2 s = __hmul2(h[0], h[0]);
-                    s = __hfma2(h[1], h[1], s), s = __hfma2(h[2], h[2], s), s = __hfma2(h[3], h[3], s);
-                    const float2 f = __half22float2(s);
-                    xn += f.x + f.y;
+    if (warp == kWarpCopy) {
+        // ---- copies, through all segments without a stop: the stage of tile q is free once the sums of tile
+        // q - 5 have run (whole warp, one elected lane per tile) --------------------------------------------------
+        int q = 0;
+        for (long long w = work_begin; w < work_end;) {
+            const Segment sg = segment_at(w);
+            for (int i = 0; i < sg.tiles; ++i, ++q) {
+                if (q >= kUStages) lost |= !mbar_wait(&bar_empty[q % kUStages], (q / kUStages - 1) & 1);
+                unsigned char* dst = xs + (q % kUStages) * kUTileBytes;
+                uint64_t* bar = &bar_full[q % kUStages];
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(bar, kUTileBytes);
+                    tma_load_3d(dst, &xmap, 0, (sg.tile0 + i) * kUTile, sg.unit, bar);
+                    tma_load_3d(dst + kUBoxBytes, &xmap, 64, (sg.tile0 + i) * kUTile, sg.unit, bar);
                 }
+                __syncwarp();
             }
-            // near-ties: only a centre whose distance lies inside the bound can win; the warp forms the exact FP32
-            // sums of those few (same arithmetic, same order as `nearest`), one tied token at a time
-            const float bound = kTieBound * (1.01f * xn + cmax);
-            uint32_t inside = 0u;
-            if (live && !((d2 - d1) > bound)) {
-#pragma unroll
-                for (int c = 0; c < 32; ++c) inside |= !((d[c] - d1) > bound) ? 1u << c : 0u;
-            }
-            uint32_t redo = __ballot_sync(kFull, inside != 0u);
-            while (redo) {
-                const int src = __ffs(redo) - 1;
-                redo &= redo - 1;
-                uint32_t cands = __shfl_sync(kFull, inside, src) & (p.clusters >= 32 ? 0xffffffffu : (1u << p.clusters) - 1u);
-                const __half* xr = xu + static_cast<size_t>(t_begin + i * kUTile + quarter * 32 + src) * kHeadDim;
-                float xv[4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) xv[k] = __half2float(xr[lane + 32 * k]);
-                float best = INFINITY;
-                int bc = 0;
-                while (cands) {  // ascending centre index: the lower one wins ties
-                    const int c = __ffs(cands) - 1;
-                    cands &= cands - 1;
-                    const float* crow = cen_s + c * kHeadDim;
-                    float acc = 0.f;
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float df = xv[e] - crow[lane + 32 * e];
-                        acc = fmaf(df, df, acc);
-                    }
-#pragma unroll
-                    for (int off = 16; off > 0; off >>= 1) acc = acc + __shfl_xor_sync(kFull, acc, off);
-                    if (acc < best) best = acc, bc = c;
-                }
-                if (lane == src) c1 = bc;
-            }
-            if (live) {
-                if (last) {
-                    ids_u[row] = c1;
-                } else if (first) {
-                    ids_u[row] = __float_as_int(xn);
-                }
-                atomicAdd(&cnt_s[c1], 1);
-            }
-            // one-hot buffer g was last read by the sums of tile i - 3
-            if (i >= kUGroups) lost |= !mbar_wait(&bar_sums[g], (use - 1) & 1);
-            unsigned char* ob = oh + g * kUOneHotBytes;
-            if (prev >= 0) *reinterpret_cast<unsigned short*>(ob + prev) = 0;
-            prev = -1;
-            if (live) {
-                prev = (row_in_tile >> 6) * (32 * 128) + sw128(c1, (row_in_tile & 63) >> 3) + ((row_in_tile & 7) << 1);
-                *reinterpret_cast<unsigned short*>(ob + prev) = 0x3C00;  // 1.0
-            }
-            proxy_fence();  // the tensor core (async proxy) reads what this thread wrote
-            mbar_arrive(&bar_onehot[g]);
-        }
-    } else if (warp == kWarpDist) {
-        // ---- distance MMAs (whole warp, one elected lane per instruction): tile j goes to buffer j % 3 as soon as
-        // the group has read tile j - 3 out of it -------------------------------------------------------------------
-        const uint64_t a0 = umma_desc(smem_u32(xs), 16, 1024), b0 = umma_desc(smem_u32(cop), 16, 1024);
-        for (int j = 0; j < n_tiles; ++j) {
-            const int buf = j % kUGroups;
-            if (j >= kUGroups) lost |= !mbar_wait(&bar_dist_free[buf], (j / kUGroups - 1) & 1);
-            lost |= !mbar_wait(&bar_full[j % kUStages], (j / kUStages) & 1);
-            tc_fence_after();
-            const uint64_t a = a0 + static_cast<uint64_t>(((j % kUStages) * kUTileBytes) >> 4);
-            const uint32_t d = tmem + kUColD + buf * 64;
-            if (elect_one()) {  // the eight MMAs and their commit in one elected stretch
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {  // 16 coordinates per step: 32 bytes inside the swizzled 128-byte row
-                    const uint64_t ak = a + static_cast<uint64_t>(((ks >> 2) * kUBoxBytes + (ks & 3) * 32) >> 4);
-                    const uint64_t bk = b0 + static_cast<uint64_t>(((ks >> 2) * (kN * 128) + (ks & 3) * 32) >> 4);
-                    umma_f16(d, ak, bk, umma_idesc(kN, false), ks > 0);
-                }
-                umma_commit(&bar_dist[buf]);
-            }
-            __syncwarp();
-        }
-    } else if (warp == kWarpCopy) {
-        // ---- copies: a stage is refilled as soon as the sums of the tile it held have run ---------------------
-        for (int i = 0; i + kUStages < n_tiles; ++i) {
-            lost |= !mbar_wait(&bar_sums[i % kUGroups], (i / kUGroups) & 1);
-            load_tile(i + kUStages);
+            w += sg.tiles;
         }
     } else {
-        // ---- sum MMAs ---------------------------------------------------------------------------------------
-        const uint64_t a0 = umma_desc(smem_u32(xs), kUBoxBytes, 1024);  // MN-major: other half of the coordinates at LBO
-        const uint64_t b0 = umma_desc(smem_u32(oh), 16, 1024);
-        for (int i = 0; i < n_tiles; ++i) {
-            const int buf = i % kUGroups;
-            const uint64_t a = a0 + static_cast<uint64_t>(((i % kUStages) * kUTileBytes) >> 4);
-            const uint64_t o = b0 + static_cast<uint64_t>((buf * kUOneHotBytes) >> 4);
-            const uint32_t d = tmem + kUColS + (i % kUSumBuffers) * 32;
-            lost |= !mbar_wait(&bar_onehot[buf], (i / kUGroups) & 1);
-            tc_fence_after();
-            if (elect_one()) {
+        int q0 = 0;     // tiles of the earlier segments of this CTA
+        int prev = -1;  // byte offset of the element this thread set in its group's one-hot buffer
+        for (long long w = work_begin; w < work_end;) {
+            const Segment sg = segment_at(w);
+            const int unit = sg.unit, n_tiles = sg.tiles;
+            const int t_begin = sg.tile0 * kUTile, t_end = min(p.tokens, t_begin + n_tiles * kUTile);
+            const float* cen_g = p.centres + static_cast<size_t>(unit) * p.clusters * kHeadDim;
+            // ---- per segment: centre operand (FP16 hi | lo rows, swizzled), FP32 centres, |c|^2 -------------------
+            {
+                // four coordinates per thread and step, all loads of a thread in flight together
+                constexpr int kSteps = (32 * kHeadDim / 4 + kUWorkers - 1) / kUWorkers;
+                float4 v[kSteps];
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {  // 16 tokens per step: two 8-row groups of the tile = 2048 bytes
-                    const uint64_t ak = a + static_cast<uint64_t>((ks * 2048) >> 4);
-                    const uint64_t bk = o + static_cast<uint64_t>(((ks >> 2) * (32 * 128) + (ks & 3) * 32) >> 4);
-                    umma_f16(d, ak, bk, umma_idesc(32, true), (i >= kUSumBuffers || ks > 0) ? 1u : 0u);
+                for (int k = 0; k < kSteps; ++k) {
+                    const int i4 = tid + k * kUWorkers;
+                    v[k] = (i4 < 32 * kHeadDim / 4 && i4 / (kHeadDim / 4) < p.clusters) ? __ldg(reinterpret_cast<const float4*>(cen_g) + i4)
+                                                                                          : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
-                umma_commit(&bar_sums[buf]);
+#pragma unroll
+                for (int k = 0; k < kSteps; ++k) {
+                    const int i4 = tid + k * kUWorkers;
+                    if (i4 >= 32 * kHeadDim / 4) break;
+                    const int c = i4 / (kHeadDim / 4), d = (i4 % (kHeadDim / 4)) * 4;
+                    reinterpret_cast<float4*>(cen_s)[i4] = v[k];
+                    const __half2 h01 = __floats2half2_rn(v[k].x, v[k].y), h23 = __floats2half2_rn(v[k].z, v[k].w);
+                    unsigned char* at = cop + (d >> 6) * (kN * 128) + ((d & 7) << 1);
+                    *reinterpret_cast<uint2*>(at + sw128(c, (d & 63) >> 3)) =
+                        make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+                    float2 f01 = __half22float2(h01), f23 = __half22float2(h23);  // what the MMA sees: hi (+ lo)
+                    if (HILO) {
+                        const __half2 l01 = __floats2half2_rn(v[k].x - f01.x, v[k].y - f01.y);
+                        const __half2 l23 = __floats2half2_rn(v[k].z - f23.x, v[k].w - f23.y);
+                        *reinterpret_cast<uint2*>(at + sw128(32 + c, (d & 63) >> 3)) =
+                            make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
+                        const float2 g01 = __half22float2(l01), g23 = __half22float2(l23);
+                        f01.x += g01.x, f01.y += g01.y, f23.x += g23.x, f23.y += g23.y;
+                    }
+                    // |c|^2: the 32 threads of a warp hold one centre (the worker count is a multiple of 32)
+                    float sq = fmaf(f01.x, f01.x, fmaf(f01.y, f01.y, fmaf(f23.x, f23.x, f23.y * f23.y)));
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) sq += __shfl_xor_sync(kFull, sq, off);
+                    if (lane == 0) cn_s[c] = c < p.clusters ? sq : INFINITY;
+                }
             }
-            __syncwarp();
+            if (tid < 32) cnt_s[tid] = 0;
+            proxy_fence();  // the operands written above are read by the tensor core (async proxy)
+            workers_sync();
+            float cmax = lane < p.clusters ? cn_s[lane] : 0.f;  // largest |c|^2, in every thread
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) cmax = fmaxf(cmax, __shfl_xor_sync(kFull, cmax, off));
+            const __half* xu = p.x + static_cast<size_t>(unit) * p.x_stride * kHeadDim;
+
+            if (warp < kWarpDist) {
+                // ---- ranking: one thread per token; group g takes the tiles with q = g (mod 3), distance buffer g
+                // and one-hot buffer g ---------------------------------------------------------------------------
+                const int g = warp / kUGroupWarps, quarter = warp % kUGroupWarps, row_in_tile = quarter * 32 + lane;
+                const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+                // |x|^2 of a token is the same in every Lloyd iteration: the first one forms it and stores it (as FP32
+                // bits) where the token's id goes, the following ones read it from there one tile of the group ahead,
+                // the last one writes the id
+                int32_t* ids_u = p.ids + static_cast<size_t>(unit) * p.tokens;
+                const int i_first = (g + kUGroups - q0 % kUGroups) % kUGroups;
+                float xn_next = 0.f;
+                if (!first && t_begin + i_first * kUTile + row_in_tile < t_end)
+                    xn_next = __int_as_float(ids_u[t_begin + i_first * kUTile + row_in_tile]);
+                for (int i = i_first; i < n_tiles; i += kUGroups) {
+                    const int q = q0 + i, use = q / kUGroups, st = q % kUStages;
+                    const int row = t_begin + i * kUTile + row_in_tile;
+                    const bool live = row < t_end;
+                    float xn = xn_next;
+                    if (!first && row + kUGroups * kUTile < t_end) xn_next = __int_as_float(ids_u[row + kUGroups * kUTile]);
+                    lost |= !mbar_wait(&bar_dist[g], use & 1);
+                    tc_fence_after();
+                    float d[32];
+                    tmem_ld32(tmem + lane_base + kUColD + g * 64, d);
+                    if constexpr (HILO) {
+                        float lo[32];
+                        tmem_ld32(tmem + lane_base + kUColD + g * 64 + 32, lo);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) d[c] += lo[c];
+                    } else {
+                        tmem_ld_wait();
+                    }
+                    tc_fence_before();
+                    mbar_arrive(&bar_dist_free[g]);  // the next distances of this group may be issued
+                    float d1 = INFINITY, d2 = INFINITY;
+                    int c1 = 0;
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {  // branch-free: best, second best, index of the best
+                        d[c] = fmaf(-2.f, d[c], cn_s[c]);
+                        d2 = fminf(d2, fmaxf(d[c], d1));
+                        c1 = d[c] < d1 ? c : c1;  // a strict comparison keeps the lower index on ties
+                        d1 = fminf(d1, d[c]);
+                    }
+                    if (first) {
+                        // |x|^2 for the near-tie bound: packed FP16 products, eight at a time (an overflow gives +inf:
+                        // re-rank)
+                        lost |= !mbar_wait(&bar_full[st], (q / kUStages) & 1);
+                        const unsigned char* xt = xs + st * kUTileBytes;
+                        xn = 0.f;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const uint4 v = *reinterpret_cast<const uint4*>(xt + (j >> 3) * kUBoxBytes + sw128(row_in_tile, j & 7));
+                            const __half2* h = reinterpret_cast<const __half2*>(&v);
+                            __half2 s = __hmul2(h[0], h[0]);
+                            s = __hfma2(h[1], h[1], s), s = __hfma2(h[2], h[2], s), s = __hfma2(h[3], h[3], s);
+                            const float2 f = __half22float2(s);
+                            xn += f.x + f.y;
+                        }
+                    }
+                    // near-ties: only a centre whose distance lies inside the bound can win; the warp forms the exact
+                    // FP32 sums of those few (same arithmetic, same order as `nearest`), one tied token at a time
+                    const float bound = kTieBound * (1.01f * xn + cmax);
+                    uint32_t inside = 0u;
+                    if (live && !((d2 - d1) > bound)) {
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) inside |= !((d[c] - d1) > bound) ? 1u << c : 0u;
+                    }
+                    uint32_t redo = __ballot_sync(kFull, inside != 0u);
+                    while (redo) {
+                        const int src = __ffs(redo) - 1;
+                        redo &= redo - 1;
+                        uint32_t cands = __shfl_sync(kFull, inside, src) & (p.clusters >= 32 ? 0xffffffffu : (1u << p.clusters) - 1u);
+                        const __half* xr = xu + static_cast<size_t>(t_begin + i * kUTile + quarter * 32 + src) * kHeadDim;
+                        float xv[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) xv[k] = __half2float(xr[lane + 32 * k]);
+                        float best = INFINITY;
+                        int bc = 0;
+                        while (cands) {  // ascending centre index: the lower one wins ties
+                            const int c = __ffs(cands) - 1;
+                            cands &= cands - 1;
+                            const float* crow = cen_s + c * kHeadDim;
+                            float acc = 0.f;
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float df = xv[e] - crow[lane + 32 * e];
+                                acc = fmaf(df, df, acc);
+                            }
+#pragma unroll
+                            for (int off = 16; off > 0; off >>= 1) acc = acc + __shfl_xor_sync(kFull, acc, off);
+                            if (acc < best) best = acc, bc = c;
+                        }
+                        if (lane == src) c1 = bc;
+                    }
+                    if (live) {
+                        if (last) {
+                            ids_u[row] = c1;
+                        } else if (first) {
+                            ids_u[row] = __float_as_int(xn);
+                        }
+                        atomicAdd(&cnt_s[c1], 1);
+                    }
+                    // one-hot buffer g was last read by the sums of tile q - 3
+                    if (q >= kUGroups) lost |= !mbar_wait(&bar_sums[g], (use - 1) & 1);
+                    unsigned char* ob = oh + g * kUOneHotBytes;
+                    if (prev >= 0) *reinterpret_cast<unsigned short*>(ob + prev) = 0;
+                    prev = -1;
+                    if (live) {
+                        prev = (row_in_tile >> 6) * (32 * 128) + sw128(c1, (row_in_tile & 63) >> 3) + ((row_in_tile & 7) << 1);
+                        *reinterpret_cast<unsigned short*>(ob + prev) = 0x3C00;  // 1.0
+                    }
+                    proxy_fence();  // the tensor core (async proxy) reads what this thread wrote
+                    mbar_arrive(&bar_onehot[g]);
+                }
+            } else if (warp == kWarpDist) {
+                // ---- distance MMAs (whole warp, one elected lane per tile): tile q goes to buffer q % 3 as soon as
+                // the group has read tile q - 3 out of it ----------------------------------------------------------
+                const uint64_t a0 = umma_desc(smem_u32(xs), 16, 1024), b0 = umma_desc(smem_u32(cop), 16, 1024);
+                for (int i = 0; i < n_tiles; ++i) {
+                    const int q = q0 + i, buf = q % kUGroups;
+                    if (q >= kUGroups) lost |= !mbar_wait(&bar_dist_free[buf], (q / kUGroups - 1) & 1);
+                    lost |= !mbar_wait(&bar_full[q % kUStages], (q / kUStages) & 1);
+                    tc_fence_after();
+                    const uint64_t a = a0 + static_cast<uint64_t>(((q % kUStages) * kUTileBytes) >> 4);
+                    const uint32_t d = tmem + kUColD + buf * 64;
+                    if (elect_one()) {  // the eight MMAs and their commit in one elected stretch
+#pragma unroll
+                        for (int ks = 0; ks < 8; ++ks) {  // 16 coordinates per step: 32 bytes inside the swizzled 128-byte row
+                            const uint64_t ak = a + static_cast<uint64_t>(((ks >> 2) * kUBoxBytes + (ks & 3) * 32) >> 4);
+                            const uint64_t bk = b0 + static_cast<uint64_t>(((ks >> 2) * (kN * 128) + (ks & 3) * 32) >> 4);
+                            umma_f16(d, ak, bk, umma_idesc(kN, false), ks > 0);
+                        }
+                        umma_commit(&bar_dist[buf]);
+                    }
+                    __syncwarp();
+                }
+            } else {
+                // ---- sum MMAs: the first four tiles of a segment start the four accumulators ----------------------
+                const uint64_t a0 = umma_desc(smem_u32(xs), kUBoxBytes, 1024);  // MN-major: other half of the coordinates at LBO
+                const uint64_t b0 = umma_desc(smem_u32(oh), 16, 1024);
+                for (int i = 0; i < n_tiles; ++i) {
+                    const int q = q0 + i, buf = q % kUGroups;
+                    const uint64_t a = a0 + static_cast<uint64_t>(((q % kUStages) * kUTileBytes) >> 4);
+                    const uint64_t o = b0 + static_cast<uint64_t>((buf * kUOneHotBytes) >> 4);
+                    const uint32_t d = tmem + kUColS + (q % kUSumBuffers) * 32;
+                    lost |= !mbar_wait(&bar_onehot[buf], (q / kUGroups) & 1);
+                    tc_fence_after();
+                    if (elect_one()) {
+#pragma unroll
+                        for (int ks = 0; ks < 8; ++ks) {  // 16 tokens per step: two 8-row groups of the tile = 2048 bytes
+                            const uint64_t ak = a + static_cast<uint64_t>((ks * 2048) >> 4);
+                            const uint64_t bk = o + static_cast<uint64_t>(((ks >> 2) * (32 * 128) + (ks & 3) * 32) >> 4);
+                            umma_f16(d, ak, bk, umma_idesc(32, true), (i >= kUSumBuffers || ks > 0) ? 1u : 0u);
+                        }
+                        umma_commit(&bar_sums[buf]);
+                        umma_commit(&bar_empty[q % kUStages]);
+                    }
+                    __syncwarp();
+                }
+            }
+            // ---- end of the segment: its sums go out (the commit of the last sum MMAs covers all of them) -----------
+            const bool flusher = warp < 2 * kUGroupWarps;  // groups 0 and 1: coordinate row_in_tile, sixteen clusters each
+            if (flusher) {
+                const int q_last = q0 + n_tiles - 1;
+                lost |= !mbar_wait(&bar_sums[q_last % kUGroups], (q_last / kUGroups) & 1);
+                tc_fence_after();
+            }
+            workers_sync();
+            if (flusher) {
+                const int half = warp / kUGroupWarps, quarter = warp % kUGroupWarps, row_in_tile = quarter * 32 + lane;
+                const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+                long long* sums_g = p.sums + static_cast<size_t>(unit) * p.clusters * kHeadDim;
+#pragma unroll
+                for (int part = 0; part < 2; ++part) {
+                    float sum[8];  // the accumulators added in the order they were started
+                    tmem_ld8(tmem + lane_base + kUColS + (q0 % kUSumBuffers) * 32 + 16 * half + 8 * part, sum);
+                    tmem_ld_wait();
+                    for (int a = 1; a < kUSumBuffers && a < n_tiles; ++a) {
+                        float more[8];
+                        tmem_ld8(tmem + lane_base + kUColS + ((q0 + a) % kUSumBuffers) * 32 + 16 * half + 8 * part, more);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) sum[k] += more[k];
+                    }
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const int c = 16 * half + 8 * part + k;
+                        if (c < p.clusters && cnt_s[c] > 0)
+                            atomicAdd(reinterpret_cast<unsigned long long*>(sums_g + c * kHeadDim + row_in_tile),
+                                      static_cast<unsigned long long>(__float2ll_rn(sum[k] * kFix)));
+                    }
+                }
+            }
+            if (tid < p.clusters && cnt_s[tid] > 0) atomicAdd(&p.counts[unit * p.clusters + tid], cnt_s[tid]);
+            tc_fence_before();
+            workers_sync();  // accumulators, counters and the centre tables are free for the next segment
+            tc_fence_after();
+            q0 += n_tiles;
+            w += n_tiles;
         }
     }
-    // the commit of the last sums covers every MMA of this CTA
-    const bool flusher = warp < 2 * kUGroupWarps;  // groups 0 and 1: coordinate row_in_tile, sixteen clusters each
-    if (flusher) {
-        lost |= !mbar_wait(&bar_sums[(n_tiles - 1) % kUGroups], ((n_tiles - 1) / kUGroups) & 1);
-        tc_fence_after();
-    }
-    __syncthreads();
-    if (flusher) {
-        const int half = warp / kUGroupWarps, quarter = warp % kUGroupWarps, row_in_tile = quarter * 32 + lane;
-        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        long long* sums_g = p.sums + static_cast<size_t>(unit) * p.clusters * kHeadDim;
-#pragma unroll
-        for (int part = 0; part < 2; ++part) {
-            float sum[8];  // the accumulators added in index order
-            tmem_ld8(tmem + lane_base + kUColS + 16 * half + 8 * part, sum);
-            tmem_ld_wait();
-            for (int a = 1; a < kUSumBuffers && a < n_tiles; ++a) {
-                float more[8];
-                tmem_ld8(tmem + lane_base + kUColS + a * 32 + 16 * half + 8 * part, more);
-                tmem_ld_wait();
-#pragma unroll
-                for (int k = 0; k < 8; ++k) sum[k] += more[k];
-            }
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const int c = 16 * half + 8 * part + k;
-                if (c < p.clusters && cnt_s[c] > 0)
-                    atomicAdd(reinterpret_cast<unsigned long long*>(sums_g + c * kHeadDim + row_in_tile),
-                              static_cast<unsigned long long>(__float2ll_rn(sum[k] * kFix)));
-            }
-        }
-    }
-    if (tid < p.clusters && cnt_s[tid] > 0) atomicAdd(&p.counts[unit * p.clusters + tid], cnt_s[tid]);
     if (lost) atomicOr(p.status, RESKV_STATUS_WAIT_TIMEOUT);
     tc_fence_before();
     __syncthreads();
@@ -972,21 +1018,33 @@ int launch_umma(const KmeansParams& p, int value, int iterations, void* centroid
             return rc;
         prepared |= 1ull << (dev & 63);
     }
-    // tokens per CTA: one CTA per SM at a time, a CTA costs its tiles plus about six tile times of set-up, pipeline
-    // fill and flush; take the number of chunks per unit with the shortest estimated makespan
-    const int tiles = (p.tokens + kUTile - 1) / kUTile, sms = sm_count();
-    int chunk = kUTile;
-    long long best = -1;
-    for (int k = 1; k <= tiles; ++k) {
-        const int per = (tiles + k - 1) / k;
-        if (per * kUTile > kUChunkMax) continue;
-        const long long ctas = static_cast<long long>(p.units) * ((tiles + per - 1) / per);
-        const long long cost = ((ctas + sms - 1) / sms) * (per + 6);
-        if (best < 0 || cost < best) best = cost, chunk = per * kUTile;
+    // One CTA per SM, every CTA an equal share of all units' tiles.  A CTA pays about ten tile times per segment
+    // (pipeline drain, flush, new centre tables, refill), so the share is chosen - between the even split and
+    // half as much again - for the shortest slowest CTA: a share that divides the units evenly often beats the
+    // smallest one.
+    const int tiles_unit = (p.tokens + kUTile - 1) / kUTile, seg_max = kUChunkMax / kUTile;
+    const long long tiles_total = static_cast<long long>(p.units) * tiles_unit;
+    const long long even = (tiles_total + sm_count() - 1) / sm_count();
+    long long share = even < 4 ? 4 : even, best_cost = -1;
+    for (long long cand = share; cand <= share + share / 2 + 1; ++cand) {
+        long long worst = 0;
+        for (long long w0 = 0; w0 < tiles_total; w0 += cand) {
+            const long long w1 = w0 + cand < tiles_total ? w0 + cand : tiles_total;
+            long long segments = 0;
+            for (long long w = w0; w < w1;) {  // same walk as the kernel's
+                const long long in_unit = tiles_unit - w % tiles_unit;
+                long long n = in_unit < w1 - w ? in_unit : w1 - w;
+                if (n > seg_max) n = seg_max;
+                w += n, ++segments;
+            }
+            const long long cost = (w1 - w0) + 10 * segments;
+            if (cost > worst) worst = cost;
+        }
+        if (best_cost < 0 || worst < best_cost) best_cost = worst, share = cand;
     }
-    const dim3 grid((p.tokens + chunk - 1) / chunk, p.units);
+    const dim3 grid(static_cast<unsigned>((tiles_total + share - 1) / share));
     for (int it = 0; it < iterations; ++it) {
-        kmeans_assign_umma_kernel<HILO><<<grid, kUThreads, smem, s>>>(p, xmap, chunk, it == 0, it + 1 == iterations);
+        kmeans_assign_umma_kernel<HILO><<<grid, kUThreads, smem, s>>>(p, xmap, static_cast<int>(share), it == 0, it + 1 == iterations);
         kmeans_update_kernel<<<p.units, 256, 0, s>>>(p, value, it + 1 == iterations ? static_cast<__half*>(centroids) : nullptr);
     }
     return check_cuda(cudaGetLastError(), "kmeans launch");
