@@ -58,14 +58,17 @@ def test_tensor_core_sums_stay_within_one_fp16_ulp_of_the_exact_means(value, cou
 
 
 @pytest.mark.parametrize("value", [False, True])
-def test_both_tensor_core_forms_agree_over_a_full_run(value):
-    """Ten iterations at a size with several chunks per unit and a ragged last tile: the tcgen05 and the mma.sync
-    form assign (almost) every token alike and end on centres within rounding of each other."""
+@pytest.mark.parametrize("shape,iterations", [((2, 4, 4133), 10), ((5, 8, 300), 10), ((8, 8, 25600), 3)],
+                         ids=["ragged-tail", "many-short-units", "long-units"])
+def test_both_tensor_core_forms_agree_over_a_full_run(value, shape, iterations):
+    """The tcgen05 and the mma.sync form assign (almost) every token alike and end on centres within rounding of
+    each other: with a ragged last tile; with units shorter than a CTA's share of tiles (a CTA of the tcgen05 form
+    then crosses several unit boundaries); with units longer than the 8192 tokens one set of partial sums takes."""
     from reskv_b200.synthetic import mixture
 
-    x = mixture(2, 4, 4133, seed=17, clusters=20)
-    a_c, a_i = _cluster(x, 32, 10, value)
-    b_c, b_i = _cluster(x, 32, 10, value, warp_mma=True)
+    x = mixture(*shape, seed=17, clusters=20)
+    a_c, a_i = _cluster(x, 32, iterations, value)
+    b_c, b_i = _cluster(x, 32, iterations, value, warp_mma=True)
     assert (a_i != b_i).mean() < 2e-3
     np.testing.assert_allclose(a_c.astype(np.float32), b_c.astype(np.float32), atol=2e-2, rtol=2e-2)
 
