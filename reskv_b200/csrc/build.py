@@ -5,7 +5,8 @@
 One ``nvcc`` invocation per ``.cu`` file (object files under ``build/``), then a
 shared link next to this file.  Nothing links against torch or Python: the
 library is plain CUDA runtime code behind the C ABI of ``include/reskv_b200.h``.
-nvcc cross-compiles, so no GPU is needed to build.
+nvcc cross-compiles, so no GPU is needed to build.  ``RESKV_NVCC_FLAGS`` (environment) adds compiler flags for
+experiment builds, e.g. ``RESKV_NVCC_FLAGS="-DRESKV_MMA_CTAS_PER_SM=3" python -m reskv_b200.csrc.build --force``.
 """
 
 from __future__ import annotations
@@ -46,11 +47,13 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     objdir = HERE / "build"
     objdir.mkdir(exist_ok=True)
     headers = sorted(HERE.glob("*.cuh")) + [HERE.parent.parent / "include" / "reskv_b200.h"]
+    # extra compiler flags for experiment builds (e.g. -DRESKV_MMA_CTAS_PER_SM=3); use together with --force
+    extra = os.environ.get("RESKV_NVCC_FLAGS", "").split()
     jobs = []
     for src in sources():
         obj = objdir / (src.stem + ".o")
         if force or _stale(obj, [src, *headers]):
-            cmd = [nvcc, *ARCH_FLAGS, *COMMON, "-c", str(src), "-o", str(obj)]
+            cmd = [nvcc, *ARCH_FLAGS, *COMMON, *extra, "-c", str(src), "-o", str(obj)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append(cmd)

@@ -887,7 +887,11 @@ __global__ void __launch_bounds__(kThreadsM, RESKV_MMA_CTAS_PER_SM) decode_mma_k
                         if (16 * mb < p.cv) {
                             const __half2 lo = __float2half2_rn(16.f * mb), hi = __float2half2_rn(16.f * mb + 8.f);
                             const __half2 a0 = __heq2(d01, lo), a1 = __heq2(d01, hi), a2 = __heq2(d23, lo), a3 = __heq2(d23, hi);
+#ifdef RESKV_ABLATE_ACCUMULATORS
+                            mma_16816(bacc[0], *reinterpret_cast<const uint32_t*>(&a0), *reinterpret_cast<const uint32_t*>(&a1),
+#else
                             mma_16816(bacc[mb], *reinterpret_cast<const uint32_t*>(&a0), *reinterpret_cast<const uint32_t*>(&a1),
+#endif
                                       *reinterpret_cast<const uint32_t*>(&a2), *reinterpret_cast<const uint32_t*>(&a3), pb0, pb1);
                         }
                     }
@@ -923,10 +927,17 @@ __global__ void __launch_bounds__(kThreadsM, RESKV_MMA_CTAS_PER_SM) decode_mma_k
                             f2.bits4(ks, h2);
                             f3.bits4(ks, h3);
                         }
+#ifdef RESKV_ABLATE_ACCUMULATORS  // timing experiment only (wrong results): all value MMAs add into one accumulator
+                        mma_16816(acc[0], h0[0] | (h1[0] << 16), h0[1] | (h1[1] << 16), h2[0] | (h3[0] << 16),
+                                  h2[1] | (h3[1] << 16), pb0, pb1);
+                        mma_16816(acc[0], h0[2] | (h1[2] << 16), h0[3] | (h1[3] << 16), h2[2] | (h3[2] << 16),
+                                  h2[3] | (h3[3] << 16), pb0, pb1);
+#else
                         mma_16816(acc[2 * ks], h0[0] | (h1[0] << 16), h0[1] | (h1[1] << 16), h2[0] | (h3[0] << 16),
                                   h2[1] | (h3[1] << 16), pb0, pb1);
                         mma_16816(acc[2 * ks + 1], h0[2] | (h1[2] << 16), h0[3] | (h1[3] << 16), h2[2] | (h3[2] << 16),
                                   h2[3] | (h3[3] << 16), pb0, pb1);
+#endif
                     }
                 }
                 __syncwarp();  // rank-base table is rewritten next tile
