@@ -682,16 +682,22 @@ int launch_simt(const DecodeParams& p, int units, cudaStream_t s) {
     return p.cv <= 32 ? launch_simt_cvs<GQA, L, 1>(p, units, s) : launch_simt_cvs<GQA, L, 2>(p, units, s);
 }
 
-template <int GQA, int NNZ>
-int launch_partial_mma(const DecodeParams& p, int, cudaStream_t stream) {
+template <int GQA, int NNZ, int BETA>
+int launch_partial_mma_beta(const DecodeParams& p, cudaStream_t stream) {
     using ML = mma::LayoutMmaBitmap<NNZ>;
     const size_t smem = mma::smem_bytes<GQA, ML>(p.ck);
-    auto kern = mma::decode_mma_kernel<GQA, ML>;
+    auto kern = mma::decode_mma_kernel<GQA, ML, BETA>;
     static unsigned long long done = 0;
     if (int rc = allow_smem(kern, mma::smem_bytes<GQA, ML>(kMaxClusters), done, "cudaFuncSetAttribute(decode_bitmap_mma)"))
         return rc;
     kern<<<p.grid, mma::kThreadsM, smem, stream>>>(p);
     return check_cuda(cudaGetLastError(), "decode_bitmap_mma launch");
+}
+
+// up to 32 value centroids: the instance with two cluster-mass blocks
+template <int GQA, int NNZ>
+int launch_partial_mma(const DecodeParams& p, int, cudaStream_t stream) {
+    return p.cv <= 32 ? launch_partial_mma_beta<GQA, NNZ, 2>(p, stream) : launch_partial_mma_beta<GQA, NNZ, 4>(p, stream);
 }
 
 // 0 = tensor-core kernel (default), 1 = warp-per-token SIMT kernel

@@ -440,7 +440,9 @@ struct LayoutMmaStructInt4 {
 #define RESKV_MMA_CTAS_PER_SM 2  // resident CTAs the register allocation aims at (4 warps each)
 #endif
 
-template <int GQA, class ML>
+// BETA = 16-cluster blocks of the cluster-mass accumulators: 4 serves every value-centroid count, 2 (counts up to
+// 32, eight registers fewer) is 2 % faster and is what the launchers pick while the table is that small.
+template <int GQA, class ML, int BETA = 4>
 __global__ void __launch_bounds__(kThreadsM, RESKV_MMA_CTAS_PER_SM) decode_mma_kernel(const DecodeParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int kStages = stages_for<ML>();
@@ -685,9 +687,9 @@ __global__ void __launch_bounds__(kThreadsM, RESKV_MMA_CTAS_PER_SM) decode_mma_k
         l_part[0] = l_part[1] = 0.f;
         // cluster mass beta[value cluster][head] of this warp's tokens, accumulated by the tensor cores as
         // onehot(value id)^T . P: rows = clusters 16 mb + g (+ 8), columns = heads 2q, 2q + 1
-        float bacc[4][4];
+        float bacc[BETA][4];
 #pragma unroll
-        for (int mb = 0; mb < 4; ++mb) bacc[mb][0] = bacc[mb][1] = bacc[mb][2] = bacc[mb][3] = 0.f;
+        for (int mb = 0; mb < BETA; ++mb) bacc[mb][0] = bacc[mb][1] = bacc[mb][2] = bacc[mb][3] = 0.f;
 
         // cluster ids (and FP16 scales) of this warp's 16 tokens of the next tile: lanes 0..15 hold the
         // key side of token `lane`, lanes 16..31 the value side of token `lane - 16`
@@ -859,7 +861,7 @@ __global__ void __launch_bounds__(kThreadsM, RESKV_MMA_CTAS_PER_SM) decode_mma_k
                         acc[i][1] *= alpha[1], acc[i][3] *= alpha[1];
                     }
 #pragma unroll
-                    for (int mb = 0; mb < 4; ++mb) {
+                    for (int mb = 0; mb < BETA; ++mb) {
                         bacc[mb][0] *= alpha[0], bacc[mb][2] *= alpha[0];
                         bacc[mb][1] *= alpha[1], bacc[mb][3] *= alpha[1];
                     }
@@ -883,7 +885,7 @@ __global__ void __launch_bounds__(kThreadsM, RESKV_MMA_CTAS_PER_SM) decode_mma_k
                     const __half2 d01 = __hsub2(__halves2half2(__int2half_rn(w0), __int2half_rn(w1)), gg);
                     const __half2 d23 = __hsub2(__halves2half2(__int2half_rn(w2), __int2half_rn(w3)), gg);
 #pragma unroll
-                    for (int mb = 0; mb < 4; ++mb) {
+                    for (int mb = 0; mb < BETA; ++mb) {
                         if (16 * mb < p.cv) {
                             const __half2 lo = __float2half2_rn(16.f * mb), hi = __float2half2_rn(16.f * mb + 8.f);
                             const __half2 a0 = __heq2(d01, lo), a1 = __heq2(d01, hi), a2 = __heq2(d23, lo), a3 = __heq2(d23, hi);
@@ -979,7 +981,10 @@ __global__ void __launch_bounds__(kThreadsM, RESKV_MMA_CTAS_PER_SM) decode_mma_k
                 }
                 float* bdst = beta_s + (warp * GQA + h) * kMaxClusters + g;
 #pragma unroll
-                for (int mb = 0; mb < 4; ++mb) bdst[16 * mb] = bacc[mb][u], bdst[16 * mb + 8] = bacc[mb][2 + u];
+                for (int mb = 0; mb < 4; ++mb) {
+                    bdst[16 * mb] = mb < BETA ? bacc[mb < BETA ? mb : 0][u] : 0.f;
+                    bdst[16 * mb + 8] = mb < BETA ? bacc[mb < BETA ? mb : 0][2 + u] : 0.f;
+                }
             }
         }
         __syncthreads();

@@ -7,10 +7,10 @@ namespace reskv {
 namespace {
 #include "decode_mma.cuh"
 
-template <int GQA, class ML>
-int launch(const DecodeParams& p, int, cudaStream_t stream) {
+template <int GQA, class ML, int BETA>
+int launch_beta(const DecodeParams& p, cudaStream_t stream) {
     const size_t smem = mma::smem_bytes<GQA, ML>(p.ck);
-    auto kern = mma::decode_mma_kernel<GQA, ML>;
+    auto kern = mma::decode_mma_kernel<GQA, ML, BETA>;
     // allowed once per kernel instance and device (bit mask over device ordinals), for the largest centroid table
     static unsigned long long done = 0;
     int dev = 0;
@@ -24,6 +24,12 @@ int launch(const DecodeParams& p, int, cudaStream_t stream) {
     }
     kern<<<p.grid, mma::kThreadsM, smem, stream>>>(p);
     return check_cuda(cudaGetLastError(), "decode_mma (packed layout) launch");
+}
+
+// up to 32 value centroids: the instance with two cluster-mass blocks
+template <int GQA, class ML>
+int launch(const DecodeParams& p, int, cudaStream_t stream) {
+    return p.cv <= 32 ? launch_beta<GQA, ML, 2>(p, stream) : launch_beta<GQA, ML, 4>(p, stream);
 }
 
 template <int GQA>
