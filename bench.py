@@ -737,6 +737,9 @@ def run_gpu(a):
     # GROUP appends; `lead` appends make the fourth timed step of the device-resident loop such a step.
     lead = ((-(W + 4)) % GROUP - (layer.live - RECENT)) % GROUP
     total = lead + W + 2 * K
+    # room for every group these steps will compress, as a serving loop reserves it at prefill: the timed group
+    # compression is then the steady-state one (no buffer growth inside it)
+    layer.compressed = layer.compressed.reserve(layer.compressed.seq_len + total + GROUP)
     q_all = gaussian(total, B, H_Q, 1, DIM, seed=seed + 2, device=dev)
     k_new = gaussian(total, B, H_KV, 1, DIM, seed=seed + 3, device=dev)
     v_new = gaussian(total, B, H_KV, 1, DIM, seed=seed + 4, device=dev)

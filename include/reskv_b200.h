@@ -297,6 +297,33 @@ int reskv_encode_structured_int4(const void* x, const void* centroids, const int
                                  int tokens, int64_t x_tok_stride, int clusters, void* packed, void* meta,
                                  void* scale, int64_t out_tok_stride, void* stream);
 
+/* ---- one decode group, appended in place ------------------------------------------------
+ * What `compress(..., previous=cache)` does for the group that leaves the dense window
+ * (reskv/compression.py:150-170 with _incremental_cluster :56-69 and _encode :72-101, then
+ * CompressedTensor.append, reskv/tensors.py:105-119), for K and V in one call and without
+ * intermediate tensors: reskv_kmeans_incremental of both sides, the packer of (layout, bits, nnz)
+ * writing rows [seq_len, seq_len + tokens) of the cache's capacity buffers, the ids narrowed to
+ * int8 into the same rows.  x_k / x_v f16 [B*KH,x_tok_stride,128]: the group's pre-RoPE keys and
+ * its values (e.g. a token slice of the window buffers).  *_centroids_old f16
+ * [B*KH,*_clusters_old,128], *_centroids_new [B*KH,*_clusters_new,128] with new == old or old + 1
+ * (new may be the old table itself when the count stays).  *_ids int8 [B*KH,*_tok_stride];
+ * *_payload / *_meta / *_scale: the buffers of the layout (null where it has none), every row
+ * *_tok_stride tokens per unit, all given at token 0.  ids_scratch: int32 [2,B*KH,tokens].
+ * Results are those of the separate calls, bit for bit. */
+int reskv_compress_group(int layout, int bits, int nnz, const void* x_k, const void* x_v, int batch, int kv_heads,
+                         int tokens, int64_t x_tok_stride, const void* k_centroids_old, int k_clusters_old,
+                         void* k_centroids_new, int k_clusters_new, void* k_ids, void* k_payload, void* k_meta,
+                         void* k_scale, int64_t k_tok_stride, const void* v_centroids_old, int v_clusters_old,
+                         void* v_centroids_new, int v_clusters_new, void* v_ids, void* v_payload, void* v_meta,
+                         void* v_scale, int64_t v_tok_stride, int seq_len, int32_t* ids_scratch, void* stream);
+
+/* Moves tokens [src, src + count) of every unit of the three window buffers (f16
+ * [B*KH,window_capacity,128], 16-byte aligned) to [dst, dst + count), dst <= src; the ranges may
+ * overlap.  Replaces the slice copies that slide the window after a group left it
+ * (reskv/cache.py:61-77). */
+int reskv_window_shift(void* window_k, void* window_raw, void* window_v, int batch, int kv_heads, int window_capacity,
+                       int dst, int src, int count, void* stream);
+
 /* ---- clustering ------------------------------------------------------------------
  * Lloyd iterations per (sequence, KV head); replaces the torch loop of cluster()
  * (reskv/compression.py:19-53: cdist + argmin + one_hot + bmm per iteration).

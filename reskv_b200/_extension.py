@@ -74,6 +74,11 @@ SIGNATURES = {
     "reskv_encode_quantized": (_I, [_P, _P, _P, _I, _I, _I, _L, _I, _I, _I, _P, _P, _L, _P]),
     "reskv_encode_tiled_fp16": (_I, [_P, _P, _P, _I, _I, _I, _L, _I, _I, _I, _P, _P, _L, _P]),
     "reskv_encode_structured_int4": (_I, [_P, _P, _P, _I, _I, _I, _L, _I, _P, _P, _P, _L, _P]),
+    "reskv_compress_group": (
+        _I,
+        [_I, _I, _I, _P, _P, _I, _I, _I, _L] + [_P, _I, _P, _I, _P, _P, _P, _P, _L] * 2 + [_I, _P, _P],
+    ),
+    "reskv_window_shift": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "reskv_kmeans_workspace_bytes": (_Z, [_I, _I, _I]),
     "reskv_kmeans": (_I, [_P, _I, _I, _I, _L, _I, _I, _I, _P, _Z, _P, _P, _P]),
     "reskv_kmeans_status": (_I, [_P, _I, _I, _I, _P, _P]),
@@ -282,6 +287,30 @@ class CompressionOps(_Ops):
         check(self.lib.reskv_kmeans_incremental(x.data_ptr(), b, h, t, xs, centroids.data_ptr(), old, out.data_ptr(),
                                                 new, ids.data_ptr(), _stream(x.device)))
         return out, ids
+
+
+    def compress_group(self, plan: KernelPlan, x_k, x_v, sides, seq_len: int):
+        """One decode group of K and V clustered, packed and written behind token ``seq_len`` of the capacity
+        buffers, in one library call.  ``sides`` = for K then V ``(old table f16 [B*H,C,128], new table f16
+        [B,H,C or C+1,128] (the old one when the count stays), buffers (ids i8, payload, metadata, scale)
+        [B,H,capacity,...])``.  ``x_k`` / ``x_v`` share one token stride."""
+        b, h, t, _ = x_k.shape
+        xs = token_stride_of(x_k)
+        if x_k.dtype != torch.float16 or x_v.dtype != torch.float16 or xs is None or xs != token_stride_of(x_v):
+            raise ValueError("compress_group expects FP16 x[B,H,T,128] of one token stride")
+        layout = {"unstructured": LAYOUT_UNSTRUCTURED, "tiled": LAYOUT_TILED, "structured": LAYOUT_STRUCTURED,
+                  "compact": LAYOUT_COMPACT}[plan.layout]
+        args = []
+        for old, new, buffers in sides:
+            _same_device(self.device.index, old, new, *buffers)
+            ids = buffers[0]
+            if ids.dtype != torch.int8 or not all(buf is None or buf.is_contiguous() for buf in buffers):
+                raise ValueError("compress_group expects contiguous capacity buffers with int8 ids")
+            args += [old.data_ptr(), old.shape[1], new.data_ptr(), new.shape[2]]
+            args += [0 if buf is None else buf.data_ptr() for buf in buffers] + [ids.shape[2]]
+        scratch = torch.empty((2, b * h, t), dtype=torch.int32, device=x_k.device)
+        check(self.lib.reskv_compress_group(layout, plan.bits, plan.nnz, x_k.data_ptr(), x_v.data_ptr(), b, h, t, xs, *args,
+                                            seq_len, scratch.data_ptr(), _stream(x_k.device)), launches=5)
 
 
 def token_stride_of(x: torch.Tensor):

@@ -140,9 +140,16 @@ class ResKVLayerCache(_HFLayer or _LayerBase):
         self.compressed = compress(self.raw_keys[:, :, s : s + n], self.values[:, :, s : s + n], self.config,
                                    previous=self.compressed, plan=self.plan)
         remain = self.live - s - n
-        for buf in (self.keys, self.raw_keys, self.values):
-            tail = buf[:, :, s + n : self.live]
-            buf[:, :, s : s + remain].copy_(tail if remain <= n else tail.clone())  # clone only when the ranges overlap
+        if self.keys.dtype == torch.float16 and self.keys.is_cuda:
+            from ._extension import _stream, check
+
+            b, h, cap, _ = self.keys.shape
+            check(self._lib.reskv_window_shift(self.keys.data_ptr(), self.raw_keys.data_ptr(), self.values.data_ptr(),
+                                               b, h, cap, s, s + n, remain, _stream(self.keys.device)))
+        else:
+            for buf in (self.keys, self.raw_keys, self.values):
+                tail = buf[:, :, s + n : self.live]
+                buf[:, :, s : s + remain].copy_(tail if remain <= n else tail.clone())  # clone only when the ranges overlap
         self.live = s + remain
 
     # -- Hugging Face cache-layer interface ---------------------------------------

@@ -143,6 +143,38 @@ def _check_external(centres, ids, key: torch.Tensor, limit: int) -> None:
         raise ValueError("external cluster IDs are out of range")
 
 
+def _append_group_in_place(key, value, previous: CompressedKV, config, plan: KernelPlan):
+    """``compress(key, value, previous=previous)`` when the new tokens can be written straight behind the live
+    tokens of ``previous``'s buffers: one library call clusters the group (``_incremental_cluster``), packs it
+    (``_encode``) and writes ids and packed rows in place, for K and V -- the same kernels, no intermediate
+    tensors.  Returns ``None`` when ``previous`` was already extended by a sibling window (the caller then takes
+    the functional path, which copies)."""
+    n, t = previous.seq_len, key.shape[2]
+    if previous.key._live[0] != n or previous.value._live[0] != n:
+        return None
+    if min(previous.key.token_stride, previous.value.token_stride) < n + t:  # full: twice the needed length
+        previous = CompressedKV(*(side.reserve(max(2 * (n + t), 256)) for side in (previous.key, previous.value)))
+    if token_stride_of(key) is None or token_stride_of(key) != token_stride_of(value):
+        key, value = key.contiguous(), value.contiguous()
+    b, h = key.shape[:2]
+    sides = []
+    for side in (previous.key, previous.value):
+        old = side._native[0]
+        count = old.shape[1]
+        new = side.centroids
+        if count < config.max_clusters:
+            new = torch.empty((b, h, count + 1, 128), dtype=torch.float16, device=key.device)
+        elif not new.is_contiguous():
+            new = old.view(b, h, count, 128)
+        sides.append((old, new, side._buffers))
+    _ops(key).compress_group(plan, key, value, sides, n)
+    windows = []
+    for side, (_, new, _) in zip((previous.key, previous.value), sides):
+        side._live[0] = n + t
+        windows.append(side._grown(new, n + t))
+    return CompressedKV(*windows)
+
+
 @torch.no_grad()
 def compress(
     key: torch.Tensor,
@@ -176,6 +208,11 @@ def compress(
     if clustering is not None:
         for centres, ids in clustering:
             _check_external(centres, ids, key, config.max_clusters)
+
+    if previous is not None and clustering is None:
+        extended = _append_group_in_place(key, value, previous, config, plan)
+        if extended is not None:
+            return extended
 
     packed = []
     for side, x in enumerate((key, value)):  # 0 = K, 1 = V

@@ -918,8 +918,10 @@ __global__ void kmeans_update_kernel(KmeansParams p, int value, __half* final_ou
     for (int c = threadIdx.x; c < p.clusters; c += blockDim.x) p.counts[unit * p.clusters + c] = 0;
 }
 
-// Decode-time step: one CTA per unit.  Optionally appends the mean of the
-// group's tokens as centre `old_clusters`, then assigns the tokens.
+// Decode-time step: grid (units, parts).  Optionally appends the mean of the group's tokens as centre
+// `old_clusters`, then assigns the tokens.  Every CTA of a unit forms the same mean (the same additions in the
+// same order); part 0 writes the new table; the tokens are assigned in `parts` contiguous slices, so that a
+// small batch still fills the machine.
 __global__ void __launch_bounds__(kThreads) kmeans_incremental_kernel(const __half* x, int64_t x_stride,
                                                                       const __half* old_cen, int old_clusters,
                                                                       __half* new_cen, int new_clusters, int tokens,
@@ -927,22 +929,34 @@ __global__ void __launch_bounds__(kThreads) kmeans_incremental_kernel(const __ha
     extern __shared__ __align__(16) unsigned char smem[];
     float* cen_s = reinterpret_cast<float*>(smem);  // [new_clusters][128]
     const int unit = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool writer = blockIdx.y == 0;
     const __half* xg = x + static_cast<size_t>(unit) * x_stride * kHeadDim;
     for (int i = tid; i < old_clusters * kHeadDim; i += kThreads) {
         const __half v = old_cen[static_cast<size_t>(unit) * old_clusters * kHeadDim + i];
         cen_s[i] = __half2float(v);
-        new_cen[static_cast<size_t>(unit) * new_clusters * kHeadDim + i] = v;
+        if (writer) new_cen[static_cast<size_t>(unit) * new_clusters * kHeadDim + i] = v;
     }
     if (new_clusters > old_clusters && tid < kHeadDim) {
-        // mean of the group, FP32 accumulation in token order, rounded to FP16
+        // mean of the group, FP32 accumulation in token order, rounded to FP16; the loads of eight tokens are
+        // requested together, the additions stay sequential
         float s = 0.f;
-        for (int t = 0; t < tokens; ++t) s += __half2float(xg[static_cast<size_t>(t) * kHeadDim + tid]);
+        int t = 0;
+        for (; t + 8 <= tokens; t += 8) {
+            __half v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = xg[static_cast<size_t>(t + u) * kHeadDim + tid];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) s += __half2float(v[u]);
+        }
+        for (; t < tokens; ++t) s += __half2float(xg[static_cast<size_t>(t) * kHeadDim + tid]);
         const __half m = __float2half_rn(s / static_cast<float>(tokens));
         cen_s[old_clusters * kHeadDim + tid] = __half2float(m);
-        new_cen[(static_cast<size_t>(unit) * new_clusters + old_clusters) * kHeadDim + tid] = m;
+        if (writer) new_cen[(static_cast<size_t>(unit) * new_clusters + old_clusters) * kHeadDim + tid] = m;
     }
     __syncthreads();
-    for (int t = warp; t < tokens; t += kWarps) {
+    const int per = (tokens + gridDim.y - 1) / gridDim.y;
+    const int t_end = min(tokens, static_cast<int>(blockIdx.y + 1) * per);
+    for (int t = blockIdx.y * per + warp; t < t_end; t += kWarps) {
         float xv[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) xv[i] = __half2float(xg[static_cast<size_t>(t) * kHeadDim + lane + 32 * i]);
@@ -1154,7 +1168,10 @@ extern "C" int reskv_kmeans_incremental(const void* x, int batch, int kv_heads, 
         return fail(RESKV_ERR_INVALID, "kmeans_incremental: centre counts must satisfy 1 <= old <= new <= old + 1 <= 64");
     if (x_tok_stride < tokens) return fail(RESKV_ERR_INVALID, "kmeans_incremental: token stride smaller than token count");
     const size_t smem = static_cast<size_t>(new_clusters) * kHeadDim * sizeof(float);
-    kmeans_incremental_kernel<<<batch * kv_heads, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+    // slices of the group per unit: enough CTAs for one per SM, at least one warp-load of tokens each
+    int parts = 1;
+    while (parts < 8 && batch * kv_heads * parts < sm_count() && tokens >= 2 * kWarps * parts) parts *= 2;
+    kmeans_incremental_kernel<<<dim3(batch * kv_heads, parts), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __half*>(x), x_tok_stride, static_cast<const __half*>(old_centroids), old_clusters,
         static_cast<__half*>(new_centroids), new_clusters, tokens, ids);
     return check_cuda(cudaGetLastError(), "kmeans_incremental launch");

@@ -75,6 +75,7 @@ class CompressedTensor:
     # some window has already written there.  A window shorter than that has a sibling that appended
     # first, so its own ``append`` must not write into the shared buffers (it copies instead).
     _live: list = field(default=None, init=False, repr=False)
+    _flat: tuple = field(default=(), init=False, repr=False)  # ``_buffers`` as [B*H, capacity, ...] views
 
     def __post_init__(self):
         c, ids, p = self.centroids, self.cluster_ids, self.payload
@@ -123,18 +124,29 @@ class CompressedTensor:
             self.scale = self.scale.contiguous() if self.scale is not None else None
             self._buffers = (self.cluster_ids, self.payload, self.metadata, self.scale)
             self._live = [n]
-        cap = self._buffers[0].shape[2]
+        self._native = self._native_views(c, n)
 
-        def rows(buf):
-            if buf is None:
-                return None
-            flat = buf.reshape(b * h, cap, -1)[:, :n]
-            return flat.squeeze(-1) if buf.ndim == 3 else flat
+    def _native_views(self, centroids, n: int) -> tuple:
+        """What the kernels are given: the centroid table as ``[B*H, C, 128]`` and the first ``n`` tokens of every
+        capacity buffer as ``[B*H, n, w]`` (``[B*H, n]`` for ids and scales)."""
+        b, h, cap = self._buffers[0].shape[:3]
+        if not self._flat:  # the buffers with (B, H) merged: made once per set of buffers, windows share them
+            self._flat = tuple(None if buf is None else buf.reshape(b * h, cap, -1).squeeze(-1) if buf.ndim == 3
+                               else buf.reshape(b * h, cap, -1) for buf in self._buffers)
+        return (centroids.reshape(b * h, -1, 128).contiguous(),
+                *(None if flat is None else flat.narrow(1, 0, n) for flat in self._flat))
 
-        self._native = (
-            c.reshape(b * h, -1, 128).contiguous(),
-            *(rows(buf) for buf in self._buffers),
-        )
+    def _grown(self, centroids, length: int) -> "CompressedTensor":
+        """Window over the first ``length`` tokens of this tensor's own buffers with a newer centroid table, for
+        library calls that have just written tokens ``[seq_len, length)`` there: same plan, same buffers, same
+        written-length marker, nothing to validate again."""
+        new = CompressedTensor.__new__(CompressedTensor)
+        new.centroids, new.plan, new._buffers, new._live = centroids, self.plan, self._buffers, self._live
+        new._flat = self._flat
+        new.cluster_ids, new.payload, new.metadata, new.scale = (
+            None if buf is None else buf.narrow(2, 0, length) for buf in self._buffers)
+        new._native = new._native_views(centroids, length)
+        return new
 
     @classmethod
     def _window(cls, centroids, buffers, length, plan, live=None) -> "CompressedTensor":
@@ -144,6 +156,7 @@ class CompressedTensor:
         self.centroids = centroids
         self.plan = plan
         self._buffers = tuple(buffers)
+        self._flat = ()
         self._live = [length] if live is None else live
         views = [buf[:, :, :length] if buf is not None else None for buf in buffers]
         self.cluster_ids, self.payload, self.metadata, self.scale = views
