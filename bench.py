@@ -775,12 +775,19 @@ def run_gpu(a):
             for ev in e[-2:]:
                 ev.record()  # creates the native event handle
             lib.reskv_decode_set_timing_events(e[-2].cuda_event, e[-1].cuda_event)
-        if timed == 2:
-            e[0].record()
+        # inside the timed region only the rare step that compresses a group (its window is one short of full)
+        # gets events around the cache update
+        around_update = timed == 2 or (timed == 1 and layer.live + 1 == layer.keys.shape[2])
+        if around_update:
+            u = (e[0], e[1]) if timed == 2 else tuple(torch.cuda.Event(enable_timing=True) for _ in range(2))
+            u[0].record()
         before = layer.compressed.seq_len
         keys, values = layer.update(k_r, v, {"raw_keys": k})
-        if timed == 2:
-            e[1].record()
+        if around_update:
+            u[1].record()
+            if timed == 1:
+                upd_events.append(u)
+                compressed_at.append(True)
         out = attention(q, layer.compressed, position=p, inv_freq=inv_freq, recent=(q_r, keys, values))
         if timed:
             lib.reskv_decode_set_timing_events(None, None)
@@ -891,7 +898,7 @@ def run_gpu(a):
                 "attention": att_ms / K,
                 "cache_update_append": statistics.median(upd_append) if upd_append else None,
                 "group_compression_steps_in_timed_region": state["groups"],
-                "group_compression_steps_in_phase_pass": len(upd_compress),
+                "group_compression_steps_measured": len(upd_compress),
                 "cache_update_with_group_compression": statistics.mean(upd_compress) if upd_compress else None,
                 "prefill_cluster_and_compress_ms": prefill_compress_ms},
         }
