@@ -116,3 +116,40 @@ def test_operator_tables_refuse_tensors_of_another_device():
     with pytest.raises(ValueError, match="must live on cuda:0"):
         _same_device(0, torch.zeros(1))
     _same_device(0, None)
+
+
+def test_group_entry_points_check_their_arguments_before_any_launch():
+    """``reskv_compress_group`` / ``reskv_window_shift``: null pointers, a group that does not fit the buffers, bad
+    shift ranges and host memory are all refused with RESKV_ERR_INVALID (nothing is launched, so no GPU is needed)."""
+    import numpy as np
+
+    from reskv_b200._extension import ERR_INVALID, library
+
+    lib = library()
+    x = np.zeros((1, 64, 128), np.float16)
+    cen = np.zeros((1, 8, 128), np.float16)
+    ids = np.zeros((1, 256), np.int8)
+    pay = np.zeros((1, 256, 32), np.float16)
+    bm = np.zeros((1, 256, 2), np.int64)
+    scratch = np.zeros((2, 1, 64), np.int32)
+    p = lambda a: a.ctypes.data  # noqa: E731
+    side = (p(cen), 8, p(cen), 8, p(ids), p(pay), p(bm), None)
+
+    def group(seq_len, x_k=p(x), stride=256):
+        return lib.reskv_compress_group(0, 16, 32, x_k, p(x), 1, 1, 64, 64, *side, stride, *side, stride, seq_len,
+                                        p(scratch), None)
+
+    assert group(0, x_k=None) == ERR_INVALID and b"null" in lib.reskv_last_error()
+    assert group(200) == ERR_INVALID and b"do not fit" in lib.reskv_last_error()
+    assert group(-1) == ERR_INVALID
+    assert group(0) == ERR_INVALID and b"compress_group: k_ids" in lib.reskv_last_error()  # host pointers
+
+    win = np.zeros((3, 1, 16, 128), np.float16)
+    w = [p(win[i]) for i in range(3)]
+    assert all(a % 16 == 0 for a in w)
+    for dst, src, count in ((5, 4, 2), (0, 10, 7), (-1, 4, 2), (0, 4, -1)):
+        assert lib.reskv_window_shift(*w, 1, 1, 16, dst, src, count, None) == ERR_INVALID
+        assert b"window_shift" in lib.reskv_last_error()
+    assert lib.reskv_window_shift(None, w[1], w[2], 1, 1, 16, 0, 4, 2, None) == ERR_INVALID
+    assert lib.reskv_window_shift(*w, 1, 1, 16, 0, 4, 2, None) == ERR_INVALID  # host memory
+    assert b"window_shift: window_k" in lib.reskv_last_error()
