@@ -775,8 +775,11 @@ def run_gpu(a):
         p = state["pos"]
         if q_r is None:
             k_r, q_r = rope(k, p, inv_freq), rope(q, p, inv_freq)
-        if timed:
-            e = [torch.cuda.Event(enable_timing=True) for _ in range(5 if timed == 2 else 2)]
+        if timed == 1:
+            e = event_pool.pop()  # made (and recorded once, which creates the native handles) before the timed region
+            lib.reskv_decode_set_timing_events(e[0].cuda_event, e[1].cuda_event)
+        elif timed == 2:
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
             for ev in e[-2:]:
                 ev.record()  # creates the native event handle
             lib.reskv_decode_set_timing_events(e[-2].cuda_event, e[-1].cuda_event)
@@ -817,6 +820,10 @@ def run_gpu(a):
 
     for i in range(lead + W):
         step(q_all[i], k_new[i], v_new[i], False, q_rot[i], k_rot[i])
+    event_pool = [tuple(torch.cuda.Event(enable_timing=True) for _ in range(2)) for _ in range(K)]
+    for pair in event_pool:
+        for ev in pair:
+            ev.record()
 
     # ---- timed region 1: inputs resident in HBM ---------------------------------------
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
