@@ -712,7 +712,11 @@ def run_gpu(a):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     ext.library()  # fail loudly if the native library is missing
-    clocks = ClockSampler(local).start()
+    # rank 0 reports the line, so only its GPU is sampled: a sampler per rank would multiply the driver queries
+    # that run next to the timed region without adding anything to the report
+    clocks = ClockSampler(local)
+    if rank == 0:
+        clocks.start()
 
     B, K, W = a.batch, a.steps, a.warmup
     nnz = int(128 * (1 - a.sparsity))
