@@ -90,3 +90,19 @@ def test_token_stride_of_recognises_token_slices_only():
     assert token_stride_of(big[:, :, ::2]) is None           # every other token
     assert token_stride_of(big[:, ::2]) is None              # units no longer evenly spaced
     assert token_stride_of(big.transpose(1, 2)) is None
+
+
+def test_grown_window_is_the_validated_window():
+    """``_grown`` (the unchecked constructor the in-place group path uses) yields exactly the views that the
+    validating ``_window`` builds over the same buffers, and shares the written-length marker."""
+    base = _tensor(100, 5).reserve(400)
+    newer = torch.randn(1, 2, 5, 128).half()
+    fast = base._grown(newer, 164)
+    slow = CompressedTensor._window(newer, base._buffers, 164, base.plan, base._live)
+    assert fast.seq_len == slow.seq_len == 164 and fast.token_stride == 400 and fast._live is base._live
+    for a, b in zip(fast.tensors, slow.tensors):
+        assert (a is None) == (b is None)
+        if a is not None:
+            assert a.shape == b.shape and a.stride() == b.stride() and a.data_ptr() == b.data_ptr() and a.dtype == b.dtype
+    # the old window is untouched and a further one can be derived from the new one
+    assert base.seq_len == 100 and fast._grown(newer, 228).seq_len == 228
